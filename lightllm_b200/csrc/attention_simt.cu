@@ -1,0 +1,290 @@
+// Paged attention over block tables on CUDA cores: any mix of spans (prompt portions of any
+// length beside single decode tokens), causal by absolute position, optional window, any head
+// size and group size.  All arithmetic is float; q, k, v may be float or bf16.
+//
+// Scores and softmax follow src/kv_cache/paged_attention.cu:153-163:
+//     s = (q . k) * scale;  m' = max(m, s);  l = l*exp(m - m') + exp(s - m');
+//     acc = acc*exp(m - m') + exp(s - m') * v;   out = acc / l
+// with kv_head = q_head / (Hq / Hkv) (:115).  Differences from the reference: the running
+// maximum starts at -inf and the result is exactly acc / l (the reference starts at -1e38 and
+// divides by l + 1e-8, :130,169); a token's own key is visible (the reference's decode stops
+// before it, src/engine/engine_server.cpp:1802); later portions of a prompt are causal too
+// (engine_server.cpp:1755-1761 passes causal=false); the page size is a parameter (the
+// reference fixes 16, paged_attention.cu:28).
+//
+// Work is cut into tiles of BQ query rows of one span; a block takes one tile and one kv head,
+// i.e. BQ * G query vectors (G = Hq / Hkv) that share every key/value tile it stages in shared
+// memory.  With nsplit > 1 the key range of a tile is cut into nsplit pieces whose partial
+// (acc, m, l) go to scratch and are merged by a second kernel
+// (as paged_attention.cu:323-460,476-532 does with a fixed 4 splits).
+#include "common.cuh"
+
+#include <math.h>
+
+namespace {
+
+constexpr int BK = 32;      // keys per staged tile = one per lane
+constexpr int NWARPS = 4;
+
+struct AttnParams {
+    const void* q;
+    const void* k_cache;
+    const void* v_cache;
+    void* out;
+    const int* tile_span;
+    const int* tile_q0;
+    const int* span_row;
+    const int* span_len;
+    const int* span_pos;
+    const int* block_table;
+    int max_pages, page_size, Hq, Hkv, hd, window, BQ, nsplit;
+    float scale;
+    float* part_acc;  // [tiles, Hkv, nsplit, BQ*G, hd]
+    float* part_ml;   // [tiles, Hkv, nsplit, BQ*G, 2]
+};
+
+template <typename T>
+__global__ void __launch_bounds__(NWARPS * 32) paged_attention_kernel(AttnParams p) {
+    extern __shared__ float smem[];
+    const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int G = p.Hq / p.Hkv;
+    const int hd = p.hd;
+    const int nqv = p.BQ * G;
+    const int kstride = hd | 1;
+    float* Qs = smem;                       // [nqv][hd]
+    float* Acc = Qs + (size_t)nqv * hd;     // [nqv][hd]
+    float* Ms = Acc + (size_t)nqv * hd;     // [nqv]
+    float* Ls = Ms + nqv;                   // [nqv]
+    float* Ks = Ls + nqv;                   // [BK][kstride]
+    float* Vs = Ks + BK * kstride;          // [BK][hd]
+    float* Ps = Vs + BK * hd;               // [NWARPS][BK]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int span = p.tile_span[tile];
+    const int q0 = p.tile_q0[tile];
+    const int row0 = p.span_row[span] + q0;
+    const int slen = p.span_len[span];
+    const int pos0 = p.span_pos[span] + q0;        // position of the tile's first query
+    const int nrows = min(p.BQ, slen - q0);        // valid query rows of this tile
+    const int* bt = p.block_table + (size_t)span * p.max_pages;
+    const T* q = (const T*)p.q;
+    const T* kc = (const T*)p.k_cache;
+    const T* vc = (const T*)p.v_cache;
+
+    // Key range of the tile: [lo, hi); of this split: [klo, khi).
+    const int hi = pos0 + nrows;
+    int lo = 0;
+    if (p.window > 0) lo = max(0, pos0 - p.window + 1);
+    int klo = lo, khi = hi;
+    if (p.nsplit > 1) {
+        int chunk = (hi - lo + p.nsplit - 1) / p.nsplit;
+        chunk = ((chunk + BK - 1) / BK) * BK;
+        klo = lo + split * chunk;
+        khi = min(hi, klo + chunk);
+    }
+
+    for (int i = threadIdx.x; i < nqv * hd; i += blockDim.x) {
+        const int v = i / hd, d = i - v * hd;
+        const int r = v / G, g = v - r * G;
+        float val = 0.0f;
+        if (r < nrows) val = llb_to_float(q[((size_t)(row0 + r) * p.Hq + kvh * G + g) * hd + d]);
+        Qs[i] = val;
+        Acc[i] = 0.0f;
+    }
+    for (int i = threadIdx.x; i < nqv; i += blockDim.x) {
+        Ms[i] = -INFINITY;
+        Ls[i] = 0.0f;
+    }
+    __syncthreads();
+
+    for (int kb = klo; kb < khi; kb += BK) {
+        // Stage BK keys and values of this kv head; rows past khi are zero.
+        for (int j = warp; j < BK; j += NWARPS) {
+            const int kpos = kb + j;
+            if (kpos < khi) {
+                const int page = bt[kpos / p.page_size];
+                const size_t slot = (size_t)page * p.page_size + (kpos % p.page_size);
+                const T* kr = kc + (slot * p.Hkv + kvh) * hd;
+                const T* vr = vc + (slot * p.Hkv + kvh) * hd;
+                for (int d = lane; d < hd; d += 32) {
+                    Ks[j * kstride + d] = llb_to_float(kr[d]);
+                    Vs[j * hd + d] = llb_to_float(vr[d]);
+                }
+            } else {
+                for (int d = lane; d < hd; d += 32) {
+                    Ks[j * kstride + d] = 0.0f;
+                    Vs[j * hd + d] = 0.0f;
+                }
+            }
+        }
+        __syncthreads();
+
+        const int kpos = kb + lane;
+        for (int v = warp; v < nqv; v += NWARPS) {
+            const int r = v / G;
+            if (r >= nrows) continue;  // uniform over the warp
+            const int qpos = pos0 + r;
+            const bool visible = kpos < khi && kpos <= qpos && (p.window <= 0 || qpos - kpos < p.window);
+            float s = -INFINITY;
+            if (visible) {
+                const float* qv = Qs + (size_t)v * hd;
+                const float* kr = Ks + lane * kstride;
+                float dot = 0.0f;
+                for (int d = 0; d < hd; ++d) dot = fmaf(qv[d], kr[d], dot);
+                s = dot * p.scale;
+            }
+            const float m_old = Ms[v];
+            const float m_new = fmaxf(m_old, llb_warp_max(s));
+            if (m_new == -INFINITY) continue;  // nothing visible yet; uniform over the warp
+            const float pr = visible ? expf(s - m_new) : 0.0f;
+            const float corr = (m_old == -INFINITY) ? 0.0f : expf(m_old - m_new);
+            const float l_new = Ls[v] * corr + llb_warp_sum(pr);
+            Ps[warp * BK + lane] = pr;
+            __syncwarp();
+            for (int d = lane; d < hd; d += 32) {
+                float a = Acc[(size_t)v * hd + d] * corr;
+#pragma unroll 8
+                for (int j = 0; j < BK; ++j) a = fmaf(Ps[warp * BK + j], Vs[j * hd + d], a);
+                Acc[(size_t)v * hd + d] = a;
+            }
+            __syncwarp();
+            if (lane == 0) {
+                Ms[v] = m_new;
+                Ls[v] = l_new;
+            }
+            __syncwarp();
+        }
+        __syncthreads();
+    }
+
+    if (p.nsplit == 1) {
+        T* out = (T*)p.out;
+        for (int v = warp; v < nqv; v += NWARPS) {
+            const int r = v / G, g = v - r * G;
+            if (r >= nrows) continue;
+            const float inv = 1.0f / Ls[v];
+            T* o = out + ((size_t)(row0 + r) * p.Hq + kvh * G + g) * hd;
+            for (int d = lane; d < hd; d += 32) o[d] = llb_from_float<T>(Acc[(size_t)v * hd + d] * inv);
+        }
+    } else {
+        const size_t base = (((size_t)tile * p.Hkv + kvh) * p.nsplit + split) * nqv;
+        for (int v = warp; v < nqv; v += NWARPS) {
+            float* pa = p.part_acc + (base + v) * hd;
+            for (int d = lane; d < hd; d += 32) pa[d] = Acc[(size_t)v * hd + d];
+            if (lane == 0) {
+                p.part_ml[(base + v) * 2 + 0] = Ms[v];
+                p.part_ml[(base + v) * 2 + 1] = Ls[v];
+            }
+        }
+    }
+}
+
+// Merge of the split partials: out = sum_s e^{m_s - M} acc_s / sum_s e^{m_s - M} l_s.
+template <typename T>
+__global__ void attention_merge_kernel(AttnParams p) {
+    const int tile = blockIdx.x, head = blockIdx.y;
+    const int G = p.Hq / p.Hkv;
+    const int kvh = head / G, g = head - kvh * G;
+    const int nqv = p.BQ * G;
+    const int span = p.tile_span[tile];
+    const int q0 = p.tile_q0[tile];
+    const int nrows = min(p.BQ, p.span_len[span] - q0);
+    const int row0 = p.span_row[span] + q0;
+    T* out = (T*)p.out;
+    for (int r = 0; r < nrows; ++r) {
+        const int v = r * G + g;
+        float M = -INFINITY;
+        for (int s = 0; s < p.nsplit; ++s) {
+            const size_t idx = (((size_t)tile * p.Hkv + kvh) * p.nsplit + s) * nqv + v;
+            M = fmaxf(M, p.part_ml[idx * 2]);
+        }
+        float L = 0.0f;
+        for (int s = 0; s < p.nsplit; ++s) {
+            const size_t idx = (((size_t)tile * p.Hkv + kvh) * p.nsplit + s) * nqv + v;
+            const float m = p.part_ml[idx * 2];
+            if (m != -INFINITY) L += expf(m - M) * p.part_ml[idx * 2 + 1];
+        }
+        const float inv = 1.0f / L;
+        for (int d = threadIdx.x; d < p.hd; d += blockDim.x) {
+            float a = 0.0f;
+            for (int s = 0; s < p.nsplit; ++s) {
+                const size_t idx = (((size_t)tile * p.Hkv + kvh) * p.nsplit + s) * nqv + v;
+                const float m = p.part_ml[idx * 2];
+                if (m != -INFINITY) a += expf(m - M) * p.part_acc[idx * p.hd + d];
+            }
+            out[((size_t)(row0 + r) * p.Hq + head) * p.hd + d] = llb_from_float<T>(a * inv);
+        }
+    }
+}
+
+size_t attention_smem_bytes(int BQ, int G, int hd) {
+    const size_t nqv = (size_t)BQ * G;
+    const size_t floats = 2 * nqv * hd + 2 * nqv + (size_t)BK * (hd | 1) + (size_t)BK * hd + NWARPS * BK;
+    return floats * sizeof(float);
+}
+
+template <typename T>
+int launch_attention(const AttnParams& p, int num_tiles, cudaStream_t stream) {
+    const size_t smem = attention_smem_bytes(p.BQ, p.Hq / p.Hkv, p.hd);
+    LLB_REQUIRE(smem <= 220 * 1024, "attention: BQ=%d with %d heads per group and head_dim %d needs %zu bytes of "
+                "shared memory; use a smaller BQ", p.BQ, p.Hq / p.Hkv, p.hd, smem);
+    static size_t configured = 0;  // largest opt-in so far for this instantiation
+    if (smem > 48 * 1024 && smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(paged_attention_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)smem);
+        if (e != cudaSuccess) return llb_fail("attention: cannot opt in to %zu bytes of shared memory: %s", smem,
+                                              cudaGetErrorString(e));
+        configured = smem;
+    }
+    dim3 grid(num_tiles, p.Hkv, p.nsplit);
+    paged_attention_kernel<T><<<grid, NWARPS * 32, smem, stream>>>(p);
+    int rc = llb_check_launch("paged_attention");
+    if (rc) return rc;
+    if (p.nsplit > 1) {
+        dim3 mgrid(num_tiles, p.Hq);
+        const int threads = p.hd >= 128 ? 128 : (p.hd >= 64 ? 64 : 32);
+        attention_merge_kernel<T><<<mgrid, threads, 0, stream>>>(p);
+        rc = llb_check_launch("attention_merge");
+    }
+    return rc;
+}
+
+}  // namespace
+
+// Shared memory one block needs for the given tile height; the caller picks BQ with it.
+LLB_EXPORT long long llb_attention_smem_bytes(int BQ, int group, int hd) {
+    return (long long)attention_smem_bytes(BQ, group, hd);
+}
+
+// Floats of scratch that nsplit > 1 needs: acc and (m, l).
+LLB_EXPORT long long llb_attention_scratch_floats(int num_tiles, int Hq, int hd, int BQ, int nsplit) {
+    return (long long)num_tiles * Hq * BQ * nsplit * (hd + 2);
+}
+
+// q, out [T, Hq, hd]; k_cache, v_cache [slots, Hkv, hd] with slot = page*page_size + offset;
+// tile_span, tile_q0 [num_tiles]; span_row, span_len, span_pos [S]; block_table [S, max_pages].
+// window <= 0 means every earlier key is visible.  scratch: llb_attention_scratch_floats floats
+// when nsplit > 1, else unused.
+LLB_EXPORT int llb_paged_attention(const void* q, const void* k_cache, const void* v_cache, void* out, int dtype,
+                                   const int* tile_span, const int* tile_q0, int num_tiles, const int* span_row,
+                                   const int* span_len, const int* span_pos, const int* block_table,
+                                   int max_pages, int page_size, int Hq, int Hkv, int hd, int window, float scale,
+                                   int BQ, int nsplit, float* scratch, cudaStream_t stream) {
+    if (num_tiles == 0) return 0;
+    LLB_REQUIRE(num_tiles > 0 && Hq > 0 && Hkv > 0 && hd > 0 && page_size > 0 && max_pages > 0 && BQ > 0,
+                "attention: bad sizes");
+    LLB_REQUIRE(Hq % Hkv == 0, "attention: %d query heads are not a multiple of %d kv heads", Hq, Hkv);
+    LLB_REQUIRE(nsplit >= 1 && nsplit <= 65535 && Hkv <= 65535, "attention: bad split count %d", nsplit);
+    LLB_REQUIRE(nsplit == 1 || scratch != nullptr, "attention: nsplit=%d needs scratch", nsplit);
+    AttnParams p;
+    p.q = q; p.k_cache = k_cache; p.v_cache = v_cache; p.out = out;
+    p.tile_span = tile_span; p.tile_q0 = tile_q0;
+    p.span_row = span_row; p.span_len = span_len; p.span_pos = span_pos; p.block_table = block_table;
+    p.max_pages = max_pages; p.page_size = page_size; p.Hq = Hq; p.Hkv = Hkv; p.hd = hd;
+    p.window = window; p.BQ = BQ; p.nsplit = nsplit; p.scale = scale;
+    p.part_acc = scratch;
+    p.part_ml = scratch ? scratch + (size_t)num_tiles * Hq * BQ * nsplit * hd : nullptr;
+    if (dtype == LLB_F32) return launch_attention<float>(p, num_tiles, stream);
+    if (dtype == LLB_BF16) return launch_attention<__nv_bfloat16>(p, num_tiles, stream);
+    return llb_fail("attention: unknown dtype %d", dtype);
+}

@@ -1,0 +1,206 @@
+"""Python binding of the kernel library: thin, checked wrappers over its ``extern "C"`` entry points.
+
+Every wrapper takes torch tensors that live on the GPU, checks dtype, shape and contiguity,
+and launches on torch's current stream.  There is no fallback: if the library cannot be built
+or loaded, or a tensor is not on a CUDA device, the call raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import build as _build
+
+F32, BF16 = 0, 1
+EPI_STORE, EPI_STORE_F32, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
+ABI_VERSION = 3
+
+_lib: Optional[ctypes.CDLL] = None
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded kernel library (built on first use)."""
+    global _lib
+    if _lib is None:
+        path = _build.library_path(build=True)
+        try:
+            handle = ctypes.CDLL(path)
+        except OSError as e:
+            raise KernelError(f"cannot load the kernel library {path}: {e}") from None
+        handle.llb_last_error.restype = ctypes.c_char_p
+        handle.llb_attention_smem_bytes.restype = ctypes.c_longlong
+        handle.llb_attention_scratch_floats.restype = ctypes.c_longlong
+        if handle.llb_abi_version() != ABI_VERSION:
+            raise KernelError(f"{path} has ABI version {handle.llb_abi_version()}, expected {ABI_VERSION}")
+        _lib = handle
+    return _lib
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        raise KernelError(lib().llb_last_error().decode("utf-8", "replace"))
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"unsupported dtype {t.dtype}; the kernels take float32 and bfloat16")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    if t is None:
+        return ctypes.c_void_p(0)
+    if not t.is_cuda:
+        raise KernelError("tensor is not on a CUDA device; there is no CPU path")
+    if not t.is_contiguous():
+        raise KernelError(f"tensor of shape {tuple(t.shape)} must be contiguous")
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def _i32(t: Optional[torch.Tensor], what: str) -> ctypes.c_void_p:
+    if t is not None and t.dtype != torch.int32:
+        raise KernelError(f"{what} must be int32, got {t.dtype}")
+    return _ptr(t)
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, err: Optional[torch.Tensor] = None) -> None:
+    """out[t,:] = table[ids[t],:] as float.  ids int32 [T], table [V,D], out float32 [T,D]."""
+    T, (V, D) = ids.numel(), table.shape
+    if out.dtype != torch.float32 or tuple(out.shape) != (T, D):
+        raise KernelError(f"embedding: out must be float32 [{T},{D}], got {out.dtype} {tuple(out.shape)}")
+    _check(lib().llb_embedding(_i32(ids, "ids"), _ptr(table), _dt(table), _ptr(out), T, D, V,
+                               _i32(err, "err"), _stream()))
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+            rows: Optional[torch.Tensor] = None) -> None:
+    """out[r,:] = rmsnorm(x[rows[r],:]) * weight (rows = None: row r of x)."""
+    D = x.shape[-1]
+    R = rows.numel() if rows is not None else x.numel() // D
+    if weight.numel() != D or out.numel() != R * D:
+        raise KernelError(f"rmsnorm: sizes do not fit: x {tuple(x.shape)} weight {tuple(weight.shape)} out {tuple(out.shape)}")
+    _check(lib().llb_rmsnorm(_ptr(x), _dt(x), _ptr(weight), _dt(weight), _ptr(out), _dt(out),
+                             _i32(rows, "rows"), R, D, ctypes.c_float(eps), _stream()))
+
+
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], epilogue: int,
+              out: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None) -> None:
+    """CUDA-core contraction a[M,K] @ w[N,K]^T with a fused epilogue (see EPI_*)."""
+    M, K = a.shape
+    N, K2 = w.shape
+    if K != K2:
+        raise KernelError(f"gemm: a is {tuple(a.shape)} but w is {tuple(w.shape)}")
+    _check_epilogue_args(a, N, M, bias, epilogue, out, residual)
+    _check(lib().llb_gemm_simt(_ptr(a), _dt(a), _ptr(w), _ptr(bias), _dt(w), _ptr(out), _ptr(residual),
+                               epilogue, M, N, K, _stream()))
+
+
+def _check_epilogue_args(a, N, M, bias, epilogue, out, residual) -> None:
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N):
+        raise KernelError(f"gemm: bias must be float32 [{N}], got {bias.dtype} {tuple(bias.shape)}")
+    if epilogue == EPI_RESIDUAL:
+        if residual is None or residual.dtype != torch.float32 or tuple(residual.shape) != (M, N):
+            raise KernelError(f"gemm: residual must be float32 [{M},{N}]")
+        return
+    want_shape = (M, N // 2) if epilogue == EPI_SWIGLU else (M, N)
+    want_dtype = torch.float32 if epilogue == EPI_STORE_F32 else a.dtype
+    if out is None or tuple(out.shape) != want_shape or out.dtype != want_dtype:
+        got = None if out is None else (out.dtype, tuple(out.shape))
+        raise KernelError(f"gemm: out must be {want_dtype} {want_shape}, got {got}")
+
+
+def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, slot_mapping: Optional[torch.Tensor],
+                  inv_freq: Optional[torch.Tensor], rotary_dim: int, interleaved: bool, q_out: torch.Tensor,
+                  k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
+                  num_heads: int, num_kv_heads: int, head_dim: int) -> None:
+    """Rotate q and k by position and write k, v rows into their cache slots.
+
+    qkv [T, (Hq + 2*Hkv)*hd]; q_out [T, Hq*hd]; caches [slots, Hkv, hd].  Without caches
+    (``k_cache is None``) only q is produced and qkv holds Hq heads only."""
+    T = qkv.shape[0]
+    write_kv = k_cache is not None
+    hkv = num_kv_heads if write_kv else 0
+    if qkv.shape[1] != (num_heads + 2 * hkv) * head_dim:
+        raise KernelError(f"rope_kv_write: qkv has {qkv.shape[1]} columns, expected {(num_heads + 2 * hkv) * head_dim}")
+    if q_out.dtype != qkv.dtype or q_out.numel() != T * num_heads * head_dim:
+        raise KernelError("rope_kv_write: q_out does not fit")
+    if write_kv and (k_cache.dtype != qkv.dtype or v_cache.dtype != qkv.dtype):
+        raise KernelError("rope_kv_write: cache dtype differs from the activations'")
+    if inv_freq is not None and (inv_freq.dtype != torch.float32 or inv_freq.numel() != rotary_dim // 2):
+        raise KernelError("rope_kv_write: inv_freq must be float32 [rotary_dim/2]")
+    _check(lib().llb_rope_kv_write(_ptr(qkv), _dt(qkv), _i32(positions, "positions"),
+                                   _i32(slot_mapping, "slot_mapping"), _ptr(inv_freq), rotary_dim,
+                                   1 if interleaved else 0, _ptr(q_out), _ptr(k_cache), _ptr(v_cache),
+                                   T, num_heads, hkv, head_dim, 1 if write_kv else 0, _stream()))
+
+
+def attention_smem_bytes(bq: int, group: int, head_dim: int) -> int:
+    return int(lib().llb_attention_smem_bytes(bq, group, head_dim))
+
+
+def attention_scratch_floats(num_tiles: int, num_heads: int, head_dim: int, bq: int, nsplit: int) -> int:
+    return int(lib().llb_attention_scratch_floats(num_tiles, num_heads, head_dim, bq, nsplit))
+
+
+def paged_attention_simt(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
+                         tile_span: torch.Tensor, tile_q0: torch.Tensor, num_tiles: int,
+                         span_row: torch.Tensor, span_len: torch.Tensor, span_pos: torch.Tensor,
+                         block_table: torch.Tensor, max_pages: int, page_size: int,
+                         num_heads: int, num_kv_heads: int, head_dim: int, window: int, scale: float,
+                         bq: int, nsplit: int = 1, scratch: Optional[torch.Tensor] = None) -> None:
+    """Attention of every query row of the listed tiles over its request's pages."""
+    if k_cache.dtype != q.dtype or v_cache.dtype != q.dtype or out.dtype != q.dtype:
+        raise KernelError("attention: q, caches and out must share a dtype")
+    if nsplit > 1:
+        need = attention_scratch_floats(num_tiles, num_heads, head_dim, bq, nsplit)
+        if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
+            raise KernelError(f"attention: nsplit={nsplit} needs {need} floats of scratch")
+    _check(lib().llb_paged_attention(
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _dt(q),
+        _i32(tile_span, "tile_span"), _i32(tile_q0, "tile_q0"), num_tiles,
+        _i32(span_row, "span_row"), _i32(span_len, "span_len"), _i32(span_pos, "span_pos"),
+        _i32(block_table, "block_table"), max_pages, page_size, num_heads, num_kv_heads, head_dim,
+        window, ctypes.c_float(scale), bq, nsplit, _ptr(scratch), _stream()))
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r] = first index of the largest logit of row r.  logits float32 [R,V]."""
+    R, V = logits.shape
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise KernelError("argmax: logits must be float32 with unit inner stride")
+    if not logits.is_cuda:
+        raise KernelError("argmax: logits are not on a CUDA device; there is no CPU path")
+    _check(lib().llb_argmax(ctypes.c_void_p(logits.data_ptr()), R, V, ctypes.c_longlong(logits.stride(0)),
+                            _i32(out, "out"), _stream()))
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: Optional[torch.Tensor],
+           top_p: Optional[torch.Tensor], min_p: Optional[torch.Tensor], uniform: torch.Tensor,
+           out: torch.Tensor) -> None:
+    """One token per row from softmax(logits / temperature) after the top-k/top-p/min-p filters."""
+    R, V = logits.shape
+    if logits.dtype != torch.float32 or logits.stride(1) != 1 or not logits.is_cuda:
+        raise KernelError("sample: logits must be float32 on a CUDA device with unit inner stride")
+    for name, t in (("temperature", temperature), ("top_p", top_p), ("min_p", min_p), ("uniform", uniform)):
+        if t is not None and (t.dtype != torch.float32 or t.numel() != R):
+            raise KernelError(f"sample: {name} must be float32 [{R}]")
+    _check(lib().llb_sample(ctypes.c_void_p(logits.data_ptr()), R, V, ctypes.c_longlong(logits.stride(0)),
+                            _ptr(temperature), _i32(top_k, "top_k"), _ptr(top_p), _ptr(min_p), _ptr(uniform),
+                            _i32(out, "out"), _stream()))
+
+
+def has_tcgen05() -> bool:
+    """Whether the library carries the tcgen05 tensor-core contraction."""
+    return hasattr(lib(), "llb_gemm_tcgen05")

@@ -1,0 +1,93 @@
+// RMSNorm over rows of the residual stream, optionally only over a list of rows.
+//
+// ss = sum_d x_d^2 in float (src/ops/norm.cu:19-23); inv = 1 / sqrt(ss / D + eps) (:48-49);
+// y_d = x_d * inv * w_d, then the cast (:50-54).  One block per row; the reference uses two
+// launches and a global buffer for ss, here the row stays in registers between the passes
+// when it fits.
+#include "common.cuh"
+
+template <typename TI, typename TW, typename TO, int PER_THREAD>
+__global__ void rmsnorm_kernel(const TI* __restrict__ x, const TW* __restrict__ w, TO* __restrict__ out,
+                               const int* __restrict__ rows, int D, float eps) {
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    const TI* xr = x + (size_t)src * D;
+    TO* o = out + (size_t)r * D;
+
+    float v[PER_THREAD > 0 ? PER_THREAD : 1];
+    float ss = 0.0f;
+    if (PER_THREAD > 0) {
+#pragma unroll
+        for (int i = 0; i < PER_THREAD; ++i) {
+            const int d = threadIdx.x + i * blockDim.x;
+            v[i] = d < D ? llb_to_float(xr[d]) : 0.0f;
+            ss += v[i] * v[i];
+        }
+    } else {
+        for (int d = threadIdx.x; d < D; d += blockDim.x) {
+            const float a = llb_to_float(xr[d]);
+            ss += a * a;
+        }
+    }
+    __shared__ float warp_part[32];
+    __shared__ float total;
+    ss = llb_warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float t = threadIdx.x < (blockDim.x >> 5) ? warp_part[threadIdx.x] : 0.0f;
+        t = llb_warp_sum(t);
+        if (threadIdx.x == 0) total = t;
+    }
+    __syncthreads();
+    const float inv = 1.0f / sqrtf(total / (float)D + eps);
+    if (PER_THREAD > 0) {
+#pragma unroll
+        for (int i = 0; i < PER_THREAD; ++i) {
+            const int d = threadIdx.x + i * blockDim.x;
+            if (d < D) o[d] = llb_from_float<TO>(v[i] * inv * llb_to_float(w[d]));
+        }
+    } else {
+        for (int d = threadIdx.x; d < D; d += blockDim.x)
+            o[d] = llb_from_float<TO>(llb_to_float(xr[d]) * inv * llb_to_float(w[d]));
+    }
+}
+
+template <typename TI, typename TW, typename TO>
+static int launch_rmsnorm(const void* x, const void* w, void* out, const int* rows, int R, int D, float eps,
+                          cudaStream_t stream) {
+    const int threads = 256;
+    if (D <= threads * 4)
+        rmsnorm_kernel<TI, TW, TO, 4><<<R, threads, 0, stream>>>((const TI*)x, (const TW*)w, (TO*)out, rows, D, eps);
+    else if (D <= threads * 16)
+        rmsnorm_kernel<TI, TW, TO, 16><<<R, threads, 0, stream>>>((const TI*)x, (const TW*)w, (TO*)out, rows, D, eps);
+    else
+        rmsnorm_kernel<TI, TW, TO, 0><<<R, threads, 0, stream>>>((const TI*)x, (const TW*)w, (TO*)out, rows, D, eps);
+    return llb_check_launch("rmsnorm");
+}
+
+template <typename TI, typename TW>
+static int dispatch_out(int out_dtype, const void* x, const void* w, void* out, const int* rows, int R, int D,
+                        float eps, cudaStream_t s) {
+    if (out_dtype == LLB_F32) return launch_rmsnorm<TI, TW, float>(x, w, out, rows, R, D, eps, s);
+    if (out_dtype == LLB_BF16) return launch_rmsnorm<TI, TW, __nv_bfloat16>(x, w, out, rows, R, D, eps, s);
+    return llb_fail("rmsnorm: unknown output dtype %d", out_dtype);
+}
+
+template <typename TI>
+static int dispatch_w(int w_dtype, int out_dtype, const void* x, const void* w, void* out, const int* rows, int R,
+                      int D, float eps, cudaStream_t s) {
+    if (w_dtype == LLB_F32) return dispatch_out<TI, float>(out_dtype, x, w, out, rows, R, D, eps, s);
+    if (w_dtype == LLB_BF16) return dispatch_out<TI, __nv_bfloat16>(out_dtype, x, w, out, rows, R, D, eps, s);
+    return llb_fail("rmsnorm: unknown weight dtype %d", w_dtype);
+}
+
+// x [*, D], w [D], out [R, D]; rows: R source-row indices into x, or null for rows 0..R-1.
+LLB_EXPORT int llb_rmsnorm(const void* x, int x_dtype, const void* w, int w_dtype, void* out, int out_dtype,
+                           const int* rows, int R, int D, float eps, cudaStream_t stream) {
+    if (R == 0) return 0;
+    LLB_REQUIRE(R > 0 && D > 0, "rmsnorm: bad sizes R=%d D=%d", R, D);
+    if (x_dtype == LLB_F32) return dispatch_w<float>(w_dtype, out_dtype, x, w, out, rows, R, D, eps, stream);
+    if (x_dtype == LLB_BF16) return dispatch_w<__nv_bfloat16>(w_dtype, out_dtype, x, w, out, rows, R, D, eps, stream);
+    return llb_fail("rmsnorm: unknown input dtype %d", x_dtype);
+}

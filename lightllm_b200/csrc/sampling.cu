@@ -1,0 +1,240 @@
+// Token selection on the device: greedy argmax, and temperature sampling with the top-k,
+// top-p and min-p filters, one block per row of logits.
+//
+// Order of operations as src/ops/sampling.cpp:22-335: temperature < 1e-5 is greedy (first
+// index of the strictly largest logit, :36-59); else logits * 1/max(T, 1e-8) (:81-84); top-k
+// keeps values >= the k-th largest, ties kept (:91-137); softmax with the maximum subtracted
+// (:143-193); top-p keeps the most probable tokens until their mass reaches p and
+// renormalises (:198-243); min-p drops probabilities below min_p * max and renormalises
+// (:248-278); the draw is the first index whose cumulative mass reaches the uniform number,
+// skipping entries without mass (:284-334).  The reference sorts on the CPU; here each filter
+// is a threshold on the value found by a bitwise search over the float's ordered bit pattern
+// (32 counting passes), so a tie at the top-p boundary keeps all tied tokens where the
+// reference's sort keeps an unspecified subset.  The uniform number comes from the caller
+// (one per row), so the random stream belongs to the request, not to the kernel.
+#include "common.cuh"
+
+#include <math.h>
+
+namespace {
+
+constexpr int THREADS = 1024;
+
+// Order-preserving map from float to unsigned: a < b  <=>  key(a) < key(b).
+__device__ __forceinline__ unsigned ordered_key(float f) {
+    const unsigned u = __float_as_uint(f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+__device__ float block_sum(float v, float* sh) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    v = llb_warp_sum(v);
+    __syncthreads();
+    if (lane == 0) sh[w] = v;
+    __syncthreads();
+    float t = threadIdx.x < (blockDim.x >> 5) ? sh[threadIdx.x] : 0.0f;
+    if (w == 0) {
+        t = llb_warp_sum(t);
+        if (lane == 0) sh[32] = t;
+    }
+    __syncthreads();
+    return sh[32];
+}
+
+__device__ float block_max(float v, float* sh) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    v = llb_warp_max(v);
+    __syncthreads();
+    if (lane == 0) sh[w] = v;
+    __syncthreads();
+    float t = threadIdx.x < (blockDim.x >> 5) ? sh[threadIdx.x] : -INFINITY;
+    if (w == 0) {
+        t = llb_warp_max(t);
+        if (lane == 0) sh[32] = t;
+    }
+    __syncthreads();
+    return sh[32];
+}
+
+// First index of the largest value of a row.
+__device__ int block_argmax(const float* x, int V, float* shf, int* shi) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        const float v = x[i];
+        if (v > best) { best = v; bi = i; }   // ascending i per thread keeps its first maximum
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    __syncthreads();
+    if (lane == 0) { shf[w] = best; shi[w] = bi; }
+    __syncthreads();
+    if (w == 0) {
+        best = lane < (blockDim.x >> 5) ? shf[lane] : -INFINITY;
+        bi = lane < (blockDim.x >> 5) ? shi[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+        }
+        if (lane == 0) shi[32] = (bi == 0x7fffffff) ? 0 : bi;
+    }
+    __syncthreads();
+    return shi[32];
+}
+
+__global__ void __launch_bounds__(THREADS) argmax_kernel(const float* __restrict__ logits, int V, long long stride,
+                                                         int* __restrict__ out) {
+    __shared__ float shf[33];
+    __shared__ int shi[33];
+    const int r = blockIdx.x;
+    const int idx = block_argmax(logits + (size_t)r * stride, V, shf, shi);
+    if (threadIdx.x == 0) out[r] = idx;
+}
+
+// params per row: temperature, top_p, min_p, uniform; top_k per row as int.
+__global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict__ logits, int V, long long stride,
+                                                         const float* __restrict__ temperature,
+                                                         const int* __restrict__ top_k,
+                                                         const float* __restrict__ top_p,
+                                                         const float* __restrict__ min_p,
+                                                         const float* __restrict__ uniform, int* __restrict__ out) {
+    __shared__ float shf[33];
+    __shared__ int shi[33];
+    __shared__ float chunk_sum[THREADS];
+    const int r = blockIdx.x;
+    const float* x = logits + (size_t)r * stride;
+    const float temp = temperature[r];
+    if (temp < 1e-5f) {
+        const int idx = block_argmax(x, V, shf, shi);
+        if (threadIdx.x == 0) out[r] = idx;
+        return;
+    }
+    const float inv_temp = 1.0f / fmaxf(temp, 1e-8f);
+    const int k = top_k ? top_k[r] : 0;
+    const float tp = top_p ? top_p[r] : 1.0f;
+    const float mp = min_p ? min_p[r] : 0.0f;
+
+    float mx = -INFINITY;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) mx = fmaxf(mx, x[i] * inv_temp);
+    mx = block_max(mx, shf);
+    if (mx == -INFINITY || !(mx == mx)) {  // every logit is -inf, or NaN: fall back to argmax
+        const int idx = block_argmax(x, V, shf, shi);
+        if (threadIdx.x == 0) out[r] = idx;
+        return;
+    }
+
+    // top-k: key of the k-th largest scaled logit (largest K with count(key >= K) >= k).
+    unsigned key_k = 0u;
+    if (k > 0 && k < V) {
+        for (int bit = 31; bit >= 0; --bit) {
+            const unsigned cand = key_k | (1u << bit);
+            float cnt = 0.0f;
+            for (int i = threadIdx.x; i < V; i += blockDim.x) cnt += ordered_key(x[i] * inv_temp) >= cand ? 1.0f : 0.0f;
+            cnt = block_sum(cnt, shf);
+            if (cnt >= (float)k) key_k = cand;
+        }
+    }
+    // e_i = exp(x_i/T - max) of the kept entries; everything below is in terms of e (max e = 1).
+    auto e_of = [&](int i) -> float {
+        const float s = x[i] * inv_temp;
+        if (ordered_key(s) < key_k) return 0.0f;
+        return expf(s - mx);
+    };
+    float z = 0.0f;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) z += e_of(i);
+    z = block_sum(z, shf);
+
+    // top-p: largest threshold on e whose kept mass still reaches p * z.
+    unsigned key_p = 0u;
+    if (tp < 1.0f) {
+        const float need = tp * z;
+        for (int bit = 31; bit >= 0; --bit) {
+            const unsigned cand = key_p | (1u << bit);
+            float mass = 0.0f;
+            for (int i = threadIdx.x; i < V; i += blockDim.x) {
+                const float e = e_of(i);
+                if (e > 0.0f && ordered_key(e) >= cand) mass += e;
+            }
+            mass = block_sum(mass, shf);
+            if (mass >= need) key_p = cand;
+        }
+    }
+    // min-p: probabilities below min_p * max probability are dropped; max e is 1.
+    const float e_min = mp > 0.0f ? mp : 0.0f;
+    auto kept_of = [&](int i) -> float {
+        const float e = e_of(i);
+        if (e <= 0.0f || ordered_key(e) < key_p || e < e_min) return 0.0f;
+        return e;
+    };
+
+    // Draw: first index whose running mass reaches u * total.  Threads own contiguous chunks.
+    const int per = (V + blockDim.x - 1) / blockDim.x;
+    const int begin = min(V, (int)threadIdx.x * per), end = min(V, begin + per);
+    float mine = 0.0f;
+    for (int i = begin; i < end; ++i) mine += kept_of(i);
+    chunk_sum[threadIdx.x] = mine;
+    const float total = block_sum(mine, shf);   // contains the barriers that publish chunk_sum
+    if (threadIdx.x == 0) {
+        int choice = -1;
+        if (total > 0.0f) {
+            const float target = uniform[r] * total;
+            float run = 0.0f;
+            int c = 0;
+            for (; c < (int)blockDim.x; ++c) {
+                if (chunk_sum[c] > 0.0f && run + chunk_sum[c] >= target) break;
+                run += chunk_sum[c];
+            }
+            if (c < (int)blockDim.x) {
+                const int b = min(V, c * per), e = min(V, b + per);
+                int last_mass = -1;
+                for (int i = b; i < e; ++i) {
+                    const float m = kept_of(i);
+                    if (m > 0.0f) {
+                        last_mass = i;
+                        run += m;
+                        if (run >= target) { choice = i; break; }
+                    }
+                }
+                if (choice < 0) choice = last_mass;
+            }
+            if (choice < 0) {  // rounding left the target above the total: last entry with mass
+                for (int i = V - 1; i >= 0 && choice < 0; --i)
+                    if (kept_of(i) > 0.0f) choice = i;
+            }
+        }
+        shi[32] = choice;
+    }
+    __syncthreads();
+    int choice = shi[32];
+    if (choice < 0) choice = block_argmax(x, V, shf, shi);   // uniform over the block
+    if (threadIdx.x == 0) out[r] = choice;
+}
+
+}  // namespace
+
+// logits [R, V] float with row stride `stride` elements; out [R] int32.
+LLB_EXPORT int llb_argmax(const float* logits, int R, int V, long long stride, int* out, cudaStream_t stream) {
+    if (R == 0) return 0;
+    LLB_REQUIRE(R > 0 && V > 0 && stride >= V, "argmax: bad sizes R=%d V=%d stride=%lld", R, V, stride);
+    argmax_kernel<<<R, THREADS, 0, stream>>>(logits, V, stride, out);
+    return llb_check_launch("argmax");
+}
+
+// Per row: temperature [R]; top_k [R] int (0 = off) or null; top_p [R] (1 = off) or null;
+// min_p [R] (0 = off) or null; uniform [R] in [0, 1).  out [R] int32.
+LLB_EXPORT int llb_sample(const float* logits, int R, int V, long long stride, const float* temperature,
+                          const int* top_k, const float* top_p, const float* min_p, const float* uniform, int* out,
+                          cudaStream_t stream) {
+    if (R == 0) return 0;
+    LLB_REQUIRE(R > 0 && V > 0 && stride >= V, "sample: bad sizes R=%d V=%d stride=%lld", R, V, stride);
+    LLB_REQUIRE(temperature && uniform && out, "sample: null argument");
+    sample_kernel<<<R, THREADS, 0, stream>>>(logits, V, stride, temperature, top_k, top_p, min_p, uniform, out);
+    return llb_check_launch("sample");
+}

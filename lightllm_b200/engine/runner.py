@@ -1,0 +1,188 @@
+"""The step function: one batch of (request, its next tokens) in, logits at the wanted places out.
+
+It runs only the tokens it is given, as one batch, against the cache that earlier steps left:
+portions of prompts beside single decoded tokens, cut anywhere.  The reference's
+``EngineServer::step`` (src/engine/engine_server.cpp:1350-2123) splits its entries into three
+attention paths (:1603-1612), re-uploads block tables for every layer (:1793-1809),
+synchronises the device per layer (:1589) and samples inside the step; here there is one path,
+one host-to-device copy of the step's metadata, no synchronisation, and the step returns logits
+(sampling is the caller's).
+"""
+from __future__ import annotations
+
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache import CacheManager
+from ..models import Model
+from ..parts import CacheView
+from .batch import Span, StepContext, StepEntry
+
+
+class StepError(ValueError):
+    """The batch given to a step is malformed."""
+
+
+class ModelRunner:
+    """Owns the device-side step metadata and runs the model over a batch."""
+
+    def __init__(self, model: Model, cache: CacheManager, max_batch_tokens: int, max_spans: Optional[int] = None):
+        if model.device is None or model.device.type != "cuda":
+            raise RuntimeError("the model is not on a CUDA device; the engine has no CPU path")
+        self.model = model
+        self.cache = cache
+        self.device = model.device
+        self.max_batch_tokens = int(max_batch_tokens)
+        self.max_spans = int(max_spans or cache.max_seqs)
+        self.ngroups = len(cache.layout.groups)
+        self.max_pages = cache.max_pages_per_seq
+        # Fixed layout of the metadata buffer (int32 words), so that its addresses never change.
+        S, T, G, P = self.max_spans, self.max_batch_tokens, self.ngroups, self.max_pages
+        off = 0
+        self._off: Dict[str, int] = {}
+        for name, n in (("span_row", S), ("span_len", S), ("span_pos", S), ("span_slot", S), ("iota", S),
+                        ("zeros", S), ("block_tables", G * S * P), ("want_rows", T), ("token_ids", T),
+                        ("positions", T), ("slot_mapping", G * T)):
+            self._off[name] = off
+            off += n
+        self._words = off
+        self._host = [torch.zeros(off, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._host_done = [None, None]
+        self._turn = 0
+        self._dev = torch.zeros(off, dtype=torch.int32, device=self.device)
+        self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.views: List[Optional[CacheView]] = []
+        for ref in cache.layout.refs:
+            if ref.group is None and ref.state_plane is None:
+                self.views.append(None)
+                continue
+            k = v = None
+            if ref.group is not None:
+                k, v = cache.plane_kv(ref.group, ref.plane)
+            st = cache.state[ref.state_plane] if ref.state_plane is not None else None
+            self.views.append(CacheView(ref.group, k, v, st, ref.owns))
+        self.last_h2d_bytes = 0
+
+    # ------------------------------------------------------------------------------------------
+    def _build_context(self, entries: Sequence[StepEntry]) -> StepContext:
+        cache = self.cache
+        vocab = self.model.spec.vocab_size
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        if len(entries) > self.max_spans:
+            raise StepError(f"{len(entries)} entries in one step; the limit is {self.max_spans}")
+        seen = set()
+        spans: List[Span] = []
+        row = 0
+        for e in entries:
+            if e.seq_id in seen:
+                raise StepError(f"request {e.seq_id!r} appears twice in one step")
+            seen.add(e.seq_id)
+            n = len(e.tokens)
+            if n == 0:
+                raise StepError(f"request {e.seq_id!r} brings no tokens")
+            seq = cache.get(e.seq_id)
+            for w in e.want:
+                if not 0 <= w < n:
+                    raise StepError(f"request {e.seq_id!r} wants place {w} of {n} tokens")
+            spans.append(Span(e.seq_id, seq.slot, seq.length, n, row))
+            row += n
+        T = row
+        if T > self.max_batch_tokens:
+            raise StepError(f"{T} tokens in one step; the limit is {self.max_batch_tokens}")
+        if max(s.start + s.length for s in spans) > self.model.spec.max_positions:
+            raise StepError(f"a request would pass the model's {self.model.spec.max_positions} positions")
+
+        o, S, P, G = self._off, len(spans), self.max_pages, self.ngroups
+        Smax, Tmax = self.max_spans, self.max_batch_tokens
+        ids = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
+        if ids.min() < 0 or ids.max() >= vocab:
+            bad = int(ids[(ids < 0) | (ids >= vocab)][0])
+            raise StepError(f"token id {bad} is outside the vocabulary of {vocab}")
+        # Pages for the new tokens are taken before anything runs; OutOfPages leaves all as it was.
+        cache.reserve_all((e.seq_id, len(e.tokens)) for e in entries)
+
+        turn = self._turn
+        self._turn ^= 1
+        if self._host_done[turn] is not None:
+            self._host_done[turn].synchronize()
+        host = self._host[turn].numpy()
+        host[o["token_ids"]: o["token_ids"] + T] = ids
+        pos = np.concatenate([np.arange(s.start, s.start + s.length, dtype=np.int32) for s in spans])
+        host[o["positions"]: o["positions"] + T] = pos
+        host[o["span_row"]: o["span_row"] + S] = [s.row for s in spans]
+        host[o["span_len"]: o["span_len"] + S] = [s.length for s in spans]
+        host[o["span_pos"]: o["span_pos"] + S] = [s.start for s in spans]
+        host[o["span_slot"]: o["span_slot"] + S] = [s.slot for s in spans]
+        host[o["iota"]: o["iota"] + S] = np.arange(S, dtype=np.int32)
+        host[o["zeros"]: o["zeros"] + S] = 0
+        ps = cache.page_size
+        for g in range(G):
+            bt = host[o["block_tables"] + g * Smax * P: o["block_tables"] + (g + 1) * Smax * P].reshape(Smax, P)
+            sm = host[o["slot_mapping"] + g * Tmax: o["slot_mapping"] + g * Tmax + T]
+            for i, s in enumerate(spans):
+                table = np.asarray(cache.block_table(s.seq_id, g), dtype=np.int32)
+                bt[i, : len(table)] = table
+                p = pos[s.row: s.row + s.length]
+                sm[s.row: s.row + s.length] = table[p // ps] * ps + p % ps
+        want = [s.row + w for s, e in zip(spans, entries) for w in e.want]
+        R = len(want)
+        host[o["want_rows"]: o["want_rows"] + R] = want
+
+        self._dev.copy_(self._host[turn], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._host_done[turn] = ev
+        self.last_h2d_bytes = self._words * 4
+
+        d = self._dev
+        ctx = StepContext()
+        ctx.T, ctx.spans = T, spans
+        ctx.token_ids = d[o["token_ids"]: o["token_ids"] + T]
+        ctx.positions = d[o["positions"]: o["positions"] + T]
+        ctx.span_row = d[o["span_row"]: o["span_row"] + S]
+        ctx.span_len = d[o["span_len"]: o["span_len"] + S]
+        ctx.span_pos = d[o["span_pos"]: o["span_pos"] + S]
+        ctx.span_slot = d[o["span_slot"]: o["span_slot"] + S]
+        ctx.iota = d[o["iota"]: o["iota"] + S]
+        ctx.zeros = d[o["zeros"]: o["zeros"] + S]
+        ctx.slot_mapping = [d[o["slot_mapping"] + g * Tmax: o["slot_mapping"] + g * Tmax + T] for g in range(G)]
+        ctx.block_tables = [d[o["block_tables"] + g * Smax * P: o["block_tables"] + g * Smax * P + S * P].view(S, P)
+                            for g in range(G)]
+        ctx.want_rows = d[o["want_rows"]: o["want_rows"] + R]
+        ctx.num_want = R
+        ctx.max_pages, ctx.page_size = P, ps
+        ctx.decode_only = all(s.length == 1 for s in spans)
+        ctx.max_context = max(s.start + s.length for s in spans)
+        ctx.dtype, ctx.device = self.model.dtype, self.device
+        ctx.cache, ctx.err = cache, self.err
+        return ctx
+
+    def forward(self, ctx: StepContext) -> Optional[torch.Tensor]:
+        """Run the layers over the batch that ``ctx`` describes; logits float32 [R, V] or None."""
+        m = self.model
+        residual = m.embedding.forward(ctx.token_ids, ctx)
+        for entry, view in zip(m.run, self.views):
+            m.layers[entry.layer].forward(residual, ctx, view)
+        if ctx.num_want == 0:
+            return None
+        x = m.final_norm.forward_rows(residual, ctx.want_rows, ctx)
+        return m.head.forward(x, ctx)
+
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """One step.  Returns the logits at the wanted places, in the order of the entries and of
+        each entry's ``want``, as a float32 ``[wanted, vocab]`` tensor on the device (``None`` if
+        nothing is wanted).  Afterwards every request holds its new tokens."""
+        ctx = self._build_context(entries)
+        logits = self.forward(ctx)
+        for e in entries:
+            self.cache.advance(e.seq_id, len(e.tokens))
+        return logits
+
+    def check_device_errors(self) -> None:
+        """Raise if a kernel flagged a fault (an id outside the vocabulary reached the device)."""
+        if int(self.err.item()) != 0:
+            self.err.zero_()
+            raise RuntimeError("a kernel reported an out-of-range token id")

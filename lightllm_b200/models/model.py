@@ -1,0 +1,95 @@
+"""A model as the engine runs it: parts built from a :class:`ModelSpec`, weights bound by name."""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from ..cache import CacheLayout
+from ..config import ModelConfig, ModelSpec, load_config, model_spec_for
+from ..parts import Block, Part, build_part
+from ..weights import WeightSpec, dedup_specs, load_checkpoint_tensors
+
+# Tensor-name endings that a checkpoint may carry without the model reading them.
+IGNORED_SUFFIXES = ("rotary_emb.inv_freq",)
+
+
+def _walk(part: Part):
+    yield part
+    for c in part.children():
+        yield from _walk(c)
+
+
+class Model:
+    """Embedding, the layers, the run list over them, final norm and head.
+
+    The run list is data (``spec.run``): it may name a layer twice (the weights are shared, each
+    run has its own cache plane) or let a run read an earlier run's cache."""
+
+    def __init__(self, spec: ModelSpec):
+        spec.validate()
+        self.spec = spec
+        self.embedding = build_part("embedding", spec.embedding)
+        self.layers: List[Block] = [Block(ls) for ls in spec.layers]
+        self.final_norm = build_part("norm", spec.final_norm)
+        self.head = build_part("head", spec.head)
+        self.run = list(spec.run)
+        self.cache_layout = CacheLayout.build(
+            [self.layers[e.layer].mixer.cache_spec() for e in self.run], [e.cache_of for e in self.run])
+        self.dtype: Optional[torch.dtype] = None
+        self.device: Optional[torch.device] = None
+
+    def parts(self) -> List[Part]:
+        out: List[Part] = []
+        for top in [self.embedding, *self.layers, self.final_norm, self.head]:
+            out.extend(_walk(top))
+        return out
+
+    def weight_specs(self) -> List[WeightSpec]:
+        specs: List[WeightSpec] = []
+        for p in self.parts():
+            if not isinstance(p, Block):
+                specs.extend(p.weight_specs())
+        return dedup_specs(specs)
+
+    def bind(self, tensors: Dict[str, torch.Tensor], dtype: torch.dtype, device: torch.device) -> None:
+        self.dtype, self.device = dtype, device
+        for p in self.parts():
+            if not isinstance(p, Block):
+                p.bind(tensors, dtype, device)
+
+    def weight_bytes(self) -> int:
+        """Bytes of the tensors a step reads (a tied table counts once)."""
+        seen, total = set(), 0
+        for p in self.parts():
+            for v in vars(p).values():
+                if isinstance(v, torch.Tensor) and v.data_ptr() not in seen:
+                    seen.add(v.data_ptr())
+                    total += v.numel() * v.element_size()
+        return total
+
+
+def weight_specs_of(spec: ModelSpec) -> List[WeightSpec]:
+    return Model(spec).weight_specs()
+
+
+_DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, torch.float32: torch.float32,
+           torch.bfloat16: torch.bfloat16}
+
+
+def compute_dtype(name) -> torch.dtype:
+    try:
+        return _DTYPES[name]
+    except KeyError:
+        raise ValueError(f"dtype must be 'float32' or 'bfloat16', got {name!r}") from None
+
+
+def load_model(model_dir: str, dtype, device: torch.device) -> Model:
+    """Build the model that ``model_dir/config.json`` names and bind ``model.safetensors`` to it."""
+    config = load_config(model_dir)
+    model = Model(model_spec_for(config))
+    model.config = config
+    dt = compute_dtype(dtype)
+    tensors = load_checkpoint_tensors(model_dir, model.weight_specs(), dt, device, IGNORED_SUFFIXES)
+    model.bind(tensors, dt, device)
+    return model

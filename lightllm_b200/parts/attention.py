@@ -1,0 +1,141 @@
+"""The attention mixer: grouped-query attention over the paged cache."""
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional
+
+import torch
+
+from ..cache import CacheSpec, KVSpec
+from ..config import PartSpec, part_class, register_part
+from ..csrc import ops
+from ..weights import WeightSpec
+from . import linear as L
+from .base import CacheView, Mixer
+
+# Shared memory budget per block used to pick the tile height of the CUDA-core kernel.
+_SMEM_BUDGET = 100 * 1024
+_SMEM_LIMIT = 200 * 1024
+
+
+class AttentionMixer(Mixer):
+    """q, k, v projections (one fused contraction, bias in its epilogue), position encoding
+    fused with the cache write, attention of every query over its request's pages, output
+    projection added into the residual stream.
+
+    Formulas: src/engine/engine_server.cpp:1542-1549 (projections), src/ops/rope.cu:54-59
+    (rotation), src/kv_cache/paged_attention.cu:115,153-163 (grouping, scores, softmax),
+    engine_server.cpp:1870-1871 (output projection and residual).  Unlike the reference the
+    q/k/v biases are loaded and added, a token sees its own key, every portion is causal, and
+    ``window`` limits a query to the latest ``window`` keys (itself included)."""
+
+    def __init__(self, prefix: str, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 position: Optional[PartSpec] = None, qkv_bias: bool = True, out_bias: bool = False,
+                 window: Optional[int] = None, scale: Optional[float] = None,
+                 names: Optional[Dict[str, str]] = None):
+        if num_heads % num_kv_heads:
+            raise ValueError(f"{num_heads} query heads are not a multiple of {num_kv_heads} kv heads")
+        self.prefix = prefix
+        self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim = hidden_size, num_heads, num_kv_heads, head_dim
+        self.qkv_bias, self.out_bias = qkv_bias, out_bias
+        self.window = window
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
+        self.names = {"q": "q_proj", "k": "k_proj", "v": "v_proj", "o": "o_proj"}
+        self.names.update(names or {})
+        position = position or PartSpec("none")
+        self.position = part_class("position", position.kind)(position.prefix, **position.params)
+        self.w_qkv = self.b_qkv = self.w_o = self.b_o = None
+
+    def _n(self, which: str, what: str) -> str:
+        return f"{self.prefix}.{self.names[which]}.{what}"
+
+    def children(self):
+        return [self.position]
+
+    def cache_spec(self) -> CacheSpec:
+        return CacheSpec(kv=KVSpec(self.num_kv_heads, self.head_dim, self.window))
+
+    def weight_specs(self) -> List[WeightSpec]:
+        D, hq, hkv = self.hidden_size, self.num_heads * self.head_dim, self.num_kv_heads * self.head_dim
+        specs = [WeightSpec(self._n("q", "weight"), (hq, D)), WeightSpec(self._n("k", "weight"), (hkv, D)),
+                 WeightSpec(self._n("v", "weight"), (hkv, D)), WeightSpec(self._n("o", "weight"), (D, hq))]
+        if self.qkv_bias:
+            specs += [WeightSpec(self._n("q", "bias"), (hq,)), WeightSpec(self._n("k", "bias"), (hkv,)),
+                      WeightSpec(self._n("v", "bias"), (hkv,))]
+        if self.out_bias:
+            specs.append(WeightSpec(self._n("o", "bias"), (D,)))
+        return specs + self.position.weight_specs()
+
+    def bind(self, tensors, dtype, device) -> None:
+        ws = [tensors[self._n(p, "weight")] for p in "qkv"]
+        wdt = torch.float32 if any(w.dtype == torch.float32 for w in ws) else ws[0].dtype
+        self.w_qkv = torch.cat([w.to(wdt) for w in ws], dim=0).contiguous()
+        self.w_o = tensors[self._n("o", "weight")]
+        if self.qkv_bias:
+            self.b_qkv = torch.cat([tensors[self._n(p, "bias")].float() for p in "qkv"]).contiguous()
+        if self.out_bias:
+            self.b_o = tensors[self._n("o", "bias")].float().contiguous()
+        self.position.bind(tensors, dtype, device)
+
+    # ------------------------------------------------------------------------------------------
+    def forward(self, x, residual, ctx, cache: CacheView) -> None:
+        T = x.shape[0]
+        hq, hkv, hd = self.num_heads, self.num_kv_heads, self.head_dim
+        writes = cache.writes
+        if writes:
+            qkv = L.linear(x, self.w_qkv, self.b_qkv, L.STORE)
+        else:  # the keys and values of another run entry are read; only q is projected
+            qkv = L.linear(x, self.w_qkv[: hq * hd], None if self.b_qkv is None else self.b_qkv[: hq * hd], L.STORE)
+        table = self.position.rotary_table()
+        if table is None:
+            table = (None, 0, False)
+            qv = qkv[:, : hq * hd].reshape(T, hq, hd)
+            kv = qkv[:, hq * hd: (hq + hkv) * hd].reshape(T, hkv, hd) if writes else None
+            q2, k2 = self.position.apply(qv, kv, ctx.positions)
+            if q2 is not qv:
+                qkv[:, : hq * hd] = q2.reshape(T, hq * hd)
+            if writes and k2 is not kv:
+                qkv[:, hq * hd: (hq + hkv) * hd] = k2.reshape(T, hkv * hd)
+        inv_freq, rotary_dim, interleaved = table
+        q = torch.empty((T, hq * hd), dtype=x.dtype, device=x.device)
+        ops.rope_kv_write(qkv, ctx.positions, ctx.slot_mapping[cache.group] if writes else None, inv_freq,
+                          rotary_dim, interleaved, q, cache.k if writes else None, cache.v if writes else None,
+                          hq, hkv, hd)
+        attn = torch.empty((T, hq * hd), dtype=x.dtype, device=x.device)
+        self.attend(q, cache, ctx, attn)
+        L.linear(attn, self.w_o, self.b_o, L.RESIDUAL, residual=residual)
+
+    def tile_height(self) -> int:
+        group = self.num_heads // self.num_kv_heads
+        for bq in (16, 8, 4, 2, 1):
+            need = ops.attention_smem_bytes(bq, group, self.head_dim)
+            if need <= _SMEM_BUDGET or (bq == 1 and need <= _SMEM_LIMIT):
+                return bq
+        raise ops.KernelError(
+            f"attention with {group} query heads per kv head and head_dim {self.head_dim} does not fit "
+            f"in shared memory even with one query row per block")
+
+    def attend(self, q, cache: CacheView, ctx, out) -> None:
+        """out[t] = attention of query row t over positions <= its own (within the window)."""
+        g = cache.group
+        window = self.window or 0
+        if ctx.decode_only:
+            bq = 1
+            S = ctx.num_spans
+            span = ctx.max_context if window == 0 else min(ctx.max_context, window)
+            want = max(1, -(-2 * 148 // (S * self.num_kv_heads)))       # blocks to fill the SMs twice
+            nsplit = max(1, min(want, -(-span // 128)))
+        else:
+            bq, nsplit = self.tile_height(), 1
+        tile_span, tile_q0, ntiles = ctx.tiles(bq)
+        scratch = None
+        if nsplit > 1:
+            scratch = torch.empty(ops.attention_scratch_floats(ntiles, self.num_heads, self.head_dim, bq, nsplit),
+                                  dtype=torch.float32, device=q.device)
+        ops.paged_attention_simt(q, cache.k, cache.v, out, tile_span, tile_q0, ntiles,
+                                 ctx.span_row, ctx.span_len, ctx.span_pos, ctx.block_tables[g],
+                                 ctx.max_pages, ctx.page_size, self.num_heads, self.num_kv_heads, self.head_dim,
+                                 window, self.scale, bq, nsplit, scratch)
+
+
+register_part("mixer", "attention", AttentionMixer)

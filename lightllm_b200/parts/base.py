@@ -1,0 +1,97 @@
+"""Interfaces of the parts a layer is put together from.
+
+A part is built from a :class:`~lightllm_b200.config.PartSpec` as ``cls(prefix, **params)``:
+every size and constant is a parameter, and no part knows which model it is in.  It lists the
+checkpoint tensors it reads (:meth:`Part.weight_specs`), receives them already on the device in
+:meth:`Part.bind`, and then runs on the GPU.
+
+Roles and what each must provide:
+
+``norm``       ``forward(residual[T, D] float32, ctx) -> x[T, D]`` in the compute dtype, and
+               ``forward_rows(residual, rows[R] int32, ctx) -> x[R, D]``.
+``mixer``      ``cache_spec() -> CacheSpec | None`` and
+               ``forward(x[T, D], residual[T, D] float32, ctx, cache)``, which **adds** its output
+               into ``residual`` in place.  ``cache`` is a :class:`CacheView` of the planes the
+               layout gave this run of the layer, or ``None`` if it asked for nothing.
+``ffn``        ``forward(x[T, D], residual[T, D] float32, ctx)``, adding into ``residual``.
+``position``   ``rotary_table() -> (inv_freq, rotary_dim, interleaved) | None`` for encodings the
+               fused rotation kernel can apply, else ``apply(q, k, positions) -> (q, k)``.
+``embedding``  ``forward(token_ids[T] int32, ctx) -> residual[T, D] float32``.
+``head``       ``forward(x[R, D], ctx) -> logits[R, V] float32``.
+
+The residual stream is float32 in both precisions, so the residual sum is exact to float.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional
+
+import torch
+
+from ..cache import CacheSpec
+from ..weights import WeightSpec
+
+
+class Part:
+    role = "part"
+
+    def weight_specs(self) -> List[WeightSpec]:
+        return []
+
+    def bind(self, tensors: Dict[str, torch.Tensor], dtype: torch.dtype, device: torch.device) -> None:
+        """Take this part's tensors out of ``tensors`` (by the names it declared)."""
+
+    def children(self) -> List["Part"]:
+        return []
+
+
+@dataclass
+class CacheView:
+    """The cache planes of one run of a layer.
+
+    ``k``, ``v``: ``[pages * page_size, kv_heads, head_dim]`` or ``None``; ``group`` indexes
+    ``ctx.slot_mapping`` and ``ctx.block_tables``; ``state``: ``[max_seqs, *shape]`` or ``None``,
+    indexed by ``Span.slot``; ``writes`` is False when the planes belong to another run entry."""
+
+    group: Optional[int] = None
+    k: Optional[torch.Tensor] = None
+    v: Optional[torch.Tensor] = None
+    state: Optional[torch.Tensor] = None
+    writes: bool = True
+
+
+class Mixer(Part):
+    role = "mixer"
+
+    def cache_spec(self) -> Optional[CacheSpec]:
+        return None
+
+    def forward(self, x, residual, ctx, cache: Optional[CacheView]) -> None:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    role = "ffn"
+
+    def forward(self, x, residual, ctx) -> None:
+        raise NotImplementedError
+
+
+class Norm(Part):
+    role = "norm"
+
+    def forward(self, residual, ctx):
+        raise NotImplementedError
+
+    def forward_rows(self, residual, rows, ctx):
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    role = "position"
+
+    def rotary_table(self):
+        return None
+
+    def apply(self, q, k, positions):
+        return q, k

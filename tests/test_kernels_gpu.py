@@ -1,0 +1,291 @@
+"""Each kernel alone against a plain PyTorch float32 reference of the same op, at sizes other
+than the engine's."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from tests.plain.qwen2_plain import (plain_attention, plain_draw, plain_rmsnorm, plain_rope, plain_sampling_probs,
+                                     plain_silu)
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from lightllm_b200.csrc import ops as o
+    o.lib()
+    return o
+
+
+def dev():
+    return torch.device("cuda:0")
+
+
+def rnd(shape, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype).to(dev())
+
+
+DT = [torch.float32, torch.bfloat16]
+
+
+@pytest.mark.parametrize("table_dtype", DT)
+def test_embedding(ops, table_dtype):
+    V, D = 301, 72
+    table = rnd((V, D), table_dtype, 1)
+    ids = torch.tensor([0, 300, 5, 5, 17, 123], dtype=torch.int32, device=dev())
+    out = torch.empty((6, D), dtype=torch.float32, device=dev())
+    err = torch.zeros(1, dtype=torch.int32, device=dev())
+    ops.embedding(ids, table, out, err)
+    assert torch.equal(out, table.float()[ids.long()])
+    assert int(err.item()) == 0
+    bad = torch.tensor([1, V], dtype=torch.int32, device=dev())
+    out2 = torch.empty((2, D), dtype=torch.float32, device=dev())
+    ops.embedding(bad, table, out2, err)
+    assert int(err.item()) == 1 and float(out2[1].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("D", [24, 896, 1000, 1536, 5000])
+@pytest.mark.parametrize("out_dtype", DT)
+@pytest.mark.parametrize("w_dtype", DT)
+def test_rmsnorm(ops, D, out_dtype, w_dtype):
+    x = rnd((7, D), torch.float32, 2, 3.0)
+    w = (1 + 0.1 * rnd((D,), torch.float32, 3)).to(w_dtype)
+    for eps in (1e-6, 1e-2):
+        out = torch.empty((7, D), dtype=out_dtype, device=dev())
+        ops.rmsnorm(x, w, eps, out)
+        ref = plain_rmsnorm(x.cpu(), w.float().cpu(), eps)
+        tol = 1e-5 if out_dtype == torch.float32 else 2e-2
+        assert torch.allclose(out.float().cpu(), ref, atol=tol, rtol=tol)
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32, device=dev())
+    out = torch.empty((3, D), dtype=out_dtype, device=dev())
+    ops.rmsnorm(x, w, 1e-6, out, rows=rows)
+    ref = plain_rmsnorm(x.cpu()[[6, 0, 3]], w.float().cpu(), 1e-6)
+    assert torch.allclose(out.float().cpu(), ref, atol=2e-2 if out_dtype == torch.bfloat16 else 1e-5, rtol=2e-2)
+
+
+GEMM_SHAPES = [(1, 50, 37), (3, 127, 172), (8, 64, 896), (9, 66, 45), (70, 130, 172), (129, 1000, 96), (5, 2, 8)]
+
+
+def gemm_reference(a, w, bias, epi, residual):
+    acc = a.double().cpu() @ w.double().cpu().t()
+    if bias is not None:
+        acc = acc + bias.double().cpu()
+    if epi == 2:
+        return residual.double().cpu() + acc
+    if epi == 3:
+        g, u = acc[:, 0::2], acc[:, 1::2]
+        return plain_silu(g) * u
+    return acc
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+@pytest.mark.parametrize("epi", [0, 1, 2, 3])
+@pytest.mark.parametrize("dtypes", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                    (torch.bfloat16, torch.float32)])
+def test_gemm_simt(ops, M, N, K, epi, dtypes):
+    adt, wdt = dtypes
+    a, w = rnd((M, K), adt, 4), rnd((N, K), wdt, 5, 0.2)
+    for bias in (None, rnd((N,), torch.float32, 6)):
+        residual = rnd((M, N), torch.float32, 7)
+        res0 = residual.clone()
+        out = None
+        if epi in (0, 3):
+            out = torch.empty((M, N // 2 if epi == 3 else N), dtype=adt, device=dev())
+        elif epi == 1:
+            out = torch.empty((M, N), dtype=torch.float32, device=dev())
+        ops.gemm_simt(a, w, bias, epi, out, residual if epi == 2 else None)
+        ref = gemm_reference(a, w, bias, epi, res0)
+        got = (residual if epi == 2 else out).double().cpu()
+        exact_out = epi in (1, 2) or adt == torch.float32
+        tol = 2e-5 * math.sqrt(K) if exact_out else 1e-2
+        assert torch.allclose(got, ref, atol=tol * max(1.0, float(ref.abs().max())), rtol=0), \
+            f"max diff {float((got - ref).abs().max())}"
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("hd,rd,inter", [(16, 16, False), (32, 32, True), (64, 64, False), (48, 32, False),
+                                         (128, 64, True)])
+def test_rope_kv_write(ops, dtype, hd, rd, inter):
+    T, Hq, Hkv, page, npages = 11, 3, 1, 8, 6
+    qkv = rnd((T, (Hq + 2 * Hkv) * hd), dtype, 8)
+    pos = torch.tensor([0, 1, 2, 40, 41, 7, 100, 3000, 5, 6, 7], dtype=torch.int32, device=dev())
+    slots = torch.tensor([3, 9, 47, 0, 1, 2, 21, 22, 8, -1, 30], dtype=torch.int32, device=dev())
+    theta = 10000.0
+    inv = torch.from_numpy((1.0 / np.power(np.float64(theta), np.arange(0, rd, 2, dtype=np.float64) / rd))
+                           .astype(np.float32)).to(dev())
+    kc = torch.full((npages * page, Hkv, hd), 77.0, dtype=dtype, device=dev())
+    vc = torch.full((npages * page, Hkv, hd), 77.0, dtype=dtype, device=dev())
+    q = torch.empty((T, Hq * hd), dtype=dtype, device=dev())
+    ops.rope_kv_write(qkv, pos, slots, inv, rd, inter, q, kc, vc, Hq, Hkv, hd)
+    x = qkv.float().cpu()
+    qr = plain_rope(x[:, : Hq * hd].reshape(T, Hq, hd), pos.cpu(), theta, rd, inter)
+    kr = plain_rope(x[:, Hq * hd: (Hq + Hkv) * hd].reshape(T, Hkv, hd), pos.cpu(), theta, rd, inter)
+    vr = x[:, (Hq + Hkv) * hd:].reshape(T, Hkv, hd)
+    tol = 2e-5 if dtype == torch.float32 else 2e-2
+    assert torch.allclose(q.float().cpu().reshape(T, Hq, hd), qr, atol=tol, rtol=tol)
+    kexp = torch.full((npages * page, Hkv, hd), 77.0)
+    vexp = kexp.clone()
+    for t, s in enumerate(slots.tolist()):
+        if s >= 0:
+            kexp[s], vexp[s] = kr[t], vr[t]
+    assert torch.allclose(kc.float().cpu(), kexp, atol=tol, rtol=tol)
+    assert torch.allclose(vc.float().cpu(), vexp.to(dtype).float(), atol=0, rtol=0)
+    # q only (another entry's cache is read): nothing is written
+    q2 = torch.empty((T, Hq * hd), dtype=dtype, device=dev())
+    ops.rope_kv_write(qkv[:, : Hq * hd].contiguous(), pos, None, inv, rd, inter, q2, None, None, Hq, Hkv, hd)
+    assert torch.equal(q2, q)
+
+
+def paged_setup(dtype, lens, starts, Hq, Hkv, hd, page, seed, spike=False):
+    """Random requests laid out in shuffled pages.  Returns what the kernel needs and, per
+    request, the contiguous q, k, v of its whole context for the plain reference."""
+    g = torch.Generator().manual_seed(seed)
+    S = len(lens)
+    ctx = [s + n for s, n in zip(starts, lens)]
+    max_pages = max(-(-c // page) for c in ctx) + 1
+    total_pages = sum(-(-c // page) for c in ctx) + 3
+    perm = torch.randperm(total_pages, generator=g).tolist()
+    kc = torch.full((total_pages * page, Hkv, hd), float("nan"), dtype=torch.float32)
+    vc = torch.full((total_pages * page, Hkv, hd), float("nan"), dtype=torch.float32)
+    bt = torch.full((S, max_pages), -1, dtype=torch.int32)
+    full = []
+    rows = 0
+    for i in range(S):
+        k = torch.randn((ctx[i], Hkv, hd), generator=g).to(dtype).float()
+        v = torch.randn((ctx[i], Hkv, hd), generator=g).to(dtype).float()
+        qf = torch.randn((ctx[i], Hq, hd), generator=g).to(dtype).float()
+        if spike:  # one far key stands out for the last query: a stale or skipped page shows
+            far = min(3, ctx[i] - 1)
+            k[far] = 0
+            k[far, :, 0] = 8.0
+            qf[-1] = 0
+            qf[-1, :, 0] = 8.0
+            v[far] = 5.0
+        for lp in range(-(-ctx[i] // page)):
+            phys = perm.pop()
+            bt[i, lp] = phys
+            n = min(page, ctx[i] - lp * page)
+            kc[phys * page: phys * page + n] = k[lp * page: lp * page + n]
+            vc[phys * page: phys * page + n] = v[lp * page: lp * page + n]
+        full.append((qf, k, v))
+        rows += lens[i]
+    q = torch.cat([full[i][0][starts[i]:] for i in range(S)], dim=0)
+    d = dev()
+    span_row = torch.tensor(np.cumsum([0] + lens[:-1]), dtype=torch.int32, device=d)
+    return dict(q=q.to(dtype).to(d).reshape(rows, Hq * hd), kc=kc.to(dtype).to(d), vc=vc.to(dtype).to(d),
+                bt=bt.to(d), max_pages=max_pages, span_row=span_row,
+                span_len=torch.tensor(lens, dtype=torch.int32, device=d),
+                span_pos=torch.tensor(starts, dtype=torch.int32, device=d), full=full, rows=rows)
+
+
+def attention_reference(full, lens, starts, hd, window):
+    outs = []
+    for (qf, k, v), n, s in zip(full, lens, starts):
+        o = plain_attention(qf, k, v, 1.0 / math.sqrt(hd), window)
+        outs.append(o[s:])
+    return torch.cat(outs, dim=0)
+
+
+def tiles_for(lens, bq):
+    ts, tq = [], []
+    for i, n in enumerate(lens):
+        for q0 in range(0, n, bq):
+            ts.append(i)
+            tq.append(q0)
+    d = dev()
+    return torch.tensor(ts, dtype=torch.int32, device=d), torch.tensor(tq, dtype=torch.int32, device=d), len(ts)
+
+
+ATTN_CASES = [
+    # Hq, Hkv, hd, page, lens, starts, window, bq
+    (4, 2, 16, 16, [5, 17, 33], [0, 0, 0], None, 8),
+    (3, 1, 32, 8, [1, 9, 40, 2], [70, 0, 31, 64], None, 4),
+    (14, 2, 64, 16, [1, 1, 50], [300, 15, 200], None, 16),
+    (5, 5, 48, 16, [1, 30, 3], [100, 17, 19], 20, 8),
+    (6, 3, 80, 4, [2, 64], [62, 0], 7, 2),
+    (8, 1, 128, 16, [7, 1], [9, 500], None, 4),
+]
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("case", ATTN_CASES)
+@pytest.mark.parametrize("spike", [False, True])
+def test_paged_attention_simt(ops, dtype, case, spike):
+    Hq, Hkv, hd, page, lens, starts, window, bq = case
+    s = paged_setup(dtype, lens, starts, Hq, Hkv, hd, page, seed=21, spike=spike)
+    ts, tq, nt = tiles_for(lens, bq)
+    out = torch.full((s["rows"], Hq * hd), float("nan"), dtype=dtype, device=dev())
+    ops.paged_attention_simt(s["q"], s["kc"], s["vc"], out, ts, tq, nt, s["span_row"], s["span_len"], s["span_pos"],
+                             s["bt"], s["max_pages"], page, Hq, Hkv, hd, window or 0, 1.0 / math.sqrt(hd), bq)
+    ref = attention_reference(s["full"], lens, starts, hd, window).reshape(s["rows"], Hq * hd)
+    tol = 2e-5 if dtype == torch.float32 else 2e-2
+    got = out.float().cpu()
+    assert not torch.isnan(got).any()
+    assert torch.allclose(got, ref, atol=tol, rtol=tol), f"max diff {float((got - ref).abs().max())}"
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("nsplit", [2, 5, 16])
+@pytest.mark.parametrize("window", [None, 100])
+def test_paged_attention_split(ops, dtype, nsplit, window):
+    Hq, Hkv, hd, page = 14, 2, 64, 16
+    lens, starts = [1, 1, 1, 1], [700, 0, 33, 257]
+    s = paged_setup(dtype, lens, starts, Hq, Hkv, hd, page, seed=22, spike=True)
+    ts, tq, nt = tiles_for(lens, 1)
+    out = torch.full((4, Hq * hd), float("nan"), dtype=dtype, device=dev())
+    scratch = torch.empty(ops.attention_scratch_floats(nt, Hq, hd, 1, nsplit), dtype=torch.float32, device=dev())
+    ops.paged_attention_simt(s["q"], s["kc"], s["vc"], out, ts, tq, nt, s["span_row"], s["span_len"], s["span_pos"],
+                             s["bt"], s["max_pages"], page, Hq, Hkv, hd, window or 0, 1.0 / math.sqrt(hd), 1,
+                             nsplit, scratch)
+    ref = attention_reference(s["full"], lens, starts, hd, window).reshape(4, Hq * hd)
+    tol = 2e-5 if dtype == torch.float32 else 2e-2
+    got = out.float().cpu()
+    assert torch.allclose(got, ref, atol=tol, rtol=tol), f"max diff {float((got - ref).abs().max())}"
+
+
+def test_argmax_lowest_index_on_ties(ops):
+    V = 151937
+    x = rnd((5, V), torch.float32, 30)
+    x[0, 100] = x[0, 9000] = 50.0
+    x[1, V - 1] = 60.0
+    x[2, :] = 1.0
+    out = torch.empty(5, dtype=torch.int32, device=dev())
+    ops.argmax(x, out)
+    ref = [int(np.argmax(r)) for r in x.cpu().numpy()]
+    assert out.cpu().tolist() == ref
+    assert out[0].item() == 100 and out[2].item() == 0
+
+
+@pytest.mark.parametrize("temperature,top_k,top_p,min_p", [(1.0, 0, 1.0, 0.0), (0.7, 40, 1.0, 0.0),
+                                                           (1.3, 0, 0.9, 0.0), (1.0, 0, 1.0, 0.05),
+                                                           (0.8, 50, 0.95, 0.02), (0.0, 0, 1.0, 0.0)])
+def test_sample_matches_plain_distribution(ops, temperature, top_k, top_p, min_p):
+    """For many uniform numbers the kernel picks the token that the plain inverse-CDF draw picks
+    from the plain filtered distribution (up to draws that fall within rounding of a boundary)."""
+    V, R = 1003, 256
+    g = torch.Generator().manual_seed(31)
+    logits_row = torch.randn(V, generator=g) * 3.0
+    logits = logits_row[None, :].repeat(R, 1).contiguous().to(dev())
+    u = (torch.arange(R, dtype=torch.float32) + 0.5) / R
+    out = torch.empty(R, dtype=torch.int32, device=dev())
+    f = lambda v: torch.full((R,), v, dtype=torch.float32, device=dev())
+    ops.sample(logits, f(temperature), torch.full((R,), top_k, dtype=torch.int32, device=dev()), f(top_p), f(min_p),
+               u.to(dev()), out)
+    got = out.cpu().tolist()
+    if temperature < 1e-5:
+        assert set(got) == {int(torch.argmax(logits_row))}
+        return
+    p = plain_sampling_probs(logits_row.numpy(), temperature, top_k, top_p, min_p)
+    ref = [plain_draw(p, float(x)) for x in u]
+    cdf = np.cumsum(p)
+    wrong = 0
+    for gi, ri, x in zip(got, ref, u.tolist()):
+        assert p[gi] > 0.0, "a filtered token was drawn"
+        if gi != ri:
+            near = min(abs(cdf[min(gi, ri)] - x), abs(cdf[max(gi, ri) - 1] - x) if max(gi, ri) > 0 else 1.0)
+            assert near < 1e-4, f"u={x}: kernel {gi}, plain {ri}"
+            wrong += 1
+    assert wrong <= 3
