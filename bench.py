@@ -1,0 +1,277 @@
+#!/usr/bin/env python3
+"""Benchmark of the engine on one B200: decode tokens a second at Qwen2.5-0.5B sizes.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L]
+
+Prints one JSON line.  ``value`` is decoded tokens a second over K timed decode steps of a
+batch of 8 requests that each hold a 2,048-token prompt (random weights, random token ids),
+timed on the device with CUDA events.  ``e2e`` is the same through the Python entry point's
+serve loop, with host token ids in and out every step.  ``prefill`` is one 2,048-token prompt
+in one step; ``points`` are decode at batch 1 and 64; ``roofline`` relates the decode step to
+the bytes it has to read.  The engine runs on one GPU only: for ``--gpus`` above 1 it says so
+and exits with 2.  ``--impl reference`` reports why the reference cannot run here.
+"""
+import argparse
+import json
+import os
+import random
+import shutil
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# BASELINE.json configs[2]: Qwen2.5-0.5B sizes.
+QWEN25_05B = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 24, "hidden_size": 896, "num_attention_heads": 14, "num_key_value_heads": 2,
+    "intermediate_size": 4864, "vocab_size": 151936, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
+    "tie_word_embeddings": True, "max_position_embeddings": 32768, "sliding_window": 32768,
+    "max_window_layers": 24, "use_sliding_window": False, "hidden_act": "silu",
+}
+PROMPT_LEN = 2048
+CONTEXT_LEN = 4096
+PAGE_SIZE = 16
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        exe = shutil.which("nvidia-smi")
+        if not exe:
+            return
+        fd, self.path = tempfile.mkstemp(suffix=".csv")
+        os.close(fd)
+        self.proc = subprocess.Popen([exe, "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                      "-lms", "100"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        rows = []
+        with open(self.path) as f:
+            for line in f:
+                parts = [x.strip() for x in line.split(",")]
+                if len(parts) == 6 and parts[0].isdigit():
+                    rows.append(parts)
+        os.remove(self.path)
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        sm = sorted(int(r[0]) for r in rows)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in rows)]
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": int(rows[0][1]), "reasons": reasons, "samples": len(rows)}
+
+
+def make_model_dir(layers: int) -> str:
+    from lightllm_b200 import write_random_model
+    cfg = dict(QWEN25_05B)
+    cfg["num_hidden_layers"] = layers
+    cfg["max_window_layers"] = layers
+    d = tempfile.mkdtemp(prefix="llb_bench_model_")
+    write_random_model(cfg, seed=0, out_dir=d, store_dtype="bfloat16")
+    return d
+
+
+def flops_prefill(cfg, layers, T):
+    D, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    Hq, Hkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    hd = D // Hq
+    linear = 2 * T * (D * (Hq + 2 * Hkv) * hd + Hq * hd * D + 3 * D * I)
+    attn = 2 * 2 * Hq * hd * T * (T + 1) // 2      # QK^T and PV over the causal half
+    return layers * (linear + attn) + 2 * D * V    # head for the last row
+
+
+def decode_bytes(core, batch, ctx_len):
+    """Bytes a decode step has to read: every weight it uses once, and the cache of the live requests."""
+    esize = 2
+    kv = core.model.cache_layout.bytes_per_token(esize) * batch * ctx_len
+    weights = core.model.weight_bytes()
+    D, V = core.model.spec.hidden_size, core.model.spec.vocab_size
+    # the embedding table is the head's matrix when tied and is then read in full; rows gathered are negligible
+    if core.model.head.weight.data_ptr() != core.model.embedding.table.data_ptr():
+        weights -= V * D * esize
+    return weights + kv
+
+
+def time_decode(core, batch, steps, warmup, rng):
+    import torch
+    from lightllm_b200.engine import StepEntry
+    V = core.vocab_size
+    ids = list(range(batch))
+    for i in ids:
+        core.open(i)
+    # prefill every request's 2,048-token prompt (a few requests a step)
+    per_step = max(1, core.runner.max_batch_tokens // PROMPT_LEN)
+    for a in range(0, batch, per_step):
+        core.step([StepEntry(i, [rng.randrange(V) for _ in range(PROMPT_LEN)], []) for i in ids[a:a + per_step]])
+    def one():
+        return core.step([StepEntry(i, [rng.randrange(V)], [0]) for i in ids])
+    for _ in range(warmup):
+        one()
+    torch.cuda.synchronize()
+    l0 = core.launch_count()
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(steps):
+        one()
+    t1.record()
+    torch.cuda.synchronize()
+    ms = t0.elapsed_time(t1) / steps
+    launches = core.launch_count() - l0
+    ctx = PROMPT_LEN + warmup + steps // 2
+    for i in ids:
+        core.close(i)
+    return ms, launches, ctx
+
+
+def time_prefill(core, steps, warmup, rng):
+    import torch
+    from lightllm_b200.engine import StepEntry
+    V = core.vocab_size
+    times = []
+    for it in range(warmup + steps):
+        core.open("p")
+        toks = [rng.randrange(V) for _ in range(PROMPT_LEN)]
+        torch.cuda.synchronize()
+        t0 = torch.cuda.Event(enable_timing=True)
+        t1 = torch.cuda.Event(enable_timing=True)
+        t0.record()
+        core.step([StepEntry("p", toks, [PROMPT_LEN - 1])])
+        t1.record()
+        torch.cuda.synchronize()
+        if it >= warmup:
+            times.append(t0.elapsed_time(t1))
+        core.close("p")
+    return sum(times) / len(times)
+
+
+def time_e2e(engine, batch, steps, warmup, rng):
+    """Decode through the public serve loop: host token ids in, sampled ids out, every step."""
+    import torch
+    V = engine.vocab_size
+    loop = engine.new_loop()
+    for _ in range(batch):
+        loop.submit([rng.randrange(V) for _ in range(PROMPT_LEN)], max_new_tokens=warmup + steps + 8,
+                    eos_token_id=-1, temperature=0.0)
+    while any(r.state != "DECODING" for r in loop.scheduler.running) or loop.scheduler.waiting:
+        loop.step()
+    for _ in range(warmup):
+        loop.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        loop.step()
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    h2d = engine.core.runner.last_h2d_bytes
+    for r in list(loop.scheduler.running):
+        loop.scheduler.finish_request(r.id)
+    return batch * steps / dt, h2d, 4 * batch
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=QWEN25_05B["num_hidden_layers"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-points", action="store_true", help="only the headline batch (for profiling runs)")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference is a C++/CMake project without setup.py or pyproject.toml (pip: 'not "
+                          "installable'), and its build needs the absent third_party/xgrammar submodule"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    args.warmup = max(3, args.warmup)
+
+    import torch
+    from lightllm_b200 import Engine
+    rng = random.Random(0)
+    pk = peaks()
+    model_dir = make_model_dir(args.layers)
+    try:
+        max_batch = 64
+        engine = Engine(model_dir, dtype="bfloat16", max_seq_len=CONTEXT_LEN, max_batch_tokens=4 * PROMPT_LEN,
+                        page_size=PAGE_SIZE, num_pages=max_batch * (PROMPT_LEN + 512) // PAGE_SIZE,
+                        max_seqs=max_batch, chunk_size=PROMPT_LEN)
+        core = engine.core
+        clocks = ClockSampler()
+        clocks.start()
+        ms, launches, ctx = time_decode(core, args.batch, args.steps, args.warmup, rng)
+        clk = clocks.stop()
+        value = args.batch * 1000.0 / ms
+        achieved = decode_bytes(core, args.batch, ctx) / (ms * 1e-3) / 1e9
+        e2e_value, h2d, d2h = time_e2e(engine, args.batch, args.steps, args.warmup, rng)
+        pre_ms = time_prefill(core, max(3, args.steps // 8), 3, rng)
+        fl = flops_prefill(QWEN25_05B, args.layers, PROMPT_LEN)
+        points = {}
+        if not args.skip_points:
+            for b in (1, 64):
+                pms, _, _ = time_decode(core, b, args.steps, args.warmup, rng)
+                points[f"decode_b{b}"] = round(b * 1000.0 / pms, 1)
+        cfg = QWEN25_05B
+        line = {
+            "metric": "decode tok/s at batch 8 (Qwen2.5-0.5B sizes, 2,048-token prompts)",
+            "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic: random weights (seed 0), token ids uniform in vocab",
+            "config": {
+                "model": "Qwen2.5-0.5B sizes (Qwen2ForCausalLM)", "global_batch": args.batch, "seq_len": CONTEXT_LEN,
+                "prompt_len": PROMPT_LEN, "parallelism": "single GPU", "layers": args.layers,
+                "layers_of_config": cfg["num_hidden_layers"], "hidden": cfg["hidden_size"],
+                "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+                "head_dim": cfg["hidden_size"] // cfg["num_attention_heads"], "intermediate": cfg["intermediate_size"],
+                "vocab": cfg["vocab_size"], "page_size": PAGE_SIZE, "tied_embeddings": cfg["tie_word_embeddings"],
+                "l2": "inputs larger than L2: the weights read every step are ~1 GB",
+                "peaks": pk["source"],
+            },
+            "e2e": {"value": round(e2e_value, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": launches,
+            "clocks": clk,
+            "prefill": {"value": round(PROMPT_LEN * 1000.0 / pre_ms, 1), "tokens": PROMPT_LEN, "ms": round(pre_ms, 3),
+                        "frac": round(fl / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+            "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                         "frac": round(achieved / pk["hbm_gbs"], 4)},
+            "points": points,
+        }
+        print(json.dumps(line))
+    finally:
+        shutil.rmtree(model_dir, ignore_errors=True)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

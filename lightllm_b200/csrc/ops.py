@@ -34,6 +34,7 @@ def lib() -> ctypes.CDLL:
         except OSError as e:
             raise KernelError(f"cannot load the kernel library {path}: {e}") from None
         handle.llb_last_error.restype = ctypes.c_char_p
+        handle.llb_launch_count.restype = ctypes.c_ulonglong
         handle.llb_attention_smem_bytes.restype = ctypes.c_longlong
         handle.llb_attention_scratch_floats.restype = ctypes.c_longlong
         if handle.llb_abi_version() != ABI_VERSION:
@@ -199,6 +200,11 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: Optional[torc
     _check(lib().llb_sample(ctypes.c_void_p(logits.data_ptr()), R, V, ctypes.c_longlong(logits.stride(0)),
                             _ptr(temperature), _i32(top_k, "top_k"), _ptr(top_p), _ptr(min_p), _ptr(uniform),
                             _i32(out, "out"), _stream()))
+
+
+def launch_count() -> int:
+    """Kernels this library has launched in this process."""
+    return int(lib().llb_launch_count())
 
 
 def has_tcgen05() -> bool:

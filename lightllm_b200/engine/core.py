@@ -79,6 +79,11 @@ class EngineCore:
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         return self.runner.step(entries)
 
+    def launch_count(self) -> int:
+        """Kernels of the engine's own library launched so far in this process."""
+        from ..csrc import ops
+        return ops.launch_count()
+
     @property
     def vocab_size(self) -> int:
         return self.model.spec.vocab_size

@@ -1,0 +1,192 @@
+"""The serve loop: scheduler -> step function -> sampler, with per-request and per-step metrics.
+
+After the reference's ``BatchMainLoop`` (include/lightllm/engine/batch_loop.h:79-211,
+src/engine/batch_loop.cpp:108-305): ``submit`` returns an id at once, ``step`` runs one
+scheduler decision through the engine, ``run`` loops until nothing is active; TTFT, TPOT and
+latency are kept per request (batch_loop.h:35-60) and the composition of every step
+(batch_loop.h:65-74); percentiles interpolate linearly (batch_loop.cpp:369-462).
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence
+
+from ..sampling import Sampler, SamplingParams
+from .batch import StepEntry
+from .core import EngineCore
+from .scheduler import Request, ScheduleStep, Scheduler
+
+
+@dataclass
+class BatchMetrics:
+    request_id: int = 0
+    prompt_len: int = 0
+    output_len: int = 0
+    arrival_time_sec: float = 0.0
+    first_token_time_sec: float = 0.0
+    finish_time_sec: float = 0.0
+    finished: bool = False
+    first_token_recorded: bool = False
+    finish_reason: Optional[str] = None
+
+    def ttft_ms(self) -> float:
+        return (self.first_token_time_sec - self.arrival_time_sec) * 1000.0 if self.first_token_recorded else 0.0
+
+    def latency_ms(self) -> float:
+        return (self.finish_time_sec - self.arrival_time_sec) * 1000.0
+
+    def tpot_ms(self) -> float:
+        if self.output_len <= 0:
+            return 0.0
+        return (self.finish_time_sec - self.first_token_time_sec) * 1000.0 / self.output_len
+
+
+@dataclass
+class BatchStepMetrics:
+    step_number: int = 0
+    step_time_sec: float = 0.0
+    tokens_processed: int = 0
+    prefill_tokens: int = 0
+    decode_tokens: int = 0
+    num_requests: int = 0
+    num_prefill_entries: int = 0
+    num_decode_entries: int = 0
+    active_after: int = 0
+    preempted: int = 0
+
+
+def percentile(values: Sequence[float], p: float) -> float:
+    """Linear interpolation between the two nearest ranks (src/engine/batch_loop.cpp:369-386)."""
+    if not values:
+        return 0.0
+    v = sorted(values)
+    if len(v) == 1:
+        return v[0]
+    rank = p / 100.0 * (len(v) - 1)
+    lo = int(rank)
+    hi = min(lo + 1, len(v) - 1)
+    return v[lo] + (v[hi] - v[lo]) * (rank - lo)
+
+
+class BatchMainLoop:
+    def __init__(self, engine: EngineCore, chunk_size: int = 16, max_batch_tokens: int = 256,
+                 max_prefill_entries: int = 999):
+        self.engine = engine
+        max_batch_tokens = min(max_batch_tokens, engine.runner.max_batch_tokens)
+        self.scheduler = Scheduler(engine.cache, chunk_size, max_batch_tokens, max_prefill_entries)
+        self.sampler = Sampler(engine.device)
+        self.chunk_size = chunk_size
+        self._metrics: Dict[int, BatchMetrics] = {}
+        self.step_metrics: List[BatchStepMetrics] = []
+        self._requests: Dict[int, Request] = {}
+        self._next_id = 0
+        self.total_steps = 0
+        self._epoch = time.perf_counter()
+
+    def wall_clock(self) -> float:
+        return time.perf_counter() - self._epoch
+
+    def submit(self, prompt_tokens: Sequence[int], max_new_tokens: int = 64, eos_token_id: int = 151643,
+               temperature: float = 1.0, top_k: int = 0, top_p: float = 1.0, min_p: float = 0.0,
+               seed: int = 42) -> int:
+        params = SamplingParams(temperature, top_k, top_p, min_p, seed)
+        params.validate()
+        vocab = self.engine.vocab_size
+        for t in prompt_tokens:
+            if not 0 <= int(t) < vocab:
+                raise ValueError(f"token id {t} is outside the vocabulary of {vocab}")
+        rid = self._next_id
+        self._next_id += 1
+        req = Request(rid, [int(t) for t in prompt_tokens], max_new_tokens=max_new_tokens,
+                      eos_token_id=eos_token_id, sampling=params)
+        self._requests[rid] = req
+        self._metrics[rid] = BatchMetrics(rid, len(req.prompt_tokens), arrival_time_sec=self.wall_clock())
+        if max_new_tokens <= 0:
+            self.scheduler._finish(req, "length")
+        else:
+            self.scheduler.add_request(req)
+        if req.state == "FINISHED":
+            self._record_finish(req)
+        return rid
+
+    def has_active(self) -> bool:
+        return self.scheduler.num_active() > 0
+
+    def active_count(self) -> int:
+        return self.scheduler.num_active()
+
+    def step(self) -> bool:
+        """One scheduler decision run through the engine.  False when there was nothing to do."""
+        sched: ScheduleStep = self.scheduler.step()
+        for r in list(self.scheduler.finished.values()):
+            if not self._metrics[r.id].finished:
+                self._record_finish(r)
+        if sched.empty():
+            return False
+        entries, wanting = [], []
+        for e in sched.entries:
+            toks = e.request.all_tokens()[e.start_pos: e.start_pos + e.num_tokens]
+            entries.append(StepEntry(e.request.id, toks, [e.num_tokens - 1] if e.wants_logits else []))
+            if e.wants_logits:
+                wanting.append(e.request)
+        logits = self.engine.step(entries)
+        sampled: Dict[int, int] = {}
+        if wanting:
+            toks = self.sampler.sample(logits, [r.id for r in wanting], [r.sampling for r in wanting])
+            sampled = {r.id: t for r, t in zip(wanting, toks)}
+        now = self.wall_clock()
+        for r in wanting:
+            m = self._metrics[r.id]
+            if not m.first_token_recorded:
+                m.first_token_recorded, m.first_token_time_sec = True, now
+        for r in self.scheduler.on_step_done(sched, sampled):
+            self._record_finish(r)
+        self.total_steps += 1
+        pre = [e for e in sched.entries if e.is_prefill]
+        self.step_metrics.append(BatchStepMetrics(
+            self.total_steps, now, sched.total_tokens(), sum(e.num_tokens for e in pre),
+            len(sched.entries) - len(pre), len(sched.entries), len(pre), len(sched.entries) - len(pre),
+            self.scheduler.num_active(), len(sched.preempted)))
+        return True
+
+    def run(self) -> None:
+        while self.has_active():
+            if not self.step() and self.has_active():
+                raise RuntimeError("the scheduler has active requests but schedules nothing")
+
+    def _record_finish(self, r: Request) -> None:
+        m = self._metrics[r.id]
+        m.finished, m.finish_time_sec = True, self.wall_clock()
+        m.output_len, m.finish_reason = len(r.output_tokens), r.finish_reason
+        self.sampler.forget(r.id)
+
+    # ---- results and metrics ---------------------------------------------------------------------
+    def generated_tokens(self, request_id: int) -> List[int]:
+        return list(self._requests[request_id].output_tokens)
+
+    def finish_reason(self, request_id: int) -> Optional[str]:
+        return self._requests[request_id].finish_reason
+
+    def metrics(self, request_id: int) -> BatchMetrics:
+        return self._metrics[request_id]
+
+    def all_metrics(self) -> List[BatchMetrics]:
+        return list(self._metrics.values())
+
+    def total_tokens_generated(self) -> int:
+        return sum(len(r.output_tokens) for r in self._requests.values())
+
+    def _finished(self) -> List[BatchMetrics]:
+        return [m for m in self._metrics.values() if m.finished and m.first_token_recorded]
+
+    def stat(self, what: str, p: Optional[float] = None) -> float:
+        """``what`` in ttft/tpot/latency; ``p`` a percentile, or None for the mean."""
+        vals = [getattr(m, f"{what}_ms")() for m in self._finished()]
+        if not vals:
+            return 0.0
+        return sum(vals) / len(vals) if p is None else percentile(vals, p)
+
+    def throughput_tok_s(self) -> float:
+        t = self.wall_clock()
+        return self.total_tokens_generated() / t if t > 0 else 0.0

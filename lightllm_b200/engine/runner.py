@@ -38,15 +38,10 @@ class ModelRunner:
         self.max_spans = int(max_spans or cache.max_seqs)
         self.ngroups = len(cache.layout.groups)
         self.max_pages = cache.max_pages_per_seq
-        # Fixed layout of the metadata buffer (int32 words), so that its addresses never change.
+        # Capacity of the metadata buffer (int32 words).  A step packs its arrays tightly at
+        # offsets that depend only on its counts, so equal counts give equal addresses.
         S, T, G, P = self.max_spans, self.max_batch_tokens, self.ngroups, self.max_pages
-        off = 0
-        self._off: Dict[str, int] = {}
-        for name, n in (("span_row", S), ("span_len", S), ("span_pos", S), ("span_slot", S), ("iota", S),
-                        ("zeros", S), ("block_tables", G * S * P), ("want_rows", T), ("token_ids", T),
-                        ("positions", T), ("slot_mapping", G * T)):
-            self._off[name] = off
-            off += n
+        off = 6 * S + G * S * P + T + 2 * T + G * T
         self._words = off
         self._host = [torch.zeros(off, dtype=torch.int32).pin_memory() for _ in range(2)]
         self._host_done = [None, None]
@@ -95,14 +90,27 @@ class ModelRunner:
         if max(s.start + s.length for s in spans) > self.model.spec.max_positions:
             raise StepError(f"a request would pass the model's {self.model.spec.max_positions} positions")
 
-        o, S, P, G = self._off, len(spans), self.max_pages, self.ngroups
-        Smax, Tmax = self.max_spans, self.max_batch_tokens
+        S, G = len(spans), self.ngroups
         ids = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
         if ids.min() < 0 or ids.max() >= vocab:
             bad = int(ids[(ids < 0) | (ids >= vocab)][0])
             raise StepError(f"token id {bad} is outside the vocabulary of {vocab}")
         # Pages for the new tokens are taken before anything runs; OutOfPages leaves all as it was.
         cache.reserve_all((e.seq_id, len(e.tokens)) for e in entries)
+
+        ps = cache.page_size
+        max_context = max(s.start + s.length for s in spans)
+        # Block-table width of this step: the pages of its longest request, rounded up to 16.
+        P = min(self.max_pages, -(-(-(-max_context // ps)) // 16) * 16)
+        want = [s.row + w for s, e in zip(spans, entries) for w in e.want]
+        R = len(want)
+        o, off = {}, 0
+        for name, n in (("span_row", S), ("span_len", S), ("span_pos", S), ("span_slot", S), ("iota", S),
+                        ("zeros", S), ("block_tables", G * S * P), ("want_rows", R), ("token_ids", T),
+                        ("positions", T), ("slot_mapping", G * T)):
+            o[name] = off
+            off += n
+        words = off
 
         turn = self._turn
         self._turn ^= 1
@@ -118,24 +126,24 @@ class ModelRunner:
         host[o["span_slot"]: o["span_slot"] + S] = [s.slot for s in spans]
         host[o["iota"]: o["iota"] + S] = np.arange(S, dtype=np.int32)
         host[o["zeros"]: o["zeros"] + S] = 0
-        ps = cache.page_size
         for g in range(G):
-            bt = host[o["block_tables"] + g * Smax * P: o["block_tables"] + (g + 1) * Smax * P].reshape(Smax, P)
-            sm = host[o["slot_mapping"] + g * Tmax: o["slot_mapping"] + g * Tmax + T]
+            bt = host[o["block_tables"] + g * S * P: o["block_tables"] + (g + 1) * S * P].reshape(S, P)
+            sm = host[o["slot_mapping"] + g * T: o["slot_mapping"] + (g + 1) * T]
             for i, s in enumerate(spans):
                 table = np.asarray(cache.block_table(s.seq_id, g), dtype=np.int32)
-                bt[i, : len(table)] = table
+                bt[i, : len(table)] = table[:P]
                 p = pos[s.row: s.row + s.length]
-                sm[s.row: s.row + s.length] = table[p // ps] * ps + p % ps
-        want = [s.row + w for s, e in zip(spans, entries) for w in e.want]
-        R = len(want)
+                rows = table[p // ps]
+                if rows.min() < 0:
+                    raise StepError(f"request {s.seq_id!r}: a new token falls in a page that was given back")
+                sm[s.row: s.row + s.length] = rows * ps + p % ps
         host[o["want_rows"]: o["want_rows"] + R] = want
 
-        self._dev.copy_(self._host[turn], non_blocking=True)
+        self._dev[:words].copy_(self._host[turn][:words], non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()
         self._host_done[turn] = ev
-        self.last_h2d_bytes = self._words * 4
+        self.last_h2d_bytes = words * 4
 
         d = self._dev
         ctx = StepContext()
@@ -148,14 +156,14 @@ class ModelRunner:
         ctx.span_slot = d[o["span_slot"]: o["span_slot"] + S]
         ctx.iota = d[o["iota"]: o["iota"] + S]
         ctx.zeros = d[o["zeros"]: o["zeros"] + S]
-        ctx.slot_mapping = [d[o["slot_mapping"] + g * Tmax: o["slot_mapping"] + g * Tmax + T] for g in range(G)]
-        ctx.block_tables = [d[o["block_tables"] + g * Smax * P: o["block_tables"] + g * Smax * P + S * P].view(S, P)
+        ctx.slot_mapping = [d[o["slot_mapping"] + g * T: o["slot_mapping"] + (g + 1) * T] for g in range(G)]
+        ctx.block_tables = [d[o["block_tables"] + g * S * P: o["block_tables"] + (g + 1) * S * P].view(S, P)
                             for g in range(G)]
         ctx.want_rows = d[o["want_rows"]: o["want_rows"] + R]
         ctx.num_want = R
         ctx.max_pages, ctx.page_size = P, ps
         ctx.decode_only = all(s.length == 1 for s in spans)
-        ctx.max_context = max(s.start + s.length for s in spans)
+        ctx.max_context = max_context
         ctx.dtype, ctx.device = self.model.dtype, self.device
         ctx.cache, ctx.err = cache, self.err
         return ctx

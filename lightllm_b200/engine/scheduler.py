@@ -1,0 +1,265 @@
+"""The scheduler: admits requests, cuts prompts into portions under a token budget, decodes,
+finishes and frees; and decides what happens when pages run out.
+
+Policy: DecodeFirst, as ``DecodeFirstScheduler::step`` (src/engine/scheduler.cpp:34-73): every
+decoding request first gets its one token (:38-43), then the budget that is left goes to prompt
+portions of at most ``chunk_size`` tokens, oldest request first, at most
+``max_prefill_entries`` of them (:46-64).  ``Request`` keeps the reference's fields
+(include/lightllm/engine/scheduler.h:23-48).
+
+Differences from the reference, all on purpose:
+
+* a request appears at most once in a step (the reference may cut one prompt into several
+  entries of the same step, and its engine then attends wrongly);
+* the decode position is the request's true length (the reference's is stale, scheduler.cpp:41);
+* the scheduler knows the cache: a request is admitted only when a state slot and the pages of
+  its first portion are free beside one spare page for each running request; a portion shrinks
+  to the pages that are free;
+* when a decoding request needs a page and none is free, the request admitted last is
+  preempted: its pages are given back, it returns to the front of the queue, and its prompt
+  and the tokens it had generated are computed again later (its output is unchanged);
+* a request that can never fit (longer than the pool or than ``max_seq_len``) finishes at once
+  with ``finish_reason = "too_long"`` instead of corrupting the cache as the reference does
+  (src/engine/engine_server.cpp:1427-1432).
+"""
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Deque, Dict, List, Optional
+
+from ..cache import CacheManager
+from ..sampling.params import SamplingParams
+
+WAITING, PREFILL, DECODING, FINISHED = "WAITING", "PREFILL", "DECODING", "FINISHED"
+
+
+@dataclass
+class Request:
+    id: int
+    prompt_tokens: List[int]
+    output_tokens: List[int] = field(default_factory=list)
+    num_computed: int = 0            # tokens of prompt + output whose keys and values are cached
+    max_new_tokens: int = 64
+    eos_token_id: int = 151643
+    sampling: SamplingParams = field(default_factory=SamplingParams)
+    state: str = WAITING
+    finish_reason: Optional[str] = None
+    preemptions: int = 0
+
+    def all_tokens(self) -> List[int]:
+        return self.prompt_tokens + self.output_tokens
+
+    def total_len(self) -> int:
+        return len(self.prompt_tokens) + len(self.output_tokens)
+
+    def prefill_remaining(self) -> int:
+        return self.total_len() - self.num_computed
+
+
+@dataclass
+class ScheduleEntry:
+    request: Request
+    num_tokens: int
+    start_pos: int
+    is_prefill: bool
+    wants_logits: bool     # the entry's last token is the request's last: its logits give the next token
+
+    @property
+    def request_idx(self) -> int:
+        return self.request.id
+
+
+@dataclass
+class ScheduleStep:
+    entries: List[ScheduleEntry] = field(default_factory=list)
+    preempted: List[int] = field(default_factory=list)
+
+    def total_tokens(self) -> int:
+        return sum(e.num_tokens for e in self.entries)
+
+    def empty(self) -> bool:
+        return not self.entries
+
+
+class Scheduler:
+    def __init__(self, cache: CacheManager, chunk_size: int = 16, max_batch_tokens: int = 256,
+                 max_prefill_entries: int = 999):
+        if chunk_size <= 0 or max_batch_tokens <= 0 or max_prefill_entries <= 0:
+            raise ValueError("chunk_size, max_batch_tokens and max_prefill_entries must be positive")
+        self.cache = cache
+        self.chunk_size = chunk_size
+        self.max_batch_tokens = max_batch_tokens
+        self.max_prefill_entries = max_prefill_entries
+        self.waiting: Deque[Request] = deque()
+        self.running: List[Request] = []        # admitted, in admission order (PREFILL or DECODING)
+        self.finished: Dict[int, Request] = {}
+
+    # ---- the reference's interface -------------------------------------------------------------
+    def add_request(self, req: Request) -> None:
+        req.state = WAITING
+        limit = min(self.cache.max_seq_len,
+                    min(p.num_pages for p in self.cache.pools) * self.cache.page_size if self.cache.pools
+                    else self.cache.max_seq_len)
+        if not req.prompt_tokens:
+            self._finish(req, "empty_prompt")
+        elif len(req.prompt_tokens) + 1 > limit:
+            self._finish(req, "too_long")
+        else:
+            self.waiting.append(req)
+
+    def num_active(self) -> int:
+        return len(self.waiting) + len(self.running)
+
+    def finish_request(self, req_id: int, reason: str = "stopped") -> None:
+        for r in self.running:
+            if r.id == req_id:
+                self._release(r)
+                self._finish(r, reason)
+                return
+        for r in list(self.waiting):
+            if r.id == req_id:
+                self.waiting.remove(r)
+                self._finish(r, reason)
+                return
+
+    # ---- one scheduling decision ---------------------------------------------------------------
+    def step(self) -> ScheduleStep:
+        out = ScheduleStep()
+        cache = self.cache
+        budget = self.max_batch_tokens
+        asks = []
+
+        # Priority 1: one token for every decoding request; preempt from the back when pages run out.
+        decoding = [r for r in self.running if r.state == DECODING]
+        i = 0
+        while i < len(decoding):
+            r = decoding[i]
+            if cache.can_reserve_all(asks + [(r.id, 1)]):
+                asks.append((r.id, 1))
+                out.entries.append(ScheduleEntry(r, 1, r.num_computed, False, True))
+                budget -= 1
+                i += 1
+                continue
+            victim = self.running[-1]
+            if victim is r and len(self.running) == 1:
+                # alone and still no page: it has reached what the pool can hold
+                self._release(r)
+                self._finish(r, "out_of_pages")
+                decoding.pop(i)
+                continue
+            self._preempt(victim, out)
+            if victim in decoding:
+                j = decoding.index(victim)
+                decoding.pop(j)
+                if j < i:          # it had already been given its token: take that back
+                    asks = [a for a in asks if a[0] != victim.id]
+                    out.entries = [e for e in out.entries if e.request is not victim]
+                    budget += 1
+                    i -= 1
+
+        # Priority 2: the budget that is left goes to prompt portions, admitted requests first.
+        prefill_count = 0
+        for r in [r for r in self.running if r.state == PREFILL]:
+            if budget <= 0 or prefill_count >= self.max_prefill_entries:
+                break
+            n = self._portion(r, budget, asks, spare=0)
+            if n > 0:
+                self._add_prefill(out, asks, r, n)
+                budget -= n
+                prefill_count += 1
+        while self.waiting and budget > 0 and prefill_count < self.max_prefill_entries:
+            r = self.waiting[0]
+            if cache.free_slots == 0:
+                break
+            cache.open(r.id)
+            n = self._portion(r, budget, asks, spare=len(self.running))
+            if n <= 0:
+                cache.close(r.id)
+                if not self.running and not out.entries:
+                    # nothing else holds pages and it still does not fit: it never will
+                    self.waiting.popleft()
+                    self._finish(r, "too_long")
+                    continue
+                break
+            self.waiting.popleft()
+            r.state = PREFILL
+            self.running.append(r)
+            self._add_prefill(out, asks, r, n)
+            budget -= n
+            prefill_count += 1
+        return out
+
+    def _portion(self, r: Request, budget: int, asks, spare: int) -> int:
+        """Largest portion of ``r`` that the budget, the chunk size and the free pages allow,
+        leaving ``spare`` pages free in every group."""
+        n = min(self.chunk_size, r.prefill_remaining(), budget)
+        cache = self.cache
+        while n > 0:
+            if cache.can_reserve_all(asks + [(r.id, n)]) and self._spare_ok(asks + [(r.id, n)], spare):
+                return n
+            # shrink to the next page edge below
+            have = cache.get(r.id).length + n
+            edge = (have - 1) // cache.page_size * cache.page_size
+            n = edge - cache.get(r.id).length
+        return 0
+
+    def _spare_ok(self, asks, spare: int) -> bool:
+        if spare <= 0:
+            return True
+        total = [0] * len(self.cache.pools)
+        for seq_id, n in asks:
+            for g, need in enumerate(self.cache.pages_needed(seq_id, n)):
+                total[g] += need
+        return all(t + spare <= p.free_count for t, p in zip(total, self.cache.pools))
+
+    def _add_prefill(self, out: ScheduleStep, asks, r: Request, n: int) -> None:
+        asks.append((r.id, n))
+        last = r.num_computed + n == r.total_len()
+        out.entries.append(ScheduleEntry(r, n, r.num_computed, True, last))
+
+    # ---- after the step ran ----------------------------------------------------------------------
+    def on_step_done(self, step: ScheduleStep, sampled: Dict[int, int]) -> List[Request]:
+        """Account for a step that ran: ``sampled`` maps a request id to its next token for the
+        entries that wanted logits.  Returns the requests that finished."""
+        done = []
+        for e in step.entries:
+            r = e.request
+            r.num_computed += e.num_tokens
+            if not e.wants_logits:
+                continue
+            tok = sampled[r.id]
+            r.output_tokens.append(tok)
+            r.state = DECODING
+            reason = None
+            if tok == r.eos_token_id:
+                reason = "eos"
+            elif len(r.output_tokens) >= r.max_new_tokens:
+                reason = "length"
+            elif r.total_len() >= self.cache.max_seq_len:
+                reason = "max_seq_len"
+            if reason:
+                self._release(r)
+                self._finish(r, reason)
+                done.append(r)
+        return done
+
+    # ---- internals ---------------------------------------------------------------------------------
+    def _release(self, r: Request) -> None:
+        if r in self.running:
+            self.running.remove(r)
+        if r.id in self.cache.seqs:
+            self.cache.close(r.id)
+
+    def _finish(self, r: Request, reason: str) -> None:
+        r.state = FINISHED
+        r.finish_reason = reason
+        self.finished[r.id] = r
+
+    def _preempt(self, r: Request, out: ScheduleStep) -> None:
+        self._release(r)
+        r.state = WAITING
+        r.num_computed = 0
+        r.preemptions += 1
+        self.waiting.appendleft(r)
+        out.preempted.append(r.id)

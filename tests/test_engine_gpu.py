@@ -1,0 +1,463 @@
+"""The engine on the GPU beyond replay: generation through the entry point, long decoding, the
+first tokens of a sequence, sharp attention over far keys and page edges, preemption, sampling,
+each part alone, other arrangements of the run list, and a toy mixer with state of its own that
+is registered, built and stepped from here without a change to the framework."""
+import math
+import os
+import random
+from dataclasses import dataclass
+
+import numpy as np
+import pytest
+import torch
+
+from lightllm_b200 import Engine, EngineCore, EngineOptions, StepEntry, write_random_model
+from lightllm_b200.cache import CacheLayout, CacheManager, CacheSpec, KVSpec, StateSpec
+from lightllm_b200.config import (LayerSpec, ModelConfig, ModelSpec, PartSpec, RunEntry, config_from_dict,
+                                  model_spec_for, register_architecture, register_part)
+from lightllm_b200.models import Model
+from lightllm_b200.parts import AttentionMixer, CacheView, GatedMLP, LMHead, Mixer, RMSNorm, TokenEmbedding
+from lightllm_b200.weights import WeightSpec, random_tensors, save_file
+from tests.plain import qwen2_plain as P
+from tests.tiny_configs import PAGE_SIZE, config
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda:0")
+ATOL = {"float32": 1e-4, "bfloat16": 4e-2}
+
+
+def model_dir(tmp_path, name, seed=3, store="float32", edit=None):
+    d = str(tmp_path / f"model_{name}_{seed}")
+    write_random_model(config(name), seed, d, store)
+    if edit:
+        cfg, w = P.read_model_dir(d)
+        edit(w)
+        save_file({k: v.to(torch.float32 if store == "float32" else torch.bfloat16) for k, v in w.items()},
+                  os.path.join(d, "model.safetensors"))
+    return d
+
+
+def core_for(d, dtype, page=16, pages=64, max_seqs=4, max_tokens=512):
+    return EngineCore(d, EngineOptions(dtype=dtype, max_seq_len=max_tokens, max_batch_tokens=max_tokens,
+                                       page_size=page, num_pages=pages, max_seqs=max_seqs))
+
+
+def sharpen(factor):
+    """Scale q and k projections so that attention is sharp: few keys dominate a row, and a key
+    that is skipped, stale or at the wrong place changes the logits by far more than rounding."""
+    def edit(w):
+        for k in w:
+            if k.endswith("q_proj.weight") or k.endswith("k_proj.weight"):
+                w[k] = w[k] * factor
+    return edit
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_greedy_generation_through_the_entry_point(tmp_path, name, dtype):
+    d = model_dir(tmp_path, name, store="float32" if dtype == "float32" else "bfloat16")
+    cfg, w = P.read_model_dir(d)
+    rng = random.Random(1)
+    prompts = [[rng.randrange(cfg["vocab_size"]) for _ in range(n)] for n in (1, 9, 40, 23)]
+    eng = Engine(d, dtype=dtype, max_seq_len=128, max_batch_tokens=32, page_size=PAGE_SIZE[name], num_pages=40,
+                 max_seqs=4, chunk_size=16)
+    outs, why = eng.generate(prompts, max_new_tokens=10, temperature=0.0, eos_token_id=-1, return_reasons=True)
+    assert why == ["length"] * 4 and all(len(o) == 10 for o in outs)
+    for p, o in zip(prompts, outs):
+        seq = list(p)
+        for tok in o:
+            lg = P.plain_forward(cfg, w, seq)[-1]
+            top = torch.topk(lg, 2).values
+            assert tok == int(torch.argmax(lg)) or float(top[0] - top[1]) < ATOL[dtype], (seq, tok)
+            seq.append(tok)
+    eng.core.cache.check()
+    assert eng.core.cache.free_pages() == 40
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_and_first_tokens(tmp_path, dtype):
+    d = model_dir(tmp_path, "B", store="float32" if dtype == "float32" else "bfloat16")
+    cfg, w = P.read_model_dir(d)
+    rng = random.Random(2)
+    seq = [rng.randrange(1000) for _ in range(230)]
+    ref = P.plain_forward(cfg, w, seq)
+    core = core_for(d, dtype, page=8, pages=40)
+    core.open("x")
+    got = [core.step([StepEntry("x", seq[:1], [0])])]                 # the very first token alone
+    got.append(core.step([StepEntry("x", seq[1:3], [0, 1])]))          # then two
+    for t in range(3, 230):                                            # then 227 single tokens
+        got.append(core.step([StepEntry("x", [seq[t]], [0])]))
+    got = torch.cat(got).float().cpu()
+    err = (got - ref).abs().max(dim=1).values
+    assert float(err.max()) <= ATOL[dtype], f"first wrong position {int((err > ATOL[dtype]).nonzero()[0])}"
+    core.close("x")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_sharp_attention_over_far_keys_page_edges_and_reused_pages(tmp_path, name, dtype):
+    d = model_dir(tmp_path, name, seed=8, store="float32" if dtype == "float32" else "bfloat16",
+                  edit=sharpen(30.0 if dtype == "float32" else 6.0))
+    cfg, w = P.read_model_dir(d)
+    V, page = cfg["vocab_size"], PAGE_SIZE[name]
+    rng = random.Random(3)
+    maxlen = 120 if name == "A" else 300
+    seqs = {i: [rng.randrange(V) for _ in range(n)] for i, n in enumerate([maxlen, 2 * page + 1, 3 * page, 77])}
+    ref = {i: P.plain_forward(cfg, w, s) for i, s in seqs.items()}
+    core = core_for(d, dtype, page=page, pages=(maxlen + 100) // page + 3, max_seqs=3, max_tokens=maxlen + 8)
+    tol = ATOL[dtype]                                         # relative to the largest logit, see below
+    scale = max(1.0, float(ref[0].abs().max()))
+    fed = {i: 0 for i in seqs}
+    order = [0, 1]
+    core.open(0), core.open(1)
+    step = 0
+    while order:
+        entries, exp = [], []
+        for i in list(order):
+            left = len(seqs[i]) - fed[i]
+            n = min(left, rng.choice([1, 2, page - 1, page, page + 1, 2 * page]))
+            if left - n == 1:
+                n += 1
+            entries.append(StepEntry(i, seqs[i][fed[i]: fed[i] + n], list(range(n))))
+            exp.append((i, fed[i], n))
+            fed[i] += n
+        logits = core.step(entries).float().cpu()
+        row = 0
+        for i, at, n in exp:
+            err = (logits[row: row + n] - ref[i][at: at + n]).abs().max()
+            assert float(err) <= tol * scale, f"{dtype} {name}: step {step}, request {i}, positions {at}..{at + n - 1}: {float(err)}"
+            row += n
+            if fed[i] == len(seqs[i]):
+                core.close(i)
+                order.remove(i)
+                nxt = [j for j in seqs if fed[j] == 0 and j not in order]
+                if nxt:                                   # a new request takes the pages just given back
+                    core.open(nxt[0])
+                    order.append(nxt[0])
+        step += 1
+    core.cache.check()
+
+
+def test_preemption_keeps_the_output(tmp_path):
+    d = model_dir(tmp_path, "A", store="float32")
+    rng = random.Random(4)
+    prompts = [[rng.randrange(512) for _ in range(n)] for n in (20, 18, 25)]
+    roomy = Engine(d, dtype="float32", max_seq_len=128, max_batch_tokens=64, page_size=16, num_pages=40, max_seqs=4)
+    want = roomy.generate(prompts, max_new_tokens=30, temperature=0.0, eos_token_id=-1)
+    tight = Engine(d, dtype="float32", max_seq_len=128, max_batch_tokens=64, page_size=16, num_pages=7, max_seqs=4)
+    got = tight.generate(prompts, max_new_tokens=30, temperature=0.0, eos_token_id=-1)
+    assert sum(m.preempted for m in tight.last_loop.step_metrics) > 0
+    assert got == want
+    assert tight.core.cache.free_pages() == 7
+
+
+def test_temperature_sampling_is_seeded_and_per_request(tmp_path):
+    d = model_dir(tmp_path, "A", store="bfloat16")
+    eng = Engine(d, dtype="bfloat16", max_seq_len=128, max_batch_tokens=64, num_pages=40, max_seqs=4)
+    p = [[5, 6, 7, 8], [9, 10, 11]]
+    a = eng.generate(p, max_new_tokens=12, temperature=1.0, top_k=50, top_p=0.95, seed=7, eos_token_id=-1)
+    b = eng.generate(p, max_new_tokens=12, temperature=1.0, top_k=50, top_p=0.95, seed=7, eos_token_id=-1)
+    c = eng.generate(p, max_new_tokens=12, temperature=1.0, top_k=50, top_p=0.95, seed=8, eos_token_id=-1)
+    alone = eng.generate(p[:1], max_new_tokens=12, temperature=1.0, top_k=50, top_p=0.95, seed=7, eos_token_id=-1)
+    assert a == b and a != c
+    assert alone[0] == a[0]                       # what else is in the batch does not change a request's draws
+    greedy = eng.generate(p, max_new_tokens=12, temperature=0.0, eos_token_id=-1)
+    assert greedy != a
+
+
+def test_step_errors_leave_the_cache_as_it_was(tmp_path):
+    from lightllm_b200.cache import OutOfPages
+    from lightllm_b200.engine import StepError
+    d = model_dir(tmp_path, "A")
+    core = core_for(d, "float32", pages=2, max_tokens=64)
+    core.open("a"), core.open("b")
+    with pytest.raises(StepError, match="outside the vocabulary"):
+        core.step([StepEntry("a", [1, 512], [])])
+    with pytest.raises(StepError, match="twice"):
+        core.step([StepEntry("a", [1], []), StepEntry("a", [2], [])])
+    with pytest.raises(OutOfPages):
+        core.step([StepEntry("a", [1] * 20, []), StepEntry("b", [1] * 20, [])])
+    assert core.cache.free_pages() == 2 and core.cache.get("a").length == 0
+    assert core.step([StepEntry("a", [1] * 20, [19])]).shape == (1, 512)
+
+
+# ---------------------------------------------------------------------------------------------
+# Each part alone
+# ---------------------------------------------------------------------------------------------
+def bound(part, dtype, seed=0, scale=None):
+    t = random_tensors(part.weight_specs(), seed, torch.float32)
+    if scale:
+        t = {k: v * scale for k, v in t.items()}
+    dev = {k: v.to(dtype if v.ndim > 1 else torch.float32).to(DEV) for k, v in t.items()}
+    part.bind(dev, dtype, DEV)
+    return {k: v.to(dtype).float() if v.ndim > 1 else v for k, v in t.items()}
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_parts_alone(dtype):
+    tol = 1e-5 if dtype == torch.float32 else 3e-2
+    g = torch.Generator().manual_seed(5)
+    D, I, V, T = 72, 100, 333, 13
+    emb = TokenEmbedding("e", V, D)
+    w = bound(emb, dtype)
+    ids = torch.randint(0, V, (T,), generator=g, dtype=torch.int32)
+    h = emb.forward(ids.to(DEV))
+    assert h.dtype == torch.float32 and torch.equal(h.cpu(), P.plain_embedding(ids, w["e.weight"]))
+    norm = RMSNorm("n", D, 3e-5)
+    wn = bound(norm, dtype)
+    x = norm.forward(h * 50)
+    assert x.dtype == dtype
+    ref_x = P.plain_rmsnorm(h.cpu() * 50, wn["n.weight"], 3e-5)
+    assert torch.allclose(x.float().cpu(), ref_x, atol=tol, rtol=tol)
+    rows = torch.tensor([4, 0], dtype=torch.int32, device=DEV)
+    assert torch.allclose(norm.forward_rows(h * 50, rows).float().cpu(), ref_x[[4, 0]], atol=tol, rtol=tol)
+    ffn = GatedMLP("f", D, I)
+    wf = bound(ffn, dtype, scale=5.0)
+    res = torch.zeros((T, D), dtype=torch.float32, device=DEV)
+    ffn.forward(x, res)
+    ref = P.plain_swiglu(x.float().cpu(), wf["f.gate_proj.weight"], wf["f.up_proj.weight"], wf["f.down_proj.weight"])
+    assert torch.allclose(res.cpu(), ref, atol=tol * float(ref.abs().max()), rtol=tol)
+    head = LMHead("h", V, D)
+    wh = bound(head, dtype)
+    lg = head.forward(x)
+    assert lg.dtype == torch.float32
+    assert torch.allclose(lg.cpu(), P.plain_linear(x.float().cpu(), wh["h.weight"]), atol=tol, rtol=tol)
+
+
+class HandContext:
+    """A step context made by hand for one mixer: spans over a cache manager."""
+
+    def __init__(self, cache, spans, dtype):
+        from lightllm_b200.engine.batch import Span, StepContext
+        ctx = StepContext()
+        rows, sp = 0, []
+        for sid, n in spans:
+            seq = cache.get(sid)
+            cache.reserve(sid, n)
+            sp.append(Span(sid, seq.slot, seq.length, n, rows))
+            rows += n
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+        ctx.T, ctx.spans = rows, sp
+        ctx.positions = i32([s.start + j for s in sp for j in range(s.length)])
+        ctx.span_row, ctx.span_len = i32([s.row for s in sp]), i32([s.length for s in sp])
+        ctx.span_pos, ctx.span_slot = i32([s.start for s in sp]), i32([s.slot for s in sp])
+        ctx.iota, ctx.zeros = i32(list(range(len(sp)))), i32([0] * len(sp))
+        P_ = cache.max_pages_per_seq
+        bt = torch.full((len(sp), P_), -1, dtype=torch.int32)
+        for i, s in enumerate(sp):
+            t = cache.block_table(s.seq_id, 0)
+            bt[i, : len(t)] = torch.tensor(t, dtype=torch.int32)
+        ctx.block_tables = [bt.to(DEV)]
+        ctx.slot_mapping = [i32([x for s in sp for x in cache.slot_mapping(s.seq_id, 0, s.start, s.length)])]
+        ctx.max_pages, ctx.page_size = P_, cache.page_size
+        ctx.decode_only = all(s.length == 1 for s in sp)
+        ctx.max_context = max(s.start + s.length for s in sp)
+        ctx.dtype, ctx.device, ctx.cache = dtype, DEV, cache
+        self.ctx, self.cache, self.spans = ctx, cache, spans
+
+    def done(self):
+        for sid, n in self.spans:
+            self.cache.advance(sid, n)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("style,rotary_dim,window", [("neox", 24, None), ("interleaved", 16, 9)])
+def test_attention_mixer_alone(dtype, style, rotary_dim, window):
+    """The mixer with its own sizes (5 heads in groups of 5, head 24, partial rotary), fed in
+    portions beside a decoding request, against the plain parts on whole sequences."""
+    D, Hq, Hkv, hd, page = 40, 5, 1, 24, 4
+    mixer = AttentionMixer("a", D, Hq, Hkv, hd, position=PartSpec("rotary", {
+        "head_dim": hd, "theta": 777.0, "rotary_dim": rotary_dim, "style": style}), window=window, out_bias=True)
+    w = bound(mixer, dtype, scale=4.0)
+    layout = CacheLayout.build([mixer.cache_spec()], [None])
+    cache = CacheManager(layout, page, 30, 3, 80, dtype, DEV)
+    k, v = cache.plane_kv(0, 0)
+    view = CacheView(0, k, v, None, True)
+    g = torch.Generator().manual_seed(6)
+    xs = {"p": torch.randn(37, D, generator=g).to(dtype), "q": torch.randn(21, D, generator=g).to(dtype)}
+
+    def plain(x):
+        T = x.shape[0]
+        x = x.float()
+        pos = torch.arange(T)
+        lin = lambda n, b=True: P.plain_linear(x, w[f"a.{n}_proj.weight"], w.get(f"a.{n}_proj.bias") if b else None)
+        q = P.plain_rope(lin("q").reshape(T, Hq, hd), pos, 777.0, rotary_dim, style == "interleaved")
+        kk = P.plain_rope(lin("k").reshape(T, Hkv, hd), pos, 777.0, rotary_dim, style == "interleaved")
+        a = P.plain_attention(q, kk, lin("v").reshape(T, Hkv, hd), 1 / math.sqrt(hd), window)
+        return P.plain_linear(a.reshape(T, Hq * hd), w["a.o_proj.weight"], w["a.o_proj.bias"])
+
+    ref = {n: plain(x) for n, x in xs.items()}
+    cache.open("p"), cache.open("q")
+    fed = {"p": 0, "q": 0}
+    plan = [[("p", 9), ("q", 20)], [("p", 2), ("q", 1)], [("p", 13)], [("p", 1)], [("p", 12)]]
+    tol = 2e-5 if dtype == torch.float32 else 4e-2
+    for feeds in plan:
+        hc = HandContext(cache, feeds, dtype)
+        x = torch.cat([xs[n][fed[n]: fed[n] + c] for n, c in feeds]).to(DEV)
+        res = torch.zeros((x.shape[0], D), dtype=torch.float32, device=DEV)
+        mixer.forward(x, res, hc.ctx, view)
+        hc.done()
+        want = torch.cat([ref[n][fed[n]: fed[n] + c] for n, c in feeds])
+        assert torch.allclose(res.cpu(), want, atol=tol * float(want.abs().max()), rtol=tol), feeds
+        for n, c in feeds:
+            fed[n] += c
+
+
+# ---------------------------------------------------------------------------------------------
+# Other arrangements of the same parts, and a toy mixer with state of its own
+# ---------------------------------------------------------------------------------------------
+class ToyStateMixer(Mixer):
+    """A mixer with a fixed-size state per request and no pages: s_t = decay * s_{t-1} + x_t and
+    out_t = s_t W^T.  Defined here, not in the framework."""
+
+    def __init__(self, prefix, hidden_size, decay):
+        self.prefix, self.hidden_size, self.decay = prefix, hidden_size, float(decay)
+        self.w = None
+
+    def cache_spec(self):
+        return CacheSpec(state=StateSpec((self.hidden_size,), "float32"))
+
+    def weight_specs(self):
+        return [WeightSpec(f"{self.prefix}.mix.weight", (self.hidden_size, self.hidden_size), init=("normal", 0.05))]
+
+    def bind(self, tensors, dtype, device):
+        self.w = tensors[f"{self.prefix}.mix.weight"].float()
+
+    def forward(self, x, residual, ctx, cache):
+        for s in ctx.spans:
+            state = cache.state[s.slot]
+            if s.start == 0:
+                state.zero_()
+            for t in range(s.row, s.row + s.length):
+                state.mul_(self.decay).add_(x[t].float())
+                residual[t] += state @ self.w.t()
+
+
+@dataclass(frozen=True)
+class ToyConfig(ModelConfig):
+    hidden_size: int = 0
+    vocab_size: int = 0
+    heads: int = 0
+    kv_heads: int = 0
+    head_dim: int = 0
+    inner: int = 0
+    decay: float = 0.5
+    eps: float = 1e-6
+    variant: str = "state"
+
+    @staticmethod
+    def from_dict(raw, where="config.json"):
+        return ToyConfig(architecture=raw["architectures"][0], raw=dict(raw), hidden_size=raw["width"],
+                         vocab_size=raw["vocab"], heads=raw["heads"], kv_heads=raw["kv_heads"],
+                         head_dim=raw["head_dim"], inner=raw["inner"], decay=raw.get("decay", 0.5),
+                         eps=raw.get("eps", 1e-6), variant=raw.get("variant", "state"))
+
+
+def toy_spec(cfg: ToyConfig) -> ModelSpec:
+    D = cfg.hidden_size
+    norm = lambda p: PartSpec("rmsnorm", {"hidden_size": D, "eps": cfg.eps}, p)
+    attn = lambda p: PartSpec("attention", {"hidden_size": D, "num_heads": cfg.heads, "num_kv_heads": cfg.kv_heads,
+                                            "head_dim": cfg.head_dim, "qkv_bias": False,
+                                            "position": PartSpec("rotary", {"head_dim": cfg.head_dim, "theta": 100.0})}, p)
+    ffn = lambda p: PartSpec("gated_mlp", {"hidden_size": D, "intermediate_size": cfg.inner}, p)
+    if cfg.variant == "state":
+        layers = [LayerSpec(norm("l0.n1"), PartSpec("toy_state", {"hidden_size": D, "decay": cfg.decay}, "l0.toy"),
+                            norm("l0.n2"), ffn("l0.ffn")),
+                  LayerSpec(norm("l1.n1"), attn("l1.attn"), norm("l1.n2"), ffn("l1.ffn"))]
+        run = [RunEntry(0), RunEntry(1)]
+    else:   # "shared": a parallel block, a layer that runs twice, and a run that reads an earlier run's cache
+        layers = [LayerSpec(norm("l0.n1"), attn("l0.attn"), norm("l0.n2"), ffn("l0.ffn"), arrangement="parallel"),
+                  LayerSpec(norm("l1.n1"), attn("l1.attn"), norm("l1.n2"), ffn("l1.ffn"))]
+        run = [RunEntry(0), RunEntry(1), RunEntry(1), RunEntry(0, cache_of=0)]
+    return ModelSpec(cfg.architecture, D, cfg.vocab_size, 512,
+                     PartSpec("token_embedding", {"vocab_size": cfg.vocab_size, "hidden_size": D}, "emb"),
+                     layers, run, norm("final"), PartSpec("lm_head", {"vocab_size": cfg.vocab_size, "hidden_size": D}, "emb"))
+
+
+def toy_plain(raw, w, ids):
+    """The toy architectures on whole sequences, from the plain parts."""
+    D, H, Hkv, hd = raw["width"], raw["heads"], raw["kv_heads"], raw["head_dim"]
+    eps = raw.get("eps", 1e-6)
+    T = len(ids)
+    pos = torch.arange(T)
+    h = P.plain_embedding(torch.tensor(ids), w["emb.weight"])
+
+    def qkv(p, x):
+        q = P.plain_rope(P.plain_linear(x, w[p + ".q_proj.weight"]).reshape(T, H, hd), pos, 100.0)
+        k = P.plain_rope(P.plain_linear(x, w[p + ".k_proj.weight"]).reshape(T, Hkv, hd), pos, 100.0)
+        return q, k, P.plain_linear(x, w[p + ".v_proj.weight"]).reshape(T, Hkv, hd)
+
+    def attn_out(p, q, k, v):
+        return P.plain_linear(P.plain_attention(q, k, v, 1 / math.sqrt(hd)).reshape(T, H * hd), w[p + ".o_proj.weight"])
+
+    def ffn(p, x):
+        return P.plain_swiglu(x, w[p + ".gate_proj.weight"], w[p + ".up_proj.weight"], w[p + ".down_proj.weight"])
+
+    def pre_norm_attn_layer(l, h):
+        x = P.plain_rmsnorm(h, w[f"{l}.n1.weight"], eps)
+        h = h + attn_out(f"{l}.attn", *qkv(f"{l}.attn", x))
+        return h + ffn(f"{l}.ffn", P.plain_rmsnorm(h, w[f"{l}.n2.weight"], eps))
+
+    if raw.get("variant", "state") == "state":
+        x = P.plain_rmsnorm(h, w["l0.n1.weight"], eps)
+        s, outs = torch.zeros(D), []
+        for t in range(T):
+            s = raw.get("decay", 0.5) * s + x[t]
+            outs.append(s @ w["l0.toy.mix.weight"].t())
+        h = h + torch.stack(outs)
+        h = h + ffn("l0.ffn", P.plain_rmsnorm(h, w["l0.n2.weight"], eps))
+        h = pre_norm_attn_layer("l1", h)
+    else:
+        x1, x2 = P.plain_rmsnorm(h, w["l0.n1.weight"], eps), P.plain_rmsnorm(h, w["l0.n2.weight"], eps)
+        q0, k0, v0 = qkv("l0.attn", x1)
+        h = h + attn_out("l0.attn", q0, k0, v0) + ffn("l0.ffn", x2)
+        h = pre_norm_attn_layer("l1", h)
+        h = pre_norm_attn_layer("l1", h)
+        x1, x2 = P.plain_rmsnorm(h, w["l0.n1.weight"], eps), P.plain_rmsnorm(h, w["l0.n2.weight"], eps)
+        q3, _, _ = qkv("l0.attn", x1)                     # keys and values are those of run entry 0
+        h = h + attn_out("l0.attn", q3, k0, v0) + ffn("l0.ffn", x2)
+    return P.plain_linear(P.plain_rmsnorm(h, w["final.weight"], eps), w["emb.weight"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("variant", ["state", "shared"])
+def test_toy_architecture_registered_from_the_test(tmp_path, variant, dtype):
+    register_part("mixer", "toy_state", ToyStateMixer, replace=True)
+    register_architecture("ToyForCausalLM", ToyConfig.from_dict, toy_spec, replace=True)
+    raw = {"architectures": ["ToyForCausalLM"], "width": 48, "vocab": 211, "heads": 3, "kv_heads": 3, "head_dim": 16,
+           "inner": 60, "decay": 0.7, "eps": 1e-5, "variant": variant}
+    d = str(tmp_path / "toy")
+    write_random_model(raw, 9, d, "float32" if dtype == "float32" else "bfloat16")
+    cfg, w = P.read_model_dir(d)
+    core = core_for(d, dtype, page=8, pages=40, max_seqs=3, max_tokens=256)
+    layout = core.model.cache_layout
+    if variant == "state":
+        assert len(layout.state_planes) == 1 and layout.planes_per_group == [1]
+    else:
+        assert layout.planes_per_group == [3] and not layout.refs[3].owns
+    rng = random.Random(10)
+    seqs = {n: [rng.randrange(211) for _ in range(L)] for n, L in (("a", 50), ("b", 31), ("c", 44))}
+    ref = {n: toy_plain(raw, w, s) for n, s in seqs.items()}
+    fed = {n: 0 for n in seqs}
+    core.open("a"), core.open("b")
+    live, waiting = ["a", "b"], ["c"]          # "c" takes the slot (and its stale state) of whoever ends first
+    while live:
+        entries, exp = [], []
+        for n in list(live):
+            c = min(len(seqs[n]) - fed[n], rng.choice([1, 2, 7, 16]))
+            entries.append(StepEntry(n, seqs[n][fed[n]: fed[n] + c], list(range(c))))
+            exp.append((n, fed[n], c))
+            fed[n] += c
+        lg = core.step(entries).float().cpu()
+        row = 0
+        for n, at, c in exp:
+            err = float((lg[row: row + c] - ref[n][at: at + c]).abs().max())
+            assert err <= ATOL[dtype], f"{variant} {dtype}: request {n} positions {at}..{at + c - 1}: {err}"
+            row += c
+            if fed[n] == len(seqs[n]):
+                core.close(n)
+                live.remove(n)
+                if waiting:
+                    core.open(waiting[0])
+                    live.append(waiting.pop(0))
+    core.cache.check()
