@@ -1,0 +1,442 @@
+// Dense contraction on the 5th-generation tensor cores (sm_100a): bf16 operands staged in shared
+// memory by TMA, tcgen05.mma issued by one thread, float accumulators in tensor memory (TMEM),
+// read back with tcgen05.ld for a fused epilogue.
+//
+// C[M,N] = A[M,K] * W[N,K]^T with W stored [out, in] as in the checkpoint
+// (src/engine/engine_server.cpp:1542-1544; the reference calls cuBLAS, src/ops/gemm.cu:92-97).
+// Both operands are K-major, so either can take the MMA's 128-row "A" role:
+//   * many rows (prefill):  A role = 128 activation rows, B role = BN weight rows;
+//   * few rows (decode):    A role = 128 weight rows, B role = the activation rows (BN >= M),
+//                           so that no tensor-core row is wasted on padding ("swap").
+// Epilogues: store, store float, add into the float residual stream (with split-K: atomic adds),
+// SiLU(gate)*up on interleaved weight rows; the bias is added first.
+//
+// One block computes one 128 x BN tile.  Warp 0 issues TMA loads through a ring of STAGES shared
+// memory stages, warp 1 allocates TMEM and issues the MMAs, warps 2..5 run the epilogue (each
+// reads the 32 TMEM lanes it may access).  Every wait on an mbarrier is bounded in time: when it
+// runs out the kernel raises a flag in global memory, lets every role fall through to the common
+// exit, frees its TMEM and returns; the host reports the flag as an error.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int TILE_M = 128;       // rows of the A role = TMEM lanes
+constexpr int TILE_K = 64;        // bf16 elements per stage row = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 4;
+constexpr int NUM_THREADS = 192;
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // 2 s
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: false when the time limit ran out (or another role already gave up).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = globaltimer_ns();
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+            *abort_flag = 1;
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+
+// Shared memory matrix descriptor of a K-major tile with 128-byte rows and the 128-byte swizzle:
+// start address >> 4 | leading offset (unused in this mode, 1) | stride offset = 8 rows * 128 B |
+// descriptor version 1 (sm_100) | layout type 2 (128-byte swizzle).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// Instruction descriptor of kind::f16: D float (1 << 4), A and B bf16 (1 << 7, 1 << 10), both K-major,
+// N >> 3 at bit 17, M >> 4 at bit 24.
+__host__ __device__ constexpr uint32_t umma_idesc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(acc)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+
+struct GemmParams {
+    void* out;              // STORE / SWIGLU: bf16; STORE_F32: float
+    float* residual;        // RESIDUAL
+    const float* bias;      // [N] or null
+    int M, N, K;
+    int num_kb;             // K blocks in all
+    int kb_per_split;       // K blocks per grid.z slice
+    int* error_flag;        // raised when a wait ran out of time
+};
+
+template <int BN, int EPI, bool SWAP>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const GemmParams p) {
+    constexpr uint32_t A_BYTES = TILE_M * TILE_K * 2;
+    constexpr uint32_t B_BYTES = BN * TILE_K * 2;
+    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);   // swizzle needs 1024-byte alignment
+    uint8_t* a_tiles = smem;
+    uint8_t* b_tiles = smem + STAGES * A_BYTES;
+    uint64_t* full_bar = (uint64_t*)(b_tiles + STAGES * B_BYTES);
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* acc_bar = empty_bar + STAGES;
+    uint32_t* tmem_slot = (uint32_t*)(acc_bar + 1);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int a_row0 = blockIdx.x * TILE_M;     // first row of the A-role operand
+    const int b_row0 = blockIdx.y * BN;         // first row of the B-role operand
+    const int kb_begin = blockIdx.z * p.kb_per_split;
+    const int kb_end = min(p.num_kb, kb_begin + p.kb_per_split);
+    const int nkb = kb_end - kb_begin;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(acc_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (nkb > 0) {
+        if (warp == 0) {
+            if (lane == 0) {
+                for (int i = 0; i < nkb; ++i) {
+                    const int s = i % STAGES;
+                    const uint32_t phase = (i / STAGES) & 1;
+                    if (!mbar_wait(&empty_bar[s], phase ^ 1, abort_flag)) break;
+                    mbar_expect_tx(&full_bar[s], A_BYTES + B_BYTES);
+                    const int kx = (kb_begin + i) * TILE_K;
+                    tma_load_2d(a_tiles + s * A_BYTES, &map_a, kx, a_row0, &full_bar[s]);
+                    tma_load_2d(b_tiles + s * B_BYTES, &map_b, kx, b_row0, &full_bar[s]);
+                }
+            }
+        } else if (warp == 1) {
+            if (lane == 0) {
+                constexpr uint32_t idesc = umma_idesc(TILE_M, BN);
+                bool ok = true;
+                for (int i = 0; i < nkb && ok; ++i) {
+                    const int s = i % STAGES;
+                    const uint32_t phase = (i / STAGES) & 1;
+                    ok = mbar_wait(&full_bar[s], phase, abort_flag);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_addr = smem_u32(a_tiles + s * A_BYTES);
+                    const uint32_t b_addr = smem_u32(b_tiles + s * B_BYTES);
+#pragma unroll
+                    for (int k = 0; k < TILE_K / UMMA_K; ++k) {
+                        umma_bf16(tmem_base, umma_desc(a_addr + k * UMMA_K * 2), umma_desc(b_addr + k * UMMA_K * 2),
+                                  idesc, (i > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&empty_bar[s]);      // frees the stage when these MMAs have read it
+                }
+                if (ok) umma_commit(acc_bar);         // the accumulator is complete
+            }
+        } else {
+            // Epilogue: warp w may read TMEM lanes (w % 4) * 32 .. + 31.
+            const int quarter = warp & 3;
+            const bool ok = mbar_wait(acc_bar, 0, abort_flag);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (ok) {
+                const int row = quarter * 32 + lane;            // row of the tile = TMEM lane
+                constexpr int CHUNK = BN >= 32 ? 32 : 16;
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += CHUNK) {
+                    uint32_t r[32];
+                    const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
+                    if (CHUNK == 32) tmem_ld32(taddr, r); else tmem_ld16(taddr, r);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (!SWAP) {
+                        // row = token m, columns = output features n
+                        const int m = a_row0 + row;
+                        const int nb = b_row0 + c0;
+                        if (m < p.M) {
+                            if (EPI == LLB_EPI_SWIGLU) {
+                                __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)m * (p.N / 2);
+#pragma unroll
+                                for (int j = 0; j < CHUNK; j += 2) {
+                                    const int n = nb + j;
+                                    if (n + 1 < p.N) {
+                                        float g = __uint_as_float(r[j]), u = __uint_as_float(r[j + 1]);
+                                        if (p.bias) { g += p.bias[n]; u += p.bias[n + 1]; }
+                                        o[n >> 1] = __float2bfloat16_rn(llb_silu(g) * u);
+                                    }
+                                }
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < CHUNK; ++j) {
+                                    const int n = nb + j;
+                                    if (n < p.N) {
+                                        float v = __uint_as_float(r[j]);
+                                        if (p.bias && blockIdx.z == 0) v += p.bias[n];
+                                        const size_t idx = (size_t)m * p.N + n;
+                                        if (EPI == LLB_EPI_STORE) ((__nv_bfloat16*)p.out)[idx] = __float2bfloat16_rn(v);
+                                        else if (EPI == LLB_EPI_STORE_F32) ((float*)p.out)[idx] = v;
+                                        else if (gridDim.z == 1) p.residual[idx] += v;
+                                        else atomicAdd(p.residual + idx, v);
+                                    }
+                                }
+                            }
+                        }
+                    } else {
+                        // row = output feature n, columns = tokens m
+                        const int n = a_row0 + row;
+                        const int mb = b_row0 + c0;
+                        const float bias = (p.bias && n < p.N && blockIdx.z == 0) ? p.bias[n] : 0.0f;
+#pragma unroll
+                        for (int j = 0; j < CHUNK; ++j) {
+                            const int m = mb + j;
+                            float v = __uint_as_float(r[j]) + bias;
+                            if (EPI == LLB_EPI_SWIGLU) {
+                                const float other = __shfl_xor_sync(0xffffffffu, v, 1);   // gate in even rows, up in odd
+                                if ((lane & 1) == 0 && m < p.M && n + 1 < p.N)
+                                    ((__nv_bfloat16*)p.out)[(size_t)m * (p.N / 2) + (n >> 1)] =
+                                        __float2bfloat16_rn(llb_silu(v) * other);
+                            } else if (m < p.M && n < p.N) {
+                                const size_t idx = (size_t)m * p.N + n;
+                                if (EPI == LLB_EPI_STORE) ((__nv_bfloat16*)p.out)[idx] = __float2bfloat16_rn(v);
+                                else if (EPI == LLB_EPI_STORE_F32) ((float*)p.out)[idx] = v;
+                                else if (gridDim.z == 1) p.residual[idx] += v;
+                                else atomicAdd(p.residual + idx, v);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (*abort_flag && threadIdx.x == 0 && p.error_flag) atomicExch(p.error_flag, 1);
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)sym;
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr;
+    int rows, K, box_rows;
+    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && K == o.K && box_rows == o.box_rows; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        return std::hash<const void*>()(k.ptr) ^ ((size_t)k.rows * 1000003u) ^ ((size_t)k.K << 20) ^ ((size_t)k.box_rows << 40);
+    }
+};
+
+// A tensor map over a row-major bf16 matrix [rows, K] with boxes of box_rows x 64 and the 128-byte swizzle.
+int make_map(const void* ptr, int rows, int K, int box_rows, CUtensorMap* out) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    static std::mutex mu;
+    MapKey key{ptr, rows, K, box_rows};
+    {
+        std::lock_guard<std::mutex> g(mu);
+        auto it = cache.find(key);
+        if (it != cache.end()) {
+            *out = it->second;
+            return 0;
+        }
+    }
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return llb_fail("gemm_tcgen05: cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    cuuint32_t box[2] = {(cuuint32_t)TILE_K, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return llb_fail("gemm_tcgen05: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    std::lock_guard<std::mutex> g(mu);
+    if (cache.size() > 4096) cache.clear();
+    cache[key] = *out;
+    return 0;
+}
+
+template <int BN>
+constexpr size_t smem_bytes() {
+    return (size_t)STAGES * (TILE_M * TILE_K * 2 + BN * TILE_K * 2) + (2 * STAGES + 1) * 8 + 16 + 1024;
+}
+
+template <int BN, int EPI, bool SWAP>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid, cudaStream_t stream) {
+    constexpr size_t smem = smem_bytes<BN>();
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, EPI, SWAP>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return llb_fail("gemm_tcgen05: cannot opt in to %zu bytes of shared memory: %s", smem,
+                                              cudaGetErrorString(e));
+        configured = true;
+    }
+    gemm_tcgen05_kernel<BN, EPI, SWAP><<<grid, NUM_THREADS, smem, stream>>>(ma, mb, p);
+    return llb_check_launch("gemm_tcgen05");
+}
+
+template <int BN, bool SWAP>
+int dispatch_epi(int epi, const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid, cudaStream_t s) {
+    switch (epi) {
+        case LLB_EPI_STORE: return launch<BN, LLB_EPI_STORE, SWAP>(ma, mb, p, grid, s);
+        case LLB_EPI_STORE_F32: return launch<BN, LLB_EPI_STORE_F32, SWAP>(ma, mb, p, grid, s);
+        case LLB_EPI_RESIDUAL: return launch<BN, LLB_EPI_RESIDUAL, SWAP>(ma, mb, p, grid, s);
+        case LLB_EPI_SWIGLU: return launch<BN, LLB_EPI_SWIGLU, SWAP>(ma, mb, p, grid, s);
+    }
+    return llb_fail("gemm_tcgen05: unknown epilogue %d", epi);
+}
+
+}  // namespace
+
+// A [M,K] bf16, W [N,K] bf16, both row-major with K a multiple of 8 and 16-byte aligned bases;
+// bias [N] float or null.  `out`: [M,N] bf16 (STORE), [M,N] float (STORE_F32), [M,N/2] bf16 (SWIGLU, N even);
+// `residual`: [M,N] float (RESIDUAL).  split_k > 1 is allowed for RESIDUAL only.  error_flag: one int
+// that the kernel raises if a wait inside it ran out of time (the result is then invalid), or null.
+LLB_EXPORT int llb_gemm_tcgen05(const void* A, const void* W, const float* bias, void* out, float* residual,
+                                int epilogue, int M, int N, int K, int split_k, int* error_flag,
+                                cudaStream_t stream) {
+    if (M == 0) return 0;
+    LLB_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tcgen05: bad sizes M=%d N=%d K=%d", M, N, K);
+    LLB_REQUIRE(K % 8 == 0, "gemm_tcgen05: K=%d is not a multiple of 8 (rows must be 16-byte multiples for TMA)", K);
+    LLB_REQUIRE(((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_tcgen05: operands must be 16-byte aligned");
+    LLB_REQUIRE(epilogue != LLB_EPI_SWIGLU || N % 2 == 0, "gemm_tcgen05: SwiGLU epilogue needs an even N, got %d", N);
+    LLB_REQUIRE(epilogue != LLB_EPI_RESIDUAL || residual != nullptr, "gemm_tcgen05: residual epilogue without residual");
+    LLB_REQUIRE(epilogue == LLB_EPI_RESIDUAL || out != nullptr, "gemm_tcgen05: output pointer is null");
+    LLB_REQUIRE(split_k >= 1 && (split_k == 1 || epilogue == LLB_EPI_RESIDUAL),
+                "gemm_tcgen05: split_k=%d needs the residual epilogue", split_k);
+    GemmParams p;
+    p.out = out; p.residual = residual; p.bias = bias; p.M = M; p.N = N; p.K = K;
+    p.num_kb = llb_ceil_div(K, TILE_K);
+    if (split_k > p.num_kb) split_k = p.num_kb;
+    p.kb_per_split = llb_ceil_div(p.num_kb, split_k);
+    split_k = llb_ceil_div(p.num_kb, p.kb_per_split);
+    p.error_flag = error_flag;
+    const bool swap = M <= 128;
+    CUtensorMap ma, mb;
+    int rc;
+    if (swap) {
+        const int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
+        if ((rc = make_map(W, N, K, TILE_M, &ma))) return rc;
+        if ((rc = make_map(A, M, K, bn, &mb))) return rc;
+        dim3 grid(llb_ceil_div(N, TILE_M), 1, split_k);
+        switch (bn) {
+            case 16: return dispatch_epi<16, true>(epilogue, ma, mb, p, grid, stream);
+            case 32: return dispatch_epi<32, true>(epilogue, ma, mb, p, grid, stream);
+            case 64: return dispatch_epi<64, true>(epilogue, ma, mb, p, grid, stream);
+            default: return dispatch_epi<128, true>(epilogue, ma, mb, p, grid, stream);
+        }
+    }
+    constexpr int BN = 128;
+    if ((rc = make_map(A, M, K, TILE_M, &ma))) return rc;
+    if ((rc = make_map(W, N, K, BN, &mb))) return rc;
+    dim3 grid(llb_ceil_div(M, TILE_M), llb_ceil_div(N, BN), split_k);
+    LLB_REQUIRE(grid.y <= 65535, "gemm_tcgen05: N=%d is too large for one launch", N);
+    return dispatch_epi<BN, false>(epilogue, ma, mb, p, grid, stream);
+}

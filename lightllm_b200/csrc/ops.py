@@ -15,7 +15,7 @@ from . import build as _build
 
 F32, BF16 = 0, 1
 EPI_STORE, EPI_STORE_F32, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
-ABI_VERSION = 3
+ABI_VERSION = 4
 
 _lib: Optional[ctypes.CDLL] = None
 
@@ -210,3 +210,38 @@ def launch_count() -> int:
 def has_tcgen05() -> bool:
     """Whether the library carries the tcgen05 tensor-core contraction."""
     return hasattr(lib(), "llb_gemm_tcgen05")
+
+
+_async_err = {}
+
+
+def async_error_flag(device: torch.device) -> torch.Tensor:
+    """One int32 on the device that kernels with bounded waits raise when a wait ran out."""
+    key = torch.device(device).index or 0
+    t = _async_err.get(key)
+    if t is None:
+        t = _async_err[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return t
+
+
+def check_async_errors(device: torch.device) -> None:
+    """Synchronises and raises if a kernel gave up on a wait (its output is then invalid)."""
+    t = async_error_flag(device)
+    if int(t.item()) != 0:
+        t.zero_()
+        raise KernelError("a tensor-core kernel gave up waiting on a barrier; its results are invalid")
+
+
+def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], epilogue: int,
+                 out: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
+                 split_k: int = 1) -> None:
+    """Tensor-core contraction a[M,K] @ w[N,K]^T (bf16, K a multiple of 8) with a fused epilogue."""
+    M, K = a.shape
+    N, K2 = w.shape
+    if K != K2:
+        raise KernelError(f"gemm: a is {tuple(a.shape)} but w is {tuple(w.shape)}")
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("gemm_tcgen05 takes bfloat16 operands")
+    _check_epilogue_args(a, N, M, bias, epilogue, out, residual)
+    _check(lib().llb_gemm_tcgen05(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), _ptr(residual), epilogue, M, N, K,
+                                  split_k, _ptr(async_error_flag(a.device)), _stream()))

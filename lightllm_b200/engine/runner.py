@@ -191,6 +191,8 @@ class ModelRunner:
 
     def check_device_errors(self) -> None:
         """Raise if a kernel flagged a fault (an id outside the vocabulary reached the device)."""
+        from ..csrc import ops
+        ops.check_async_errors(self.device)
         if int(self.err.item()) != 0:
             self.err.zero_()
             raise RuntimeError("a kernel reported an out-of-range token id")

@@ -21,6 +21,7 @@ STORE, STORE_F32, RESIDUAL, SWIGLU = ops.EPI_STORE, ops.EPI_STORE_F32, ops.EPI_R
 
 # Rows at or below which the row-streaming CUDA-core kernel is used for bfloat16 (decode).
 SMALL_M = 8
+NUM_SMS = 148
 
 
 def tensor_core_eligible(x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -41,7 +42,12 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
     if M == 0:
         return out
     if tensor_core_eligible(x, w):
-        ops.gemm_tcgen05(x, w, bias, epilogue, out, residual)
+        split_k = 1
+        if epilogue == RESIDUAL and M <= 128:
+            # few rows: the grid has only N/128 blocks; cut K so that the weights stream from all SMs
+            tiles, kblocks = -(-N // 128), -(-x.shape[1] // 64)
+            split_k = max(1, min(kblocks, NUM_SMS // tiles))
+        ops.gemm_tcgen05(x, w, bias, epilogue, out, residual, split_k)
     else:
         ops.gemm_simt(x, w, bias, epilogue, out, residual)
     return out

@@ -109,6 +109,37 @@ def test_gemm_simt(ops, M, N, K, epi, dtypes):
             f"max diff {float((got - ref).abs().max())}"
 
 
+TC_SHAPES = [(9, 50, 40), (16, 128, 64), (17, 130, 64), (33, 1152, 896), (64, 9728, 896), (65, 896, 4864),
+             (128, 896, 896), (129, 200, 72), (300, 1000, 96), (2048, 1152, 896), (1000, 896, 4864), (12, 151936, 896)]
+
+
+@pytest.mark.parametrize("M,N,K", TC_SHAPES)
+@pytest.mark.parametrize("epi", [0, 1, 2, 3])
+def test_gemm_tcgen05(ops, M, N, K, epi):
+    """The tensor-core contraction against float64 on the same bf16 operands."""
+    if N > 100000 and epi != 1:
+        pytest.skip("the vocabulary-sized case is the head's: float output only")
+    a, w = rnd((M, K), torch.bfloat16, 40), rnd((N, K), torch.bfloat16, 41, 0.2)
+    for bias, split_k in ((None, 1), (rnd((N,), torch.float32, 42), 1), (rnd((N,), torch.float32, 42), 5)):
+        if split_k > 1 and epi != 2:
+            continue
+        residual = rnd((M, N), torch.float32, 43)
+        res0 = residual.clone()
+        out = None
+        if epi in (0, 3):
+            out = torch.full((M, N // 2 if epi == 3 else N), float("nan"), dtype=torch.bfloat16, device=dev())
+        elif epi == 1:
+            out = torch.full((M, N), float("nan"), dtype=torch.float32, device=dev())
+        ops.gemm_tcgen05(a, w, bias, epi, out, residual if epi == 2 else None, split_k)
+        ops.check_async_errors(dev())
+        ref = gemm_reference(a, w, bias, epi, res0)
+        got = (residual if epi == 2 else out).double().cpu()
+        assert not torch.isnan(got).any()
+        tol = 1e-5 * math.sqrt(K) if epi in (1, 2) else 1e-2
+        scale = max(1.0, float(ref.abs().max()))
+        assert torch.allclose(got, ref, atol=tol * scale, rtol=0), f"max diff {float((got - ref).abs().max())}"
+
+
 @pytest.mark.parametrize("dtype", DT)
 @pytest.mark.parametrize("hd,rd,inter", [(16, 16, False), (32, 32, True), (64, 64, False), (48, 32, False),
                                          (128, 64, True)])
