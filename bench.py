@@ -205,6 +205,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=QWEN25_05B["num_hidden_layers"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (for profiling runs)")
+    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
+                    help="run one part only and print a short line (for profiling runs, not a bench record)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -228,6 +230,14 @@ def main() -> int:
                         page_size=PAGE_SIZE, num_pages=max_batch * (PROMPT_LEN + 512) // PAGE_SIZE,
                         max_seqs=max_batch, chunk_size=PROMPT_LEN)
         core = engine.core
+        if args.only == "decode":
+            ms, launches, ctx = time_decode(core, args.batch, args.steps, args.warmup, rng)
+            print(json.dumps({"only": "decode", "batch": args.batch, "ms_per_step": round(ms, 4), "launches": launches}))
+            return 0
+        if args.only == "prefill":
+            pre_ms = time_prefill(core, args.steps, args.warmup, rng)
+            print(json.dumps({"only": "prefill", "tokens": PROMPT_LEN, "ms": round(pre_ms, 3)}))
+            return 0
         clocks = ClockSampler()
         clocks.start()
         ms, launches, ctx = time_decode(core, args.batch, args.steps, args.warmup, rng)

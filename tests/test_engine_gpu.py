@@ -44,7 +44,9 @@ def core_for(d, dtype, page=16, pages=64, max_seqs=4, max_tokens=512):
 
 def sharpen(factor):
     """Scale q and k projections so that attention is sharp: few keys dominate a row, and a key
-    that is skipped, stale or at the wrong place changes the logits by far more than rounding."""
+    that is skipped, stale or at the wrong place changes the logits by far more than rounding.
+    The factor is bounded by the plain implementation itself: at 30 its float32 and float64 results
+    already differ by 2e-4, at 10 by 3e-6."""
     def edit(w):
         for k in w:
             if k.endswith("q_proj.weight") or k.endswith("k_proj.weight"):
@@ -97,7 +99,7 @@ def test_long_decoding_and_first_tokens(tmp_path, dtype):
 @pytest.mark.parametrize("name", ["A", "C"])
 def test_sharp_attention_over_far_keys_page_edges_and_reused_pages(tmp_path, name, dtype):
     d = model_dir(tmp_path, name, seed=8, store="float32" if dtype == "float32" else "bfloat16",
-                  edit=sharpen(30.0 if dtype == "float32" else 6.0))
+                  edit=sharpen(10.0 if dtype == "float32" else 6.0))
     cfg, w = P.read_model_dir(d)
     V, page = cfg["vocab_size"], PAGE_SIZE[name]
     rng = random.Random(3)
