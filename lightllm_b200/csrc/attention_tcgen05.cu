@@ -1,0 +1,430 @@
+// Paged flash-attention for prompt portions on the 5th-generation tensor cores (sm_100a, bf16).
+//
+// One block takes 128 consecutive query rows of one span and one query head.  Keys and values
+// come from the request's pages, 128 keys at a time: TMA copies each page of the tile (a box of
+// page_size rows x 64 elements) into a swizzled shared-memory tile, double buffered.  Then
+//     S = Q K^T          tcgen05.mma, both operands K-major, S in tensor memory (128 columns)
+//     softmax            one thread per query row reads its row of S with tcgen05.ld; scale, mask by
+//                        absolute position (and window), running max and sum in float
+//     O_tile = P V       P (bf16) goes back to shared memory as the A operand; V is the B operand in
+//                        MN-major form (its rows are keys), result in tensor memory
+//     O = O * e^(m_old - m_new) + O_tile   in registers, float
+// and finally O / l is written as bf16.  Formulas as src/kv_cache/paged_attention.cu:153-163 (scores,
+// online softmax) with the same departures as the CUDA-core kernel of this library: -inf start, exact
+// acc / l, the token's own key visible, every portion causal, page size a parameter.
+//
+// Head sizes 64 and 128; page sizes that divide 128 and are multiples of 8.  Other shapes use the
+// CUDA-core kernel.  Every wait on an mbarrier is bounded in time; when one runs out the block raises
+// the error flag, falls through to the exit, frees its tensor memory and returns.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BQ = 128;     // query rows per block = TMEM lanes
+constexpr int BKV = 128;    // keys per tile
+constexpr int NUM_THREADS = 128;
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = globaltimer_ns();
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+            *abort_flag = 1;
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+// K-major operand tile, 128-byte rows, 128-byte swizzle: 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// MN-major operand (rows of the tile are the contraction index): 64 contiguous MN elements per
+// 128-byte row, groups of 8 rows 1024 bytes apart (stride offset), MN atoms `lbo` bytes apart.
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t addr, uint32_t lbo) {
+    return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)((lbo >> 4) & 0x3FFF) << 16) |
+           ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// kind::f16 instruction descriptor: float D, bf16 A and B; b_mn = 1 marks B as MN-major (bit 16).
+__host__ __device__ constexpr uint32_t idesc_bf16(int m, int n, int b_mn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn << 16) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(acc)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&r)[32]) {
+    uint32_t* u = reinterpret_cast<uint32_t*>(r);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]),
+          "=r"(u[8]), "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15]),
+          "=r"(u[16]), "=r"(u[17]), "=r"(u[18]), "=r"(u[19]), "=r"(u[20]), "=r"(u[21]), "=r"(u[22]), "=r"(u[23]),
+          "=r"(u[24]), "=r"(u[25]), "=r"(u[26]), "=r"(u[27]), "=r"(u[28]), "=r"(u[29]), "=r"(u[30]), "=r"(u[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+struct AttnTcParams {
+    __nv_bfloat16* out;        // [T, Hq, HD]
+    const int* tile_span;
+    const int* tile_q0;
+    const int* span_row;
+    const int* span_len;
+    const int* span_pos;
+    const int* block_table;    // [S, max_pages]
+    int max_pages, page_size, Hq, Hkv, window, num_slots;
+    float scale_log2e;         // scale * log2(e): scores are kept in base-2 units
+    int* error_flag;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(NUM_THREADS)
+attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                         const __grid_constant__ CUtensorMap map_v, const AttnTcParams p) {
+    constexpr int KB = HD / 64;                       // 64-element blocks along the head dimension
+    constexpr uint32_t TILE_BYTES = 128 * 128;        // a [128 rows][64 elements] bf16 tile
+    constexpr uint32_t TMEM_COLS = 256;               // S: columns 0..127, P V: columns 128..128+HD-1
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* q_s = smem;                              // KB tiles
+    uint8_t* k_s = q_s + KB * TILE_BYTES;             // 2 stages x KB tiles
+    uint8_t* v_s = k_s + 2 * KB * TILE_BYTES;         // 2 stages x KB tiles
+    uint8_t* p_s = v_s + 2 * KB * TILE_BYTES;         // 2 tiles (keys 0..63, 64..127)
+    uint64_t* bar_q = (uint64_t*)(p_s + 2 * TILE_BYTES);
+    uint64_t* bar_kv = bar_q + 1;                     // [2]
+    uint64_t* bar_s = bar_kv + 2;
+    uint64_t* bar_pv = bar_s + 1;
+    uint32_t* tmem_slot = (uint32_t*)(bar_pv + 1);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = blockIdx.x, head = blockIdx.y;
+    const int kvh = head / (p.Hq / p.Hkv);
+    const int span = p.tile_span[tile];
+    const int q0 = p.tile_q0[tile];
+    const int row0 = p.span_row[span] + q0;
+    const int nrows = min(BQ, p.span_len[span] - q0);
+    const int pos0 = p.span_pos[span] + q0;
+    const int* bt = p.block_table + (size_t)span * p.max_pages;
+    const int hi = pos0 + nrows;                                   // keys [lo, hi) can be visible
+    const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    const int kt0 = (lo / BKV) * BKV;
+    const int ntiles = (hi - kt0 + BKV - 1) / BKV;
+
+    if (threadIdx.x == 0) {
+        mbar_init(bar_q, 1);
+        mbar_init(&bar_kv[0], 1);
+        mbar_init(&bar_kv[1], 1);
+        mbar_init(bar_s, 1);
+        mbar_init(bar_pv, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_s = tmem_base + ((uint32_t)(warp * 32) << 16);
+    const uint32_t tmem_o = tmem_s + 128;
+
+    // Loads of one key/value tile: each lane of warp 0 takes pages of the tile.
+    auto load_kv = [&](int j) {
+        const int st = j & 1;
+        const int kt = kt0 + j * BKV;
+        if (lane == 0) mbar_expect_tx(&bar_kv[st], 2 * KB * TILE_BYTES);
+        __syncwarp();
+        const int ppt = BKV / p.page_size;
+        for (int pg = lane; pg < ppt; pg += 32) {
+            const int lp = kt / p.page_size + pg;
+            const int page = lp < p.max_pages ? bt[lp] : -1;
+            const int y = page >= 0 ? page * p.page_size : p.num_slots;    // out of range: the box is zero-filled
+            const uint32_t off = (uint32_t)pg * p.page_size * 128;
+#pragma unroll
+            for (int kb = 0; kb < KB; ++kb) {
+                tma_load_2d(k_s + (st * KB + kb) * TILE_BYTES + off, &map_k, kvh * HD + kb * 64, y, &bar_kv[st]);
+                tma_load_2d(v_s + (st * KB + kb) * TILE_BYTES + off, &map_v, kvh * HD + kb * 64, y, &bar_kv[st]);
+            }
+        }
+    };
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_expect_tx(bar_q, KB * TILE_BYTES);
+#pragma unroll
+            for (int kb = 0; kb < KB; ++kb)
+                tma_load_2d(q_s + kb * TILE_BYTES, &map_q, head * HD + kb * 64, row0, bar_q);
+        }
+        __syncwarp();
+        if (ntiles > 0) load_kv(0);
+    }
+
+    const int r = threadIdx.x;                  // query row of this thread = TMEM lane
+    const int qpos = pos0 + r;
+    float o[HD];
+#pragma unroll
+    for (int d = 0; d < HD; ++d) o[d] = 0.0f;
+    float m_run = -INFINITY, l_run = 0.0f;
+    bool ok = mbar_wait(bar_q, 0, abort_flag);
+
+    constexpr uint32_t IDESC_S = idesc_bf16(BQ, BKV, 0);
+    constexpr uint32_t IDESC_PV = idesc_bf16(BQ, HD, 1);
+
+    for (int j = 0; j < ntiles && ok; ++j) {
+        const int st = j & 1;
+        const int kt = kt0 + j * BKV;
+        if (warp == 0 && j + 1 < ntiles) load_kv(j + 1);     // the other stage was released by tile j-1's P V
+        ok = mbar_wait(&bar_kv[st], (j >> 1) & 1, abort_flag);
+        if (!ok) break;
+        if (threadIdx.x == 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (int kb = 0; kb < KB; ++kb)
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    umma_bf16(tmem_base, desc_kmajor(smem_u32(q_s + kb * TILE_BYTES) + k * 32),
+                              desc_kmajor(smem_u32(k_s + (st * KB + kb) * TILE_BYTES) + k * 32), IDESC_S,
+                              (kb > 0 || k > 0) ? 1u : 0u);
+            umma_commit(bar_s);
+        }
+        ok = mbar_wait(bar_s, j & 1, abort_flag);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+        // Softmax of this thread's row over the 128 keys of the tile, in two passes over tensor
+        // memory (maximum first, then the probabilities), 32 columns at a time.
+        auto masked = [&](float raw, int kp) -> float {
+            const bool vis = kp <= qpos && kp < hi && kp >= lo && (p.window <= 0 || qpos - kp < p.window);
+            return vis ? raw * p.scale_log2e : -INFINITY;
+        };
+        float m_tile = -INFINITY;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+            float s[32];
+            tmem_ld32(tmem_s + c * 32, s);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) m_tile = fmaxf(m_tile, masked(s[i], kt + c * 32 + i));
+        }
+        const float m_new = fmaxf(m_run, m_tile);
+        const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;      // nothing visible yet: all p are 0
+        const float corr = (m_run == -INFINITY) ? 0.0f : exp2f(m_run - m_use);
+        float l_tile = 0.0f;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+            float s[32];
+            tmem_ld32(tmem_s + c * 32, s);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) s[i] = masked(s[i], kt + c * 32 + i);
+            // P as the A operand: row r, 16-byte chunk q of the 128-byte row lands at chunk q ^ (r & 7).
+            uint8_t* prow = p_s + (c >> 1) * TILE_BYTES + (uint32_t)r * 128;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                uint32_t w[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float p0 = exp2f(s[q * 8 + 2 * e] - m_use);
+                    const float p1 = exp2f(s[q * 8 + 2 * e + 1] - m_use);
+                    const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                    // the sum uses the rounded values, so that numerator and denominator agree
+                    l_tile += __bfloat162float(h.x) + __bfloat162float(h.y);
+                    w[e] = *reinterpret_cast<const uint32_t*>(&h);
+                }
+                const int chunk = ((c & 1) * 4 + q) ^ (r & 7);
+                *reinterpret_cast<uint4*>(prow + chunk * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        }
+        l_run = l_run * corr + l_tile;
+        m_run = m_new;
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // P is read by the tensor core
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            // O_tile[128 x HD] = P[128 x 128 keys] V[128 keys x HD]; 16 keys per instruction
+#pragma unroll
+            for (int k = 0; k < BKV / 16; ++k)
+                umma_bf16(tmem_base + 128, desc_kmajor(smem_u32(p_s + (k >> 2) * TILE_BYTES) + (k & 3) * 32),
+                          desc_mnmajor(smem_u32(v_s + st * KB * TILE_BYTES) + k * 16 * 128, TILE_BYTES), IDESC_PV,
+                          k > 0 ? 1u : 0u);
+            umma_commit(bar_pv);
+        }
+        ok = mbar_wait(bar_pv, j & 1, abort_flag);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {
+            float t[32];
+            tmem_ld32(tmem_o + c * 32, t);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * corr + t[i];
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();        // S and the P V columns may be overwritten, P and this K/V stage reused
+    }
+
+    if (ok && r < nrows) {
+        const float inv = 1.0f / l_run;
+        __nv_bfloat16* dst = p.out + ((size_t)(row0 + r) * p.Hq + head) * HD;
+#pragma unroll
+        for (int d = 0; d < HD; d += 8) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const __nv_bfloat162 h = __floats2bfloat162_rn(o[d + 2 * e] * inv, o[d + 2 * e + 1] * inv);
+                w[e] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+            *reinterpret_cast<uint4*>(dst + d) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (*abort_flag && threadIdx.x == 0 && p.error_flag) atomicExch(p.error_flag, 2);
+    if (warp == 0) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)sym;
+    });
+    return fn;
+}
+
+// A map over a row-major bf16 matrix [rows, cols] with boxes of box_rows x 64 and the 128-byte swizzle.
+int make_map(const void* ptr, long long rows, long long cols, int box_rows, CUtensorMap* out) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return llb_fail("attention_tcgen05: cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult rc = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) return llb_fail("attention_tcgen05: cuTensorMapEncodeTiled failed with code %d", (int)rc);
+    return 0;
+}
+
+template <int HD>
+int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnTcParams& p, int num_tiles,
+           cudaStream_t stream) {
+    constexpr int KB = HD / 64;
+    constexpr size_t smem = (size_t)(KB + 4 * KB + 2) * 128 * 128 + 6 * 8 + 16 + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)smem);
+        if (e != cudaSuccess) return llb_fail("attention_tcgen05: cannot opt in to %zu bytes of shared memory: %s", smem,
+                                              cudaGetErrorString(e));
+        configured = true;
+    }
+    dim3 grid(num_tiles, p.Hq);
+    attention_tcgen05_kernel<HD><<<grid, NUM_THREADS, smem, stream>>>(mq, mk, mv, p);
+    return llb_check_launch("attention_tcgen05");
+}
+
+}  // namespace
+
+// Whether the tensor-core kernel takes this shape (else the CUDA-core kernel is the one to call).
+LLB_EXPORT int llb_attention_tcgen05_supports(int hd, int page_size) {
+    return (hd == 64 || hd == 128) && page_size >= 8 && page_size <= 128 && page_size % 8 == 0 && 128 % page_size == 0;
+}
+
+// q, out [T, Hq, hd] bf16; k_cache, v_cache [num_slots, Hkv, hd] bf16 with slot = page*page_size + offset;
+// tiles of 128 query rows: tile_span, tile_q0 [num_tiles]; span_row, span_len, span_pos [S];
+// block_table [S, max_pages].  window <= 0: every earlier key is visible.
+LLB_EXPORT int llb_paged_attention_tcgen05(const void* q, const void* k_cache, const void* v_cache, void* out, int T,
+                                           const int* tile_span, const int* tile_q0, int num_tiles,
+                                           const int* span_row, const int* span_len, const int* span_pos,
+                                           const int* block_table, int max_pages, int page_size, int num_slots,
+                                           int Hq, int Hkv, int hd, int window, float scale, int* error_flag,
+                                           cudaStream_t stream) {
+    if (num_tiles == 0) return 0;
+    LLB_REQUIRE(llb_attention_tcgen05_supports(hd, page_size),
+                "attention_tcgen05: head_dim %d with page size %d is not supported (head 64 or 128; page size a "
+                "multiple of 8 that divides 128)", hd, page_size);
+    LLB_REQUIRE(Hq > 0 && Hkv > 0 && Hq % Hkv == 0 && Hq <= 65535, "attention_tcgen05: bad head counts %d/%d", Hq, Hkv);
+    LLB_REQUIRE(((uintptr_t)q % 16 == 0) && ((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0) &&
+                ((uintptr_t)out % 16 == 0), "attention_tcgen05: tensors must be 16-byte aligned");
+    CUtensorMap mq, mk, mv;
+    int rc;
+    if ((rc = make_map(q, T, (long long)Hq * hd, BQ, &mq))) return rc;
+    if ((rc = make_map(k_cache, num_slots, (long long)Hkv * hd, page_size, &mk))) return rc;
+    if ((rc = make_map(v_cache, num_slots, (long long)Hkv * hd, page_size, &mv))) return rc;
+    AttnTcParams p;
+    p.out = (__nv_bfloat16*)out;
+    p.tile_span = tile_span; p.tile_q0 = tile_q0; p.span_row = span_row; p.span_len = span_len; p.span_pos = span_pos;
+    p.block_table = block_table; p.max_pages = max_pages; p.page_size = page_size; p.Hq = Hq; p.Hkv = Hkv;
+    p.window = window; p.num_slots = num_slots; p.scale_log2e = scale * 1.4426950408889634f; p.error_flag = error_flag;
+    if (hd == 64) return launch<64>(mq, mk, mv, p, num_tiles, stream);
+    return launch<128>(mq, mk, mv, p, num_tiles, stream);
+}

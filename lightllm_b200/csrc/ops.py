@@ -15,7 +15,7 @@ from . import build as _build
 
 F32, BF16 = 0, 1
 EPI_STORE, EPI_STORE_F32, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
-ABI_VERSION = 4
+ABI_VERSION = 5
 
 _lib: Optional[ctypes.CDLL] = None
 
@@ -174,6 +174,29 @@ def paged_attention_simt(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
         _i32(span_row, "span_row"), _i32(span_len, "span_len"), _i32(span_pos, "span_pos"),
         _i32(block_table, "block_table"), max_pages, page_size, num_heads, num_kv_heads, head_dim,
         window, ctypes.c_float(scale), bq, nsplit, _ptr(scratch), _stream()))
+
+
+def attention_tcgen05_supports(head_dim: int, page_size: int) -> bool:
+    return bool(lib().llb_attention_tcgen05_supports(head_dim, page_size))
+
+
+def paged_attention_tcgen05(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
+                            tile_span: torch.Tensor, tile_q0: torch.Tensor, num_tiles: int,
+                            span_row: torch.Tensor, span_len: torch.Tensor, span_pos: torch.Tensor,
+                            block_table: torch.Tensor, max_pages: int, page_size: int,
+                            num_heads: int, num_kv_heads: int, head_dim: int, window: int, scale: float) -> None:
+    """Tensor-core attention of the listed tiles (128 query rows each) over the requests' pages; bf16."""
+    for t in (q, k_cache, v_cache, out):
+        if t.dtype != torch.bfloat16:
+            raise KernelError("attention_tcgen05 takes bfloat16 tensors")
+    T = q.shape[0]
+    num_slots = k_cache.shape[0]
+    _check(lib().llb_paged_attention_tcgen05(
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), T,
+        _i32(tile_span, "tile_span"), _i32(tile_q0, "tile_q0"), num_tiles,
+        _i32(span_row, "span_row"), _i32(span_len, "span_len"), _i32(span_pos, "span_pos"),
+        _i32(block_table, "block_table"), max_pages, page_size, num_slots, num_heads, num_kv_heads, head_dim,
+        window, ctypes.c_float(scale), _ptr(async_error_flag(q.device)), _stream()))
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:

@@ -73,21 +73,27 @@ class StepContext:
     def num_spans(self) -> int:
         return len(self.spans)
 
-    def tiles(self, bq: int):
-        """Tiles of ``bq`` query rows, none crossing a span: ``(tile_span, tile_q0, count)``
-        as device int32 arrays.  Built once per step and tile height."""
-        hit = self._tiles.get(bq)
+    def tiles(self, bq: int, min_len: int = 1, max_len: Optional[int] = None):
+        """Tiles of ``bq`` query rows, none crossing a span, over the spans whose length lies in
+        ``[min_len, max_len]``: ``(tile_span, tile_q0, count)`` as device int32 arrays.  Built once
+        per step for each choice."""
+        key = (bq, min_len, max_len)
+        hit = self._tiles.get(key)
         if hit is not None:
             return hit
-        if self.decode_only or bq >= max(s.length for s in self.spans):
+        chosen = [(i, s) for i, s in enumerate(self.spans)
+                  if s.length >= min_len and (max_len is None or s.length <= max_len)]
+        if len(chosen) == len(self.spans) and bq >= max(s.length for s in self.spans):
             hit = (self.iota, self.zeros, len(self.spans))
+        elif not chosen:
+            hit = (self.iota, self.zeros, 0)
         else:
             ts, tq = [], []
-            for i, s in enumerate(self.spans):
+            for i, s in chosen:
                 for q0 in range(0, s.length, bq):
                     ts.append(i)
                     tq.append(q0)
             arr = torch.from_numpy(np.asarray([ts, tq], dtype=np.int32)).to(self.device, non_blocking=False)
             hit = (arr[0], arr[1], len(ts))
-        self._tiles[bq] = hit
+        self._tiles[key] = hit
         return hit

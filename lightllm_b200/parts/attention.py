@@ -16,6 +16,8 @@ from .base import CacheView, Mixer
 # Shared memory budget per block used to pick the tile height of the CUDA-core kernel.
 _SMEM_BUDGET = 100 * 1024
 _SMEM_LIMIT = 200 * 1024
+# Portions of at least this many rows run on the tensor-core attention kernel (tiles of 128 rows).
+TENSOR_CORE_MIN_ROWS = 32
 
 
 class AttentionMixer(Mixer):
@@ -119,23 +121,34 @@ class AttentionMixer(Mixer):
         """out[t] = attention of query row t over positions <= its own (within the window)."""
         g = cache.group
         window = self.window or 0
+        common = (ctx.span_row, ctx.span_len, ctx.span_pos, ctx.block_tables[g], ctx.max_pages, ctx.page_size,
+                  self.num_heads, self.num_kv_heads, self.head_dim, window, self.scale)
         if ctx.decode_only:
-            bq = 1
             S = ctx.num_spans
             span = ctx.max_context if window == 0 else min(ctx.max_context, window)
             want = max(1, -(-2 * 148 // (S * self.num_kv_heads)))       # blocks to fill the SMs twice
             nsplit = max(1, min(want, -(-span // 128)))
-        else:
-            bq, nsplit = self.tile_height(), 1
-        tile_span, tile_q0, ntiles = ctx.tiles(bq)
+            self._simt(q, cache, out, ctx.tiles(1), common, 1, nsplit)
+            return
+        short_max = None
+        if (q.dtype == torch.bfloat16 and ops.attention_tcgen05_supports(self.head_dim, ctx.page_size)
+                and max(s.length for s in ctx.spans) >= TENSOR_CORE_MIN_ROWS):
+            # long portions go to the tensor cores in tiles of 128 rows; short ones stay on CUDA cores
+            tile_span, tile_q0, ntiles = ctx.tiles(128, min_len=TENSOR_CORE_MIN_ROWS)
+            ops.paged_attention_tcgen05(q, cache.k, cache.v, out, tile_span, tile_q0, ntiles, *common)
+            short_max = TENSOR_CORE_MIN_ROWS - 1
+        bq = self.tile_height()
+        tiles = ctx.tiles(bq, max_len=short_max)
+        if tiles[2] > 0:
+            self._simt(q, cache, out, tiles, common, bq, 1)
+
+    def _simt(self, q, cache, out, tiles, common, bq, nsplit) -> None:
+        tile_span, tile_q0, ntiles = tiles
         scratch = None
         if nsplit > 1:
             scratch = torch.empty(ops.attention_scratch_floats(ntiles, self.num_heads, self.head_dim, bq, nsplit),
                                   dtype=torch.float32, device=q.device)
-        ops.paged_attention_simt(q, cache.k, cache.v, out, tile_span, tile_q0, ntiles,
-                                 ctx.span_row, ctx.span_len, ctx.span_pos, ctx.block_tables[g],
-                                 ctx.max_pages, ctx.page_size, self.num_heads, self.num_kv_heads, self.head_dim,
-                                 window, self.scale, bq, nsplit, scratch)
+        ops.paged_attention_simt(q, cache.k, cache.v, out, tile_span, tile_q0, ntiles, *common, bq, nsplit, scratch)
 
 
 register_part("mixer", "attention", AttentionMixer)

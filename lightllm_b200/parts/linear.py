@@ -20,7 +20,7 @@ from ..csrc import ops
 STORE, STORE_F32, RESIDUAL, SWIGLU = ops.EPI_STORE, ops.EPI_STORE_F32, ops.EPI_RESIDUAL, ops.EPI_SWIGLU
 
 # Rows at or below which the row-streaming CUDA-core kernel is used for bfloat16 (decode).
-SMALL_M = 8
+SMALL_M = 0
 NUM_SMS = 148
 
 

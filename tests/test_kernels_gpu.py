@@ -281,6 +281,46 @@ def test_paged_attention_split(ops, dtype, nsplit, window):
     assert torch.allclose(got, ref, atol=tol, rtol=tol), f"max diff {float((got - ref).abs().max())}"
 
 
+TC_ATTN_CASES = [
+    # Hq, Hkv, hd, page, lens, starts, window
+    (2, 1, 64, 16, [128], [0], None),
+    (14, 2, 64, 16, [300, 40, 129], [0, 77, 500], None),
+    (4, 4, 64, 8, [33, 250], [1000, 3], 100),
+    (6, 2, 128, 32, [200, 64], [5, 130], None),
+    (3, 1, 128, 16, [512], [0], 130),
+    (2, 2, 64, 128, [260], [40], None),
+]
+
+
+@pytest.mark.parametrize("case", TC_ATTN_CASES)
+@pytest.mark.parametrize("spike", [False, True])
+def test_paged_attention_tcgen05(ops, case, spike):
+    Hq, Hkv, hd, page, lens, starts, window = case
+    assert ops.attention_tcgen05_supports(hd, page)
+    s = paged_setup(torch.bfloat16, lens, starts, Hq, Hkv, hd, page, seed=23, spike=spike)
+    # unwritten cache rows are finite in the engine (the pool starts as zeros); keep that here
+    s["kc"] = torch.nan_to_num(s["kc"], nan=3.0)
+    s["vc"] = torch.nan_to_num(s["vc"], nan=-7.0)
+    ts, tq, nt = tiles_for(lens, 128)
+    out = torch.full((s["rows"], Hq * hd), float("nan"), dtype=torch.bfloat16, device=dev())
+    ops.paged_attention_tcgen05(s["q"], s["kc"], s["vc"], out, ts, tq, nt, s["span_row"], s["span_len"], s["span_pos"],
+                                s["bt"], s["max_pages"], page, Hq, Hkv, hd, window or 0, 1.0 / math.sqrt(hd))
+    ops.check_async_errors(dev())
+    ref = attention_reference(s["full"], lens, starts, hd, window).reshape(s["rows"], Hq * hd)
+    got = out.float().cpu()
+    assert not torch.isnan(got).any()
+    assert torch.allclose(got, ref, atol=2e-2, rtol=2e-2), f"max diff {float((got - ref).abs().max())}"
+
+
+def test_attention_tcgen05_refuses_other_shapes(ops):
+    assert not ops.attention_tcgen05_supports(48, 16) and not ops.attention_tcgen05_supports(64, 24)
+    z = torch.zeros((4, 48), dtype=torch.bfloat16, device=dev())
+    i = torch.zeros(1, dtype=torch.int32, device=dev())
+    with pytest.raises(ops.KernelError, match="not supported"):
+        ops.paged_attention_tcgen05(z, z.view(4, 1, 48), z.view(4, 1, 48), z, i, i, 1, i, i, i, i.view(1, 1), 1, 16,
+                                    1, 1, 48, 0, 1.0)
+
+
 def test_argmax_lowest_index_on_ties(ops):
     V = 151937
     x = rnd((5, V), torch.float32, 30)

@@ -19,7 +19,7 @@ pytestmark = pytest.mark.gpu
 # activations carry 8 bits of mantissa through every layer.
 ATOL = {"float32": 1e-4, "bfloat16": 4e-2}
 LENGTHS = {"A": [5, 17, 33, 70, 101, 64, 49, 90], "B": [3, 9, 40, 70, 129, 200, 65, 96],
-           "C": [4, 21, 47, 70, 150, 260, 80, 111]}
+           "C": [4, 21, 47, 70, 150, 260, 80, 111], "D": [3, 40, 131, 300, 129, 700, 64, 257]}
 
 
 def make_sequences(name, seed):
@@ -44,15 +44,15 @@ def build_trace(name):
         if len(toks) > 2:
             tr.last_one_by_one(f"t{rid}")
     for i, rid in enumerate(seqs):
-        tr.portions(f"p{rid}", [[16, 7, 2, 5, 3, 2], [2, 2, 9, 31, 4], [13, 2, 64, 3]][i % 3])
+        tr.portions(f"p{rid}", [[16, 7, 2, 5, 3, 2], [2, 2, 9, 31, 4], [13, 2, 64, 3], [200, 33, 2, 129]][i % 4])
     single_max = tr.max_tokens
     mixed_ids = [f"m{rid}" for rid in seqs]
     prompt_len = {f"m{rid}": max(2, len(toks) - 12) if len(toks) > 14 else len(toks) for rid, toks in seqs.items()}
-    tr.mixed(mixed_ids, prompt_len, seed=5)
+    tr.mixed(mixed_ids, prompt_len, seed=5, sizes=(2, 3, 7, 16, 40, 130) if name == "D" else (2, 3, 5, 7, 16))
     return tr, seqs
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_replay_all_regimes(name, dtype, tmp_path):
     model_dir = str(tmp_path / "model")

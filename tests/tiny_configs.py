@@ -23,8 +23,16 @@ TINY_C = {
     "tie_word_embeddings": False, "max_position_embeddings": 384, "use_sliding_window": True,
     "sliding_window": 20, "max_window_layers": 1, "hidden_act": "silu",
 }
-PAGE_SIZE = {"A": 16, "B": 8, "C": 16}
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+# D has heads of 64 (the tensor-core attention path in bfloat16), groups of 3 and a window on its last layer.
+TINY_D = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 2, "hidden_size": 136, "num_attention_heads": 6, "num_key_value_heads": 2,
+    "head_dim": 64, "intermediate_size": 344, "vocab_size": 1537, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
+    "tie_word_embeddings": True, "max_position_embeddings": 1024, "use_sliding_window": True,
+    "sliding_window": 150, "max_window_layers": 1, "hidden_act": "silu",
+}
+PAGE_SIZE = {"A": 16, "B": 8, "C": 16, "D": 16}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
 
 
 def config(name):

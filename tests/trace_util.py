@@ -72,7 +72,8 @@ class Trace:
             i += 1
             self.step([(rid, c, range(c))], end=[rid] if at == n else [])
 
-    def mixed(self, rids: Sequence[str], prompt_len: Dict[str, int], seed: int, max_live: int = 4) -> None:
+    def mixed(self, rids: Sequence[str], prompt_len: Dict[str, int], seed: int, max_live: int = 4,
+              sizes: Sequence[int] = (2, 3, 5, 7, 16)) -> None:
         """Up to ``max_live`` requests at a time: portions of prompts (2..16 tokens) beside single
         decoded tokens; a request sometimes sits a step out; new ones start as others end."""
         rng = random.Random(seed)
@@ -88,7 +89,7 @@ class Trace:
                 if len(live) > 1 and rng.random() < 0.2:
                     continue                                   # left out of this step
                 if at < prompt_len[rid]:
-                    c = min(rng.choice([2, 3, 5, 7, 16]), prompt_len[rid] - at)
+                    c = min(rng.choice(list(sizes)), prompt_len[rid] - at)
                     if prompt_len[rid] - at - c == 1:
                         c += 1
                     feeds.append((rid, c, [c - 1] if rng.random() < 0.5 or at + c == prompt_len[rid] else []))
