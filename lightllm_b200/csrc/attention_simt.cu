@@ -288,3 +288,57 @@ LLB_EXPORT int llb_paged_attention(const void* q, const void* k_cache, const voi
     if (dtype == LLB_BF16) return launch_attention<__nv_bfloat16>(p, num_tiles, stream);
     return llb_fail("attention: unknown dtype %d", dtype);
 }
+
+// ---------------------------------------------------------------------------------------------
+// The same attention for callers that cannot allocate: the scratch of the splits lives in this
+// file.  See attention_noalloc.h for who needs this, the size limit and the rules of use.
+// ---------------------------------------------------------------------------------------------
+#include "attention_noalloc.h"
+
+// In device code this name is the array.  In host code it is only a handle for the runtime's
+// symbol functions, never an address to hand to a kernel.
+static __device__ __align__(256) float g_noalloc_scratch[LLB_NOALLOC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int NOALLOC_MAX_DEVICES = 64;
+float* g_noalloc_scratch_addr[NOALLOC_MAX_DEVICES] = {};   // device address of the array, per device
+
+// Once per device, with that device current: ask the runtime where the array lives on it.
+int noalloc_scratch(float** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return llb_fail("attention_noalloc: cudaGetDevice failed: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return llb_fail("attention_noalloc: device index %d is out of range", dev);
+    if (g_noalloc_scratch_addr[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess || p == nullptr)
+            return llb_fail("attention_noalloc: cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(e));
+        g_noalloc_scratch_addr[dev] = (float*)p;
+    }
+    *out = g_noalloc_scratch_addr[dev];
+    return 0;
+}
+}  // namespace
+
+LLB_EXPORT long long llb_noalloc_scratch_floats(void) { return LLB_NOALLOC_SCRATCH_FLOATS; }
+
+LLB_EXPORT int llb_paged_attention_noalloc(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                           int dtype, const int* tile_span, const int* tile_q0, int num_tiles,
+                                           const int* span_row, const int* span_len, const int* span_pos,
+                                           const int* block_table, int max_pages, int page_size, int Hq, int Hkv,
+                                           int hd, int window, float scale, int BQ, int nsplit, cudaStream_t stream) {
+    if (num_tiles == 0) return 0;
+    LLB_REQUIRE(num_tiles > 0 && Hq > 0 && hd > 0 && BQ > 0 && nsplit >= 1, "attention_noalloc: bad sizes");
+    const long long need = llb_attention_scratch_floats(num_tiles, Hq, hd, BQ, nsplit);
+    LLB_REQUIRE(need <= (long long)LLB_NOALLOC_SCRATCH_FLOATS,
+                "attention_noalloc: %d tiles x %d heads x %d rows x %d splits x (head_dim %d + 2) needs %lld floats of "
+                "scratch; the built-in scratch holds %lld. Use fewer splits or the entry point that takes scratch",
+                num_tiles, Hq, BQ, nsplit, hd, need, (long long)LLB_NOALLOC_SCRATCH_FLOATS);
+    float* scratch = nullptr;
+    int rc = noalloc_scratch(&scratch);
+    if (rc) return rc;
+    return llb_paged_attention(q, k_cache, v_cache, out, dtype, tile_span, tile_q0, num_tiles, span_row, span_len,
+                               span_pos, block_table, max_pages, page_size, Hq, Hkv, hd, window, scale, BQ, nsplit,
+                               scratch, stream);
+}
