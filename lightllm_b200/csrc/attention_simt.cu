@@ -217,6 +217,234 @@ __global__ void attention_merge_kernel(AttnParams p) {
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Decode: one query row per tile (BQ == 1).  No block-wide barrier inside the key loop: each warp
+// streams its own 32-key tiles of the split (lane = key for the scores, lane = pair of dimensions for
+// the values), reads keys with 16-byte loads straight from the pages, and keeps (m, l, acc) of the
+// G heads of the group in registers.  The four warps are merged through shared memory at the end.
+// ---------------------------------------------------------------------------------------------
+template <typename T> struct Vec16;
+template <> struct Vec16<float> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ void load(const float* p, float (&f)[4]) {
+        const float4 v = *reinterpret_cast<const float4*>(p);
+        f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+    }
+    static __device__ __forceinline__ void load2(const float* p, float& a, float& b) {
+        const float2 v = *reinterpret_cast<const float2*>(p);
+        a = v.x; b = v.y;
+    }
+};
+template <> struct Vec16<__nv_bfloat16> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&f)[8]) {
+        const uint4 v = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 t = __bfloat1622float2(h[i]);
+            f[2 * i] = t.x; f[2 * i + 1] = t.y;
+        }
+    }
+    static __device__ __forceinline__ void load2(const __nv_bfloat16* p, float& a, float& b) {
+        const float2 t = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+        a = t.x; b = t.y;
+    }
+};
+
+template <typename T, int GMAX, int NPMAX>
+__global__ void __launch_bounds__(NWARPS * 32) paged_decode_kernel(AttnParams p) {
+    extern __shared__ float smem[];
+    constexpr int VEC = Vec16<T>::N;
+    const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int G = p.Hq / p.Hkv;
+    const int hd = p.hd;
+    float* Qs = smem;                                   // [G][hd]
+    float* Ps = Qs + G * hd;                            // [NWARPS][GMAX][32]
+    float* Wacc = Ps + NWARPS * GMAX * 32;              // [NWARPS][G][hd]
+    float* Wml = Wacc + NWARPS * G * hd;                // [NWARPS][G][2]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int span = p.tile_span[tile];
+    const int q0 = p.tile_q0[tile];
+    const int row0 = p.span_row[span] + q0;
+    const int qpos = p.span_pos[span] + q0;
+    const int* bt = p.block_table + (size_t)span * p.max_pages;
+    const T* q = (const T*)p.q;
+    const T* kc = (const T*)p.k_cache;
+    const T* vc = (const T*)p.v_cache;
+
+    const int hi = qpos + 1;
+    const int lo = p.window > 0 ? max(0, qpos - p.window + 1) : 0;
+    int klo = lo, khi = hi;
+    if (p.nsplit > 1) {
+        int chunk = (hi - lo + p.nsplit - 1) / p.nsplit;
+        chunk = ((chunk + BK - 1) / BK) * BK;
+        klo = lo + split * chunk;
+        khi = min(hi, klo + chunk);
+    }
+    for (int i = threadIdx.x; i < G * hd; i += blockDim.x)
+        Qs[i] = llb_to_float(q[((size_t)row0 * p.Hq + kvh * G) * hd + i]);
+    __syncthreads();
+
+    float m[GMAX], l[GMAX], acc[GMAX][NPMAX][2];
+#pragma unroll
+    for (int g = 0; g < GMAX; ++g) {
+        m[g] = -INFINITY;
+        l[g] = 0.0f;
+#pragma unroll
+        for (int n = 0; n < NPMAX; ++n) acc[g][n][0] = acc[g][n][1] = 0.0f;
+    }
+    float* myP = Ps + warp * GMAX * 32;
+    const size_t row_stride = (size_t)p.Hkv * hd;
+
+    for (int kb = klo + warp * BK; kb < khi; kb += NWARPS * BK) {
+        const int kpos = kb + lane;
+        const bool valid = kpos < khi;
+        size_t slot = 0;
+        if (valid) slot = (size_t)bt[kpos / p.page_size] * p.page_size + (kpos % p.page_size);
+        float dot[GMAX];
+#pragma unroll
+        for (int g = 0; g < GMAX; ++g) dot[g] = 0.0f;
+        if (valid) {
+            const T* kr = kc + slot * row_stride + (size_t)kvh * hd;
+#pragma unroll 4
+            for (int c = 0; c < hd; c += VEC) {
+                float kf[VEC];
+                Vec16<T>::load(kr + c, kf);
+#pragma unroll
+                for (int g = 0; g < GMAX; ++g) {
+                    if (g < G) {
+                        const float* qv = Qs + g * hd + c;
+#pragma unroll
+                        for (int e = 0; e < VEC; ++e) dot[g] = fmaf(qv[e], kf[e], dot[g]);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < GMAX; ++g) {
+            if (g < G) {
+                const float sc = valid ? dot[g] * p.scale : -INFINITY;
+                const float m_new = fmaxf(m[g], llb_warp_max(sc));      // finite: the tile has a valid key
+                const float pr = valid ? expf(sc - m_new) : 0.0f;
+                const float corr = (m[g] == -INFINITY) ? 0.0f : expf(m[g] - m_new);
+                l[g] = l[g] * corr + llb_warp_sum(pr);
+                m[g] = m_new;
+                myP[g * 32 + lane] = pr;
+#pragma unroll
+                for (int n = 0; n < NPMAX; ++n) {
+                    acc[g][n][0] *= corr;
+                    acc[g][n][1] *= corr;
+                }
+            }
+        }
+        __syncwarp();
+        const int nkeys = min(BK, khi - kb);
+#pragma unroll 4
+        for (int j = 0; j < nkeys; ++j) {
+            const size_t sj = __shfl_sync(0xffffffffu, slot, j);
+            const T* vr = vc + sj * row_stride + (size_t)kvh * hd;
+#pragma unroll
+            for (int n = 0; n < NPMAX; ++n) {
+                const int d = n * 64 + 2 * lane;
+                if (d < hd) {
+                    float v0, v1;
+                    Vec16<T>::load2(vr + d, v0, v1);
+#pragma unroll
+                    for (int g = 0; g < GMAX; ++g) {
+                        if (g < G) {
+                            const float pj = myP[g * 32 + j];
+                            acc[g][n][0] = fmaf(pj, v0, acc[g][n][0]);
+                            acc[g][n][1] = fmaf(pj, v1, acc[g][n][1]);
+                        }
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    }
+
+    // Merge the four warps.
+#pragma unroll
+    for (int g = 0; g < GMAX; ++g) {
+        if (g < G) {
+#pragma unroll
+            for (int n = 0; n < NPMAX; ++n) {
+                const int d = n * 64 + 2 * lane;
+                if (d < hd) {
+                    Wacc[(warp * G + g) * hd + d] = acc[g][n][0];
+                    Wacc[(warp * G + g) * hd + d + 1] = acc[g][n][1];
+                }
+            }
+            if (lane == 0) {
+                Wml[(warp * G + g) * 2] = m[g];
+                Wml[(warp * G + g) * 2 + 1] = l[g];
+            }
+        }
+    }
+    __syncthreads();
+    const size_t base = (((size_t)tile * p.Hkv + kvh) * p.nsplit + split) * G;
+    for (int i = threadIdx.x; i < G * hd; i += blockDim.x) {
+        const int g = i / hd, d = i - g * hd;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < NWARPS; ++w) M = fmaxf(M, Wml[(w * G + g) * 2]);
+        float L = 0.0f, a = 0.0f;
+#pragma unroll
+        for (int w = 0; w < NWARPS; ++w) {
+            const float mw = Wml[(w * G + g) * 2];
+            if (mw != -INFINITY) {
+                const float e = expf(mw - M);
+                L += e * Wml[(w * G + g) * 2 + 1];
+                a += e * Wacc[(w * G + g) * hd + d];
+            }
+        }
+        if (p.nsplit == 1) {
+            ((T*)p.out)[((size_t)row0 * p.Hq + kvh * G + g) * hd + d] = llb_from_float<T>(a / L);
+        } else {
+            p.part_acc[(base + g) * hd + d] = a;
+            if (d == 0) {
+                p.part_ml[(base + g) * 2] = M;
+                p.part_ml[(base + g) * 2 + 1] = L;
+            }
+        }
+    }
+}
+
+size_t decode_smem_bytes(int G, int gmax, int hd) {
+    return ((size_t)G * hd + (size_t)NWARPS * gmax * 32 + (size_t)NWARPS * G * hd + (size_t)NWARPS * G * 2) * sizeof(float);
+}
+
+template <typename T, int GMAX>
+int launch_decode_np(const AttnParams& p, dim3 grid, size_t smem, cudaStream_t stream) {
+    if (p.hd <= 64) paged_decode_kernel<T, GMAX, 1><<<grid, NWARPS * 32, smem, stream>>>(p);
+    else if (p.hd <= 128) paged_decode_kernel<T, GMAX, 2><<<grid, NWARPS * 32, smem, stream>>>(p);
+    else paged_decode_kernel<T, GMAX, 4><<<grid, NWARPS * 32, smem, stream>>>(p);
+    return llb_check_launch("paged_decode");
+}
+
+// Whether the decode kernel takes this shape; else the general kernel runs it.
+template <typename T>
+bool decode_eligible(const AttnParams& p) {
+    const int G = p.Hq / p.Hkv;
+    const int gmax = G <= 1 ? 1 : G <= 2 ? 2 : G <= 4 ? 4 : G <= 8 ? 8 : 16;
+    return p.BQ == 1 && G <= 16 && p.hd <= 256 && p.hd % 2 == 0 && (p.hd * sizeof(T)) % 16 == 0 &&
+           ((uintptr_t)p.k_cache % 16 == 0) && ((uintptr_t)p.v_cache % 16 == 0) &&
+           decode_smem_bytes(G, gmax, p.hd) <= 48 * 1024;
+}
+
+template <typename T>
+int launch_decode(const AttnParams& p, int num_tiles, cudaStream_t stream) {
+    const int G = p.Hq / p.Hkv;
+    dim3 grid(num_tiles, p.Hkv, p.nsplit);
+    if (G <= 1) return launch_decode_np<T, 1>(p, grid, decode_smem_bytes(G, 1, p.hd), stream);
+    if (G <= 2) return launch_decode_np<T, 2>(p, grid, decode_smem_bytes(G, 2, p.hd), stream);
+    if (G <= 4) return launch_decode_np<T, 4>(p, grid, decode_smem_bytes(G, 4, p.hd), stream);
+    if (G <= 8) return launch_decode_np<T, 8>(p, grid, decode_smem_bytes(G, 8, p.hd), stream);
+    return launch_decode_np<T, 16>(p, grid, decode_smem_bytes(G, 16, p.hd), stream);
+}
+
 size_t attention_smem_bytes(int BQ, int G, int hd) {
     const size_t nqv = (size_t)BQ * G;
     const size_t floats = 2 * nqv * hd + 2 * nqv + (size_t)BK * (hd | 1) + (size_t)BK * hd + NWARPS * BK;
@@ -236,9 +464,14 @@ int launch_attention(const AttnParams& p, int num_tiles, cudaStream_t stream) {
                                               cudaGetErrorString(e));
         configured = smem;
     }
-    dim3 grid(num_tiles, p.Hkv, p.nsplit);
-    paged_attention_kernel<T><<<grid, NWARPS * 32, smem, stream>>>(p);
-    int rc = llb_check_launch("paged_attention");
+    int rc;
+    if (decode_eligible<T>(p)) {
+        rc = launch_decode<T>(p, num_tiles, stream);
+    } else {
+        dim3 grid(num_tiles, p.Hkv, p.nsplit);
+        paged_attention_kernel<T><<<grid, NWARPS * 32, smem, stream>>>(p);
+        rc = llb_check_launch("paged_attention");
+    }
     if (rc) return rc;
     if (p.nsplit > 1) {
         dim3 mgrid(num_tiles, p.Hq);

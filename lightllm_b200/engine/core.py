@@ -36,6 +36,7 @@ class EngineOptions:
     kv_cache_mb: Optional[float] = None
     max_seqs: int = 64
     device: str = "cuda:0"
+    use_cuda_graphs: bool = True
 
 
 class EngineCore:
@@ -63,7 +64,7 @@ class EngineCore:
             num_pages = [pages_per_seq * opt.max_seqs] * len(layout.groups)
         self.cache = CacheManager(layout, opt.page_size, num_pages, opt.max_seqs, self.max_seq_len,
                                   self.dtype, self.device)
-        self.runner = ModelRunner(self.model, self.cache, opt.max_batch_tokens, opt.max_seqs)
+        self.runner = ModelRunner(self.model, self.cache, opt.max_batch_tokens, opt.max_seqs, opt.use_cuda_graphs)
 
     # The requests' lifetime, as the reference's create_request_state / release_request
     # (src/engine/engine_server.cpp:625-688, 694-717).
@@ -82,7 +83,7 @@ class EngineCore:
     def launch_count(self) -> int:
         """Kernels of the engine's own library launched so far in this process."""
         from ..csrc import ops
-        return ops.launch_count()
+        return ops.launch_count() + self.runner.graph_launches
 
     @property
     def vocab_size(self) -> int:

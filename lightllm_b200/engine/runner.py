@@ -28,7 +28,8 @@ class StepError(ValueError):
 class ModelRunner:
     """Owns the device-side step metadata and runs the model over a batch."""
 
-    def __init__(self, model: Model, cache: CacheManager, max_batch_tokens: int, max_spans: Optional[int] = None):
+    def __init__(self, model: Model, cache: CacheManager, max_batch_tokens: int, max_spans: Optional[int] = None,
+                 use_cuda_graphs: bool = True, max_graphs: int = 64):
         if model.device is None or model.device.type != "cuda":
             raise RuntimeError("the model is not on a CUDA device; the engine has no CPU path")
         self.model = model
@@ -59,6 +60,15 @@ class ModelRunner:
             st = cache.state[ref.state_plane] if ref.state_plane is not None else None
             self.views.append(CacheView(ref.group, k, v, st, ref.owns))
         self.last_h2d_bytes = 0
+        # Decode-only steps are launch-bound, so they are captured into CUDA graphs: one per
+        # (requests, wanted rows, block-table width), captured the second time a shape is seen.
+        self.use_cuda_graphs = bool(use_cuda_graphs) and model.graph_safe()
+        self.max_graphs = max_graphs
+        self._graphs: Dict[tuple, tuple] = {}
+        self._graph_seen: Dict[tuple, int] = {}
+        self._graph_pool = None
+        self.graph_replays = 0
+        self.graph_launches = 0          # kernels launched through graph replays
 
     # ------------------------------------------------------------------------------------------
     def _build_context(self, entries: Sequence[StepEntry]) -> StepContext:
@@ -184,10 +194,38 @@ class ModelRunner:
         each entry's ``want``, as a float32 ``[wanted, vocab]`` tensor on the device (``None`` if
         nothing is wanted).  Afterwards every request holds its new tokens."""
         ctx = self._build_context(entries)
-        logits = self.forward(ctx)
+        if self.use_cuda_graphs and ctx.decode_only:
+            logits = self._forward_graphed(ctx)
+        else:
+            logits = self.forward(ctx)
         for e in entries:
             self.cache.advance(e.seq_id, len(e.tokens))
         return logits
+
+    def _forward_graphed(self, ctx: StepContext) -> Optional[torch.Tensor]:
+        """A decode-only step through a CUDA graph.  The metadata buffer has equal addresses for equal
+        counts, so a graph captured for (requests, wanted rows, block-table width) serves every later
+        step of that shape; only the metadata copy stays outside."""
+        from ..csrc import ops
+        key = (ctx.num_spans, ctx.num_want, ctx.max_pages)
+        hit = self._graphs.get(key)
+        if hit is None:
+            seen = self._graph_seen.get(key, 0) + 1
+            self._graph_seen[key] = seen
+            if seen < 2 or len(self._graphs) >= self.max_graphs:
+                return self.forward(ctx)          # first sight of a shape (also the warm-up), or no room left
+            before = ops.launch_count()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, pool=self._graph_pool):
+                out = self.forward(ctx)
+            if self._graph_pool is None:
+                self._graph_pool = graph.pool()
+            hit = self._graphs[key] = (graph, out, ops.launch_count() - before)
+        graph, out, nodes = hit
+        graph.replay()
+        self.graph_replays += 1
+        self.graph_launches += nodes
+        return None if out is None else out.clone()
 
     def check_device_errors(self) -> None:
         """Raise if a kernel flagged a fault (an id outside the vocabulary reached the device)."""

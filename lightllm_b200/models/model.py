@@ -58,6 +58,11 @@ class Model:
             if not isinstance(p, Block):
                 p.bind(tensors, dtype, device)
 
+    def graph_safe(self) -> bool:
+        """Whether every part's forward only launches kernels whose arguments are fixed by the step's
+        counts (no host-side branching on the batch's contents), so a step can be captured in a CUDA graph."""
+        return all(getattr(p, "graph_safe", False) for p in self.parts() if not isinstance(p, Block))
+
     def weight_bytes(self) -> int:
         """Bytes of the tensors a step reads (a tied table counts once)."""
         seen, total = set(), 0

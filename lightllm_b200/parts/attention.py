@@ -31,6 +31,8 @@ class AttentionMixer(Mixer):
     q/k/v biases are loaded and added, a token sees its own key, every portion is causal, and
     ``window`` limits a query to the latest ``window`` keys (itself included)."""
 
+    graph_safe = True
+
     def __init__(self, prefix: str, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position: Optional[PartSpec] = None, qkv_bias: bool = True, out_bias: bool = False,
                  window: Optional[int] = None, scale: Optional[float] = None,
@@ -125,7 +127,8 @@ class AttentionMixer(Mixer):
                   self.num_heads, self.num_kv_heads, self.head_dim, window, self.scale)
         if ctx.decode_only:
             S = ctx.num_spans
-            span = ctx.max_context if window == 0 else min(ctx.max_context, window)
+            bound = ctx.max_pages * ctx.page_size          # the same for every step of this shape
+            span = bound if window == 0 else min(bound, window)
             want = max(1, -(-2 * 148 // (S * self.num_kv_heads)))       # blocks to fill the SMs twice
             nsplit = max(1, min(want, -(-span // 128)))
             self._simt(q, cache, out, ctx.tiles(1), common, 1, nsplit)

@@ -34,6 +34,9 @@ from ..weights import WeightSpec
 
 class Part:
     role = "part"
+    # True when forward() only launches kernels whose arguments are fixed by the step's counts; a model of
+    # such parts has its decode steps captured in CUDA graphs.  Parts that branch on the host say False.
+    graph_safe = False
 
     def weight_specs(self) -> List[WeightSpec]:
         return []

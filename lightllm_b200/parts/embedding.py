@@ -16,6 +16,8 @@ class TokenEmbedding(Part):
     """``h[t, :] = table[id_t, :]`` into the float32 residual stream (src/ops/embedding.cu:9-18).
     An id outside the vocabulary is an error, not a clamp to 0 as in the reference."""
 
+    graph_safe = True
+
     role = "embedding"
 
     def __init__(self, prefix: str, vocab_size: int, hidden_size: int, weight_name: str = "weight"):
@@ -39,6 +41,8 @@ class LMHead(Part):
     """``logits = x @ W^T`` in float32.  ``weight_name`` is the head's own matrix, or the
     embedding table's name when the two are tied (the reference always uses the table,
     src/engine/engine_server.cpp:1968,2042, whatever ``tie_word_embeddings`` says)."""
+
+    graph_safe = True
 
     role = "head"
 

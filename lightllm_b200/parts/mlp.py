@@ -19,6 +19,8 @@ class GatedMLP(FeedForward):
     produces each (gate, up) pair in adjacent columns and the epilogue writes only
     ``silu(gate) * up``; the down projection adds into the residual stream in its epilogue."""
 
+    graph_safe = True
+
     def __init__(self, prefix: str, hidden_size: int, intermediate_size: int, activation: str = "silu",
                  bias: bool = False, names: Optional[Dict[str, str]] = None):
         if activation != "silu":

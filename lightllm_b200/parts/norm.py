@@ -15,6 +15,8 @@ class RMSNorm(Norm):
     """``y = x / sqrt(mean(x^2) + eps) * weight`` with the statistics in float32
     (src/ops/norm.cu:19-23,48-54).  ``weight_name`` is the full checkpoint name."""
 
+    graph_safe = True
+
     def __init__(self, prefix: str, hidden_size: int, eps: float, weight_name: str = "weight"):
         self.name = f"{prefix}.{weight_name}" if prefix else weight_name
         self.hidden_size = hidden_size

@@ -20,6 +20,8 @@ class RotaryEmbedding(PositionEncoding):
     ``style`` is ``"neox"`` (half-split pairs) or ``"interleaved"`` (adjacent pairs);
     ``rotary_dim`` below ``head_dim`` leaves the upper dimensions unrotated."""
 
+    graph_safe = True
+
     def __init__(self, prefix: str, head_dim: int, theta: float, rotary_dim: Optional[int] = None,
                  style: str = "neox"):
         rotary_dim = head_dim if rotary_dim is None else rotary_dim
@@ -41,6 +43,8 @@ class RotaryEmbedding(PositionEncoding):
 
 class NoPositionEncoding(PositionEncoding):
     """Leaves q and k as they are."""
+
+    graph_safe = True
 
     def __init__(self, prefix: str = ""):
         pass

@@ -242,6 +242,13 @@ ATTN_CASES = [
     (5, 5, 48, 16, [1, 30, 3], [100, 17, 19], 20, 8),
     (6, 3, 80, 4, [2, 64], [62, 0], 7, 2),
     (8, 1, 128, 16, [7, 1], [9, 500], None, 4),
+    # one query row per tile: the decode kernel
+    (14, 2, 64, 16, [1, 1, 1], [300, 15, 0], None, 1),
+    (3, 1, 32, 8, [1, 1], [70, 5], None, 1),
+    (5, 5, 48, 16, [1, 1, 1], [100, 17, 19], 20, 1),
+    (16, 1, 128, 16, [1, 1], [130, 31], None, 1),
+    (8, 2, 256, 32, [1], [200], 64, 1),
+    (6, 3, 20, 4, [1, 1], [62, 3], None, 1),          # head size the 16-byte loads refuse: general kernel
 ]
 
 
