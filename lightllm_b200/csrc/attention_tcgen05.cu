@@ -114,6 +114,69 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ bool key_visible(int kp, int qpos, int hi, int lo, int window) {
+    return kp <= qpos && kp < hi && kp >= lo && (window <= 0 || qpos - kp < window);
+}
+// Largest raw score of this thread's row among the visible keys of the tile.
+template <bool MASKED>
+__device__ __forceinline__ float row_max(uint32_t tmem_s, int kt, int qpos, int hi, int lo, int window) {
+    float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+        float s[32];
+        tmem_ld32(tmem_s + c * 32, s);
+        if (MASKED) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                if (!key_visible(kt + c * 32 + i, qpos, hi, lo, window)) s[i] = -INFINITY;
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+            m0 = fmaxf(m0, s[i]); m1 = fmaxf(m1, s[i + 1]); m2 = fmaxf(m2, s[i + 2]); m3 = fmaxf(m3, s[i + 3]);
+        }
+    }
+    return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+}
+// p = 2^(s*c - m) of the row's 128 scores, written as bf16 into the swizzled A-operand tiles; returns
+// their sum (float, before rounding).  Row r, 16-byte chunk q of a 128-byte row lands at chunk q ^ (r & 7).
+template <bool MASKED>
+__device__ __forceinline__ float row_probs(uint32_t tmem_s, uint8_t* p_s, int r, float c_scale, float m_use, int kt,
+                                           int qpos, int hi, int lo, int window) {
+    float l0 = 0.0f, l1 = 0.0f;
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+        float s[32];
+        tmem_ld32(tmem_s + c * 32, s);
+        if (MASKED) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                if (!key_visible(kt + c * 32 + i, qpos, hi, lo, window)) s[i] = -INFINITY;
+        }
+        uint8_t* prow = p_s + (c >> 1) * (128 * 128) + (uint32_t)r * 128;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float p0 = fast_exp2(fmaf(s[q * 8 + 2 * e], c_scale, -m_use));
+                const float p1 = fast_exp2(fmaf(s[q * 8 + 2 * e + 1], c_scale, -m_use));
+                l0 += p0;
+                l1 += p1;
+                const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                w[e] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+            const int chunk = ((c & 1) * 4 + q) ^ (r & 7);
+            *reinterpret_cast<uint4*>(prow + chunk * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    }
+    return l0 + l1;
+}
+
 struct AttnTcParams {
     __nv_bfloat16* out;        // [T, Hq, HD]
     const int* tile_span;
@@ -124,6 +187,7 @@ struct AttnTcParams {
     const int* block_table;    // [S, max_pages]
     int max_pages, page_size, Hq, Hkv, window, num_slots;
     float scale_log2e;         // scale * log2(e): scores are kept in base-2 units
+    uint32_t dynamic_smem_bytes;
     int* error_flag;
 };
 
@@ -134,18 +198,28 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     constexpr int KB = HD / 64;                       // 64-element blocks along the head dimension
     constexpr uint32_t TILE_BYTES = 128 * 128;        // a [128 rows][64 elements] bf16 tile
     constexpr uint32_t TMEM_COLS = 256;               // S: columns 0..127, P V: columns 128..128+HD-1
+    // Barriers live in static shared memory; the operand tiles in dynamic shared memory, aligned to
+    // 1024 bytes for the swizzle.  The sizes are chosen so that two blocks of the head-64 kernel fit
+    // in one SM, which leaves no room to spare: the fit is checked before anything is copied.
+    __shared__ __align__(8) uint64_t bars[5];
+    __shared__ uint32_t tmem_slot_s;
+    __shared__ int abort_s;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* q_s = smem;                              // KB tiles
     uint8_t* k_s = q_s + KB * TILE_BYTES;             // 2 stages x KB tiles
     uint8_t* v_s = k_s + 2 * KB * TILE_BYTES;         // 2 stages x KB tiles
     uint8_t* p_s = v_s + 2 * KB * TILE_BYTES;         // 2 tiles (keys 0..63, 64..127)
-    uint64_t* bar_q = (uint64_t*)(p_s + 2 * TILE_BYTES);
-    uint64_t* bar_kv = bar_q + 1;                     // [2]
-    uint64_t* bar_s = bar_kv + 2;
-    uint64_t* bar_pv = bar_s + 1;
-    uint32_t* tmem_slot = (uint32_t*)(bar_pv + 1);
-    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    uint64_t* bar_q = &bars[0];
+    uint64_t* bar_kv = &bars[1];                      // [2]
+    uint64_t* bar_s = &bars[3];
+    uint64_t* bar_pv = &bars[4];
+    uint32_t* tmem_slot = &tmem_slot_s;
+    volatile int* abort_flag = &abort_s;
+    if (p_s + 2 * TILE_BYTES > smem_raw + p.dynamic_smem_bytes) {     // uniform over the block
+        if (threadIdx.x == 0 && p.error_flag) atomicExch(p.error_flag, 3);
+        return;
+    }
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile = blockIdx.x, head = blockIdx.y;
@@ -247,47 +321,19 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
         // Softmax of this thread's row over the 128 keys of the tile, in two passes over tensor
-        // memory (maximum first, then the probabilities), 32 columns at a time.
-        auto masked = [&](float raw, int kp) -> float {
-            const bool vis = kp <= qpos && kp < hi && kp >= lo && (p.window <= 0 || qpos - kp < p.window);
-            return vis ? raw * p.scale_log2e : -INFINITY;
-        };
-        float m_tile = -INFINITY;
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-            float s[32];
-            tmem_ld32(tmem_s + c * 32, s);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) m_tile = fmaxf(m_tile, masked(s[i], kt + c * 32 + i));
-        }
+        // memory (maximum first, then the probabilities), 32 columns at a time.  Tiles that lie wholly
+        // below the diagonal and inside the window of every row of the block skip the masking.
+        const bool interior = (kt + BKV - 1 <= pos0) && (p.window <= 0 || (pos0 + BQ - 1) - kt < p.window);
+        float m_tile;
+        if (interior) m_tile = row_max<false>(tmem_s, kt, qpos, hi, lo, p.window);
+        else m_tile = row_max<true>(tmem_s, kt, qpos, hi, lo, p.window);
+        m_tile *= p.scale_log2e;                                      // the scale is positive
         const float m_new = fmaxf(m_run, m_tile);
         const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;      // nothing visible yet: all p are 0
-        const float corr = (m_run == -INFINITY) ? 0.0f : exp2f(m_run - m_use);
-        float l_tile = 0.0f;
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-            float s[32];
-            tmem_ld32(tmem_s + c * 32, s);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) s[i] = masked(s[i], kt + c * 32 + i);
-            // P as the A operand: row r, 16-byte chunk q of the 128-byte row lands at chunk q ^ (r & 7).
-            uint8_t* prow = p_s + (c >> 1) * TILE_BYTES + (uint32_t)r * 128;
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                uint32_t w[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float p0 = exp2f(s[q * 8 + 2 * e] - m_use);
-                    const float p1 = exp2f(s[q * 8 + 2 * e + 1] - m_use);
-                    const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                    // the sum uses the rounded values, so that numerator and denominator agree
-                    l_tile += __bfloat162float(h.x) + __bfloat162float(h.y);
-                    w[e] = *reinterpret_cast<const uint32_t*>(&h);
-                }
-                const int chunk = ((c & 1) * 4 + q) ^ (r & 7);
-                *reinterpret_cast<uint4*>(prow + chunk * 16) = make_uint4(w[0], w[1], w[2], w[3]);
-            }
-        }
+        const float corr = (m_run == -INFINITY) ? 0.0f : fast_exp2(m_run - m_use);
+        float l_tile;
+        if (interior) l_tile = row_probs<false>(tmem_s, p_s, r, p.scale_log2e, m_use, kt, qpos, hi, lo, p.window);
+        else l_tile = row_probs<true>(tmem_s, p_s, r, p.scale_log2e, m_use, kt, qpos, hi, lo, p.window);
         l_run = l_run * corr + l_tile;
         m_run = m_new;
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // P is read by the tensor core
@@ -378,7 +424,8 @@ template <int HD>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnTcParams& p, int num_tiles,
            cudaStream_t stream) {
     constexpr int KB = HD / 64;
-    constexpr size_t smem = (size_t)(KB + 4 * KB + 2) * 128 * 128 + 6 * 8 + 16 + 1024;
+    // tiles + what aligning to 1024 bytes can cost after the 48 bytes of static shared memory
+    constexpr size_t smem = (size_t)(KB + 4 * KB + 2) * 128 * 128 + 976;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -388,7 +435,9 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
         configured = true;
     }
     dim3 grid(num_tiles, p.Hq);
-    attention_tcgen05_kernel<HD><<<grid, NUM_THREADS, smem, stream>>>(mq, mk, mv, p);
+    AttnTcParams pp = p;
+    pp.dynamic_smem_bytes = (uint32_t)smem;
+    attention_tcgen05_kernel<HD><<<grid, NUM_THREADS, smem, stream>>>(mq, mk, mv, pp);
     return llb_check_launch("attention_tcgen05");
 }
 

@@ -11,9 +11,10 @@
 // Epilogues: store, store float, add into the float residual stream (with split-K: atomic adds),
 // SiLU(gate)*up on interleaved weight rows; the bias is added first.
 //
-// One block computes one 128 x BN tile.  Warp 0 issues TMA loads through a ring of STAGES shared
-// memory stages, warp 1 allocates TMEM and issues the MMAs, warps 2..5 run the epilogue (each
-// reads the 32 TMEM lanes it may access).  Every wait on an mbarrier is bounded in time: when it
+// One block computes one 128 x BN tile (two blocks share an SM, so that one's epilogue overlaps the
+// other's main loop).  Warp 0 issues TMA loads through a ring of STAGES shared memory stages, warp 1
+// allocates TMEM and issues the MMAs, warps 2..5 run the epilogue (each reads the 32 TMEM lanes it may
+// access) and write whole 16-byte vectors per thread.  Every wait on an mbarrier is bounded in time: when it
 // runs out the kernel raises a flag in global memory, lets every role fall through to the common
 // exit, frees its TMEM and returns; the host reports the flag as an error.
 #include <cuda.h>
@@ -28,7 +29,7 @@ namespace {
 constexpr int TILE_M = 128;       // rows of the A role = TMEM lanes
 constexpr int TILE_K = 64;        // bf16 elements per stage row = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
-constexpr int STAGES = 4;
+constexpr int STAGES = 3;
 constexpr int NUM_THREADS = 192;
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // 2 s
 
@@ -142,7 +143,7 @@ struct GemmParams {
 };
 
 template <int BN, int EPI, bool SWAP>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(NUM_THREADS, 2)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const GemmParams p) {
     constexpr uint32_t A_BYTES = TILE_M * TILE_K * 2;
@@ -234,33 +235,84 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     if (CHUNK == 32) tmem_ld32(taddr, r); else tmem_ld16(taddr, r);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                     if (!SWAP) {
-                        // row = token m, columns = output features n
+                        // row = token m, columns = output features n: 32 consecutive columns per thread
                         const int m = a_row0 + row;
                         const int nb = b_row0 + c0;
-                        if (m < p.M) {
-                            if (EPI == LLB_EPI_SWIGLU) {
-                                __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)m * (p.N / 2);
+                        if (m < p.M && nb < p.N) {
+                            float v[CHUNK];
 #pragma unroll
-                                for (int j = 0; j < CHUNK; j += 2) {
-                                    const int n = nb + j;
-                                    if (n + 1 < p.N) {
-                                        float g = __uint_as_float(r[j]), u = __uint_as_float(r[j + 1]);
-                                        if (p.bias) { g += p.bias[n]; u += p.bias[n + 1]; }
-                                        o[n >> 1] = __float2bfloat16_rn(llb_silu(g) * u);
+                            for (int j = 0; j < CHUNK; ++j) v[j] = __uint_as_float(r[j]);
+                            const bool full = nb + CHUNK <= p.N;
+                            if (p.bias && blockIdx.z == 0) {
+#pragma unroll
+                                for (int j = 0; j < CHUNK; ++j)
+                                    if (full || nb + j < p.N) v[j] += p.bias[nb + j];
+                            }
+                            if (EPI == LLB_EPI_SWIGLU) {
+                                __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)m * (p.N / 2) + (nb >> 1);
+                                if (full && (p.N % 16) == 0) {     // 16-byte stores of 8 outputs
+#pragma unroll
+                                    for (int j = 0; j < CHUNK; j += 16) {
+                                        uint32_t w[4];
+#pragma unroll
+                                        for (int e = 0; e < 4; ++e) {
+                                            const __nv_bfloat162 h = __floats2bfloat162_rn(
+                                                llb_silu(v[j + 4 * e]) * v[j + 4 * e + 1],
+                                                llb_silu(v[j + 4 * e + 2]) * v[j + 4 * e + 3]);
+                                            w[e] = *reinterpret_cast<const uint32_t*>(&h);
+                                        }
+                                        *reinterpret_cast<uint4*>(o + (j >> 1)) = make_uint4(w[0], w[1], w[2], w[3]);
                                     }
+                                } else {
+#pragma unroll
+                                    for (int j = 0; j < CHUNK; j += 2)
+                                        if (nb + j + 1 < p.N) o[j >> 1] = __float2bfloat16_rn(llb_silu(v[j]) * v[j + 1]);
+                                }
+                            } else if (EPI == LLB_EPI_STORE) {
+                                __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)m * p.N + nb;
+                                if (full && (p.N % 8) == 0) {
+#pragma unroll
+                                    for (int j = 0; j < CHUNK; j += 8) {
+                                        uint32_t w[4];
+#pragma unroll
+                                        for (int e = 0; e < 4; ++e) {
+                                            const __nv_bfloat162 h = __floats2bfloat162_rn(v[j + 2 * e], v[j + 2 * e + 1]);
+                                            w[e] = *reinterpret_cast<const uint32_t*>(&h);
+                                        }
+                                        *reinterpret_cast<uint4*>(o + j) = make_uint4(w[0], w[1], w[2], w[3]);
+                                    }
+                                } else {
+#pragma unroll
+                                    for (int j = 0; j < CHUNK; ++j)
+                                        if (nb + j < p.N) o[j] = __float2bfloat16_rn(v[j]);
+                                }
+                            } else if (EPI == LLB_EPI_STORE_F32) {
+                                float* o = (float*)p.out + (size_t)m * p.N + nb;
+                                if (full && (p.N % 4) == 0) {
+#pragma unroll
+                                    for (int j = 0; j < CHUNK; j += 4)
+                                        *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                                } else {
+#pragma unroll
+                                    for (int j = 0; j < CHUNK; ++j)
+                                        if (nb + j < p.N) o[j] = v[j];
                                 }
                             } else {
+                                float* o = p.residual + (size_t)m * p.N + nb;
+                                if (gridDim.z == 1 && full && (p.N % 4) == 0) {
 #pragma unroll
-                                for (int j = 0; j < CHUNK; ++j) {
-                                    const int n = nb + j;
-                                    if (n < p.N) {
-                                        float v = __uint_as_float(r[j]);
-                                        if (p.bias && blockIdx.z == 0) v += p.bias[n];
-                                        const size_t idx = (size_t)m * p.N + n;
-                                        if (EPI == LLB_EPI_STORE) ((__nv_bfloat16*)p.out)[idx] = __float2bfloat16_rn(v);
-                                        else if (EPI == LLB_EPI_STORE_F32) ((float*)p.out)[idx] = v;
-                                        else if (gridDim.z == 1) p.residual[idx] += v;
-                                        else atomicAdd(p.residual + idx, v);
+                                    for (int j = 0; j < CHUNK; j += 4) {
+                                        float4 t = *reinterpret_cast<float4*>(o + j);
+                                        t.x += v[j]; t.y += v[j + 1]; t.z += v[j + 2]; t.w += v[j + 3];
+                                        *reinterpret_cast<float4*>(o + j) = t;
+                                    }
+                                } else {
+#pragma unroll
+                                    for (int j = 0; j < CHUNK; ++j) {
+                                        if (nb + j < p.N) {
+                                            if (gridDim.z == 1) o[j] += v[j];
+                                            else atomicAdd(o + j, v[j]);
+                                        }
                                     }
                                 }
                             }
