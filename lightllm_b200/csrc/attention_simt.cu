@@ -180,9 +180,13 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_kernel(AttnParams
 }
 
 // Merge of the split partials: out = sum_s e^{m_s - M} acc_s / sum_s e^{m_s - M} l_s.
+// One warp per (tile, head): the lanes first share the splits (weights w_s = e^{m_s - M} / L go to
+// shared memory), then the output dimensions, reading every split's row with independent loads.
+constexpr int MERGE_MAX_SPLITS = 256;
 template <typename T>
-__global__ void attention_merge_kernel(AttnParams p) {
-    const int tile = blockIdx.x, head = blockIdx.y;
+__global__ void __launch_bounds__(32) attention_merge_kernel(AttnParams p) {
+    __shared__ float wsm[MERGE_MAX_SPLITS];
+    const int tile = blockIdx.x, head = blockIdx.y, lane = threadIdx.x;
     const int G = p.Hq / p.Hkv;
     const int kvh = head / G, g = head - kvh * G;
     const int nqv = p.BQ * G;
@@ -191,29 +195,30 @@ __global__ void attention_merge_kernel(AttnParams p) {
     const int nrows = min(p.BQ, p.span_len[span] - q0);
     const int row0 = p.span_row[span] + q0;
     T* out = (T*)p.out;
+    const size_t base0 = ((size_t)tile * p.Hkv + kvh) * p.nsplit;
     for (int r = 0; r < nrows; ++r) {
         const int v = r * G + g;
         float M = -INFINITY;
-        for (int s = 0; s < p.nsplit; ++s) {
-            const size_t idx = (((size_t)tile * p.Hkv + kvh) * p.nsplit + s) * nqv + v;
-            M = fmaxf(M, p.part_ml[idx * 2]);
-        }
+        for (int s = lane; s < p.nsplit; s += 32) M = fmaxf(M, p.part_ml[((base0 + s) * nqv + v) * 2]);
+        M = llb_warp_max(M);
         float L = 0.0f;
-        for (int s = 0; s < p.nsplit; ++s) {
-            const size_t idx = (((size_t)tile * p.Hkv + kvh) * p.nsplit + s) * nqv + v;
+        for (int s = lane; s < p.nsplit; s += 32) {
+            const size_t idx = (base0 + s) * nqv + v;
             const float m = p.part_ml[idx * 2];
-            if (m != -INFINITY) L += expf(m - M) * p.part_ml[idx * 2 + 1];
+            const float w = (m == -INFINITY) ? 0.0f : expf(m - M);
+            wsm[s] = w;
+            L += w * p.part_ml[idx * 2 + 1];
         }
+        L = llb_warp_sum(L);
+        __syncwarp();
         const float inv = 1.0f / L;
-        for (int d = threadIdx.x; d < p.hd; d += blockDim.x) {
+        for (int d = lane; d < p.hd; d += 32) {
             float a = 0.0f;
-            for (int s = 0; s < p.nsplit; ++s) {
-                const size_t idx = (((size_t)tile * p.Hkv + kvh) * p.nsplit + s) * nqv + v;
-                const float m = p.part_ml[idx * 2];
-                if (m != -INFINITY) a += expf(m - M) * p.part_acc[idx * p.hd + d];
-            }
+#pragma unroll 8
+            for (int s = 0; s < p.nsplit; ++s) a = fmaf(wsm[s], p.part_acc[((base0 + s) * nqv + v) * p.hd + d], a);
             out[((size_t)(row0 + r) * p.Hq + head) * p.hd + d] = llb_from_float<T>(a * inv);
         }
+        __syncwarp();
     }
 }
 
@@ -301,14 +306,27 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_decode_kernel(AttnParams p)
     for (int kb = klo + warp * BK; kb < khi; kb += NWARPS * BK) {
         const int kpos = kb + lane;
         const bool valid = kpos < khi;
+        const int nkeys = min(BK, khi - kb);
         size_t slot = 0;
         if (valid) slot = (size_t)bt[kpos / p.page_size] * p.page_size + (kpos % p.page_size);
+        // Values first (NPMAX == 1: all 32 rows of the tile are requested before any arithmetic, so the
+        // memory system sees them at once); each lane owns two dimensions of every row.
+        float v0r[NPMAX == 1 ? BK : 1], v1r[NPMAX == 1 ? BK : 1];
+        if (NPMAX == 1) {
+            const int d = 2 * lane;
+#pragma unroll
+            for (int j = 0; j < BK; ++j) {
+                const size_t sj = __shfl_sync(0xffffffffu, slot, j);
+                v0r[j] = v1r[j] = 0.0f;
+                if (j < nkeys && d < hd) Vec16<T>::load2(vc + sj * row_stride + (size_t)kvh * hd + d, v0r[j], v1r[j]);
+            }
+        }
         float dot[GMAX];
 #pragma unroll
         for (int g = 0; g < GMAX; ++g) dot[g] = 0.0f;
         if (valid) {
             const T* kr = kc + slot * row_stride + (size_t)kvh * hd;
-#pragma unroll 4
+#pragma unroll 8
             for (int c = 0; c < hd; c += VEC) {
                 float kf[VEC];
                 Vec16<T>::load(kr + c, kf);
@@ -340,23 +358,36 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_decode_kernel(AttnParams p)
             }
         }
         __syncwarp();
-        const int nkeys = min(BK, khi - kb);
-#pragma unroll 4
-        for (int j = 0; j < nkeys; ++j) {
-            const size_t sj = __shfl_sync(0xffffffffu, slot, j);
-            const T* vr = vc + sj * row_stride + (size_t)kvh * hd;
+        if (NPMAX == 1) {
 #pragma unroll
-            for (int n = 0; n < NPMAX; ++n) {
-                const int d = n * 64 + 2 * lane;
-                if (d < hd) {
-                    float v0, v1;
-                    Vec16<T>::load2(vr + d, v0, v1);
+            for (int j = 0; j < BK; ++j) {
 #pragma unroll
-                    for (int g = 0; g < GMAX; ++g) {
-                        if (g < G) {
-                            const float pj = myP[g * 32 + j];
-                            acc[g][n][0] = fmaf(pj, v0, acc[g][n][0]);
-                            acc[g][n][1] = fmaf(pj, v1, acc[g][n][1]);
+                for (int g = 0; g < GMAX; ++g) {
+                    if (g < G) {
+                        const float pj = myP[g * 32 + j];      // 0 for keys past the end
+                        acc[g][0][0] = fmaf(pj, v0r[j], acc[g][0][0]);
+                        acc[g][0][1] = fmaf(pj, v1r[j], acc[g][0][1]);
+                    }
+                }
+            }
+        } else {
+#pragma unroll 8
+            for (int j = 0; j < nkeys; ++j) {
+                const size_t sj = __shfl_sync(0xffffffffu, slot, j);
+                const T* vr = vc + sj * row_stride + (size_t)kvh * hd;
+#pragma unroll
+                for (int n = 0; n < NPMAX; ++n) {
+                    const int d = n * 64 + 2 * lane;
+                    if (d < hd) {
+                        float v0, v1;
+                        Vec16<T>::load2(vr + d, v0, v1);
+#pragma unroll
+                        for (int g = 0; g < GMAX; ++g) {
+                            if (g < G) {
+                                const float pj = myP[g * 32 + j];
+                                acc[g][n][0] = fmaf(pj, v0, acc[g][n][0]);
+                                acc[g][n][1] = fmaf(pj, v1, acc[g][n][1]);
+                            }
                         }
                     }
                 }
@@ -475,8 +506,7 @@ int launch_attention(const AttnParams& p, int num_tiles, cudaStream_t stream) {
     if (rc) return rc;
     if (p.nsplit > 1) {
         dim3 mgrid(num_tiles, p.Hq);
-        const int threads = p.hd >= 128 ? 128 : (p.hd >= 64 ? 64 : 32);
-        attention_merge_kernel<T><<<mgrid, threads, 0, stream>>>(p);
+        attention_merge_kernel<T><<<mgrid, 32, 0, stream>>>(p);
         rc = llb_check_launch("attention_merge");
     }
     return rc;
@@ -507,7 +537,8 @@ LLB_EXPORT int llb_paged_attention(const void* q, const void* k_cache, const voi
     LLB_REQUIRE(num_tiles > 0 && Hq > 0 && Hkv > 0 && hd > 0 && page_size > 0 && max_pages > 0 && BQ > 0,
                 "attention: bad sizes");
     LLB_REQUIRE(Hq % Hkv == 0, "attention: %d query heads are not a multiple of %d kv heads", Hq, Hkv);
-    LLB_REQUIRE(nsplit >= 1 && nsplit <= 65535 && Hkv <= 65535, "attention: bad split count %d", nsplit);
+    LLB_REQUIRE(nsplit >= 1 && nsplit <= MERGE_MAX_SPLITS && Hkv <= 65535,
+                "attention: split count %d is outside 1..%d", nsplit, MERGE_MAX_SPLITS);
     LLB_REQUIRE(nsplit == 1 || scratch != nullptr, "attention: nsplit=%d needs scratch", nsplit);
     AttnParams p;
     p.q = q; p.k_cache = k_cache; p.v_cache = v_cache; p.out = out;
