@@ -232,7 +232,20 @@ def main() -> int:
         core = engine.core
         if args.only == "decode":
             ms, launches, ctx = time_decode(core, args.batch, args.steps, args.warmup, rng)
-            print(json.dumps({"only": "decode", "batch": args.batch, "ms_per_step": round(ms, 4), "launches": launches}))
+            r = core.runner
+            extra = {"graph_replays": r.graph_replays, "graphs": len(r._graphs)}
+            if r._graphs:      # the same captured step replayed back to back: device time without any host work
+                g = next(iter(r._graphs.values()))[0]
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(20):
+                    g.replay()
+                e1.record()
+                torch.cuda.synchronize()
+                extra["replay_only_ms"] = round(e0.elapsed_time(e1) / 20, 4)
+            print(json.dumps({"only": "decode", "batch": args.batch, "ms_per_step": round(ms, 4), "launches": launches,
+                              **extra}))
             return 0
         if args.only == "prefill":
             pre_ms = time_prefill(core, args.steps, args.warmup, rng)

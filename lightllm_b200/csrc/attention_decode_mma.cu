@@ -1,0 +1,397 @@
+// Split-KV paged attention for decode (one query row per request) on tensor cores, bf16.
+//
+// The G query heads that share a kv head (G <= 16) are the 16 rows of a warp-level MMA tile
+// (mma.sync m16n8k16), so a 32-key tile of K and V costs a few dozen instructions instead of the
+// thousands the CUDA-core kernel spends on it.  Each warp streams its own key tiles: cp.async copies
+// the page rows into the warp's shared-memory buffers (two buffers, so the next tile is in flight
+// while this one is computed), ldmatrix reads them as MMA fragments (K as is, V transposed), scores
+// and the online softmax stay in registers in float (src/kv_cache/paged_attention.cu:153-163, with
+// this library's departures: -inf start, exact acc / l, the token's own key visible).  The four warps
+// of a block are merged through shared memory; with nsplit > 1 the blocks' partial (acc, m, l) go to
+// scratch and a second kernel merges them (paged_attention.cu:476-532 does the same for 4 fixed splits).
+//
+// Both kernels are programmatic dependent launches: everything that does not depend on the previous
+// kernel (block tables, positions, ranges) is read before griddepcontrol.wait.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BK = 32;          // keys per tile
+constexpr int NWARPS = 4;
+constexpr int MERGE_MAX_SPLITS = 256;
+
+struct DecodeParams {
+    const __nv_bfloat16* q;        // [T, Hq, HD]
+    const __nv_bfloat16* k_cache;  // [slots, Hkv, HD]
+    const __nv_bfloat16* v_cache;
+    __nv_bfloat16* out;            // [T, Hq, HD]
+    const int* tile_span;
+    const int* tile_q0;
+    const int* span_row;
+    const int* span_pos;
+    const int* block_table;
+    int max_pages, page_size, Hq, Hkv, window, nsplit;
+    float scale_log2e;
+    float* part_acc;               // [tiles, Hkv, nsplit, G, HD]
+    float* part_ml;                // [tiles, Hkv, nsplit, G, 2]   (m in base-2 units, l)
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+    const int n = valid ? 16 : 0;     // 0 source bytes: the 16 bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+                 "{%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// Shared memory tile [32 keys][HD] bf16; the 16-byte chunk c of row r sits at chunk c ^ (r & 7), so that
+// the eight rows an ldmatrix touches fall into different banks.
+template <int HD>
+__device__ __forceinline__ uint32_t tile_addr(uint32_t base, int row, int chunk) {
+    return base + (uint32_t)row * (HD * 2) + (uint32_t)((chunk ^ (row & 7)) * 16);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(NWARPS * 32) paged_decode_mma_kernel(DecodeParams p) {
+    constexpr int CH = HD / 8;                 // 16-byte chunks per row
+    constexpr int TILE_BYTES = BK * HD * 2;
+    constexpr int KS = HD / 16;                // k-steps of Q K^T
+    constexpr int NT = HD / 8;                 // n-tiles of P V
+    extern __shared__ __align__(128) uint8_t smem[];
+    // per warp: K[2], V[2]; afterwards reused for the merge of the warps
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t wbase = smem_u32(smem) + warp * 4 * TILE_BYTES;
+    const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int G = p.Hq / p.Hkv;
+
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int span = p.tile_span[tile];
+    const int q0 = p.tile_q0[tile];
+    const int row0 = p.span_row[span] + q0;
+    const int qpos = p.span_pos[span] + q0;
+    const int* bt = p.block_table + (size_t)span * p.max_pages;
+    const int hi = qpos + 1;
+    const int lo = p.window > 0 ? max(0, qpos - p.window + 1) : 0;
+    int klo = lo, khi = hi;
+    if (p.nsplit > 1) {
+        int chunk = (hi - lo + p.nsplit - 1) / p.nsplit;
+        chunk = ((chunk + BK - 1) / BK) * BK;
+        klo = lo + split * chunk;
+        khi = min(hi, klo + chunk);
+    }
+    const size_t row_stride = (size_t)p.Hkv * HD;
+    // cache row of this lane's key in a tile that starts at kb (only block tables are read: no dependency)
+    auto slot_of = [&](int kb) -> long long {
+        const int kpos = kb + lane;
+        if (kpos >= khi) return -1;
+        return (long long)bt[kpos / p.page_size] * p.page_size + (kpos % p.page_size);
+    };
+    const int kb_first = klo + warp * BK;
+    long long slot_next = kb_first < khi ? slot_of(kb_first) : -1;
+
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    // Q fragments: rows = heads of the group (zero beyond G), K-steps over the head dimension.
+    uint32_t qf[KS][4];
+    {
+        const int r0 = lane >> 2, r1 = r0 + 8, c = (lane & 3) * 2;
+        const __nv_bfloat16* qb = p.q + ((size_t)row0 * p.Hq + kvh * G) * HD;
+#pragma unroll
+        for (int s = 0; s < KS; ++s) {
+            qf[s][0] = r0 < G ? *reinterpret_cast<const uint32_t*>(qb + r0 * HD + s * 16 + c) : 0u;
+            qf[s][1] = r1 < G ? *reinterpret_cast<const uint32_t*>(qb + r1 * HD + s * 16 + c) : 0u;
+            qf[s][2] = r0 < G ? *reinterpret_cast<const uint32_t*>(qb + r0 * HD + s * 16 + 8 + c) : 0u;
+            qf[s][3] = r1 < G ? *reinterpret_cast<const uint32_t*>(qb + r1 * HD + s * 16 + 8 + c) : 0u;
+        }
+    }
+    // Issue the copies of one tile into buffer `buf`: 32 rows x CH chunks of K and of V.
+    auto issue = [&](int buf, long long slot) {
+        const uint32_t kbase = wbase + buf * TILE_BYTES, vbase = wbase + (2 + buf) * TILE_BYTES;
+#pragma unroll
+        for (int it = 0; it < CH; ++it) {
+            const int idx = it * 32 + lane;
+            const int row = idx / CH, ch = idx % CH;
+            const long long s = __shfl_sync(0xffffffffu, slot, row);
+            const bool valid = s >= 0;
+            const size_t off = (valid ? (size_t)s : 0) * row_stride + (size_t)kvh * HD + ch * 8;
+            cp_async16(tile_addr<HD>(kbase, row, ch), p.k_cache + off, valid);
+            cp_async16(tile_addr<HD>(vbase, row, ch), p.v_cache + off, valid);
+        }
+        cp_async_commit();
+    };
+
+    float o[NT][4];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+
+    int buf = 0;
+    if (kb_first < khi) issue(0, slot_next);
+    for (int kb = kb_first; kb < khi; kb += NWARPS * BK) {
+        const int kb_next = kb + NWARPS * BK;
+        if (kb_next < khi) {
+            issue(buf ^ 1, slot_of(kb_next));
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncwarp();
+        const uint32_t kbase = wbase + buf * TILE_BYTES, vbase = wbase + (2 + buf) * TILE_BYTES;
+
+        // S[16 x 32] = Q K^T: four n-tiles of 8 keys.
+        float s[4][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
+#pragma unroll
+        for (int ks = 0; ks < KS; ks += 2) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                // matrices: keys 8i..8i+7 x dims [16ks, +8), [16ks+8, +8), [16ks+16, +8), [16ks+24, +8)
+                uint32_t b[4];
+                ldmatrix_x4(tile_addr<HD>(kbase, i * 8 + (lane & 7), ks * 2 + (lane >> 3)), b);
+                mma_bf16(s[i], qf[ks], b[0], b[1]);
+                mma_bf16(s[i], qf[ks + 1], b[2], b[3]);
+            }
+        }
+        // Online softmax for rows r0 = lane / 4 (values [0], [1]) and r0 + 8 (values [2], [3]).
+        const int c0 = (lane & 3) * 2;
+        float mt[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = kb + i * 8 + c0 + (e & 1);
+                const float v = key < khi ? s[i][e] * p.scale_log2e : -INFINITY;
+                s[i][e] = v;
+                mt[e >> 1] = fmaxf(mt[e >> 1], v);
+            }
+        }
+        float corr[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            mt[h] = fmaxf(mt[h], __shfl_xor_sync(0xffffffffu, mt[h], 1));
+            mt[h] = fmaxf(mt[h], __shfl_xor_sync(0xffffffffu, mt[h], 2));
+            const float m_new = fmaxf(m_run[h], mt[h]);       // finite: every tile has at least one key
+            corr[h] = m_run[h] == -INFINITY ? 0.0f : fast_exp2(m_run[h] - m_new);
+            m_run[h] = m_new;
+        }
+        float lt[2] = {0.0f, 0.0f};
+        uint32_t pf[2][4];      // P as A fragments for the two k-steps of 16 keys
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float p0 = fast_exp2(s[i][0] - m_run[0]), p1 = fast_exp2(s[i][1] - m_run[0]);
+            const float p2 = fast_exp2(s[i][2] - m_run[1]), p3 = fast_exp2(s[i][3] - m_run[1]);
+            lt[0] += p0 + p1;
+            lt[1] += p2 + p3;
+            // n-tiles 2j and 2j+1 of S are the k-halves of A for k-step j: a0,a1 from tile 2j; a2,a3 from 2j+1
+            pf[i >> 1][(i & 1) * 2 + 0] = pack_bf16(p0, p1);
+            pf[i >> 1][(i & 1) * 2 + 1] = pack_bf16(p2, p3);
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            lt[h] += __shfl_xor_sync(0xffffffffu, lt[h], 1);
+            lt[h] += __shfl_xor_sync(0xffffffffu, lt[h], 2);
+            l_run[h] = l_run[h] * corr[h] + lt[h];
+        }
+#pragma unroll
+        for (int i = 0; i < NT; ++i) {
+            o[i][0] *= corr[0]; o[i][1] *= corr[0];
+            o[i][2] *= corr[1]; o[i][3] *= corr[1];
+        }
+        // O[16 x HD] += P[16 x 32] V[32 x HD]: V fragments come transposed out of shared memory.
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {              // k-step: keys 16j .. 16j+15
+#pragma unroll
+            for (int i = 0; i < NT; i += 2) {      // two n-tiles (16 dims) per ldmatrix.x4
+                // matrices: (keys 16j..+7, dims 8i..), (keys 16j+8..+15, dims 8i..), (keys 16j..+7, dims 8i+8..), (keys 16j+8.., dims 8i+8..)
+                uint32_t b[4];
+                const int mat = lane >> 3;
+                ldmatrix_x4_trans(tile_addr<HD>(vbase, j * 16 + (mat & 1) * 8 + (lane & 7), i + (mat >> 1)), b);
+                mma_bf16(o[i], pf[j], b[0], b[1]);
+                mma_bf16(o[i + 1], pf[j], b[2], b[3]);
+            }
+        }
+        buf ^= 1;
+        __syncwarp();
+    }
+
+    // Merge the four warps through shared memory (the tile buffers are free now).
+    __syncthreads();
+    float* wacc = reinterpret_cast<float*>(smem);                  // [NWARPS][16][HD]
+    float* wml = wacc + NWARPS * 16 * HD;                           // [NWARPS][16][2]
+    {
+        const int r0 = lane >> 2, c = (lane & 3) * 2;
+#pragma unroll
+        for (int i = 0; i < NT; ++i) {
+            float* a0 = wacc + ((size_t)(warp * 16 + r0) * HD) + i * 8 + c;
+            float* a1 = wacc + ((size_t)(warp * 16 + r0 + 8) * HD) + i * 8 + c;
+            a0[0] = o[i][0]; a0[1] = o[i][1];
+            a1[0] = o[i][2]; a1[1] = o[i][3];
+        }
+        if ((lane & 3) == 0) {
+            wml[(warp * 16 + r0) * 2] = m_run[0];     wml[(warp * 16 + r0) * 2 + 1] = l_run[0];
+            wml[(warp * 16 + r0 + 8) * 2] = m_run[1]; wml[(warp * 16 + r0 + 8) * 2 + 1] = l_run[1];
+        }
+    }
+    __syncthreads();
+    const size_t base = (((size_t)tile * p.Hkv + kvh) * p.nsplit + split) * G;
+    for (int i = threadIdx.x; i < G * HD; i += blockDim.x) {
+        const int g = i / HD, d = i - g * HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < NWARPS; ++w) M = fmaxf(M, wml[(w * 16 + g) * 2]);
+        float L = 0.0f, a = 0.0f;
+#pragma unroll
+        for (int w = 0; w < NWARPS; ++w) {
+            const float mw = wml[(w * 16 + g) * 2];
+            if (mw != -INFINITY) {
+                const float e = fast_exp2(mw - M);
+                L += e * wml[(w * 16 + g) * 2 + 1];
+                a += e * wacc[(size_t)(w * 16 + g) * HD + d];
+            }
+        }
+        if (p.nsplit == 1) {
+            p.out[((size_t)row0 * p.Hq + kvh * G + g) * HD + d] = __float2bfloat16_rn(a / L);
+        } else {
+            p.part_acc[(base + g) * HD + d] = a;
+            if (d == 0) {
+                p.part_ml[(base + g) * 2] = M;
+                p.part_ml[(base + g) * 2 + 1] = L;
+            }
+        }
+    }
+}
+
+// out = sum_s 2^(m_s - M) acc_s / sum_s 2^(m_s - M) l_s; one warp per (tile, head).
+__global__ void __launch_bounds__(32) decode_merge_kernel(DecodeParams p, int HD) {
+    __shared__ float wsm[MERGE_MAX_SPLITS];
+    const int tile = blockIdx.x, head = blockIdx.y, lane = threadIdx.x;
+    const int G = p.Hq / p.Hkv;
+    const int kvh = head / G, g = head - kvh * G;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int span = p.tile_span[tile];
+    const int row0 = p.span_row[span] + p.tile_q0[tile];
+    const size_t base0 = ((size_t)tile * p.Hkv + kvh) * p.nsplit;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    float M = -INFINITY;
+    for (int s = lane; s < p.nsplit; s += 32) M = fmaxf(M, p.part_ml[((base0 + s) * G + g) * 2]);
+    M = llb_warp_max(M);
+    float L = 0.0f;
+    for (int s = lane; s < p.nsplit; s += 32) {
+        const size_t idx = (base0 + s) * G + g;
+        const float m = p.part_ml[idx * 2];
+        const float w = (m == -INFINITY) ? 0.0f : fast_exp2(m - M);
+        wsm[s] = w;
+        L += w * p.part_ml[idx * 2 + 1];
+    }
+    L = llb_warp_sum(L);
+    __syncwarp();
+    const float inv = 1.0f / L;
+    for (int d = lane; d < HD; d += 32) {
+        float a = 0.0f;
+#pragma unroll 8
+        for (int s = 0; s < p.nsplit; ++s) a = fmaf(wsm[s], p.part_acc[((base0 + s) * G + g) * HD + d], a);
+        p.out[((size_t)row0 * p.Hq + head) * HD + d] = __float2bfloat16_rn(a * inv);
+    }
+}
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
+template <int HD>
+int launch(const DecodeParams& p, int num_tiles, cudaStream_t stream) {
+    constexpr size_t smem = (size_t)NWARPS * 4 * BK * HD * 2;      // also covers the merge: 4 x 16 x HD floats + m, l
+    static_assert(smem >= (size_t)NWARPS * 16 * HD * 4 + NWARPS * 16 * 2 * 4, "merge area does not fit");
+    static bool configured = false;
+    if (!configured && smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(paged_decode_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return llb_fail("decode attention: cannot opt in to %zu bytes of shared memory: %s", smem,
+                                              cudaGetErrorString(e));
+        configured = true;
+    }
+    cudaError_t e = launch_pdl(paged_decode_mma_kernel<HD>, dim3(num_tiles, p.Hkv, p.nsplit), dim3(NWARPS * 32), smem,
+                               stream, p);
+    if (e != cudaSuccess) return llb_fail("decode attention: launch failed: %s", cudaGetErrorString(e));
+    int rc = llb_check_launch("paged_decode_mma");
+    if (rc) return rc;
+    if (p.nsplit > 1) {
+        e = launch_pdl(decode_merge_kernel, dim3(num_tiles, p.Hq), dim3(32), 0, stream, p, HD);
+        if (e != cudaSuccess) return llb_fail("decode merge: launch failed: %s", cudaGetErrorString(e));
+        rc = llb_check_launch("decode_merge");
+    }
+    return rc;
+}
+
+}  // namespace
+
+// Whether this kernel takes the shape (else the CUDA-core kernel of attention_simt.cu is the one to call).
+LLB_EXPORT int llb_paged_decode_mma_supports(int Hq, int Hkv, int hd) {
+    return Hkv > 0 && Hq % Hkv == 0 && Hq / Hkv <= 16 && (hd == 64 || hd == 128);
+}
+
+// One query row per tile: q, out [T, Hq, hd] bf16 (row = span_row[tile_span[t]] + tile_q0[t], position
+// span_pos + tile_q0); caches [slots, Hkv, hd] bf16; block_table [S, max_pages].  scratch: num_tiles * Hq *
+// nsplit * (hd + 2) floats when nsplit > 1.
+LLB_EXPORT int llb_paged_decode_mma(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                    const int* tile_span, const int* tile_q0, int num_tiles, const int* span_row,
+                                    const int* span_pos, const int* block_table, int max_pages, int page_size,
+                                    int Hq, int Hkv, int hd, int window, float scale, int nsplit, float* scratch,
+                                    cudaStream_t stream) {
+    if (num_tiles == 0) return 0;
+    LLB_REQUIRE(llb_paged_decode_mma_supports(Hq, Hkv, hd), "decode attention: %d/%d heads of size %d are not supported "
+                "(groups of at most 16, head size 64 or 128)", Hq, Hkv, hd);
+    LLB_REQUIRE(nsplit >= 1 && nsplit <= MERGE_MAX_SPLITS && (nsplit == 1 || scratch != nullptr),
+                "decode attention: split count %d is outside 1..%d or scratch is missing", nsplit, MERGE_MAX_SPLITS);
+    LLB_REQUIRE(page_size > 0 && max_pages > 0 && Hkv <= 65535, "decode attention: bad sizes");
+    LLB_REQUIRE(((uintptr_t)q % 16 == 0) && ((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0),
+                "decode attention: tensors must be 16-byte aligned");
+    DecodeParams p;
+    p.q = (const __nv_bfloat16*)q; p.k_cache = (const __nv_bfloat16*)k_cache; p.v_cache = (const __nv_bfloat16*)v_cache;
+    p.out = (__nv_bfloat16*)out; p.tile_span = tile_span; p.tile_q0 = tile_q0; p.span_row = span_row; p.span_pos = span_pos;
+    p.block_table = block_table; p.max_pages = max_pages; p.page_size = page_size; p.Hq = Hq; p.Hkv = Hkv;
+    p.window = window; p.nsplit = nsplit; p.scale_log2e = scale * 1.4426950408889634f;
+    const int G = Hq / Hkv;
+    p.part_acc = scratch;
+    p.part_ml = scratch ? scratch + (size_t)num_tiles * Hkv * nsplit * G * hd : nullptr;
+    if (hd == 64) return launch<64>(p, num_tiles, stream);
+    return launch<128>(p, num_tiles, stream);
+}

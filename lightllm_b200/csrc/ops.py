@@ -15,7 +15,7 @@ from . import build as _build
 
 F32, BF16 = 0, 1
 EPI_STORE, EPI_STORE_F32, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
-ABI_VERSION = 5
+ABI_VERSION = 9
 
 _lib: Optional[ctypes.CDLL] = None
 
@@ -176,6 +176,92 @@ def paged_attention_simt(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
         window, ctypes.c_float(scale), bq, nsplit, _ptr(scratch), _stream()))
 
 
+DEPI_STORE_F32, DEPI_RESIDUAL, DEPI_SWIGLU, DEPI_ROPE_KV = 1, 2, 3, 4
+
+
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
+    """(cos, sin) of ``positions[t] * inv_freq[i]`` as float32 ``[T, len(inv_freq), 2]``."""
+    T, half = positions.numel(), inv_freq.numel()
+    out = torch.empty((T, half, 2), dtype=torch.float32, device=positions.device)
+    _check(lib().llb_rope_table(_i32(positions, "positions"), _ptr(inv_freq), _ptr(out), T, half, _stream()))
+    return out
+
+
+_splitk = {}
+
+
+def reserve_splitk_scratch(device: torch.device, floats: int, tiles: int) -> None:
+    """Make sure the device has a zeroed meeting place of ``floats`` floats and ``tiles`` counters for
+    split-K contractions with fused epilogues.  Call it when a model is bound, never inside a step."""
+    key = torch.device(device).index or 0
+    have = _splitk.get(key)
+    if have is None or have[0].numel() < floats or have[1].numel() < tiles:
+        floats = max(floats, have[0].numel() if have else 0)
+        tiles = max(tiles, have[1].numel() if have else 0)
+        _splitk[key] = (torch.zeros(floats, dtype=torch.float32, device=device),
+                        torch.zeros(tiles, dtype=torch.int32, device=device))
+
+
+def splitk_scratch(device: torch.device):
+    return _splitk.get(torch.device(device).index or 0)
+
+
+def gemm_decode_supports(M: int, N: int, K: int, norm: bool, epilogue: int, head_dim: int = 0) -> bool:
+    return bool(lib().llb_gemm_decode_supports(M, N, K, 1 if norm else 0, epilogue, head_dim))
+
+
+def gemm_decode(w: torch.Tensor, epilogue: int, M: int, *, a: Optional[torch.Tensor] = None,
+                x: Optional[torch.Tensor] = None, x_rows: Optional[torch.Tensor] = None,
+                norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0, bias: Optional[torch.Tensor] = None,
+                out: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None, split_k: int = 1,
+                slot_mapping: Optional[torch.Tensor] = None,
+                rope_table: Optional[torch.Tensor] = None, rotary_dim: int = 0, interleaved: bool = False,
+                num_heads: int = 0, num_kv_heads: int = 0, head_dim: int = 0, q_out: Optional[torch.Tensor] = None,
+                k_cache: Optional[torch.Tensor] = None, v_cache: Optional[torch.Tensor] = None) -> None:
+    """The fused contraction of a step with at most 64 rows (see csrc/gemm_decode.cu).
+
+    Operand: ``a`` [M, K] bf16, or the float rows ``x[x_rows]`` (``x[:M]`` without ``x_rows``) to be
+    RMS-normalised with ``norm_weight`` and ``eps`` inside the kernel.  Epilogues: DEPI_STORE_F32
+    (``out`` float [M, N]), DEPI_RESIDUAL (adds into ``residual``), DEPI_SWIGLU (``out`` bf16 [M, N/2]),
+    DEPI_ROPE_KV (rotary by ``rope_table`` from :func:`rope_table`, ``q_out`` and the cache rows ``slot_mapping``)."""
+    N, K = w.shape
+    if w.dtype != torch.bfloat16:
+        raise KernelError("gemm_decode takes bfloat16 weights")
+    norm = x is not None
+    if norm:
+        if x.dtype != torch.float32 or x.shape[-1] != K or norm_weight is None or norm_weight.numel() != K:
+            raise KernelError("gemm_decode: the normalised operand must be float32 [*, K] with a weight of K")
+    elif a is None or a.dtype != torch.bfloat16 or tuple(a.shape) != (M, K):
+        raise KernelError(f"gemm_decode: a must be bfloat16 [{M},{K}]")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N):
+        raise KernelError(f"gemm_decode: bias must be float32 [{N}]")
+    if epilogue == DEPI_RESIDUAL and (residual is None or residual.dtype != torch.float32 or tuple(residual.shape) != (M, N)):
+        raise KernelError(f"gemm_decode: residual must be float32 [{M},{N}]")
+    if epilogue == DEPI_STORE_F32 and (out is None or out.dtype != torch.float32 or tuple(out.shape) != (M, N)):
+        raise KernelError(f"gemm_decode: out must be float32 [{M},{N}]")
+    if epilogue == DEPI_SWIGLU and (out is None or out.dtype != torch.bfloat16 or tuple(out.shape) != (M, N // 2)):
+        raise KernelError(f"gemm_decode: out must be bfloat16 [{M},{N // 2}]")
+    if epilogue == DEPI_ROPE_KV:
+        if q_out is None or q_out.dtype != torch.bfloat16 or q_out.numel() != M * num_heads * head_dim:
+            raise KernelError("gemm_decode: q_out does not fit")
+        if rotary_dim and (rope_table is None or rope_table.dtype != torch.float32
+                           or rope_table.numel() != M * rotary_dim):
+            raise KernelError("gemm_decode: rope_table must be float32 [M, rotary_dim/2, 2]")
+        if slot_mapping is not None and (k_cache is None or v_cache is None or k_cache.dtype != torch.bfloat16):
+            raise KernelError("gemm_decode: the cache must be bfloat16")
+    scratch = splitk_scratch(w.device) if (split_k > 1 and epilogue in (DEPI_SWIGLU, DEPI_ROPE_KV)) else None
+    if scratch is not None and scratch[1].numel() < -(-N // 128):
+        scratch = None
+    _check(lib().llb_gemm_decode(
+        _ptr(w), _ptr(a), _ptr(x), _i32(x_rows, "x_rows"), _ptr(norm_weight),
+        1 if (norm_weight is not None and norm_weight.dtype == torch.bfloat16) else 0, ctypes.c_float(eps),
+        1 if norm else 0, _ptr(bias), _ptr(out), _ptr(residual), epilogue, M, N, K, split_k,
+        _i32(slot_mapping, "slot_mapping"), _ptr(rope_table), rotary_dim,
+        1 if interleaved else 0, num_heads, num_kv_heads, head_dim, _ptr(q_out), _ptr(k_cache), _ptr(v_cache),
+        _ptr(scratch[0]) if scratch else ctypes.c_void_p(0), ctypes.c_longlong(scratch[0].numel() if scratch else 0),
+        _ptr(scratch[1]) if scratch else ctypes.c_void_p(0), _ptr(async_error_flag(w.device)), _stream()))
+
+
 def attention_tcgen05_supports(head_dim: int, page_size: int) -> bool:
     return bool(lib().llb_attention_tcgen05_supports(head_dim, page_size))
 
@@ -197,6 +283,30 @@ def paged_attention_tcgen05(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
         _i32(span_row, "span_row"), _i32(span_len, "span_len"), _i32(span_pos, "span_pos"),
         _i32(block_table, "block_table"), max_pages, page_size, num_slots, num_heads, num_kv_heads, head_dim,
         window, ctypes.c_float(scale), _ptr(async_error_flag(q.device)), _stream()))
+
+
+def paged_decode_mma_supports(num_heads: int, num_kv_heads: int, head_dim: int) -> bool:
+    return bool(lib().llb_paged_decode_mma_supports(num_heads, num_kv_heads, head_dim))
+
+
+def paged_decode_mma(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
+                     tile_span: torch.Tensor, tile_q0: torch.Tensor, num_tiles: int, span_row: torch.Tensor,
+                     span_pos: torch.Tensor, block_table: torch.Tensor, max_pages: int, page_size: int,
+                     num_heads: int, num_kv_heads: int, head_dim: int, window: int, scale: float,
+                     nsplit: int = 1, scratch: Optional[torch.Tensor] = None) -> None:
+    """Tensor-core decode attention: one query row per tile over its request's pages; bf16."""
+    for t in (q, k_cache, v_cache, out):
+        if t.dtype != torch.bfloat16:
+            raise KernelError("paged_decode_mma takes bfloat16 tensors")
+    if nsplit > 1:
+        need = attention_scratch_floats(num_tiles, num_heads, head_dim, 1, nsplit)
+        if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
+            raise KernelError(f"decode attention: nsplit={nsplit} needs {need} floats of scratch")
+    _check(lib().llb_paged_decode_mma(
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _i32(tile_span, "tile_span"), _i32(tile_q0, "tile_q0"),
+        num_tiles, _i32(span_row, "span_row"), _i32(span_pos, "span_pos"), _i32(block_table, "block_table"),
+        max_pages, page_size, num_heads, num_kv_heads, head_dim, window, ctypes.c_float(scale), nsplit,
+        _ptr(scratch), _stream()))
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:

@@ -6,9 +6,28 @@
 // when it fits.
 #include "common.cuh"
 
+// Launch with the programmatic-stream-serialization attribute (the kernel calls griddepcontrol.wait itself).
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 template <typename TI, typename TW, typename TO, int PER_THREAD>
 __global__ void rmsnorm_kernel(const TI* __restrict__ x, const TW* __restrict__ w, TO* __restrict__ out,
                                const int* __restrict__ rows, int D, float eps) {
+    // Programmatic dependent launch: let the next kernel start its preamble, then wait for the one before.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
     const TI* xr = x + (size_t)src * D;
@@ -57,12 +76,14 @@ template <typename TI, typename TW, typename TO>
 static int launch_rmsnorm(const void* x, const void* w, void* out, const int* rows, int R, int D, float eps,
                           cudaStream_t stream) {
     const int threads = 256;
+    cudaError_t e;
     if (D <= threads * 4)
-        rmsnorm_kernel<TI, TW, TO, 4><<<R, threads, 0, stream>>>((const TI*)x, (const TW*)w, (TO*)out, rows, D, eps);
+        e = launch_pdl(rmsnorm_kernel<TI, TW, TO, 4>, dim3(R), dim3(threads), stream, (const TI*)x, (const TW*)w, (TO*)out, rows, D, eps);
     else if (D <= threads * 16)
-        rmsnorm_kernel<TI, TW, TO, 16><<<R, threads, 0, stream>>>((const TI*)x, (const TW*)w, (TO*)out, rows, D, eps);
+        e = launch_pdl(rmsnorm_kernel<TI, TW, TO, 16>, dim3(R), dim3(threads), stream, (const TI*)x, (const TW*)w, (TO*)out, rows, D, eps);
     else
-        rmsnorm_kernel<TI, TW, TO, 0><<<R, threads, 0, stream>>>((const TI*)x, (const TW*)w, (TO*)out, rows, D, eps);
+        e = launch_pdl(rmsnorm_kernel<TI, TW, TO, 0>, dim3(R), dim3(threads), stream, (const TI*)x, (const TW*)w, (TO*)out, rows, D, eps);
+    if (e != cudaSuccess) return llb_fail("rmsnorm: launch failed: %s", cudaGetErrorString(e));
     return llb_check_launch("rmsnorm");
 }
 

@@ -68,6 +68,7 @@ class StepContext:
         self.cache = None
         self.err: Optional[torch.Tensor] = None
         self._tiles: Dict[int, Any] = {}
+        self.memo: Dict[Any, Any] = {}          # per-step values that parts share (e.g. rotary tables)
 
     @property
     def num_spans(self) -> int:

@@ -18,6 +18,7 @@ import torch
 from ..cache import CacheManager
 from ..models import Model
 from ..parts import CacheView
+from ..parts.base import LazyNorm
 from .batch import Span, StepContext, StepEntry
 
 
@@ -186,8 +187,9 @@ class ModelRunner:
             m.layers[entry.layer].forward(residual, ctx, view)
         if ctx.num_want == 0:
             return None
-        x = m.final_norm.forward_rows(residual, ctx.want_rows, ctx)
-        return m.head.forward(x, ctx)
+        if m.head.accepts_lazy_norm:
+            return m.head.forward(LazyNorm(residual, m.final_norm, ctx, rows=ctx.want_rows), ctx)
+        return m.head.forward(m.final_norm.forward_rows(residual, ctx.want_rows, ctx), ctx)
 
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """One step.  Returns the logits at the wanted places, in the order of the entries and of

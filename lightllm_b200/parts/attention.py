@@ -11,7 +11,7 @@ from ..config import PartSpec, part_class, register_part
 from ..csrc import ops
 from ..weights import WeightSpec
 from . import linear as L
-from .base import CacheView, Mixer
+from .base import CacheView, LazyNorm, Mixer
 
 # Shared memory budget per block used to pick the tile height of the CUDA-core kernel.
 _SMEM_BUDGET = 100 * 1024
@@ -80,9 +80,50 @@ class AttentionMixer(Mixer):
         if self.out_bias:
             self.b_o = tensors[self._n("o", "bias")].float().contiguous()
         self.position.bind(tensors, dtype, device)
+        L.reserve_fused_scratch(device, self.w_qkv.shape[0])
 
     # ------------------------------------------------------------------------------------------
+    accepts_lazy_norm = True
+
+    def _project_fused(self, x, ctx, cache: CacheView):
+        """Norm (if still pending), q/k/v projection, bias, rotary positions and the cache write in one
+        kernel, for steps of few rows in bfloat16.  Returns q, or None when the shape is not taken."""
+        table = self.position.rotary_table()
+        if table is None or self.w_qkv.dtype != torch.bfloat16 or not hasattr(self.position, "step_table"):
+            return None
+        if isinstance(x, LazyNorm) and not (x.fusable() is not None and x.num_rows <= L.FUSE_NORM_MAX_ROWS):
+            x = x.materialize()
+        lazy = isinstance(x, LazyNorm)
+        rms = x.fusable() if lazy else None
+        T = x.num_rows if lazy else x.shape[0]
+        act_dtype = x.norm.out_dtype if lazy else x.dtype
+        hq, hkv, hd = self.num_heads, self.num_kv_heads, self.head_dim
+        w = self.w_qkv if cache.writes else self.w_qkv[: hq * hd]
+        if not L.decode_eligible(T, w, act_dtype, lazy, ops.DEPI_ROPE_KV, hd):
+            return None
+        b = self.b_qkv if (cache.writes or self.b_qkv is None) else self.b_qkv[: hq * hd]
+        inv_freq, rotary_dim, interleaved = table
+        q = torch.empty((T, hq * hd), dtype=torch.bfloat16, device=w.device)
+        operand = dict(x=x.residual, norm_weight=rms[0], eps=rms[1]) if lazy else dict(a=x)
+        ops.gemm_decode(w, ops.DEPI_ROPE_KV, T, bias=b, split_k=L.split_k_fused(T, w.shape[0], w.shape[1]),
+                        slot_mapping=ctx.slot_mapping[cache.group] if cache.writes else None,
+                        rope_table=self.position.step_table(ctx) if rotary_dim else None,
+                        rotary_dim=rotary_dim, interleaved=interleaved, num_heads=hq, num_kv_heads=hkv, head_dim=hd,
+                        q_out=q, k_cache=cache.k if cache.writes else None, v_cache=cache.v if cache.writes else None,
+                        **operand)
+        return q
+
     def forward(self, x, residual, ctx, cache: CacheView) -> None:
+        q = self._project_fused(x, ctx, cache)
+        if q is None:
+            if isinstance(x, LazyNorm):
+                x = x.materialize()
+            q = self._project(x, ctx, cache)
+        attn = torch.empty_like(q)
+        self.attend(q, cache, ctx, attn)
+        L.linear(attn, self.w_o, self.b_o, L.RESIDUAL, residual=residual)
+
+    def _project(self, x, ctx, cache: CacheView):
         T = x.shape[0]
         hq, hkv, hd = self.num_heads, self.num_kv_heads, self.head_dim
         writes = cache.writes
@@ -105,9 +146,7 @@ class AttentionMixer(Mixer):
         ops.rope_kv_write(qkv, ctx.positions, ctx.slot_mapping[cache.group] if writes else None, inv_freq,
                           rotary_dim, interleaved, q, cache.k if writes else None, cache.v if writes else None,
                           hq, hkv, hd)
-        attn = torch.empty((T, hq * hd), dtype=x.dtype, device=x.device)
-        self.attend(q, cache, ctx, attn)
-        L.linear(attn, self.w_o, self.b_o, L.RESIDUAL, residual=residual)
+        return q
 
     def tile_height(self) -> int:
         group = self.num_heads // self.num_kv_heads
@@ -131,7 +170,17 @@ class AttentionMixer(Mixer):
             span = bound if window == 0 else min(bound, window)
             want = max(1, -(-2 * 148 // (S * self.num_kv_heads)))       # blocks to fill the SMs twice
             nsplit = max(1, min(want, -(-span // 128)))
-            self._simt(q, cache, out, ctx.tiles(1), common, 1, nsplit)
+            if q.dtype == torch.bfloat16 and ops.paged_decode_mma_supports(self.num_heads, self.num_kv_heads, self.head_dim):
+                tile_span, tile_q0, ntiles = ctx.tiles(1)
+                scratch = None
+                if nsplit > 1:
+                    scratch = torch.empty(ops.attention_scratch_floats(ntiles, self.num_heads, self.head_dim, 1, nsplit),
+                                          dtype=torch.float32, device=q.device)
+                ops.paged_decode_mma(q, cache.k, cache.v, out, tile_span, tile_q0, ntiles, ctx.span_row, ctx.span_pos,
+                                     ctx.block_tables[g], ctx.max_pages, ctx.page_size, self.num_heads,
+                                     self.num_kv_heads, self.head_dim, window, self.scale, nsplit, scratch)
+            else:
+                self._simt(q, cache, out, ctx.tiles(1), common, 1, nsplit)
             return
         short_max = None
         if (q.dtype == torch.bfloat16 and ops.attention_tcgen05_supports(self.head_dim, ctx.page_size)

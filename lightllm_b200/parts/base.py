@@ -37,6 +37,8 @@ class Part:
     # True when forward() only launches kernels whose arguments are fixed by the step's counts; a model of
     # such parts has its decode steps captured in CUDA graphs.  Parts that branch on the host say False.
     graph_safe = False
+    # True when forward() takes a LazyNorm in place of the normalised tensor.
+    accepts_lazy_norm = False
 
     def weight_specs(self) -> List[WeightSpec]:
         return []
@@ -46,6 +48,34 @@ class Part:
 
     def children(self) -> List["Part"]:
         return []
+
+
+class LazyNorm:
+    """The normalised input of a mixer, feed-forward or head, not yet computed.
+
+    A block hands this to parts that set ``accepts_lazy_norm``: they may fold the norm into their
+    first kernel (``fusable()`` gives the weight and eps of an RMSNorm) or ask for the tensor
+    (``materialize()``).  ``rows`` selects rows of the residual stream (the head's wanted rows)."""
+
+    def __init__(self, residual: torch.Tensor, norm: "Norm", ctx=None, rows: Optional[torch.Tensor] = None):
+        self.residual, self.norm, self.ctx, self.rows = residual, norm, ctx, rows
+        self._value = None
+
+    @property
+    def num_rows(self) -> int:
+        return self.rows.numel() if self.rows is not None else self.residual.shape[0]
+
+    def fusable(self):
+        f = getattr(self.norm, "rms_parameters", None)
+        return f() if f is not None else None
+
+    def materialize(self) -> torch.Tensor:
+        if self._value is None:
+            if self.rows is not None:
+                self._value = self.norm.forward_rows(self.residual, self.rows, self.ctx)
+            else:
+                self._value = self.norm.forward(self.residual, self.ctx)
+        return self._value
 
 
 @dataclass

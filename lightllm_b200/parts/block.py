@@ -4,7 +4,7 @@ from __future__ import annotations
 from typing import List
 
 from ..config import LayerSpec, part_class
-from .base import Part
+from .base import LazyNorm, Part
 
 ARRANGEMENTS = ("pre_norm", "parallel")
 
@@ -31,11 +31,18 @@ class Block(Part):
     def children(self) -> List[Part]:
         return [self.norm1, self.mixer, self.norm2, self.ffn]
 
+    @staticmethod
+    def _normed(part, norm, residual, ctx):
+        """The part's input: the norm left to the part when it can fold it into its first kernel."""
+        if part.accepts_lazy_norm:
+            return LazyNorm(residual, norm, ctx)
+        return norm.forward(residual, ctx)
+
     def forward(self, residual, ctx, cache) -> None:
         if self.arrangement == "pre_norm":
-            self.mixer.forward(self.norm1.forward(residual, ctx), residual, ctx, cache)
-            self.ffn.forward(self.norm2.forward(residual, ctx), residual, ctx)
-        else:
+            self.mixer.forward(self._normed(self.mixer, self.norm1, residual, ctx), residual, ctx, cache)
+            self.ffn.forward(self._normed(self.ffn, self.norm2, residual, ctx), residual, ctx)
+        else:   # both branches read the same h, so both norms are computed before anything is added
             x1 = self.norm1.forward(residual, ctx)
             x2 = self.norm2.forward(residual, ctx)
             self.mixer.forward(x1, residual, ctx, cache)

@@ -58,6 +58,8 @@ class LMHead(Part):
         self.weight = tensors[self.name]
 
     def forward(self, x, ctx=None):
+        # The norm is not folded into this contraction: with a vocabulary's worth of blocks, each would
+        # repeat the norm of every row.
         return L.linear(x, self.weight, None, L.STORE_F32)
 
 

@@ -30,6 +30,42 @@ def tensor_core_eligible(x: torch.Tensor, w: torch.Tensor) -> bool:
             and ops.has_tcgen05())
 
 
+DECODE_ROWS = 64     # steps of at most this many rows use the fused decode contraction
+# Rows up to which the norm is folded into the contraction's prologue.  Measured on B200 at Qwen2.5-0.5B sizes
+# the separate norm kernel (2 us) beats the prologue (5 us at 8 rows, 30 us at 64), so it is off.
+FUSE_NORM_MAX_ROWS = 0
+
+
+def decode_eligible(M: int, w: torch.Tensor, act_dtype: torch.dtype, norm: bool, epilogue: int, head_dim: int = 0) -> bool:
+    return (M <= DECODE_ROWS and act_dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and ops.has_tcgen05()
+            and ops.gemm_decode_supports(M, w.shape[0], w.shape[1], norm, epilogue, head_dim))
+
+
+def split_k_for(M: int, N: int, K: int) -> int:
+    """Few rows leave only N/128 blocks; cut K so that the weights stream from all SMs."""
+    tiles, kblocks = -(-N // 128), -(-K // 64)
+    return max(1, min(kblocks, NUM_SMS // tiles))
+
+
+def split_k_fused(M: int, N: int, K: int) -> int:
+    """Splits for a decode contraction whose epilogue is fused (the splits meet in scratch).  Meeting
+    costs three more round trips to memory, so it only pays when the grid would otherwise leave most
+    SMs idle (the q/k/v projection: 9 blocks), and only for few rows, where the atomic adds are cheap."""
+    tiles, kblocks = -(-N // 128), -(-K // 64)
+    if M > 16 or tiles * 4 > NUM_SMS:
+        return 1
+    return max(1, min(kblocks, NUM_SMS // tiles))
+
+
+def reserve_fused_scratch(device: torch.device, N: int) -> None:
+    """Called when a part with a fused decode contraction of N output features is bound."""
+    if torch.device(device).type == "cuda":
+        ops.reserve_splitk_scratch(device, DECODE_ROWS * N, -(-N // 128))
+
+
+_DECODE_EPI = {STORE_F32: ops.DEPI_STORE_F32, RESIDUAL: ops.DEPI_RESIDUAL, SWIGLU: ops.DEPI_SWIGLU}
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, epilogue: int = STORE,
            out: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
     """Run the contraction; returns ``out`` (allocated here when not given), or ``None`` for the
@@ -41,13 +77,33 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
         out = torch.empty((M, cols), dtype=dt, device=x.device)
     if M == 0:
         return out
-    if tensor_core_eligible(x, w):
+
+    if epilogue in _DECODE_EPI and decode_eligible(M, w, x.dtype, False, _DECODE_EPI[epilogue]):
         split_k = 1
-        if epilogue == RESIDUAL and M <= 128:
-            # few rows: the grid has only N/128 blocks; cut K so that the weights stream from all SMs
-            tiles, kblocks = -(-N // 128), -(-x.shape[1] // 64)
-            split_k = max(1, min(kblocks, NUM_SMS // tiles))
+        if epilogue == RESIDUAL:
+            split_k = split_k_for(M, N, x.shape[1])
+        elif epilogue == SWIGLU:
+            split_k = split_k_fused(M, N, x.shape[1])
+        ops.gemm_decode(w, _DECODE_EPI[epilogue], M, a=x, bias=bias, out=out, residual=residual, split_k=split_k)
+    elif tensor_core_eligible(x, w):
+        split_k = split_k_for(M, N, x.shape[1]) if (epilogue == RESIDUAL and M <= 128) else 1
         ops.gemm_tcgen05(x, w, bias, epilogue, out, residual, split_k)
     else:
         ops.gemm_simt(x, w, bias, epilogue, out, residual)
     return out
+
+
+def linear_normed(lazy, w: torch.Tensor, bias: Optional[torch.Tensor], epilogue: int) -> torch.Tensor:
+    """``linear`` on a LazyNorm input: the norm runs inside the contraction when the shape allows."""
+    M, N = lazy.num_rows, w.shape[0]
+    rms = lazy.fusable()
+    if rms is not None and epilogue in _DECODE_EPI and 0 < M <= FUSE_NORM_MAX_ROWS and \
+            decode_eligible(M, w, lazy.norm.out_dtype, True, _DECODE_EPI[epilogue]):
+        cols = N // 2 if epilogue == SWIGLU else N
+        out = torch.empty((M, cols), dtype=torch.float32 if epilogue == STORE_F32 else torch.bfloat16,
+                          device=w.device)
+        ops.gemm_decode(w, _DECODE_EPI[epilogue], M, x=lazy.residual, x_rows=lazy.rows, norm_weight=rms[0],
+                        eps=rms[1], bias=bias, out=out,
+                        split_k=split_k_fused(M, N, w.shape[1]) if epilogue == SWIGLU else 1)
+        return out
+    return linear(lazy.materialize(), w, bias, epilogue)

@@ -8,7 +8,7 @@ import torch
 from ..config import register_part
 from ..weights import WeightSpec
 from . import linear as L
-from .base import FeedForward
+from .base import FeedForward, LazyNorm
 
 
 class GatedMLP(FeedForward):
@@ -48,13 +48,19 @@ class GatedMLP(FeedForward):
         I, D = g.shape
         self.w_gate_up = torch.stack([g.to(wdt), u.to(wdt)], dim=1).reshape(2 * I, D).contiguous()
         self.w_down = tensors[self._n("down", "weight")]
+        L.reserve_fused_scratch(device, 2 * I)
         if self.bias:
             bg, bu = tensors[self._n("gate", "bias")].float(), tensors[self._n("up", "bias")].float()
             self.b_gate_up = torch.stack([bg, bu], dim=1).reshape(2 * I).contiguous()
             self.b_down = tensors[self._n("down", "bias")].float().contiguous()
 
+    accepts_lazy_norm = True
+
     def forward(self, x, residual, ctx=None) -> None:
-        act = L.linear(x, self.w_gate_up, self.b_gate_up, L.SWIGLU)
+        if isinstance(x, LazyNorm):
+            act = L.linear_normed(x, self.w_gate_up, self.b_gate_up, L.SWIGLU)
+        else:
+            act = L.linear(x, self.w_gate_up, self.b_gate_up, L.SWIGLU)
         L.linear(act, self.w_down, self.b_down, L.RESIDUAL, residual=residual)
 
 

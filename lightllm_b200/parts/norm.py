@@ -31,6 +31,10 @@ class RMSNorm(Norm):
         self.weight = tensors[self.name]
         self.out_dtype = dtype
 
+    def rms_parameters(self):
+        """(weight, eps) for kernels that fold this norm into their prologue."""
+        return self.weight, self.eps
+
     def forward(self, residual, ctx=None):
         out = torch.empty(residual.shape, dtype=self.out_dtype, device=residual.device)
         ops.rmsnorm(residual, self.weight, self.eps, out)

@@ -40,6 +40,16 @@ class RotaryEmbedding(PositionEncoding):
     def rotary_table(self):
         return self.inv_freq, self.rotary_dim, self.style == "interleaved"
 
+    def step_table(self, ctx):
+        """(cos, sin) of every token of the step, computed once per step and shared by all layers
+        whose encoding has the same frequencies."""
+        from ..csrc import ops
+        key = ("rope_table", self.rotary_dim, self.theta)
+        hit = ctx.memo.get(key)
+        if hit is None:
+            hit = ctx.memo[key] = ops.rope_table(ctx.positions, self.inv_freq)
+        return hit
+
 
 class NoPositionEncoding(PositionEncoding):
     """Leaves q and k as they are."""

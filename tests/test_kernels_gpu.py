@@ -140,6 +140,113 @@ def test_gemm_tcgen05(ops, M, N, K, epi):
         assert torch.allclose(got, ref, atol=tol * scale, rtol=0), f"max diff {float((got - ref).abs().max())}"
 
 
+DECODE_SHAPES = [(1, 1152, 896), (8, 9728, 896), (13, 896, 4864), (16, 130, 64), (17, 200, 136), (40, 1000, 96),
+                 (64, 384, 192)]
+
+
+@pytest.mark.parametrize("M,N,K", DECODE_SHAPES)
+@pytest.mark.parametrize("norm", [False, True])
+@pytest.mark.parametrize("epi", ["store_f32", "residual", "swiglu"])
+def test_gemm_decode(ops, M, N, K, norm, epi):
+    """The fused decode contraction: optional RMSNorm prologue, float / residual (split-K) / SwiGLU epilogues."""
+    code = {"store_f32": ops.DEPI_STORE_F32, "residual": ops.DEPI_RESIDUAL, "swiglu": ops.DEPI_SWIGLU}[epi]
+    if norm and not ops.gemm_decode_supports(M, N, K, norm, code):
+        pytest.skip("the resident normalised operand does not fit in shared memory at this K")
+    assert ops.gemm_decode_supports(M, N, K, norm, code)
+    w = rnd((N, K), torch.bfloat16, 50, 0.2)
+    bias = rnd((N,), torch.float32, 51)
+    x = rnd((M + 3, K), torch.float32, 52, 2.0)
+    nw = (1 + 0.1 * rnd((K,), torch.float32, 53))
+    rows = torch.tensor([(5 * i + 2) % (M + 3) for i in range(M)], dtype=torch.int32, device=dev())
+    if norm:
+        a_ref = plain_rmsnorm(x.cpu()[rows.cpu().long()], nw.cpu(), 1e-5).to(torch.bfloat16)
+        kw = dict(x=x, x_rows=rows, norm_weight=nw, eps=1e-5)
+    else:
+        a_ref = x[:M].to(torch.bfloat16).cpu()
+        kw = dict(a=a_ref.to(dev()))
+    ops.reserve_splitk_scratch(dev(), 64 * N, -(-N // 128))
+    for split_k in ((1, 3) if epi in ("residual", "swiglu") else (1,)):
+        residual = rnd((M, N), torch.float32, 54)
+        res0 = residual.clone()
+        out = None
+        if epi == "store_f32":
+            out = torch.full((M, N), float("nan"), dtype=torch.float32, device=dev())
+        elif epi == "swiglu":
+            out = torch.full((M, N // 2), float("nan"), dtype=torch.bfloat16, device=dev())
+        ops.gemm_decode(w, code, M, bias=bias, out=out, residual=residual if epi == "residual" else None,
+                        split_k=split_k, **kw)
+        ops.check_async_errors(dev())
+        ref = gemm_reference(a_ref, w, bias, {"store_f32": 1, "residual": 2, "swiglu": 3}[epi], res0)
+        got = (residual if epi == "residual" else out).double().cpu()
+        assert not torch.isnan(got).any()
+        tol = (2e-2 if norm else 1e-5 * math.sqrt(K)) if epi != "swiglu" else 2e-2
+        scale = max(1.0, float(ref.abs().max()))
+        assert torch.allclose(got, ref, atol=tol * scale, rtol=0), f"max diff {float((got - ref).abs().max())}"
+
+
+@pytest.mark.parametrize("M", [1, 8, 33])
+@pytest.mark.parametrize("hd,rd,inter,Hq,Hkv", [(64, 64, False, 14, 2), (128, 64, True, 3, 1), (32, 32, False, 6, 3),
+                                                (16, 16, False, 4, 2)])
+@pytest.mark.parametrize("norm", [False, True])
+def test_gemm_decode_rope_kv(ops, M, hd, rd, inter, Hq, Hkv, norm):
+    """q/k/v projection with bias, rotary positions and the cache write in the epilogue, against the
+    plain parts; and the q-only form that leaves the cache alone."""
+    K, page, npages = 72, 8, 12
+    N = (Hq + 2 * Hkv) * hd
+    assert ops.gemm_decode_supports(M, N, K, norm, ops.DEPI_ROPE_KV, hd)
+    w = rnd((N, K), torch.bfloat16, 60, 0.3)
+    bias = rnd((N,), torch.float32, 61)
+    x = rnd((M, K), torch.float32, 62, 2.0)
+    nw = 1 + 0.1 * rnd((K,), torch.float32, 63)
+    if norm:
+        a_ref = plain_rmsnorm(x.cpu(), nw.cpu(), 1e-6).to(torch.bfloat16)
+        kw = dict(x=x, norm_weight=nw.to(torch.bfloat16), eps=1e-6)
+        a_ref = plain_rmsnorm(x.cpu(), nw.to(torch.bfloat16).float().cpu(), 1e-6).to(torch.bfloat16)
+    else:
+        a_ref = x.to(torch.bfloat16).cpu()
+        kw = dict(a=a_ref.to(dev()))
+    g = torch.Generator().manual_seed(64)
+    pos = torch.randint(0, 3000, (M,), generator=g, dtype=torch.int32)
+    slots = torch.randperm(npages * page, generator=g)[:M].to(torch.int32)
+    if M > 2:
+        slots[1] = -1
+    theta = 10000.0
+    inv = torch.from_numpy((1.0 / np.power(np.float64(theta), np.arange(0, rd, 2, dtype=np.float64) / rd))
+                           .astype(np.float32)).to(dev())
+    kc = torch.full((npages * page, Hkv, hd), 77.0, dtype=torch.bfloat16, device=dev())
+    vc = torch.full((npages * page, Hkv, hd), 77.0, dtype=torch.bfloat16, device=dev())
+    q = torch.full((M, Hq * hd), float("nan"), dtype=torch.bfloat16, device=dev())
+    table = ops.rope_table(pos.to(dev()), inv)
+    ops.reserve_splitk_scratch(dev(), 64 * N, -(-N // 128))
+    ops.gemm_decode(w, ops.DEPI_ROPE_KV, M, bias=bias, slot_mapping=slots.to(dev()), split_k=2 if M < 20 else 1,
+                    rope_table=table, rotary_dim=rd, interleaved=inter, num_heads=Hq, num_kv_heads=Hkv, head_dim=hd,
+                    q_out=q, k_cache=kc, v_cache=vc, **kw)
+    ops.check_async_errors(dev())
+    y = (a_ref.double() @ w.double().cpu().t() + bias.double().cpu()).float()
+    qr = plain_rope(y[:, : Hq * hd].reshape(M, Hq, hd), pos, theta, rd, inter)
+    kr = plain_rope(y[:, Hq * hd: (Hq + Hkv) * hd].reshape(M, Hkv, hd), pos, theta, rd, inter)
+    vr = y[:, (Hq + Hkv) * hd:].reshape(M, Hkv, hd)
+    tol = 3e-2
+    scale = max(1.0, float(y.abs().max()))
+    assert torch.allclose(q.float().cpu().reshape(M, Hq, hd), qr, atol=tol * scale, rtol=0)
+    kexp = torch.full((npages * page, Hkv, hd), 77.0)
+    vexp = kexp.clone()
+    for t, sl in enumerate(slots.tolist()):
+        if sl >= 0:
+            kexp[sl], vexp[sl] = kr[t], vr[t]
+    assert torch.allclose(kc.float().cpu(), kexp, atol=tol * scale, rtol=0)
+    assert torch.allclose(vc.float().cpu(), vexp, atol=tol * scale, rtol=0)
+    q2 = torch.full((M, Hq * hd), float("nan"), dtype=torch.bfloat16, device=dev())
+    kw2 = dict(kw)
+    ops.gemm_decode(w[: Hq * hd], ops.DEPI_ROPE_KV, M, bias=bias[: Hq * hd].contiguous(),
+                    rope_table=table, rotary_dim=rd, interleaved=inter, num_heads=Hq, num_kv_heads=Hkv, head_dim=hd,
+                    q_out=q2, **kw2)
+    ops.check_async_errors(dev())
+    assert torch.allclose(q2.float(), q.float(), atol=tol * scale, rtol=0)
+    sc = ops.splitk_scratch(dev())
+    assert float(sc[0].abs().max()) == 0.0 and int(sc[1].abs().max()) == 0       # the meeting place is left clean
+
+
 @pytest.mark.parametrize("dtype", DT)
 @pytest.mark.parametrize("hd,rd,inter", [(16, 16, False), (32, 32, True), (64, 64, False), (48, 32, False),
                                          (128, 64, True)])
@@ -326,6 +433,38 @@ def test_attention_tcgen05_refuses_other_shapes(ops):
     with pytest.raises(ops.KernelError, match="not supported"):
         ops.paged_attention_tcgen05(z, z.view(4, 1, 48), z.view(4, 1, 48), z, i, i, 1, i, i, i, i.view(1, 1), 1, 16,
                                     1, 1, 48, 0, 1.0)
+
+
+MMA_DECODE_CASES = [
+    # Hq, Hkv, hd, page, starts (context = start + 1), window
+    (14, 2, 64, 16, [300, 15, 0, 2047], None),
+    (12, 2, 128, 16, [700, 31, 32], None),
+    (28, 4, 128, 8, [100, 1], 64),
+    (16, 1, 64, 32, [513, 64, 5], None),
+    (4, 4, 64, 16, [129], 100),
+    (3, 1, 64, 4, [77, 78, 79, 80, 81], None),
+]
+
+
+@pytest.mark.parametrize("case", MMA_DECODE_CASES)
+@pytest.mark.parametrize("nsplit", [1, 3, 16])
+@pytest.mark.parametrize("spike", [False, True])
+def test_paged_decode_mma(ops, case, nsplit, spike):
+    Hq, Hkv, hd, page, starts, window = case
+    assert ops.paged_decode_mma_supports(Hq, Hkv, hd)
+    lens = [1] * len(starts)
+    s = paged_setup(torch.bfloat16, lens, starts, Hq, Hkv, hd, page, seed=25, spike=spike)
+    s["kc"] = torch.nan_to_num(s["kc"], nan=3.0)         # unwritten cache rows are finite in the engine
+    s["vc"] = torch.nan_to_num(s["vc"], nan=-7.0)
+    ts, tq, nt = tiles_for(lens, 1)
+    out = torch.full((s["rows"], Hq * hd), float("nan"), dtype=torch.bfloat16, device=dev())
+    scratch = torch.empty(max(1, ops.attention_scratch_floats(nt, Hq, hd, 1, nsplit)), dtype=torch.float32, device=dev())
+    ops.paged_decode_mma(s["q"], s["kc"], s["vc"], out, ts, tq, nt, s["span_row"], s["span_pos"], s["bt"],
+                         s["max_pages"], page, Hq, Hkv, hd, window or 0, 1.0 / math.sqrt(hd), nsplit, scratch)
+    ref = attention_reference(s["full"], lens, starts, hd, window).reshape(s["rows"], Hq * hd)
+    got = out.float().cpu()
+    assert not torch.isnan(got).any()
+    assert torch.allclose(got, ref, atol=2e-2, rtol=2e-2), f"max diff {float((got - ref).abs().max())}"
 
 
 def test_argmax_lowest_index_on_ties(ops):
