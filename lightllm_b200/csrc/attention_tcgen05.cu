@@ -4,7 +4,7 @@
 // come from the request's pages, 128 keys at a time: TMA copies each page of the tile (a box of
 // page_size rows x 64 elements) into a swizzled shared-memory tile, double buffered.  Then
 //     S = Q K^T          tcgen05.mma, both operands K-major, S in tensor memory (128 columns)
-//     softmax            one thread per query row reads its row of S with tcgen05.ld; scale, mask by
+//     softmax            two threads per query row (each half of the tile's keys) read S with tcgen05.ld; scale, mask by
 //                        absolute position (and window), running max and sum in float
 //     O_tile = P V       P (bf16) goes back to shared memory as the A operand; V is the B operand in
 //                        MN-major form (its rows are keys), result in tensor memory
@@ -27,8 +27,8 @@ namespace {
 
 constexpr int BQ = 128;     // query rows per block = TMEM lanes
 constexpr int BKV = 128;    // keys per tile
-constexpr int NUM_THREADS = 128;
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+constexpr int NUM_THREADS = 256;   // two threads per query row: each takes half of a tile's keys and half of the output
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;   // about 2 s of SM cycles
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ unsigned long long globaltimer_ns() {
@@ -55,13 +55,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = globaltimer_ns();
-    while (true) {
+    // The time limit is checked once every 256 failed attempts, on the SM's own cycle counter: reading a
+    // timer inside the loop would add its latency to every wake-up.
+    const long long t0 = clock64();
+    for (unsigned spins = 1;; ++spins) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
-            *abort_flag = 1;
-            return false;
+        if ((spins & 255u) == 0u) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                *abort_flag = 1;
+                return false;
+            }
         }
     }
 }
@@ -122,12 +126,12 @@ __device__ __forceinline__ float fast_exp2(float x) {
 __device__ __forceinline__ bool key_visible(int kp, int qpos, int hi, int lo, int window) {
     return kp <= qpos && kp < hi && kp >= lo && (window <= 0 || qpos - kp < window);
 }
-// Largest raw score of this thread's row among the visible keys of the tile.
+// Largest raw score of this thread's row among the visible keys of its two 32-column chunks of the tile.
 template <bool MASKED>
-__device__ __forceinline__ float row_max(uint32_t tmem_s, int kt, int qpos, int hi, int lo, int window) {
+__device__ __forceinline__ float row_max(uint32_t tmem_s, int c_begin, int kt, int qpos, int hi, int lo, int window) {
     float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
+    for (int c = c_begin; c < c_begin + 2; ++c) {
         float s[32];
         tmem_ld32(tmem_s + c * 32, s);
         if (MASKED) {
@@ -142,14 +146,14 @@ __device__ __forceinline__ float row_max(uint32_t tmem_s, int kt, int qpos, int 
     }
     return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
 }
-// p = 2^(s*c - m) of the row's 128 scores, written as bf16 into the swizzled A-operand tiles; returns
+// p = 2^(s*c - m) of this thread's 64 scores of the row, written as bf16 into the swizzled A-operand tiles; returns
 // their sum (float, before rounding).  Row r, 16-byte chunk q of a 128-byte row lands at chunk q ^ (r & 7).
 template <bool MASKED>
-__device__ __forceinline__ float row_probs(uint32_t tmem_s, uint8_t* p_s, int r, float c_scale, float m_use, int kt,
-                                           int qpos, int hi, int lo, int window) {
+__device__ __forceinline__ float row_probs(uint32_t tmem_s, uint8_t* p_s, int r, int c_begin, float c_scale, float m_use,
+                                           int kt, int qpos, int hi, int lo, int window) {
     float l0 = 0.0f, l1 = 0.0f;
 #pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
+    for (int c = c_begin; c < c_begin + 2; ++c) {
         float s[32];
         tmem_ld32(tmem_s + c * 32, s);
         if (MASKED) {
@@ -188,11 +192,19 @@ struct AttnTcParams {
     int max_pages, page_size, Hq, Hkv, window, num_slots;
     float scale_log2e;         // scale * log2(e): scores are kept in base-2 units
     uint32_t dynamic_smem_bytes;
+    // Optional cut of a tile's key range into work items, so that long rows do not set the kernel's time:
+    // item i covers key tiles [tile_k0[i], tile_k0[i] + tile_nk[i]) of its query tile and, when tile_part[i] >= 0,
+    // leaves its unnormalised (O, m, l) in part_o / part_ml for the merge kernel instead of writing the output.
+    const int* tile_k0;
+    const int* tile_nk;
+    const int* tile_part;
+    float* part_o;             // [parts, Hq, 128, HD]
+    float* part_ml;            // [parts, Hq, 128, 2]  (m in base-2 units, l)
     int* error_flag;
 };
 
 template <int HD>
-__global__ void __launch_bounds__(NUM_THREADS)
+__global__ void __launch_bounds__(NUM_THREADS, HD <= 64 ? 2 : 1)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, const AttnTcParams p) {
     constexpr int KB = HD / 64;                       // 64-element blocks along the head dimension
@@ -204,6 +216,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     __shared__ __align__(8) uint64_t bars[5];
     __shared__ uint32_t tmem_slot_s;
     __shared__ int abort_s;
+    // The halves of a row agree on its maximum through this buffer.  The value is rounded up to bf16: any
+    // common shift works for the softmax, and 512 bytes keep two blocks of the head-64 kernel within one SM.
+    __shared__ __nv_bfloat16 xch[2][BQ];
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* q_s = smem;                              // KB tiles
@@ -232,8 +247,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const int* bt = p.block_table + (size_t)span * p.max_pages;
     const int hi = pos0 + nrows;                                   // keys [lo, hi) can be visible
     const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
-    const int kt0 = (lo / BKV) * BKV;
-    const int ntiles = (hi - kt0 + BKV - 1) / BKV;
+    const int k_first = p.tile_k0 ? p.tile_k0[tile] : 0;
+    const int kt0 = (lo / BKV) * BKV + k_first * BKV;
+    const int all_tiles = (hi - (lo / BKV) * BKV + BKV - 1) / BKV - k_first;
+    const int ntiles = p.tile_nk ? min(p.tile_nk[tile], all_tiles) : all_tiles;
+    const int part = p.tile_part ? p.tile_part[tile] : -1;
 
     if (threadIdx.x == 0) {
         mbar_init(bar_q, 1);
@@ -254,8 +272,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_s = tmem_base + ((uint32_t)(warp * 32) << 16);
-    const uint32_t tmem_o = tmem_s + 128;
+    const int half = warp >> 2;                       // which half of the keys (and of the output dimensions)
+    const uint32_t tmem_s = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+    const uint32_t tmem_o = tmem_s + 128 + half * (HD / 2);
 
     // Loads of one key/value tile: each lane of warp 0 takes pages of the tile.
     auto load_kv = [&](int j) {
@@ -288,11 +307,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         if (ntiles > 0) load_kv(0);
     }
 
-    const int r = threadIdx.x;                  // query row of this thread = TMEM lane
+    const int r = threadIdx.x & (BQ - 1);       // query row of this thread = TMEM lane
     const int qpos = pos0 + r;
-    float o[HD];
+    constexpr int HO = HD / 2;                  // output dimensions of this thread
+    float o[HO];
 #pragma unroll
-    for (int d = 0; d < HD; ++d) o[d] = 0.0f;
+    for (int d = 0; d < HO; ++d) o[d] = 0.0f;
     float m_run = -INFINITY, l_run = 0.0f;
     bool ok = mbar_wait(bar_q, 0, abort_flag);
 
@@ -325,15 +345,17 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         // below the diagonal and inside the window of every row of the block skip the masking.
         const bool interior = (kt + BKV - 1 <= pos0) && (p.window <= 0 || (pos0 + BQ - 1) - kt < p.window);
         float m_tile;
-        if (interior) m_tile = row_max<false>(tmem_s, kt, qpos, hi, lo, p.window);
-        else m_tile = row_max<true>(tmem_s, kt, qpos, hi, lo, p.window);
-        m_tile *= p.scale_log2e;                                      // the scale is positive
+        if (interior) m_tile = row_max<false>(tmem_s, 2 * half, kt, qpos, hi, lo, p.window);
+        else m_tile = row_max<true>(tmem_s, 2 * half, kt, qpos, hi, lo, p.window);
+        xch[half][r] = __float2bfloat16_ru(m_tile);      // rewritten only after the barriers further down
+        __syncthreads();
+        m_tile = fmaxf(__bfloat162float(xch[0][r]), __bfloat162float(xch[1][r])) * p.scale_log2e;   // the scale is positive
         const float m_new = fmaxf(m_run, m_tile);
         const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;      // nothing visible yet: all p are 0
         const float corr = (m_run == -INFINITY) ? 0.0f : fast_exp2(m_run - m_use);
         float l_tile;
-        if (interior) l_tile = row_probs<false>(tmem_s, p_s, r, p.scale_log2e, m_use, kt, qpos, hi, lo, p.window);
-        else l_tile = row_probs<true>(tmem_s, p_s, r, p.scale_log2e, m_use, kt, qpos, hi, lo, p.window);
+        if (interior) l_tile = row_probs<false>(tmem_s, p_s, r, 2 * half, p.scale_log2e, m_use, kt, qpos, hi, lo, p.window);
+        else l_tile = row_probs<true>(tmem_s, p_s, r, 2 * half, p.scale_log2e, m_use, kt, qpos, hi, lo, p.window);
         l_run = l_run * corr + l_tile;
         m_run = m_new;
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // P is read by the tensor core
@@ -353,7 +375,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-        for (int c = 0; c < HD / 32; ++c) {
+        for (int c = 0; c < HO / 32; ++c) {
             float t[32];
             tmem_ld32(tmem_o + c * 32, t);
 #pragma unroll
@@ -363,11 +385,25 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         __syncthreads();        // S and the P V columns may be overwritten, P and this K/V stage reused
     }
 
-    if (ok && r < nrows) {
-        const float inv = 1.0f / l_run;
-        __nv_bfloat16* dst = p.out + ((size_t)(row0 + r) * p.Hq + head) * HD;
+    // The halves of a row add up their sums; each writes its half of the dimensions.
+    float* lx = reinterpret_cast<float*>(p_s);         // the P tile is idle now
+    lx[half * BQ + r] = l_run;
+    __syncthreads();
+    const float l_row = lx[r] + lx[BQ + r];
+    if (ok && r < nrows && part >= 0) {
+        float* po = p.part_o + (((size_t)part * p.Hq + head) * BQ + r) * HD + half * HO;
 #pragma unroll
-        for (int d = 0; d < HD; d += 8) {
+        for (int d = 0; d < HO; d += 4) *reinterpret_cast<float4*>(po + d) = make_float4(o[d], o[d + 1], o[d + 2], o[d + 3]);
+        if (half == 0) {
+            float* pm = p.part_ml + (((size_t)part * p.Hq + head) * BQ + r) * 2;
+            pm[0] = m_run;
+            pm[1] = l_row;
+        }
+    } else if (ok && r < nrows) {
+        const float inv = 1.0f / l_row;
+        __nv_bfloat16* dst = p.out + ((size_t)(row0 + r) * p.Hq + head) * HD + half * HO;
+#pragma unroll
+        for (int d = 0; d < HO; d += 8) {
             uint32_t w[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
@@ -384,6 +420,54 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     if (warp == 0) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// Merge of the items of one query tile: out = sum_c 2^(m_c - M) O_c / sum_c 2^(m_c - M) l_c.
+struct MergeParams {
+    __nv_bfloat16* out;
+    const int* merge_span;     // [NM]
+    const int* merge_q0;
+    const int* merge_first;    // first part of the tile
+    const int* merge_count;    // number of parts
+    const int* span_row;
+    const int* span_len;
+    const float* part_o;
+    const float* part_ml;
+    int Hq, HD;
+};
+
+__global__ void __launch_bounds__(256) attention_tcgen05_merge_kernel(MergeParams p) {
+    // A group of HD/4 threads takes one row (four dimensions each, so a row's loads are contiguous); the
+    // blocks of grid.z share the tile's rows.
+    const int mt = blockIdx.x, head = blockIdx.y;
+    const int span = p.merge_span[mt], q0 = p.merge_q0[mt];
+    const int nrows = min(BQ, p.span_len[span] - q0);
+    const int first = p.merge_first[mt], count = p.merge_count[mt];
+    const int HD = p.HD;
+    const int tpr = HD / 4;                              // threads per row
+    const int d = (threadIdx.x % tpr) * 4;
+    const int rows_per_block = blockDim.x / tpr;
+    for (int r = blockIdx.z * rows_per_block + threadIdx.x / tpr; r < nrows; r += gridDim.z * rows_per_block) {
+        float M = -INFINITY;
+        for (int c = 0; c < count; ++c) M = fmaxf(M, p.part_ml[(((size_t)(first + c) * p.Hq + head) * BQ + r) * 2]);
+        float L = 0.0f;
+        float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (int c = 0; c < count; ++c) {
+            const size_t base = ((size_t)(first + c) * p.Hq + head) * BQ + r;
+            const float m = p.part_ml[base * 2];
+            if (m == -INFINITY) continue;
+            const float w = fast_exp2(m - M);
+            L += w * p.part_ml[base * 2 + 1];
+            const float4 a = *reinterpret_cast<const float4*>(p.part_o + base * HD + d);
+            acc.x += w * a.x; acc.y += w * a.y; acc.z += w * a.z; acc.w += w * a.w;
+        }
+        const float inv = 1.0f / L;
+        __nv_bfloat16* dst = p.out + ((size_t)(p.span_row[span] + q0 + r) * p.Hq + head) * HD + d;
+        const __nv_bfloat162 h0 = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+        const __nv_bfloat162 h1 = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+        *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<const uint32_t*>(&h0),
+                                                    *reinterpret_cast<const uint32_t*>(&h1));
     }
 }
 
@@ -425,7 +509,9 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
            cudaStream_t stream) {
     constexpr int KB = HD / 64;
     // tiles + what aligning to 1024 bytes can cost after the 48 bytes of static shared memory
-    constexpr size_t smem = (size_t)(KB + 4 * KB + 2) * 128 * 128 + 976;
+    // 560 bytes of static shared memory (barriers, the halves' exchange) precede the tiles; the rest of the
+    // kilobyte is what aligning the tiles to 1024 bytes can cost (checked in the kernel)
+    constexpr size_t smem = (size_t)(KB + 4 * KB + 2) * 128 * 128 + 1024 - 560;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -450,14 +536,19 @@ LLB_EXPORT int llb_attention_tcgen05_supports(int hd, int page_size) {
 
 // q, out [T, Hq, hd] bf16; k_cache, v_cache [num_slots, Hkv, hd] bf16 with slot = page*page_size + offset;
 // tiles of 128 query rows: tile_span, tile_q0 [num_tiles]; span_row, span_len, span_pos [S];
-// block_table [S, max_pages].  window <= 0: every earlier key is visible.
+// block_table [S, max_pages].  window <= 0: every earlier key is visible.  tile_k0 / tile_nk / tile_part (or all
+// null) cut tiles into items over ranges of 128-key tiles; items with tile_part >= 0 write partial results to
+// part_scratch (num_parts * Hq * 128 * (hd + 2) floats) for llb_attention_tcgen05_merge.
 LLB_EXPORT int llb_paged_attention_tcgen05(const void* q, const void* k_cache, const void* v_cache, void* out, int T,
                                            const int* tile_span, const int* tile_q0, int num_tiles,
                                            const int* span_row, const int* span_len, const int* span_pos,
                                            const int* block_table, int max_pages, int page_size, int num_slots,
-                                           int Hq, int Hkv, int hd, int window, float scale, int* error_flag,
-                                           cudaStream_t stream) {
+                                           int Hq, int Hkv, int hd, int window, float scale, const int* tile_k0,
+                                           const int* tile_nk, const int* tile_part, float* part_scratch,
+                                           int num_parts, int* error_flag, cudaStream_t stream) {
     if (num_tiles == 0) return 0;
+    LLB_REQUIRE(tile_part == nullptr || (tile_k0 && tile_nk && (num_parts == 0 || part_scratch)),
+                "attention_tcgen05: a cut key range needs tile_k0, tile_nk, tile_part and scratch");
     LLB_REQUIRE(llb_attention_tcgen05_supports(hd, page_size),
                 "attention_tcgen05: head_dim %d with page size %d is not supported (head 64 or 128; page size a "
                 "multiple of 8 that divides 128)", hd, page_size);
@@ -474,6 +565,26 @@ LLB_EXPORT int llb_paged_attention_tcgen05(const void* q, const void* k_cache, c
     p.tile_span = tile_span; p.tile_q0 = tile_q0; p.span_row = span_row; p.span_len = span_len; p.span_pos = span_pos;
     p.block_table = block_table; p.max_pages = max_pages; p.page_size = page_size; p.Hq = Hq; p.Hkv = Hkv;
     p.window = window; p.num_slots = num_slots; p.scale_log2e = scale * 1.4426950408889634f; p.error_flag = error_flag;
+    p.tile_k0 = tile_k0; p.tile_nk = tile_nk; p.tile_part = tile_part;
+    p.part_o = part_scratch;
+    p.part_ml = part_scratch ? part_scratch + (size_t)num_parts * Hq * BQ * hd : nullptr;
     if (hd == 64) return launch<64>(mq, mk, mv, p, num_tiles, stream);
     return launch<128>(mq, mk, mv, p, num_tiles, stream);
+}
+
+// Merges the partial results of cut tiles: merge_span, merge_q0, merge_first, merge_count [num_merge] name each
+// query tile, its first part and its number of parts.
+LLB_EXPORT int llb_attention_tcgen05_merge(void* out, const int* merge_span, const int* merge_q0, const int* merge_first,
+                                           const int* merge_count, int num_merge, const int* span_row,
+                                           const int* span_len, const float* part_scratch, int num_parts, int Hq,
+                                           int hd, cudaStream_t stream) {
+    if (num_merge == 0) return 0;
+    LLB_REQUIRE(num_merge > 0 && part_scratch && num_parts > 0 && Hq > 0 && Hq <= 65535 && hd % 8 == 0,
+                "attention_tcgen05_merge: bad arguments");
+    MergeParams p;
+    p.out = (__nv_bfloat16*)out; p.merge_span = merge_span; p.merge_q0 = merge_q0; p.merge_first = merge_first;
+    p.merge_count = merge_count; p.span_row = span_row; p.span_len = span_len; p.part_o = part_scratch;
+    p.part_ml = part_scratch + (size_t)num_parts * Hq * BQ * hd; p.Hq = Hq; p.HD = hd;
+    attention_tcgen05_merge_kernel<<<dim3(num_merge, Hq, BQ / (256 / (hd / 4))), 256, 0, stream>>>(p);
+    return llb_check_launch("attention_tcgen05_merge");
 }

@@ -25,8 +25,10 @@ using namespace t5;
 
 constexpr int TILE_M = 128;
 constexpr int TILE_K = 64;
-// Depth of the TMA ring: a block streams its weights at (bytes in flight) / latency, so few rows get a deep ring.
-__host__ __device__ constexpr int stages_for(int bn) { return 8; }
+// Depth of the TMA ring: a block streams its weights at (bytes in flight) / latency.  Grids of a few blocks
+// get a deep ring (8 stages, one block per SM); grids of many blocks (the head) a short one (4 stages), so
+// that two blocks share an SM.
+constexpr int DEEP = 8, SHALLOW = 4;
 constexpr int NUM_THREADS = 192;
 constexpr uint32_t A_BYTES = TILE_M * TILE_K * 2;
 
@@ -58,11 +60,10 @@ struct DecodeGemmParams {
     int* error_flag;
 };
 
-template <int BN, int EPI, bool NORM>
+template <int BN, int EPI, bool NORM, int STAGES>
 __global__ void __launch_bounds__(NUM_THREADS)
 gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                    const DecodeGemmParams p) {
-    constexpr int STAGES = stages_for(BN);
     constexpr uint32_t B_BYTES = BN * TILE_K * 2;
     constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
     __shared__ __align__(8) uint64_t full_bar[8];
@@ -350,27 +351,35 @@ int cached_map(const void* ptr, long long rows, long long cols, int box, CUtenso
     return 0;
 }
 
-size_t smem_bytes(int BN, int b_tiles, bool rope) {
-    (void)rope;     // the rotary epilogue stages its tile over the weight ring (128 x 65 floats < 8 x 16 KB)
-    return (size_t)stages_for(BN) * A_BYTES + (size_t)b_tiles * BN * TILE_K * 2 + 1024;
+size_t smem_bytes(int BN, int stages, int b_tiles) {
+    // the rotary epilogue stages its tile over the weight ring (128 x 65 floats < 8 x 16 KB)
+    return (size_t)stages * A_BYTES + (size_t)b_tiles * BN * TILE_K * 2 + 1024;
 }
 
-template <int BN, int EPI, bool NORM>
-int launch(const CUtensorMap& mw, const CUtensorMap& mx, const DecodeGemmParams& p, int split_k, cudaStream_t stream) {
-    const size_t smem = smem_bytes(BN, NORM ? p.num_kb : stages_for(BN), EPI == DEPI_ROPE_KV);
+template <int BN, int EPI, bool NORM, int STAGES>
+int launch_stages(const CUtensorMap& mw, const CUtensorMap& mx, const DecodeGemmParams& p, int split_k, cudaStream_t stream) {
+    const size_t smem = smem_bytes(BN, STAGES, NORM ? p.num_kb : STAGES);
     LLB_REQUIRE(smem <= 224 * 1024, "gemm_decode: K=%d with %d rows needs %zu bytes of shared memory", p.K, BN, smem);
     static size_t configured = 0;
     if (smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_decode_kernel<BN, EPI, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(gemm_decode_kernel<BN, EPI, NORM, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)smem);
         if (e != cudaSuccess) return llb_fail("gemm_decode: cannot opt in to %zu bytes of shared memory: %s", smem,
                                               cudaGetErrorString(e));
         configured = smem;
     }
     dim3 grid(llb_ceil_div(p.N, TILE_M), 1, split_k);
-    cudaError_t e = launch_pdl(gemm_decode_kernel<BN, EPI, NORM>, grid, dim3(NUM_THREADS), smem, stream, mw, mx, p);
+    cudaError_t e = launch_pdl(gemm_decode_kernel<BN, EPI, NORM, STAGES>, grid, dim3(NUM_THREADS), smem, stream, mw, mx, p);
     if (e != cudaSuccess) return llb_fail("gemm_decode: launch failed: %s", cudaGetErrorString(e));
     return llb_check_launch("gemm_decode");
+}
+
+template <int BN, int EPI, bool NORM>
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, const DecodeGemmParams& p, int split_k, cudaStream_t stream) {
+    // the float-store epilogue is the head's: a vocabulary's worth of blocks
+    if (EPI == DEPI_STORE_F32 && !NORM && llb_ceil_div(p.N, TILE_M) >= 2 * 148)
+        return launch_stages<BN, EPI, NORM, SHALLOW>(mw, mx, p, split_k, stream);
+    return launch_stages<BN, EPI, NORM, DEEP>(mw, mx, p, split_k, stream);
 }
 
 template <int BN, bool NORM>
@@ -400,7 +409,7 @@ LLB_EXPORT int llb_gemm_decode_supports(int M, int N, int K, int norm, int epilo
     if (M < 1 || M > 64 || K % 8 != 0 || N < 1) return 0;
     const int BN = M <= 16 ? 16 : M <= 32 ? 32 : 64;
     const int num_kb = llb_ceil_div(K, TILE_K);
-    if (smem_bytes(BN, norm ? num_kb : stages_for(BN), epilogue == DEPI_ROPE_KV) > 224 * 1024) return 0;
+    if (smem_bytes(BN, DEEP, norm ? num_kb : DEEP) > 224 * 1024) return 0;
     if (epilogue == DEPI_SWIGLU && N % 2) return 0;
     if (epilogue == DEPI_ROPE_KV && (hd < 2 || TILE_M % hd != 0)) return 0;
     return 1;

@@ -26,12 +26,15 @@
 
 namespace {
 
+// SiLU for the bf16 epilogues: the fast exponential and division are far inside bf16's rounding.
+__device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+
 constexpr int TILE_M = 128;       // rows of the A role = TMEM lanes
 constexpr int TILE_K = 64;        // bf16 elements per stage row = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int STAGES = 3;
 constexpr int NUM_THREADS = 192;
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // 2 s
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;   // about 2 s of SM cycles
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -61,13 +64,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait: false when the time limit ran out (or another role already gave up).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = globaltimer_ns();
-    while (true) {
+    // The time limit is checked once every 256 failed attempts, on the SM's own cycle counter: reading a
+    // timer inside the loop would add its latency to every wake-up.
+    const long long t0 = clock64();
+    for (unsigned spins = 1;; ++spins) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
-            *abort_flag = 1;
-            return false;
+        if ((spins & 255u) == 0u) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                *abort_flag = 1;
+                return false;
+            }
         }
     }
 }
@@ -141,6 +148,91 @@ struct GemmParams {
     int kb_per_split;       // K blocks per grid.z slice
     int* error_flag;        // raised when a wait ran out of time
 };
+
+// Epilogue of one thread in the row-major orientation: token row m, CHUNK consecutive output features
+// starting at nb, accumulators in r.  Whole 16-byte vectors are written where the row allows.
+template <int EPI, int CHUNK>
+__device__ __forceinline__ void epilogue_row(const GemmParams& p, int m, int nb, const uint32_t (&r)[32]) {
+    if (m < p.M && nb < p.N) {
+        float v[CHUNK];
+#pragma unroll
+        for (int j = 0; j < CHUNK; ++j) v[j] = __uint_as_float(r[j]);
+        const bool full = nb + CHUNK <= p.N;
+        if (p.bias && blockIdx.z == 0) {
+#pragma unroll
+            for (int j = 0; j < CHUNK; ++j)
+                if (full || nb + j < p.N) v[j] += p.bias[nb + j];
+        }
+        if (EPI == LLB_EPI_SWIGLU) {
+            __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)m * (p.N / 2) + (nb >> 1);
+            if (full && (p.N % 16) == 0) {     // 16-byte stores of 8 outputs
+#pragma unroll
+                for (int j = 0; j < CHUNK; j += 16) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const __nv_bfloat162 h = __floats2bfloat162_rn(
+                            silu_fast(v[j + 4 * e]) * v[j + 4 * e + 1],
+                            silu_fast(v[j + 4 * e + 2]) * v[j + 4 * e + 3]);
+                        w[e] = *reinterpret_cast<const uint32_t*>(&h);
+                    }
+                    *reinterpret_cast<uint4*>(o + (j >> 1)) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < CHUNK; j += 2)
+                    if (nb + j + 1 < p.N) o[j >> 1] = __float2bfloat16_rn(llb_silu(v[j]) * v[j + 1]);
+            }
+        } else if (EPI == LLB_EPI_STORE) {
+            __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)m * p.N + nb;
+            if (full && (p.N % 8) == 0) {
+#pragma unroll
+                for (int j = 0; j < CHUNK; j += 8) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const __nv_bfloat162 h = __floats2bfloat162_rn(v[j + 2 * e], v[j + 2 * e + 1]);
+                        w[e] = *reinterpret_cast<const uint32_t*>(&h);
+                    }
+                    *reinterpret_cast<uint4*>(o + j) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < CHUNK; ++j)
+                    if (nb + j < p.N) o[j] = __float2bfloat16_rn(v[j]);
+            }
+        } else if (EPI == LLB_EPI_STORE_F32) {
+            float* o = (float*)p.out + (size_t)m * p.N + nb;
+            if (full && (p.N % 4) == 0) {
+#pragma unroll
+                for (int j = 0; j < CHUNK; j += 4)
+                    *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < CHUNK; ++j)
+                    if (nb + j < p.N) o[j] = v[j];
+            }
+        } else {
+            float* o = p.residual + (size_t)m * p.N + nb;
+            if (gridDim.z == 1 && full && (p.N % 4) == 0) {
+#pragma unroll
+                for (int j = 0; j < CHUNK; j += 4) {
+                    float4 t = *reinterpret_cast<float4*>(o + j);
+                    t.x += v[j]; t.y += v[j + 1]; t.z += v[j + 2]; t.w += v[j + 3];
+                    *reinterpret_cast<float4*>(o + j) = t;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < CHUNK; ++j) {
+                    if (nb + j < p.N) {
+                        if (gridDim.z == 1) o[j] += v[j];
+                        else atomicAdd(o + j, v[j]);
+                    }
+                }
+            }
+        }
+    }
+}
 
 template <int BN, int EPI, bool SWAP>
 __global__ void __launch_bounds__(NUM_THREADS, 2)
@@ -236,87 +328,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                     if (!SWAP) {
                         // row = token m, columns = output features n: 32 consecutive columns per thread
-                        const int m = a_row0 + row;
-                        const int nb = b_row0 + c0;
-                        if (m < p.M && nb < p.N) {
-                            float v[CHUNK];
-#pragma unroll
-                            for (int j = 0; j < CHUNK; ++j) v[j] = __uint_as_float(r[j]);
-                            const bool full = nb + CHUNK <= p.N;
-                            if (p.bias && blockIdx.z == 0) {
-#pragma unroll
-                                for (int j = 0; j < CHUNK; ++j)
-                                    if (full || nb + j < p.N) v[j] += p.bias[nb + j];
-                            }
-                            if (EPI == LLB_EPI_SWIGLU) {
-                                __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)m * (p.N / 2) + (nb >> 1);
-                                if (full && (p.N % 16) == 0) {     // 16-byte stores of 8 outputs
-#pragma unroll
-                                    for (int j = 0; j < CHUNK; j += 16) {
-                                        uint32_t w[4];
-#pragma unroll
-                                        for (int e = 0; e < 4; ++e) {
-                                            const __nv_bfloat162 h = __floats2bfloat162_rn(
-                                                llb_silu(v[j + 4 * e]) * v[j + 4 * e + 1],
-                                                llb_silu(v[j + 4 * e + 2]) * v[j + 4 * e + 3]);
-                                            w[e] = *reinterpret_cast<const uint32_t*>(&h);
-                                        }
-                                        *reinterpret_cast<uint4*>(o + (j >> 1)) = make_uint4(w[0], w[1], w[2], w[3]);
-                                    }
-                                } else {
-#pragma unroll
-                                    for (int j = 0; j < CHUNK; j += 2)
-                                        if (nb + j + 1 < p.N) o[j >> 1] = __float2bfloat16_rn(llb_silu(v[j]) * v[j + 1]);
-                                }
-                            } else if (EPI == LLB_EPI_STORE) {
-                                __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)m * p.N + nb;
-                                if (full && (p.N % 8) == 0) {
-#pragma unroll
-                                    for (int j = 0; j < CHUNK; j += 8) {
-                                        uint32_t w[4];
-#pragma unroll
-                                        for (int e = 0; e < 4; ++e) {
-                                            const __nv_bfloat162 h = __floats2bfloat162_rn(v[j + 2 * e], v[j + 2 * e + 1]);
-                                            w[e] = *reinterpret_cast<const uint32_t*>(&h);
-                                        }
-                                        *reinterpret_cast<uint4*>(o + j) = make_uint4(w[0], w[1], w[2], w[3]);
-                                    }
-                                } else {
-#pragma unroll
-                                    for (int j = 0; j < CHUNK; ++j)
-                                        if (nb + j < p.N) o[j] = __float2bfloat16_rn(v[j]);
-                                }
-                            } else if (EPI == LLB_EPI_STORE_F32) {
-                                float* o = (float*)p.out + (size_t)m * p.N + nb;
-                                if (full && (p.N % 4) == 0) {
-#pragma unroll
-                                    for (int j = 0; j < CHUNK; j += 4)
-                                        *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                                } else {
-#pragma unroll
-                                    for (int j = 0; j < CHUNK; ++j)
-                                        if (nb + j < p.N) o[j] = v[j];
-                                }
-                            } else {
-                                float* o = p.residual + (size_t)m * p.N + nb;
-                                if (gridDim.z == 1 && full && (p.N % 4) == 0) {
-#pragma unroll
-                                    for (int j = 0; j < CHUNK; j += 4) {
-                                        float4 t = *reinterpret_cast<float4*>(o + j);
-                                        t.x += v[j]; t.y += v[j + 1]; t.z += v[j + 2]; t.w += v[j + 3];
-                                        *reinterpret_cast<float4*>(o + j) = t;
-                                    }
-                                } else {
-#pragma unroll
-                                    for (int j = 0; j < CHUNK; ++j) {
-                                        if (nb + j < p.N) {
-                                            if (gridDim.z == 1) o[j] += v[j];
-                                            else atomicAdd(o + j, v[j]);
-                                        }
-                                    }
-                                }
-                            }
-                        }
+                        epilogue_row<EPI, CHUNK>(p, a_row0 + row, b_row0 + c0, r);
                     } else {
                         // row = output feature n, columns = tokens m
                         const int n = a_row0 + row;
@@ -348,6 +360,143 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (*abort_flag && threadIdx.x == 0 && p.error_flag) atomicExch(p.error_flag, 1);
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Many rows (prefill): a persistent kernel, one block per SM, that walks over the 128 x 128 output tiles.
+// The TMA ring keeps running across tile boundaries, and the accumulator is double buffered in tensor
+// memory (2 x 128 columns), so the epilogue of one tile overlaps the main loop of the next.
+// Tiles are ordered rows-first, so that the blocks working at the same time share a few weight tiles in L2.
+// ---------------------------------------------------------------------------------------------
+// Tile width P_BN = 128 (6 stages) or 256 (4 stages): the wide tile re-uses each activation tile for twice as
+// many output features, which matters because the main loop is bound by the bytes an SM can pull from L2.
+
+constexpr int P_THREADS = 64 + 256;      // TMA warp, MMA warp, eight epilogue warps (two per TMEM lane quarter)
+
+template <int EPI, int P_BN>
+__global__ void __launch_bounds__(P_THREADS, 1)
+gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                               const GemmParams p) {
+    constexpr int P_STAGES = P_BN == 256 ? 4 : 6;
+    constexpr uint32_t A_BYTES = TILE_M * TILE_K * 2;
+    constexpr uint32_t B_BYTES = P_BN * TILE_K * 2;
+    constexpr uint32_t TMEM_COLS = 2 * P_BN;
+    __shared__ __align__(8) uint64_t full_bar[P_STAGES];
+    __shared__ __align__(8) uint64_t empty_bar[P_STAGES];
+    __shared__ __align__(8) uint64_t acc_full[2];
+    __shared__ __align__(8) uint64_t acc_empty[2];
+    __shared__ uint32_t tmem_slot_s;
+    __shared__ int abort_s;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* a_tiles = smem;
+    uint8_t* b_tiles = smem + P_STAGES * A_BYTES;
+    volatile int* abort_flag = &abort_s;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m_tiles = (p.M + TILE_M - 1) / TILE_M;
+    const int n_tiles = (p.N + P_BN - 1) / P_BN;
+    const int num_tiles = m_tiles * n_tiles;
+    const int nkb = p.num_kb;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < P_STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 8);        // one arrival per epilogue warp
+        }
+        abort_s = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot_s)),
+                     "r"(TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_slot_s;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;                                  // k-blocks issued so far, over all tiles
+            for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+                const int a_row0 = (t % m_tiles) * TILE_M, b_row0 = (t / m_tiles) * P_BN;
+                bool ok = true;
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int s = it % P_STAGES;
+                    ok = mbar_wait(&empty_bar[s], ((it / P_STAGES) & 1) ^ 1, abort_flag);
+                    if (!ok) break;
+                    mbar_expect_tx(&full_bar[s], A_BYTES + B_BYTES);
+                    tma_load_2d(a_tiles + s * A_BYTES, &map_a, kb * TILE_K, a_row0, &full_bar[s]);
+                    tma_load_2d(b_tiles + s * B_BYTES, &map_b, kb * TILE_K, b_row0, &full_bar[s]);
+                }
+                if (!ok) break;
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc(TILE_M, P_BN);
+            int it = 0, local = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
+                const int buf = local & 1;
+                ok = mbar_wait(&acc_empty[buf], ((local >> 1) & 1) ^ 1, abort_flag);   // the epilogue has drained it
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int s = it % P_STAGES;
+                    ok = mbar_wait(&full_bar[s], (it / P_STAGES) & 1, abort_flag);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_addr = smem_u32(a_tiles + s * A_BYTES);
+                    const uint32_t b_addr = smem_u32(b_tiles + s * B_BYTES);
+#pragma unroll
+                    for (int k = 0; k < TILE_K / UMMA_K; ++k)
+                        umma_bf16(tmem_base + buf * P_BN, umma_desc(a_addr + k * UMMA_K * 2),
+                                  umma_desc(b_addr + k * UMMA_K * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(&empty_bar[s]);
+                }
+                if (ok) umma_commit(&acc_full[buf]);
+            }
+        }
+    } else {
+        const int quarter = warp & 3;                 // the TMEM lanes this warp may read
+        const int half = (warp - 2) >> 2;             // which half of the tile's columns it drains
+        const int row = quarter * 32 + lane;
+        int local = 0;
+        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++local) {
+            const int buf = local & 1;
+            const int a_row0 = (t % m_tiles) * TILE_M, b_row0 = (t / m_tiles) * P_BN;
+            if (!mbar_wait(&acc_full[buf], (local >> 1) & 1, abort_flag)) break;      // uniform over the warp
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+            for (int c0 = half * (P_BN / 2); c0 < (half + 1) * (P_BN / 2); c0 += 32) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * P_BN + c0), r);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                epilogue_row<EPI, 32>(p, a_row0 + row, b_row0 + c0, r);
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[buf])) : "memory");
+            }
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (abort_s && threadIdx.x == 0 && p.error_flag) atomicExch(p.error_flag, 5);
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
@@ -434,6 +583,39 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, di
     return llb_check_launch("gemm_tcgen05");
 }
 
+template <int EPI, int P_BN>
+int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t stream) {
+    constexpr int P_STAGES = P_BN == 256 ? 4 : 6;
+    constexpr size_t smem = (size_t)P_STAGES * (TILE_M * TILE_K * 2 + P_BN * TILE_K * 2) + 1024;
+    static bool configured = false;
+    static int num_sms = 0;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<EPI, P_BN>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return llb_fail("gemm_tcgen05: cannot opt in to %zu bytes of shared memory: %s", smem,
+                                              cudaGetErrorString(e));
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+        configured = true;
+    }
+    const int tiles = llb_ceil_div(p.M, TILE_M) * llb_ceil_div(p.N, P_BN);
+    const int grid = tiles < num_sms ? tiles : num_sms;
+    gemm_tcgen05_persistent_kernel<EPI, P_BN><<<grid, P_THREADS, smem, stream>>>(ma, mb, p);
+    return llb_check_launch("gemm_tcgen05_persistent");
+}
+
+template <int P_BN>
+int dispatch_persistent(int epi, const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t s) {
+    switch (epi) {
+        case LLB_EPI_STORE: return launch_persistent<LLB_EPI_STORE, P_BN>(ma, mb, p, s);
+        case LLB_EPI_STORE_F32: return launch_persistent<LLB_EPI_STORE_F32, P_BN>(ma, mb, p, s);
+        case LLB_EPI_RESIDUAL: return launch_persistent<LLB_EPI_RESIDUAL, P_BN>(ma, mb, p, s);
+        case LLB_EPI_SWIGLU: return launch_persistent<LLB_EPI_SWIGLU, P_BN>(ma, mb, p, s);
+    }
+    return llb_fail("gemm_tcgen05: unknown epilogue %d", epi);
+}
+
 template <int BN, bool SWAP>
 int dispatch_epi(int epi, const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid, cudaStream_t s) {
     switch (epi) {
@@ -487,7 +669,12 @@ LLB_EXPORT int llb_gemm_tcgen05(const void* A, const void* W, const float* bias,
     }
     constexpr int BN = 128;
     if ((rc = make_map(A, M, K, TILE_M, &ma))) return rc;
+    if (split_k == 1 && N >= 2048) {       // wide tiles where their padding of N costs little
+        if ((rc = make_map(W, N, K, 256, &mb))) return rc;
+        return dispatch_persistent<256>(epilogue, ma, mb, p, stream);
+    }
     if ((rc = make_map(W, N, K, BN, &mb))) return rc;
+    if (split_k == 1) return dispatch_persistent<128>(epilogue, ma, mb, p, stream);
     dim3 grid(llb_ceil_div(M, TILE_M), llb_ceil_div(N, BN), split_k);
     LLB_REQUIRE(grid.y <= 65535, "gemm_tcgen05: N=%d is too large for one launch", N);
     return dispatch_epi<BN, false>(epilogue, ma, mb, p, grid, stream);

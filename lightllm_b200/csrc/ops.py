@@ -15,7 +15,7 @@ from . import build as _build
 
 F32, BF16 = 0, 1
 EPI_STORE, EPI_STORE_F32, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
-ABI_VERSION = 9
+ABI_VERSION = 10
 
 _lib: Optional[ctypes.CDLL] = None
 
@@ -270,19 +270,36 @@ def paged_attention_tcgen05(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
                             tile_span: torch.Tensor, tile_q0: torch.Tensor, num_tiles: int,
                             span_row: torch.Tensor, span_len: torch.Tensor, span_pos: torch.Tensor,
                             block_table: torch.Tensor, max_pages: int, page_size: int,
-                            num_heads: int, num_kv_heads: int, head_dim: int, window: int, scale: float) -> None:
-    """Tensor-core attention of the listed tiles (128 query rows each) over the requests' pages; bf16."""
+                            num_heads: int, num_kv_heads: int, head_dim: int, window: int, scale: float,
+                            cut=None) -> None:
+    """Tensor-core attention of the listed tiles (128 query rows each) over the requests' pages; bf16.
+
+    ``cut`` = ``(tile_k0, tile_nk, tile_part, num_parts, merge_span, merge_q0, merge_first, merge_count,
+    num_merge)`` cuts long key ranges into items (see ``StepContext.attention_items``); the partial results
+    are merged by a second kernel."""
     for t in (q, k_cache, v_cache, out):
         if t.dtype != torch.bfloat16:
             raise KernelError("attention_tcgen05 takes bfloat16 tensors")
     T = q.shape[0]
     num_slots = k_cache.shape[0]
+    k0 = nk = part = scratch = None
+    num_parts = 0
+    if cut is not None:
+        k0, nk, part, num_parts = cut[0], cut[1], cut[2], cut[3]
+        if num_parts:
+            scratch = torch.empty(num_parts * num_heads * 128 * (head_dim + 2), dtype=torch.float32, device=q.device)
     _check(lib().llb_paged_attention_tcgen05(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), T,
         _i32(tile_span, "tile_span"), _i32(tile_q0, "tile_q0"), num_tiles,
         _i32(span_row, "span_row"), _i32(span_len, "span_len"), _i32(span_pos, "span_pos"),
         _i32(block_table, "block_table"), max_pages, page_size, num_slots, num_heads, num_kv_heads, head_dim,
-        window, ctypes.c_float(scale), _ptr(async_error_flag(q.device)), _stream()))
+        window, ctypes.c_float(scale), _i32(k0, "tile_k0"), _i32(nk, "tile_nk"), _i32(part, "tile_part"),
+        _ptr(scratch), num_parts, _ptr(async_error_flag(q.device)), _stream()))
+    if cut is not None and num_parts:
+        _check(lib().llb_attention_tcgen05_merge(
+            _ptr(out), _i32(cut[4], "merge_span"), _i32(cut[5], "merge_q0"), _i32(cut[6], "merge_first"),
+            _i32(cut[7], "merge_count"), cut[8], _i32(span_row, "span_row"), _i32(span_len, "span_len"),
+            _ptr(scratch), num_parts, num_heads, head_dim, _stream()))
 
 
 def paged_decode_mma_supports(num_heads: int, num_kv_heads: int, head_dim: int) -> bool:

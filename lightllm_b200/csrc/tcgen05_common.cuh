@@ -11,7 +11,7 @@
 
 namespace t5 {
 
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // every wait gives up after 2 s
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;   // every wait gives up after about 2 s of SM cycles
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ unsigned long long globaltimer_ns() {
@@ -43,13 +43,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait: false when the time limit ran out or another role of the block already gave up.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = globaltimer_ns();
-    while (true) {
+    // The time limit is checked once every 256 failed attempts, on the SM's own cycle counter: reading a
+    // timer inside the loop would add its latency to every wake-up.
+    const long long t0 = clock64();
+    for (unsigned spins = 1;; ++spins) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
-            *abort_flag = 1;
-            return false;
+        if ((spins & 255u) == 0u) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                *abort_flag = 1;
+                return false;
+            }
         }
     }
 }

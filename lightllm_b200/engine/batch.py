@@ -98,3 +98,46 @@ class StepContext:
             hit = (arr[0], arr[1], len(ts))
         self._tiles[key] = hit
         return hit
+
+    def attention_items(self, min_len: int, window: int, chunk_tiles: int = 4):
+        """Work items of the tensor-core attention kernel for the spans of at least ``min_len`` rows: tiles
+        of 128 query rows whose key range (in tiles of 128 keys) is cut into pieces of ``chunk_tiles``, longest
+        first, so that a long prompt's last rows do not set the kernel's time.  Returns ``(tile_span, tile_q0,
+        count, cut)`` with ``cut`` as ``ops.paged_attention_tcgen05`` takes it."""
+        key = ("items", min_len, window, chunk_tiles)
+        hit = self._tiles.get(key)
+        if hit is not None:
+            return hit
+        items, merges, parts = [], [], 0
+        for i, s in enumerate(self.spans):
+            if s.length < min_len:
+                continue
+            for q0 in range(0, s.length, 128):
+                nrows = min(128, s.length - q0)
+                pos0 = s.start + q0
+                hi = pos0 + nrows
+                lo = max(0, pos0 - window + 1) if window > 0 else 0
+                ntiles = -(-(hi - (lo // 128) * 128) // 128)
+                if ntiles <= chunk_tiles + 1:
+                    items.append((ntiles, i, q0, 0, ntiles, -1))
+                    continue
+                nchunks = -(-ntiles // chunk_tiles)
+                merges.append((i, q0, parts, nchunks))
+                for c in range(nchunks):
+                    nk = min(chunk_tiles, ntiles - c * chunk_tiles)
+                    items.append((nk, i, q0, c * chunk_tiles, nk, parts + c))
+                parts += nchunks
+        items.sort(key=lambda t: -t[0])
+        if not items:
+            hit = (self.iota, self.zeros, 0, None)
+        else:
+            arr = torch.from_numpy(np.asarray([t[1:] for t in items], dtype=np.int32).T.copy()).to(self.device)
+            cut = None
+            if merges:
+                m = torch.from_numpy(np.asarray(merges, dtype=np.int32).T.copy()).to(self.device)
+                cut = (arr[2], arr[3], arr[4], parts, m[0], m[1], m[2], m[3], len(merges))
+            else:
+                cut = (arr[2], arr[3], arr[4], 0, None, None, None, None, 0)
+            hit = (arr[0], arr[1], len(items), cut)
+        self._tiles[key] = hit
+        return hit

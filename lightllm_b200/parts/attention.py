@@ -18,6 +18,7 @@ _SMEM_BUDGET = 100 * 1024
 _SMEM_LIMIT = 200 * 1024
 # Portions of at least this many rows run on the tensor-core attention kernel (tiles of 128 rows).
 TENSOR_CORE_MIN_ROWS = 32
+FUSED_ROPE_MAX_ROWS = 16
 
 
 class AttentionMixer(Mixer):
@@ -99,7 +100,9 @@ class AttentionMixer(Mixer):
         act_dtype = x.norm.out_dtype if lazy else x.dtype
         hq, hkv, hd = self.num_heads, self.num_kv_heads, self.head_dim
         w = self.w_qkv if cache.writes else self.w_qkv[: hq * hd]
-        if not L.decode_eligible(T, w, act_dtype, lazy, ops.DEPI_ROPE_KV, hd):
+        # Beyond 16 rows the per-row loop of the rotary epilogue costs more than a separate rotation kernel
+        # (measured at 64 rows: 25 us fused, 14 us apart).
+        if T > FUSED_ROPE_MAX_ROWS or not L.decode_eligible(T, w, act_dtype, lazy, ops.DEPI_ROPE_KV, hd):
             return None
         b = self.b_qkv if (cache.writes or self.b_qkv is None) else self.b_qkv[: hq * hd]
         inv_freq, rotary_dim, interleaved = table
@@ -186,8 +189,8 @@ class AttentionMixer(Mixer):
         if (q.dtype == torch.bfloat16 and ops.attention_tcgen05_supports(self.head_dim, ctx.page_size)
                 and max(s.length for s in ctx.spans) >= TENSOR_CORE_MIN_ROWS):
             # long portions go to the tensor cores in tiles of 128 rows; short ones stay on CUDA cores
-            tile_span, tile_q0, ntiles = ctx.tiles(128, min_len=TENSOR_CORE_MIN_ROWS)
-            ops.paged_attention_tcgen05(q, cache.k, cache.v, out, tile_span, tile_q0, ntiles, *common)
+            tile_span, tile_q0, ntiles, cut = ctx.attention_items(TENSOR_CORE_MIN_ROWS, window)
+            ops.paged_attention_tcgen05(q, cache.k, cache.v, out, tile_span, tile_q0, ntiles, *common, cut=cut)
             short_max = TENSOR_CORE_MIN_ROWS - 1
         bq = self.tile_height()
         tiles = ctx.tiles(bq, max_len=short_max)

@@ -426,6 +426,37 @@ def test_paged_attention_tcgen05(ops, case, spike):
     assert torch.allclose(got, ref, atol=2e-2, rtol=2e-2), f"max diff {float((got - ref).abs().max())}"
 
 
+@pytest.mark.parametrize("window", [None, 300])
+@pytest.mark.parametrize("chunk_tiles", [1, 2, 4])
+def test_paged_attention_tcgen05_cut_key_ranges(ops, window, chunk_tiles):
+    """Long key ranges cut into work items whose partial results a second kernel merges."""
+    from lightllm_b200.engine.batch import Span, StepContext
+    Hq, Hkv, hd, page = 6, 2, 64, 16
+    lens, starts = [1100, 40, 700], [0, 900, 333]
+    s = paged_setup(torch.bfloat16, lens, starts, Hq, Hkv, hd, page, seed=27, spike=True)
+    s["kc"] = torch.nan_to_num(s["kc"], nan=3.0)
+    s["vc"] = torch.nan_to_num(s["vc"], nan=-7.0)
+    ctx = StepContext()
+    ctx.device = dev()
+    rows = 0
+    for i, (n, st) in enumerate(zip(lens, starts)):
+        ctx.spans.append(Span(i, i, st, n, rows))
+        rows += n
+    ctx.iota = torch.arange(3, dtype=torch.int32, device=dev())
+    ctx.zeros = torch.zeros(3, dtype=torch.int32, device=dev())
+    ts, tq, nt, cut = ctx.attention_items(32, window or 0, chunk_tiles)
+    if window is None or chunk_tiles < 3:
+        assert cut is not None and cut[3] > 0 and nt > len(tiles_for(lens, 128)[0])
+    out = torch.full((s["rows"], Hq * hd), float("nan"), dtype=torch.bfloat16, device=dev())
+    ops.paged_attention_tcgen05(s["q"], s["kc"], s["vc"], out, ts, tq, nt, s["span_row"], s["span_len"], s["span_pos"],
+                                s["bt"], s["max_pages"], page, Hq, Hkv, hd, window or 0, 1.0 / math.sqrt(hd), cut=cut)
+    ops.check_async_errors(dev())
+    ref = attention_reference(s["full"], lens, starts, hd, window).reshape(s["rows"], Hq * hd)
+    got = out.float().cpu()
+    assert not torch.isnan(got).any()
+    assert torch.allclose(got, ref, atol=2e-2, rtol=2e-2), f"max diff {float((got - ref).abs().max())}"
+
+
 def test_attention_tcgen05_refuses_other_shapes(ops):
     assert not ops.attention_tcgen05_supports(48, 16) and not ops.attention_tcgen05_supports(64, 24)
     z = torch.zeros((4, 48), dtype=torch.bfloat16, device=dev())
