@@ -63,7 +63,7 @@ class ClockSampler:
         fd, self.path = tempfile.mkstemp(suffix=".csv")
         os.close(fd)
         self.proc = subprocess.Popen([exe, "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                                      "-lms", "100"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+                                      "-lms", "50"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
 
     def stop(self):
         if self.proc is None:
@@ -119,7 +119,7 @@ def decode_bytes(core, batch, ctx_len):
     return weights + kv
 
 
-def time_decode(core, batch, steps, warmup, rng):
+def time_decode(core, batch, steps, warmup, rng, clocks=None):
     import torch
     from lightllm_b200.engine import StepEntry
     V = core.vocab_size
@@ -135,6 +135,9 @@ def time_decode(core, batch, steps, warmup, rng):
     for _ in range(warmup):
         one()
     torch.cuda.synchronize()
+    if clocks is not None:
+        clocks.start()
+        time.sleep(0.12)          # let the sampler take its first reading before the timed region
     l0 = core.launch_count()
     t0 = torch.cuda.Event(enable_timing=True)
     t1 = torch.cuda.Event(enable_timing=True)
@@ -199,7 +202,7 @@ def time_e2e(engine, batch, steps, warmup, rng):
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=QWEN25_05B["num_hidden_layers"])
@@ -251,14 +254,14 @@ def main() -> int:
             pre_ms = time_prefill(core, args.steps, args.warmup, rng)
             print(json.dumps({"only": "prefill", "tokens": PROMPT_LEN, "ms": round(pre_ms, 3)}))
             return 0
+        args.steps = min(args.steps, 448)        # the pool holds 2,048 + 512 tokens per request
         clocks = ClockSampler()
-        clocks.start()
-        ms, launches, ctx = time_decode(core, args.batch, args.steps, args.warmup, rng)
+        ms, launches, ctx = time_decode(core, args.batch, args.steps, args.warmup, rng, clocks)
         clk = clocks.stop()
         value = args.batch * 1000.0 / ms
         achieved = decode_bytes(core, args.batch, ctx) / (ms * 1e-3) / 1e9
         e2e_value, h2d, d2h = time_e2e(engine, args.batch, args.steps, args.warmup, rng)
-        pre_ms = time_prefill(core, max(3, args.steps // 8), 3, rng)
+        pre_ms = time_prefill(core, 5, 3, rng)
         fl = flops_prefill(QWEN25_05B, args.layers, PROMPT_LEN)
         points = {}
         if not args.skip_points:

@@ -21,7 +21,9 @@ allocated when a device is given.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, Hashable, List, Optional, Sequence
+from typing import Any, Dict, Hashable, List, Optional, Sequence
+
+import numpy as np
 
 import torch
 
@@ -98,6 +100,8 @@ class SeqCache:
     length: int = 0
     tables: List[List[int]] = field(default_factory=list)
     first_live: List[int] = field(default_factory=list)    # first logical page not yet released
+    version: int = 0                                       # bumped whenever a table changes
+    _np: Dict[int, Any] = field(default_factory=dict)      # group -> (version, int32 array of the table)
 
 
 class CacheManager:
@@ -174,6 +178,8 @@ class CacheManager:
         for g, (need, pool) in enumerate(zip(needs, self.pools)):
             for _ in range(need):
                 seq.tables[g].append(pool.take(seq_id))
+            if need:
+                seq.version += 1
 
     def can_reserve_all(self, asks) -> bool:
         """Whether every ``(request, n_tokens)`` of ``asks`` can get its pages at the same time."""
@@ -216,6 +222,7 @@ class CacheManager:
             for lp in range(seq.first_live[g], min(dead, len(table))):
                 self.pools[g].give(table[lp], seq_id)
                 table[lp] = -1
+                seq.version += 1
             seq.first_live[g] = max(seq.first_live[g], min(dead, len(table)))
 
     def close(self, seq_id: Hashable) -> None:
@@ -243,6 +250,15 @@ class CacheManager:
 
     def block_table(self, seq_id: Hashable, group: int) -> List[int]:
         return self.get(seq_id).tables[group]
+
+    def block_table_array(self, seq_id: Hashable, group: int) -> "np.ndarray":
+        """The block table as an int32 array, rebuilt only when the table has changed."""
+        seq = self.get(seq_id)
+        hit = seq._np.get(group)
+        if hit is None or hit[0] != seq.version:
+            hit = (seq.version, np.asarray(seq.tables[group], dtype=np.int32))
+            seq._np[group] = hit
+        return hit[1]
 
     def plane_kv(self, group: int, plane: int):
         """(k, v) storage of one plane, each ``[pages * page_size, kv_heads, head_dim]``."""

@@ -377,7 +377,7 @@ int launch_stages(const CUtensorMap& mw, const CUtensorMap& mx, const DecodeGemm
 template <int BN, int EPI, bool NORM>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, const DecodeGemmParams& p, int split_k, cudaStream_t stream) {
     // the float-store epilogue is the head's: a vocabulary's worth of blocks
-    if (EPI == DEPI_STORE_F32 && !NORM && llb_ceil_div(p.N, TILE_M) >= 2 * 148)
+    if (EPI == DEPI_STORE_F32 && !NORM && llb_ceil_div(p.N, TILE_M) >= 256)
         return launch_stages<BN, EPI, NORM, SHALLOW>(mw, mx, p, split_k, stream);
     return launch_stages<BN, EPI, NORM, DEEP>(mw, mx, p, split_k, stream);
 }

@@ -126,7 +126,7 @@ class BatchMainLoop:
             return False
         entries, wanting = [], []
         for e in sched.entries:
-            toks = e.request.all_tokens()[e.start_pos: e.start_pos + e.num_tokens]
+            toks = e.request.tokens_at(e.start_pos, e.num_tokens)
             entries.append(StepEntry(e.request.id, toks, [e.num_tokens - 1] if e.wants_logits else []))
             if e.wants_logits:
                 wanting.append(e.request)

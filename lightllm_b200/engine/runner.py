@@ -111,8 +111,9 @@ class ModelRunner:
 
         ps = cache.page_size
         max_context = max(s.start + s.length for s in spans)
-        # Block-table width of this step: the pages of its longest request, rounded up to 16.
-        P = min(self.max_pages, -(-(-(-max_context // ps)) // 16) * 16)
+        # Block-table width of this step: the pages of its longest request, rounded up to 32, so that a
+        # decoding batch keeps its shape (and its captured graph) for hundreds of steps.
+        P = min(self.max_pages, -(-(-(-max_context // ps)) // 32) * 32)
         want = [s.row + w for s, e in zip(spans, entries) for w in e.want]
         R = len(want)
         o, off = {}, 0
@@ -141,7 +142,7 @@ class ModelRunner:
             bt = host[o["block_tables"] + g * S * P: o["block_tables"] + (g + 1) * S * P].reshape(S, P)
             sm = host[o["slot_mapping"] + g * T: o["slot_mapping"] + (g + 1) * T]
             for i, s in enumerate(spans):
-                table = np.asarray(cache.block_table(s.seq_id, g), dtype=np.int32)
+                table = cache.block_table_array(s.seq_id, g)
                 bt[i, : len(table)] = table[:P]
                 p = pos[s.row: s.row + s.length]
                 rows = table[p // ps]

@@ -53,6 +53,15 @@ class Request:
     def total_len(self) -> int:
         return len(self.prompt_tokens) + len(self.output_tokens)
 
+    def tokens_at(self, start: int, n: int) -> List[int]:
+        """Tokens ``start .. start+n-1`` of prompt + output, without building the whole list."""
+        np_ = len(self.prompt_tokens)
+        if start >= np_:
+            return self.output_tokens[start - np_: start - np_ + n]
+        if start + n <= np_:
+            return self.prompt_tokens[start: start + n]
+        return self.prompt_tokens[start:] + self.output_tokens[: start + n - np_]
+
     def prefill_remaining(self) -> int:
         return self.total_len() - self.num_computed
 
@@ -132,6 +141,13 @@ class Scheduler:
 
         # Priority 1: one token for every decoding request; preempt from the back when pages run out.
         decoding = [r for r in self.running if r.state == DECODING]
+        # Fast path: every decoding request gets its token (the usual case).
+        all_asks = [(r.id, 1) for r in decoding]
+        if decoding and cache.can_reserve_all(all_asks):
+            asks = all_asks
+            out.entries = [ScheduleEntry(r, 1, r.num_computed, False, True) for r in decoding]
+            budget -= len(decoding)
+            decoding = []
         i = 0
         while i < len(decoding):
             r = decoding[i]

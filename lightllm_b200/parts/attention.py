@@ -171,7 +171,7 @@ class AttentionMixer(Mixer):
             S = ctx.num_spans
             bound = ctx.max_pages * ctx.page_size          # the same for every step of this shape
             span = bound if window == 0 else min(bound, window)
-            want = max(1, -(-2 * 148 // (S * self.num_kv_heads)))       # blocks to fill the SMs twice
+            want = max(1, -(-2 * L.num_sms(q.device) // (S * self.num_kv_heads)))       # blocks to fill the SMs twice
             nsplit = max(1, min(want, -(-span // 128)))
             if q.dtype == torch.bfloat16 and ops.paged_decode_mma_supports(self.num_heads, self.num_kv_heads, self.head_dim):
                 tile_span, tile_q0, ntiles = ctx.tiles(1)

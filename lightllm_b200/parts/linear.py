@@ -21,7 +21,16 @@ STORE, STORE_F32, RESIDUAL, SWIGLU = ops.EPI_STORE, ops.EPI_STORE_F32, ops.EPI_R
 
 # Rows at or below which the row-streaming CUDA-core kernel is used for bfloat16 (decode).
 SMALL_M = 0
-NUM_SMS = 148
+_num_sms = {}
+
+
+def num_sms(device=None) -> int:
+    """Multiprocessors of the device the step runs on (asked once)."""
+    idx = torch.cuda.current_device() if device is None else (torch.device(device).index or 0)
+    n = _num_sms.get(idx)
+    if n is None:
+        n = _num_sms[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return n
 
 
 def tensor_core_eligible(x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -44,7 +53,7 @@ def decode_eligible(M: int, w: torch.Tensor, act_dtype: torch.dtype, norm: bool,
 def split_k_for(M: int, N: int, K: int) -> int:
     """Few rows leave only N/128 blocks; cut K so that the weights stream from all SMs."""
     tiles, kblocks = -(-N // 128), -(-K // 64)
-    return max(1, min(kblocks, NUM_SMS // tiles))
+    return max(1, min(kblocks, num_sms() // tiles))
 
 
 def split_k_fused(M: int, N: int, K: int) -> int:
@@ -52,9 +61,9 @@ def split_k_fused(M: int, N: int, K: int) -> int:
     costs three more round trips to memory, so it only pays when the grid would otherwise leave most
     SMs idle (the q/k/v projection: 9 blocks), and only for few rows, where the atomic adds are cheap."""
     tiles, kblocks = -(-N // 128), -(-K // 64)
-    if M > 16 or tiles * 4 > NUM_SMS:
+    if M > 16 or tiles * 4 > num_sms():
         return 1
-    return max(1, min(kblocks, NUM_SMS // tiles))
+    return max(1, min(kblocks, num_sms() // tiles))
 
 
 def reserve_fused_scratch(device: torch.device, N: int) -> None:
