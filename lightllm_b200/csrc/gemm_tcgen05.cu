@@ -147,6 +147,13 @@ struct GemmParams {
     int num_kb;             // K blocks in all
     int kb_per_split;       // K blocks per grid.z slice
     int* error_flag;        // raised when a wait ran out of time
+    // rotary epilogue of the q/k/v projection (heads of 64, NeoX pairs, whole head rotated)
+    const float2* rope_table;   // [M, 32] of (cos, sin)
+    const int* slot_mapping;    // [M] cache row of each token, negative: not written
+    __nv_bfloat16* q_out;       // [M, Hq * 64]
+    __nv_bfloat16* k_cache;     // [slots, Hkv, 64]
+    __nv_bfloat16* v_cache;
+    int Hq, Hkv;
 };
 
 // Epilogue of one thread in the row-major orientation: token row m, CHUNK consecutive output features
@@ -231,6 +238,55 @@ __device__ __forceinline__ void epilogue_row(const GemmParams& p, int m, int nb,
                 }
             }
         }
+    }
+}
+
+constexpr int EPI_ROPE64 = 4;     // q/k/v projection of heads of 64: bias, NeoX rotation, q store, K/V page write
+
+// Rotary epilogue of one thread: token row m and the 64 output features nb .. nb+63, i.e. one whole head of q, k
+// or v (src/ops/rope.cu:54-59 on every pair; cache rows as src/kv_cache/paged_attention.cu:1150-1163).
+__device__ __forceinline__ void epilogue_rope64_row(const GemmParams& p, int m, int nb, const uint32_t (&r0)[32],
+                                                    const uint32_t (&r1)[32]) {
+    if (m >= p.M || nb >= p.N) return;
+    const int q_end = p.Hq * 64, k_end = q_end + p.Hkv * 64;
+    float a[32], b[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        a[j] = __uint_as_float(r0[j]);
+        b[j] = __uint_as_float(r1[j]);
+        if (p.bias) { a[j] += p.bias[nb + j]; b[j] += p.bias[nb + 32 + j]; }
+    }
+    if (nb < k_end) {
+        const float2* cs = p.rope_table + (size_t)m * 32;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const float2 t = cs[j];
+            const float x = a[j], y = b[j];
+            a[j] = x * t.x - y * t.y;
+            b[j] = y * t.x + x * t.y;
+        }
+    }
+    __nv_bfloat16* dst;
+    if (nb < q_end) {
+        dst = p.q_out + (size_t)m * q_end + nb;
+    } else {
+        const int slot = p.slot_mapping ? p.slot_mapping[m] : -1;
+        if (slot < 0) return;
+        dst = nb < k_end ? p.k_cache + (size_t)slot * (p.Hkv * 64) + (nb - q_end)
+                         : p.v_cache + (size_t)slot * (p.Hkv * 64) + (nb - k_end);
+    }
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+        uint32_t w[4], x[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const __nv_bfloat162 h = __floats2bfloat162_rn(a[j + 2 * e], a[j + 2 * e + 1]);
+            const __nv_bfloat162 g = __floats2bfloat162_rn(b[j + 2 * e], b[j + 2 * e + 1]);
+            w[e] = *reinterpret_cast<const uint32_t*>(&h);
+            x[e] = *reinterpret_cast<const uint32_t*>(&g);
+        }
+        *reinterpret_cast<uint4*>(dst + j) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4*>(dst + 32 + j) = make_uint4(x[0], x[1], x[2], x[3]);
     }
 }
 
@@ -479,12 +535,25 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
             const int a_row0 = (t % m_tiles) * TILE_M, b_row0 = (t / m_tiles) * P_BN;
             if (!mbar_wait(&acc_full[buf], (local >> 1) & 1, abort_flag)) break;      // uniform over the warp
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (EPI == EPI_ROPE64) {
+                // one head (64 columns) at a time, so that both members of every rotary pair are in registers
 #pragma unroll 1
-            for (int c0 = half * (P_BN / 2); c0 < (half + 1) * (P_BN / 2); c0 += 32) {
-                uint32_t r[32];
-                tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * P_BN + c0), r);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                epilogue_row<EPI, 32>(p, a_row0 + row, b_row0 + c0, r);
+                for (int c0 = half * (P_BN / 2); c0 < (half + 1) * (P_BN / 2); c0 += 64) {
+                    uint32_t r0[32], r1[32];
+                    const uint32_t ta = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * P_BN + c0);
+                    tmem_ld32(ta, r0);
+                    tmem_ld32(ta + 32, r1);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    epilogue_rope64_row(p, a_row0 + row, b_row0 + c0, r0, r1);
+                }
+            } else {
+#pragma unroll 1
+                for (int c0 = half * (P_BN / 2); c0 < (half + 1) * (P_BN / 2); c0 += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * P_BN + c0), r);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    epilogue_row<(EPI == EPI_ROPE64 ? LLB_EPI_STORE : EPI), 32>(p, a_row0 + row, b_row0 + c0, r);
+                }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
@@ -678,4 +747,32 @@ LLB_EXPORT int llb_gemm_tcgen05(const void* A, const void* W, const float* bias,
     dim3 grid(llb_ceil_div(M, TILE_M), llb_ceil_div(N, BN), split_k);
     LLB_REQUIRE(grid.y <= 65535, "gemm_tcgen05: N=%d is too large for one launch", N);
     return dispatch_epi<BN, false>(epilogue, ma, mb, p, grid, stream);
+}
+
+// The q/k/v projection of a prompt portion with its whole epilogue on the tensor-core kernel: bias, NeoX rotation
+// of q and k by rope_table [M, 32] of (cos, sin), q to q_out [M, Hq*64], k and v to the cache rows slot_mapping[m].
+// Heads of 64 with the whole head rotated; N = (Hq + 2*Hkv) * 64.  M > 128 (fewer rows take the decode kernel).
+LLB_EXPORT int llb_gemm_tcgen05_rope64(const void* A, const void* W, const float* bias, int M, int N, int K,
+                                       const float* rope_table, const int* slot_mapping, void* q_out, void* k_cache,
+                                       void* v_cache, int Hq, int Hkv, int* error_flag, cudaStream_t stream) {
+    if (M == 0) return 0;
+    LLB_REQUIRE(M > 128 && K % 8 == 0 && N == (Hq + 2 * Hkv) * 64 && Hq > 0 && Hkv > 0,
+                "gemm_tcgen05_rope64: unsupported shape M=%d N=%d K=%d heads %d/%d", M, N, K, Hq, Hkv);
+    LLB_REQUIRE(rope_table && q_out && k_cache && v_cache && slot_mapping, "gemm_tcgen05_rope64: null argument");
+    LLB_REQUIRE(((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0) && ((uintptr_t)q_out % 16 == 0) &&
+                ((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0) && ((uintptr_t)rope_table % 8 == 0),
+                "gemm_tcgen05_rope64: operands must be 16-byte aligned");
+    GemmParams p = {};
+    p.bias = bias; p.M = M; p.N = N; p.K = K;
+    p.num_kb = llb_ceil_div(K, TILE_K);
+    p.kb_per_split = p.num_kb;
+    p.error_flag = error_flag;
+    p.rope_table = (const float2*)rope_table; p.slot_mapping = slot_mapping;
+    p.q_out = (__nv_bfloat16*)q_out; p.k_cache = (__nv_bfloat16*)k_cache; p.v_cache = (__nv_bfloat16*)v_cache;
+    p.Hq = Hq; p.Hkv = Hkv;
+    CUtensorMap ma, mb;
+    int rc;
+    if ((rc = make_map(A, M, K, TILE_M, &ma))) return rc;
+    if ((rc = make_map(W, N, K, 128, &mb))) return rc;
+    return launch_persistent<EPI_ROPE64, 128>(ma, mb, p, stream);
 }

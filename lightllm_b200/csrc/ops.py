@@ -15,7 +15,7 @@ from . import build as _build
 
 F32, BF16 = 0, 1
 EPI_STORE, EPI_STORE_F32, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
-ABI_VERSION = 10
+ABI_VERSION = 11
 
 _lib: Optional[ctypes.CDLL] = None
 
@@ -395,3 +395,30 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
     _check_epilogue_args(a, N, M, bias, epilogue, out, residual)
     _check(lib().llb_gemm_tcgen05(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), _ptr(residual), epilogue, M, N, K,
                                   split_k, _ptr(async_error_flag(a.device)), _stream()))
+
+
+def gemm_tcgen05_rope64(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], rope_table: torch.Tensor,
+                        slot_mapping: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor,
+                        v_cache: torch.Tensor, num_heads: int, num_kv_heads: int) -> None:
+    """The q/k/v projection of more than 128 rows with heads of 64: a[M,K] @ w[N,K]^T, bias, NeoX rotation of
+    the whole head by ``rope_table`` [M, 32, 2] (cos, sin), q to ``q_out`` [M, Hq*64], k and v to the cache rows
+    ``slot_mapping`` [M] of ``k_cache`` / ``v_cache`` [slots, Hkv, 64] (a negative slot writes nothing)."""
+    M, K = a.shape
+    N, K2 = w.shape
+    if K != K2 or N != (num_heads + 2 * num_kv_heads) * 64:
+        raise KernelError(f"gemm_tcgen05_rope64: a {tuple(a.shape)}, w {tuple(w.shape)}, heads {num_heads}/{num_kv_heads}")
+    for t, name in ((a, "a"), (w, "w"), (q_out, "q_out"), (k_cache, "k_cache"), (v_cache, "v_cache")):
+        if t.dtype != torch.bfloat16 or not t.is_contiguous():
+            raise KernelError(f"gemm_tcgen05_rope64: {name} must be contiguous bfloat16")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N):
+        raise KernelError("gemm_tcgen05_rope64: bias must be float32 of length N")
+    if rope_table.dtype != torch.float32 or rope_table.numel() != M * 64 or not rope_table.is_contiguous():
+        raise KernelError("gemm_tcgen05_rope64: rope_table must be float32 [M, 32, 2]")
+    if slot_mapping.dtype != torch.int32 or slot_mapping.numel() != M:
+        raise KernelError("gemm_tcgen05_rope64: slot_mapping must be int32 [M]")
+    if tuple(q_out.shape) != (M, num_heads * 64) or k_cache.shape[-1] != 64 or k_cache.shape[-2] != num_kv_heads \
+            or v_cache.shape != k_cache.shape:
+        raise KernelError("gemm_tcgen05_rope64: q_out must be [M, Hq*64] and the caches [..., Hkv, 64]")
+    _check(lib().llb_gemm_tcgen05_rope64(_ptr(a), _ptr(w), _ptr(bias), M, N, K, _ptr(rope_table), _ptr(slot_mapping),
+                                         _ptr(q_out), _ptr(k_cache), _ptr(v_cache), num_heads, num_kv_heads,
+                                         _ptr(async_error_flag(a.device)), _stream()))

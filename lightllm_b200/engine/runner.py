@@ -10,6 +10,7 @@ one host-to-device copy of the step's metadata, no synchronisation, and the step
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, Hashable, List, Optional, Sequence
 
 import numpy as np
@@ -61,6 +62,7 @@ class ModelRunner:
             st = cache.state[ref.state_plane] if ref.state_plane is not None else None
             self.views.append(CacheView(ref.group, k, v, st, ref.owns))
         self.last_h2d_bytes = 0
+        self._nvtx = os.environ.get("LLB_NVTX", "") not in ("", "0")
         # Decode-only steps are launch-bound, so they are captured into CUDA graphs: one per
         # (requests, wanted rows, block-table width), captured the second time a shape is seen.
         self.use_cuda_graphs = bool(use_cuda_graphs) and model.graph_safe()
@@ -181,11 +183,17 @@ class ModelRunner:
         return ctx
 
     def forward(self, ctx: StepContext) -> Optional[torch.Tensor]:
-        """Run the layers over the batch that ``ctx`` describes; logits float32 [R, V] or None."""
+        """Run the layers over the batch that ``ctx`` describes; logits float32 [R, V] or None.
+        With ``LLB_NVTX=1`` in the environment every run entry is an NVTX range (the reference only has
+        ``printf`` timings, src/engine/batch_loop.cpp:99-102)."""
         m = self.model
         residual = m.embedding.forward(ctx.token_ids, ctx)
-        for entry, view in zip(m.run, self.views):
+        for i, (entry, view) in enumerate(zip(m.run, self.views)):
+            if self._nvtx:
+                torch.cuda.nvtx.range_push(f"run{i}:layer{entry.layer}")
             m.layers[entry.layer].forward(residual, ctx, view)
+            if self._nvtx:
+                torch.cuda.nvtx.range_pop()
         if ctx.num_want == 0:
             return None
         if m.head.accepts_lazy_norm:

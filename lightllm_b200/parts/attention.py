@@ -19,6 +19,8 @@ _SMEM_LIMIT = 200 * 1024
 # Portions of at least this many rows run on the tensor-core attention kernel (tiles of 128 rows).
 TENSOR_CORE_MIN_ROWS = 32
 FUSED_ROPE_MAX_ROWS = 16
+# From this many rows on, heads of 64 get their rotation and cache write in the projection's tensor-core epilogue.
+PREFILL_ROPE_MIN_ROWS = 128
 
 
 class AttentionMixer(Mixer):
@@ -116,11 +118,30 @@ class AttentionMixer(Mixer):
                         **operand)
         return q
 
+    def _project_prefill_fused(self, x, ctx, cache: CacheView):
+        """The projection of a long portion with bias, rotation and the cache write in the epilogue of the
+        tensor-core kernel: bfloat16, heads of 64 rotated whole with NeoX pairs.  Returns q, or None."""
+        T = x.shape[0]
+        table = self.position.rotary_table()
+        if (T <= PREFILL_ROPE_MIN_ROWS or table is None or not cache.writes or self.head_dim != 64
+                or x.dtype != torch.bfloat16 or self.w_qkv.dtype != torch.bfloat16 or self.w_qkv.shape[1] % 8
+                or not hasattr(self.position, "step_table")):
+            return None
+        _, rotary_dim, interleaved = table
+        if rotary_dim != 64 or interleaved:
+            return None
+        q = torch.empty((T, self.num_heads * 64), dtype=torch.bfloat16, device=x.device)
+        ops.gemm_tcgen05_rope64(x, self.w_qkv, self.b_qkv, self.position.step_table(ctx), ctx.slot_mapping[cache.group],
+                                q, cache.k, cache.v, self.num_heads, self.num_kv_heads)
+        return q
+
     def forward(self, x, residual, ctx, cache: CacheView) -> None:
         q = self._project_fused(x, ctx, cache)
         if q is None:
             if isinstance(x, LazyNorm):
                 x = x.materialize()
+            q = self._project_prefill_fused(x, ctx, cache)
+        if q is None:
             q = self._project(x, ctx, cache)
         attn = torch.empty_like(q)
         self.attend(q, cache, ctx, attn)

@@ -246,6 +246,52 @@ def test_gemm_decode_rope_kv(ops, M, hd, rd, inter, Hq, Hkv, norm):
     sc = ops.splitk_scratch(dev())
     assert float(sc[0].abs().max()) == 0.0 and int(sc[1].abs().max()) == 0       # the meeting place is left clean
 
+@pytest.mark.parametrize("M", [129, 300, 1000])
+@pytest.mark.parametrize("Hq,Hkv,K,bias_on", [(14, 2, 896, True), (3, 1, 72, False), (5, 5, 200, True)])
+def test_gemm_tcgen05_rope64(ops, M, Hq, Hkv, K, bias_on):
+    """q/k/v projection of a long portion with bias, rotation and the cache write in the tensor-core
+    epilogue, against the plain parts."""
+    hd, page = 64, 16
+    npages = -(-M // page) + 3
+    N = (Hq + 2 * Hkv) * hd
+    w = rnd((N, K), torch.bfloat16, 160, 0.3)
+    bias = rnd((N,), torch.float32, 161) if bias_on else None
+    a = rnd((M, K), torch.bfloat16, 162, 1.0)
+    g = torch.Generator().manual_seed(164)
+    pos = torch.randint(0, 30000, (M,), generator=g, dtype=torch.int32)
+    slots = torch.randperm(npages * page, generator=g)[:M].to(torch.int32)
+    slots[1] = -1
+    slots[M - 2] = -1
+    theta = 1000000.0
+    inv = torch.from_numpy((1.0 / np.power(np.float64(theta), np.arange(0, hd, 2, dtype=np.float64) / hd))
+                           .astype(np.float32)).to(dev())
+    kc = torch.full((npages, page, Hkv, hd), 77.0, dtype=torch.bfloat16, device=dev())
+    vc = torch.full((npages, page, Hkv, hd), 77.0, dtype=torch.bfloat16, device=dev())
+    q = torch.full((M, Hq * hd), float("nan"), dtype=torch.bfloat16, device=dev())
+    table = ops.rope_table(pos.to(dev()), inv)
+    ops.gemm_tcgen05_rope64(a, w, bias, table, slots.to(dev()), q, kc, vc, Hq, Hkv)
+    ops.check_async_errors(dev())
+    y = a.double().cpu() @ w.double().cpu().t()
+    if bias_on:
+        y = y + bias.double().cpu()
+    y = y.float()
+    qr = plain_rope(y[:, : Hq * hd].reshape(M, Hq, hd), pos, theta, hd, False)
+    kr = plain_rope(y[:, Hq * hd: (Hq + Hkv) * hd].reshape(M, Hkv, hd), pos, theta, hd, False)
+    vr = y[:, (Hq + Hkv) * hd:].reshape(M, Hkv, hd)
+    scale = max(1.0, float(y.abs().max()))
+    tol = 2.0 ** -8 * scale      # one rounding to bfloat16 of a value of at most `scale`, and the table's float angles
+    assert torch.allclose(q.float().cpu().reshape(M, Hq, hd), qr, atol=tol, rtol=0)
+    kexp = torch.full((npages * page, Hkv, hd), 77.0)
+    vexp = kexp.clone()
+    for t, sl in enumerate(slots.tolist()):
+        if sl >= 0:
+            kexp[sl], vexp[sl] = kr[t], vr[t]
+    assert torch.allclose(kc.float().cpu().reshape(-1, Hkv, hd), kexp, atol=tol, rtol=0)
+    assert torch.allclose(vc.float().cpu().reshape(-1, Hkv, hd), vexp, atol=tol, rtol=0)
+    with pytest.raises(ops.KernelError):
+        ops.gemm_tcgen05_rope64(a[:100].contiguous(), w, bias, table[:100].contiguous(), slots[:100].to(dev()),
+                                q[:100].contiguous(), kc, vc, Hq, Hkv)
+
 
 @pytest.mark.parametrize("dtype", DT)
 @pytest.mark.parametrize("hd,rd,inter", [(16, 16, False), (32, 32, True), (64, 64, False), (48, 32, False),
