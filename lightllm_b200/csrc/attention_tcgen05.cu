@@ -1,11 +1,14 @@
 // Paged flash-attention for prompt portions on the 5th-generation tensor cores (sm_100a, bf16).
 //
-// One block takes 128 consecutive query rows of one span and one query head.  Keys and values
-// come from the request's pages, 128 keys at a time: TMA copies each page of the tile (a box of
-// page_size rows x 64 elements) into a swizzled shared-memory tile, double buffered.  Then
-//     S = Q K^T          tcgen05.mma, both operands K-major, S in tensor memory (128 columns)
+// A work item is 128 consecutive query rows of one span and one query head over a range of key tiles.
+// Blocks are persistent: each walks through its share of the items with three roles, a loader warp, a warp
+// that issues the tensor-core instructions, and eight softmax warps.  Keys and values come from the
+// request's pages, 128 keys at a time: TMA copies each page of the tile (a box of page_size rows x 64
+// elements) into a swizzled shared-memory tile, double buffered, ahead of use and across item boundaries.  Then
+//     S = Q K^T          tcgen05.mma, both operands K-major, S in tensor memory (128 columns); issued for tile
+//                        j+1 as soon as S of tile j has been read
 //     softmax            two threads per query row (each half of the tile's keys) read S with tcgen05.ld; scale, mask by
-//                        absolute position (and window), running max and sum in float
+//                        absolute position (and window) with selects, running max and sum in float
 //     O_tile = P V       P (bf16) goes back to shared memory as the A operand; V is the B operand in
 //                        MN-major form (its rows are keys), result in tensor memory
 //     O = O * e^(m_old - m_new) + O_tile   in registers, float
@@ -15,7 +18,7 @@
 //
 // Head sizes 64 and 128; page sizes that divide 128 and are multiples of 8.  Other shapes use the
 // CUDA-core kernel.  Every wait on an mbarrier is bounded in time; when one runs out the block raises
-// the error flag, falls through to the exit, frees its tensor memory and returns.
+// the error flag, walks through the rest of its items without work, frees its tensor memory and returns.
 #include <cuda.h>
 
 #include <mutex>
@@ -27,15 +30,12 @@ namespace {
 
 constexpr int BQ = 128;     // query rows per block = TMEM lanes
 constexpr int BKV = 128;    // keys per tile
-constexpr int NUM_THREADS = 256;   // two threads per query row: each takes half of a tile's keys and half of the output
+constexpr int NUM_THREADS = 320;   // 8 softmax warps (two threads per query row: each takes half of a tile's keys and
+                                   // half of the output), the warp that issues tensor-core work, the loader warp
+constexpr int MMA_WARP = 8, LOAD_WARP = 9;
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;   // about 2 s of SM cycles
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ unsigned long long globaltimer_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
 }
@@ -123,12 +123,14 @@ __device__ __forceinline__ float fast_exp2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-__device__ __forceinline__ bool key_visible(int kp, int qpos, int hi, int lo, int window) {
-    return kp <= qpos && kp < hi && kp >= lo && (window <= 0 || qpos - kp < window);
+// Masking is a select on the column index, never a branch: columns c_lo .. c_hi of the tile are this row's
+// visible keys (causal, the span's end, the window's start; c_hi < c_lo when none is).
+__device__ __forceinline__ float masked(float s, int col, int c_lo, int c_hi) {
+    return (col >= c_lo && col <= c_hi) ? s : -INFINITY;
 }
 // Largest raw score of this thread's row among the visible keys of its two 32-column chunks of the tile.
 template <bool MASKED>
-__device__ __forceinline__ float row_max(uint32_t tmem_s, int c_begin, int kt, int qpos, int hi, int lo, int window) {
+__device__ __forceinline__ float row_max(uint32_t tmem_s, int c_begin, int c_lo, int c_hi) {
     float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll 1
     for (int c = c_begin; c < c_begin + 2; ++c) {
@@ -136,8 +138,7 @@ __device__ __forceinline__ float row_max(uint32_t tmem_s, int c_begin, int kt, i
         tmem_ld32(tmem_s + c * 32, s);
         if (MASKED) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-                if (!key_visible(kt + c * 32 + i, qpos, hi, lo, window)) s[i] = -INFINITY;
+            for (int i = 0; i < 32; ++i) s[i] = masked(s[i], c * 32 + i, c_lo, c_hi);
         }
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
@@ -150,7 +151,7 @@ __device__ __forceinline__ float row_max(uint32_t tmem_s, int c_begin, int kt, i
 // their sum (float, before rounding).  Row r, 16-byte chunk q of a 128-byte row lands at chunk q ^ (r & 7).
 template <bool MASKED>
 __device__ __forceinline__ float row_probs(uint32_t tmem_s, uint8_t* p_s, int r, int c_begin, float c_scale, float m_use,
-                                           int kt, int qpos, int hi, int lo, int window) {
+                                           int c_lo, int c_hi) {
     float l0 = 0.0f, l1 = 0.0f;
 #pragma unroll 1
     for (int c = c_begin; c < c_begin + 2; ++c) {
@@ -158,8 +159,7 @@ __device__ __forceinline__ float row_probs(uint32_t tmem_s, uint8_t* p_s, int r,
         tmem_ld32(tmem_s + c * 32, s);
         if (MASKED) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-                if (!key_visible(kt + c * 32 + i, qpos, hi, lo, window)) s[i] = -INFINITY;
+            for (int i = 0; i < 32; ++i) s[i] = masked(s[i], c * 32 + i, c_lo, c_hi);
         }
         uint8_t* prow = p_s + (c >> 1) * (128 * 128) + (uint32_t)r * 128;
 #pragma unroll
@@ -189,7 +189,7 @@ struct AttnTcParams {
     const int* span_len;
     const int* span_pos;
     const int* block_table;    // [S, max_pages]
-    int max_pages, page_size, Hq, Hkv, window, num_slots;
+    int max_pages, page_size, Hq, Hkv, window, num_slots, num_items;
     float scale_log2e;         // scale * log2(e): scores are kept in base-2 units
     uint32_t dynamic_smem_bytes;
     // Optional cut of a tile's key range into work items, so that long rows do not set the kernel's time:
@@ -203,6 +203,45 @@ struct AttnTcParams {
     int* error_flag;
 };
 
+// What one work item is: 128 query rows of one span and one head over a range of key tiles.
+struct Item {
+    int head, span, row0, nrows, pos0, hi, lo, kt0, ntiles, part;
+};
+__device__ __forceinline__ Item make_item(const AttnTcParams& p, int idx) {
+    Item it;
+    const int tile = idx / p.Hq;
+    it.head = idx - tile * p.Hq;
+    it.span = p.tile_span[tile];
+    const int q0 = p.tile_q0[tile];
+    it.row0 = p.span_row[it.span] + q0;
+    it.nrows = min(BQ, p.span_len[it.span] - q0);
+    it.pos0 = p.span_pos[it.span] + q0;
+    it.hi = it.pos0 + it.nrows;                                    // keys [lo, hi) can be visible
+    it.lo = p.window > 0 ? max(0, it.pos0 - p.window + 1) : 0;
+    const int k_first = p.tile_k0 ? p.tile_k0[tile] : 0;
+    it.kt0 = (it.lo / BKV) * BKV + k_first * BKV;
+    const int all_tiles = (it.hi - (it.lo / BKV) * BKV + BKV - 1) / BKV - k_first;
+    it.ntiles = max(0, p.tile_nk ? min(p.tile_nk[tile], all_tiles) : all_tiles);
+    it.part = p.tile_part ? p.tile_part[tile] : -1;
+    return it;
+}
+
+// Named barriers of the block (0 is __syncthreads).
+constexpr int BAR_SOFTMAX = 1;     // the 256 softmax threads: the halves of a row have exchanged their maxima
+constexpr int BAR_P_READY = 2;     // softmax threads and the MMA warp: S is read, P is in shared memory
+constexpr int BAR_TILE_END = 3;    // softmax threads and the MMA warp: the tile's P V result is read
+__device__ __forceinline__ void named_barrier(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// A persistent block: it takes the work items blockIdx.x, blockIdx.x + gridDim.x, ... (item = query tile x head,
+// heads fastest, so that neighbouring blocks read the same keys) and keeps three roles busy:
+//   warp 9   loader: Q of the next item and the key/value tiles, two stages ahead, across item boundaries
+//   warp 8   issues the tensor-core instructions: S of tile j+1 right after P V of tile j
+//   warps 0-7  softmax, two threads per query row
+// The roles meet on mbarriers (data arrived, buffers free, tensor-core work done; every wait is bounded) and on
+// named barriers among softmax and MMA warps.  After a wait has run out every role still walks through all its
+// items and barriers, without copies, tensor-core work or stores, so that no barrier is left waiting.
 template <int HD>
 __global__ void __launch_bounds__(NUM_THREADS, HD <= 64 ? 2 : 1)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -213,7 +252,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     // Barriers live in static shared memory; the operand tiles in dynamic shared memory, aligned to
     // 1024 bytes for the swizzle.  The sizes are chosen so that two blocks of the head-64 kernel fit
     // in one SM, which leaves no room to spare: the fit is checked before anything is copied.
-    __shared__ __align__(8) uint64_t bars[5];
+    __shared__ __align__(8) uint64_t bars[8];
     __shared__ uint32_t tmem_slot_s;
     __shared__ int abort_s;
     // The halves of a row agree on its maximum through this buffer.  The value is rounded up to bf16: any
@@ -225,10 +264,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     uint8_t* k_s = q_s + KB * TILE_BYTES;             // 2 stages x KB tiles
     uint8_t* v_s = k_s + 2 * KB * TILE_BYTES;         // 2 stages x KB tiles
     uint8_t* p_s = v_s + 2 * KB * TILE_BYTES;         // 2 tiles (keys 0..63, 64..127)
-    uint64_t* bar_q = &bars[0];
-    uint64_t* bar_kv = &bars[1];                      // [2]
-    uint64_t* bar_s = &bars[3];
-    uint64_t* bar_pv = &bars[4];
+    uint64_t* bar_q_full = &bars[0];
+    uint64_t* bar_q_free = &bars[1];                  // the item's last S = Q K^T has been computed
+    uint64_t* bar_kv_full = &bars[2];                 // [2]
+    uint64_t* bar_kv_free = &bars[4];                 // [2] the tile's P V has been computed
+    uint64_t* bar_s = &bars[6];
+    uint64_t* bar_pv = &bars[7];
     uint32_t* tmem_slot = &tmem_slot_s;
     volatile int* abort_flag = &abort_s;
     if (p_s + 2 * TILE_BYTES > smem_raw + p.dynamic_smem_bytes) {     // uniform over the block
@@ -237,28 +278,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     }
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile = blockIdx.x, head = blockIdx.y;
-    const int kvh = head / (p.Hq / p.Hkv);
-    const int span = p.tile_span[tile];
-    const int q0 = p.tile_q0[tile];
-    const int row0 = p.span_row[span] + q0;
-    const int nrows = min(BQ, p.span_len[span] - q0);
-    const int pos0 = p.span_pos[span] + q0;
-    const int* bt = p.block_table + (size_t)span * p.max_pages;
-    const int hi = pos0 + nrows;                                   // keys [lo, hi) can be visible
-    const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
-    const int k_first = p.tile_k0 ? p.tile_k0[tile] : 0;
-    const int kt0 = (lo / BKV) * BKV + k_first * BKV;
-    const int all_tiles = (hi - (lo / BKV) * BKV + BKV - 1) / BKV - k_first;
-    const int ntiles = p.tile_nk ? min(p.tile_nk[tile], all_tiles) : all_tiles;
-    const int part = p.tile_part ? p.tile_part[tile] : -1;
-
     if (threadIdx.x == 0) {
-        mbar_init(bar_q, 1);
-        mbar_init(&bar_kv[0], 1);
-        mbar_init(&bar_kv[1], 1);
-        mbar_init(bar_s, 1);
-        mbar_init(bar_pv, 1);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) mbar_init(&bars[i], 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -272,60 +294,57 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
-    const int half = warp >> 2;                       // which half of the keys (and of the output dimensions)
-    const uint32_t tmem_s = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-    const uint32_t tmem_o = tmem_s + 128 + half * (HD / 2);
-
-    // Loads of one key/value tile: each lane of warp 0 takes pages of the tile.
-    auto load_kv = [&](int j) {
-        const int st = j & 1;
-        const int kt = kt0 + j * BKV;
-        if (lane == 0) mbar_expect_tx(&bar_kv[st], 2 * KB * TILE_BYTES);
-        __syncwarp();
-        const int ppt = BKV / p.page_size;
-        for (int pg = lane; pg < ppt; pg += 32) {
-            const int lp = kt / p.page_size + pg;
-            const int page = lp < p.max_pages ? bt[lp] : -1;
-            const int y = page >= 0 ? page * p.page_size : p.num_slots;    // out of range: the box is zero-filled
-            const uint32_t off = (uint32_t)pg * p.page_size * 128;
-#pragma unroll
-            for (int kb = 0; kb < KB; ++kb) {
-                tma_load_2d(k_s + (st * KB + kb) * TILE_BYTES + off, &map_k, kvh * HD + kb * 64, y, &bar_kv[st]);
-                tma_load_2d(v_s + (st * KB + kb) * TILE_BYTES + off, &map_v, kvh * HD + kb * 64, y, &bar_kv[st]);
-            }
-        }
-    };
-
-    if (warp == 0) {
-        if (lane == 0) {
-            mbar_expect_tx(bar_q, KB * TILE_BYTES);
-#pragma unroll
-            for (int kb = 0; kb < KB; ++kb)
-                tma_load_2d(q_s + kb * TILE_BYTES, &map_q, head * HD + kb * 64, row0, bar_q);
-        }
-        __syncwarp();
-        if (ntiles > 0) load_kv(0);
-    }
-
-    const int r = threadIdx.x & (BQ - 1);       // query row of this thread = TMEM lane
-    const int qpos = pos0 + r;
-    constexpr int HO = HD / 2;                  // output dimensions of this thread
-    float o[HO];
-#pragma unroll
-    for (int d = 0; d < HO; ++d) o[d] = 0.0f;
-    float m_run = -INFINITY, l_run = 0.0f;
-    bool ok = mbar_wait(bar_q, 0, abort_flag);
-
+    const int total = p.num_items;
+    const int group = p.Hq / p.Hkv;
     constexpr uint32_t IDESC_S = idesc_bf16(BQ, BKV, 0);
     constexpr uint32_t IDESC_PV = idesc_bf16(BQ, HD, 1);
+    constexpr int NUM_SOFTMAX = 256;
 
-    for (int j = 0; j < ntiles && ok; ++j) {
-        const int st = j & 1;
-        const int kt = kt0 + j * BKV;
-        if (warp == 0 && j + 1 < ntiles) load_kv(j + 1);     // the other stage was released by tile j-1's P V
-        ok = mbar_wait(&bar_kv[st], (j >> 1) & 1, abort_flag);
-        if (!ok) break;
-        if (threadIdx.x == 0) {
+    if (warp == LOAD_WARP) {
+        // ---- loader ------------------------------------------------------------------------------
+        bool ok = true;
+        uint32_t n_kv = 0, n_item = 0;
+        for (int idx = blockIdx.x; idx < total; idx += gridDim.x) {
+            const Item it = make_item(p, idx);
+            if (it.ntiles <= 0) continue;        // cannot happen with the lists the engine makes; every role skips it alike
+            const int kvh = it.head / group;
+            const int* bt = p.block_table + (size_t)it.span * p.max_pages;
+            if (n_item > 0) ok = mbar_wait(bar_q_free, (n_item - 1) & 1, abort_flag) && ok;
+            if (lane == 0 && ok) {
+                mbar_expect_tx(bar_q_full, KB * TILE_BYTES);
+#pragma unroll
+                for (int kb = 0; kb < KB; ++kb)
+                    tma_load_2d(q_s + kb * TILE_BYTES, &map_q, it.head * HD + kb * 64, it.row0, bar_q_full);
+            }
+            for (int j = 0; j < it.ntiles; ++j, ++n_kv) {
+                const int st = n_kv & 1;
+                const int kt = it.kt0 + j * BKV;
+                // page numbers first: their latency then lies under the wait for the stage
+                const int ppt = BKV / p.page_size;
+                const int lp = kt / p.page_size + lane;
+                const int page = (lane < ppt && lp < p.max_pages) ? bt[lp] : -1;
+                if (n_kv >= 2) ok = mbar_wait(&bar_kv_free[st], ((n_kv >> 1) - 1) & 1, abort_flag) && ok;
+                if (!ok) continue;
+                if (lane == 0) mbar_expect_tx(&bar_kv_full[st], 2 * KB * TILE_BYTES);
+                __syncwarp();
+                if (lane < ppt) {
+                    const int y = page >= 0 ? page * p.page_size : p.num_slots;   // out of range: the box is zero-filled
+                    const uint32_t off = (uint32_t)lane * p.page_size * 128;
+#pragma unroll
+                    for (int kb = 0; kb < KB; ++kb) {
+                        tma_load_2d(k_s + (st * KB + kb) * TILE_BYTES + off, &map_k, kvh * HD + kb * 64, y, &bar_kv_full[st]);
+                        tma_load_2d(v_s + (st * KB + kb) * TILE_BYTES + off, &map_v, kvh * HD + kb * 64, y, &bar_kv_full[st]);
+                    }
+                }
+                __syncwarp();
+            }
+            ++n_item;
+        }
+    } else if (warp == MMA_WARP) {
+        // ---- tensor-core instructions ----------------------------------------------------------------
+        bool ok = true;
+        uint32_t n_kv = 0, n_item = 0;
+        auto issue_s = [&](int st, bool last) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
             for (int kb = 0; kb < KB; ++kb)
@@ -335,82 +354,135 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                               desc_kmajor(smem_u32(k_s + (st * KB + kb) * TILE_BYTES) + k * 32), IDESC_S,
                               (kb > 0 || k > 0) ? 1u : 0u);
             umma_commit(bar_s);
-        }
-        ok = mbar_wait(bar_s, j & 1, abort_flag);
-        if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-
-        // Softmax of this thread's row over the 128 keys of the tile, in two passes over tensor
-        // memory (maximum first, then the probabilities), 32 columns at a time.  Tiles that lie wholly
-        // below the diagonal and inside the window of every row of the block skip the masking.
-        const bool interior = (kt + BKV - 1 <= pos0) && (p.window <= 0 || (pos0 + BQ - 1) - kt < p.window);
-        float m_tile;
-        if (interior) m_tile = row_max<false>(tmem_s, 2 * half, kt, qpos, hi, lo, p.window);
-        else m_tile = row_max<true>(tmem_s, 2 * half, kt, qpos, hi, lo, p.window);
-        xch[half][r] = __float2bfloat16_ru(m_tile);      // rewritten only after the barriers further down
-        __syncthreads();
-        m_tile = fmaxf(__bfloat162float(xch[0][r]), __bfloat162float(xch[1][r])) * p.scale_log2e;   // the scale is positive
-        const float m_new = fmaxf(m_run, m_tile);
-        const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;      // nothing visible yet: all p are 0
-        const float corr = (m_run == -INFINITY) ? 0.0f : fast_exp2(m_run - m_use);
-        float l_tile;
-        if (interior) l_tile = row_probs<false>(tmem_s, p_s, r, 2 * half, p.scale_log2e, m_use, kt, qpos, hi, lo, p.window);
-        else l_tile = row_probs<true>(tmem_s, p_s, r, 2 * half, p.scale_log2e, m_use, kt, qpos, hi, lo, p.window);
-        l_run = l_run * corr + l_tile;
-        m_run = m_new;
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // P is read by the tensor core
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            // O_tile[128 x HD] = P[128 x 128 keys] V[128 keys x HD]; 16 keys per instruction
+            if (last) umma_commit(bar_q_free);
+        };
+        for (int idx = blockIdx.x; idx < total; idx += gridDim.x) {
+            const Item it = make_item(p, idx);
+            if (it.ntiles <= 0) continue;
+            ok = mbar_wait(bar_q_full, n_item & 1, abort_flag) && ok;
+            for (int j = 0; j < it.ntiles; ++j, ++n_kv) {
+                const int st = n_kv & 1;
+                if (j == 0) {
+                    ok = mbar_wait(&bar_kv_full[st], (n_kv >> 1) & 1, abort_flag) && ok;
+                    if (lane == 0 && ok) issue_s(st, it.ntiles == 1);
+                    __syncwarp();
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                named_barrier(BAR_P_READY, NUM_SOFTMAX + 32);
+                if (lane == 0 && ok) {
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    // O_tile[128 x HD] = P[128 x 128 keys] V[128 keys x HD]; 16 keys per instruction
 #pragma unroll
-            for (int k = 0; k < BKV / 16; ++k)
-                umma_bf16(tmem_base + 128, desc_kmajor(smem_u32(p_s + (k >> 2) * TILE_BYTES) + (k & 3) * 32),
-                          desc_mnmajor(smem_u32(v_s + st * KB * TILE_BYTES) + k * 16 * 128, TILE_BYTES), IDESC_PV,
-                          k > 0 ? 1u : 0u);
-            umma_commit(bar_pv);
-        }
-        ok = mbar_wait(bar_pv, j & 1, abort_flag);
-        if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-        for (int c = 0; c < HO / 32; ++c) {
-            float t[32];
-            tmem_ld32(tmem_o + c * 32, t);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * corr + t[i];
-        }
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();        // S and the P V columns may be overwritten, P and this K/V stage reused
-    }
-
-    // The halves of a row add up their sums; each writes its half of the dimensions.
-    float* lx = reinterpret_cast<float*>(p_s);         // the P tile is idle now
-    lx[half * BQ + r] = l_run;
-    __syncthreads();
-    const float l_row = lx[r] + lx[BQ + r];
-    if (ok && r < nrows && part >= 0) {
-        float* po = p.part_o + (((size_t)part * p.Hq + head) * BQ + r) * HD + half * HO;
-#pragma unroll
-        for (int d = 0; d < HO; d += 4) *reinterpret_cast<float4*>(po + d) = make_float4(o[d], o[d + 1], o[d + 2], o[d + 3]);
-        if (half == 0) {
-            float* pm = p.part_ml + (((size_t)part * p.Hq + head) * BQ + r) * 2;
-            pm[0] = m_run;
-            pm[1] = l_row;
-        }
-    } else if (ok && r < nrows) {
-        const float inv = 1.0f / l_row;
-        __nv_bfloat16* dst = p.out + ((size_t)(row0 + r) * p.Hq + head) * HD + half * HO;
-#pragma unroll
-        for (int d = 0; d < HO; d += 8) {
-            uint32_t w[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const __nv_bfloat162 h = __floats2bfloat162_rn(o[d + 2 * e] * inv, o[d + 2 * e + 1] * inv);
-                w[e] = *reinterpret_cast<const uint32_t*>(&h);
+                    for (int k = 0; k < BKV / 16; ++k)
+                        umma_bf16(tmem_base + 128, desc_kmajor(smem_u32(p_s + (k >> 2) * TILE_BYTES) + (k & 3) * 32),
+                                  desc_mnmajor(smem_u32(v_s + st * KB * TILE_BYTES) + k * 16 * 128, TILE_BYTES), IDESC_PV,
+                                  k > 0 ? 1u : 0u);
+                    umma_commit(bar_pv);
+                    umma_commit(&bar_kv_free[st]);
+                }
+                __syncwarp();
+                if (j + 1 < it.ntiles) {
+                    // S of the next tile runs under the softmax threads' read of this tile's P V
+                    const uint32_t n2 = n_kv + 1;
+                    ok = mbar_wait(&bar_kv_full[n2 & 1], (n2 >> 1) & 1, abort_flag) && ok;
+                    if (lane == 0 && ok) issue_s(n2 & 1, j + 2 == it.ntiles);
+                    __syncwarp();
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                named_barrier(BAR_TILE_END, NUM_SOFTMAX + 32);
             }
-            *reinterpret_cast<uint4*>(dst + d) = make_uint4(w[0], w[1], w[2], w[3]);
+            ++n_item;
+        }
+    } else {
+        // ---- softmax ---------------------------------------------------------------------------------
+        const int half = warp >> 2;                       // which half of the keys (and of the output dimensions)
+        const uint32_t tmem_s = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+        const uint32_t tmem_o = tmem_s + 128 + half * (HD / 2);
+        const int r = threadIdx.x & (BQ - 1);       // query row of this thread = TMEM lane
+        constexpr int HO = HD / 2;                  // output dimensions of this thread
+        bool ok = true;
+        uint32_t n_s = 0;
+        for (int idx = blockIdx.x; idx < total; idx += gridDim.x) {
+            const Item it = make_item(p, idx);
+            if (it.ntiles <= 0) continue;
+            const int qpos = it.pos0 + r;
+            // visible keys of this row: positions vis_lo .. vis_hi
+            const int vis_lo = p.window > 0 ? max(it.lo, qpos - p.window + 1) : it.lo;
+            const int vis_hi = min(qpos, it.hi - 1);
+            float o[HO];
+#pragma unroll
+            for (int d = 0; d < HO; ++d) o[d] = 0.0f;
+            float m_run = -INFINITY, l_run = 0.0f;
+            for (int j = 0; j < it.ntiles; ++j, ++n_s) {
+                const int kt = it.kt0 + j * BKV;
+                ok = mbar_wait(bar_s, n_s & 1, abort_flag) && ok;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                // Softmax of this thread's row over its 64 keys of the tile, in two passes over tensor memory
+                // (maximum first, then the probabilities), 32 columns at a time.  Tiles that lie wholly below
+                // the diagonal and inside the window of every row of the block skip the masking.
+                const bool interior = (kt + BKV - 1 <= it.pos0) && (p.window <= 0 || (it.pos0 + BQ - 1) - kt < p.window);
+                const int c_lo = vis_lo - kt, c_hi = vis_hi - kt;
+                float m_tile;
+                if (interior) m_tile = row_max<false>(tmem_s, 2 * half, c_lo, c_hi);
+                else m_tile = row_max<true>(tmem_s, 2 * half, c_lo, c_hi);
+                xch[half][r] = __float2bfloat16_ru(m_tile);      // rewritten only after the barriers further down
+                named_barrier(BAR_SOFTMAX, NUM_SOFTMAX);
+                m_tile = fmaxf(__bfloat162float(xch[0][r]), __bfloat162float(xch[1][r])) * p.scale_log2e;   // the scale is positive
+                const float m_new = fmaxf(m_run, m_tile);
+                const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;      // nothing visible yet: all p are 0
+                const float corr = (m_run == -INFINITY) ? 0.0f : fast_exp2(m_run - m_use);
+                float l_tile;
+                if (interior) l_tile = row_probs<false>(tmem_s, p_s, r, 2 * half, p.scale_log2e, m_use, c_lo, c_hi);
+                else l_tile = row_probs<true>(tmem_s, p_s, r, 2 * half, p.scale_log2e, m_use, c_lo, c_hi);
+                l_run = l_run * corr + l_tile;
+                m_run = m_new;
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // P is read by the tensor core
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                named_barrier(BAR_P_READY, NUM_SOFTMAX + 32);
+                ok = mbar_wait(bar_pv, n_s & 1, abort_flag) && ok;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (int c = 0; c < HO / 32; ++c) {
+                    float t[32];
+                    tmem_ld32(tmem_o + c * 32, t);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * corr + t[i];
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                named_barrier(BAR_TILE_END, NUM_SOFTMAX + 32);   // S's successor may be read, the P V columns overwritten
+            }
+
+            // The halves of a row add up their sums; each writes its half of the dimensions.  The P tile is idle:
+            // its last reader (the tile's P V) has completed, and the next item's P is written only after a
+            // barrier of all softmax threads.
+            float* lx = reinterpret_cast<float*>(p_s);
+            lx[half * BQ + r] = l_run;
+            named_barrier(BAR_SOFTMAX, NUM_SOFTMAX);
+            const float l_row = lx[r] + lx[BQ + r];
+            if (ok && r < it.nrows && it.part >= 0) {
+                float* po = p.part_o + (((size_t)it.part * p.Hq + it.head) * BQ + r) * HD + half * HO;
+#pragma unroll
+                for (int d = 0; d < HO; d += 4)
+                    *reinterpret_cast<float4*>(po + d) = make_float4(o[d], o[d + 1], o[d + 2], o[d + 3]);
+                if (half == 0) {
+                    float* pm = p.part_ml + (((size_t)it.part * p.Hq + it.head) * BQ + r) * 2;
+                    pm[0] = m_run;
+                    pm[1] = l_row;
+                }
+            } else if (ok && r < it.nrows) {
+                const float inv = 1.0f / l_row;
+                __nv_bfloat16* dst = p.out + ((size_t)(it.row0 + r) * p.Hq + it.head) * HD + half * HO;
+#pragma unroll
+                for (int d = 0; d < HO; d += 8) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const __nv_bfloat162 h = __floats2bfloat162_rn(o[d + 2 * e] * inv, o[d + 2 * e + 1] * inv);
+                        w[e] = *reinterpret_cast<const uint32_t*>(&h);
+                    }
+                    *reinterpret_cast<uint4*>(dst + d) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            }
         }
     }
 
@@ -508,10 +580,9 @@ template <int HD>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnTcParams& p, int num_tiles,
            cudaStream_t stream) {
     constexpr int KB = HD / 64;
-    // tiles + what aligning to 1024 bytes can cost after the 48 bytes of static shared memory
-    // 560 bytes of static shared memory (barriers, the halves' exchange) precede the tiles; the rest of the
+    // 584 bytes of static shared memory (barriers, the halves' exchange) precede the tiles; the rest of the
     // kilobyte is what aligning the tiles to 1024 bytes can cost (checked in the kernel)
-    constexpr size_t smem = (size_t)(KB + 4 * KB + 2) * 128 * 128 + 1024 - 560;
+    constexpr size_t smem = (size_t)(KB + 4 * KB + 2) * 128 * 128 + 1024 - 592;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -520,9 +591,20 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
                                               cudaGetErrorString(e));
         configured = true;
     }
-    dim3 grid(num_tiles, p.Hq);
+    static int num_sms = 0;
+    if (num_sms == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || num_sms <= 0) {
+            num_sms = 0;
+            return llb_fail("attention_tcgen05: cannot ask the device for its number of SMs");
+        }
+    }
     AttnTcParams pp = p;
     pp.dynamic_smem_bytes = (uint32_t)smem;
+    pp.num_items = num_tiles * p.Hq;
+    const int resident = (HD <= 64 ? 2 : 1) * num_sms;       // persistent blocks: as many as stay on the device
+    const int grid = pp.num_items < resident ? pp.num_items : resident;
     attention_tcgen05_kernel<HD><<<grid, NUM_THREADS, smem, stream>>>(mq, mk, mv, pp);
     return llb_check_launch("attention_tcgen05");
 }
@@ -552,7 +634,7 @@ LLB_EXPORT int llb_paged_attention_tcgen05(const void* q, const void* k_cache, c
     LLB_REQUIRE(llb_attention_tcgen05_supports(hd, page_size),
                 "attention_tcgen05: head_dim %d with page size %d is not supported (head 64 or 128; page size a "
                 "multiple of 8 that divides 128)", hd, page_size);
-    LLB_REQUIRE(Hq > 0 && Hkv > 0 && Hq % Hkv == 0 && Hq <= 65535, "attention_tcgen05: bad head counts %d/%d", Hq, Hkv);
+    LLB_REQUIRE(Hq > 0 && Hkv > 0 && Hq % Hkv == 0 && Hq <= 65535 && (long long)num_tiles * Hq < (1ll << 30), "attention_tcgen05: bad head counts %d/%d", Hq, Hkv);
     LLB_REQUIRE(((uintptr_t)q % 16 == 0) && ((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0) &&
                 ((uintptr_t)out % 16 == 0), "attention_tcgen05: tensors must be 16-byte aligned");
     CUtensorMap mq, mk, mv;
