@@ -7,6 +7,8 @@ or loaded, or a tensor is not on a CUDA device, the call raises.
 from __future__ import annotations
 
 import ctypes
+import os
+import re
 from typing import Optional
 
 import torch
@@ -33,14 +35,38 @@ def lib() -> ctypes.CDLL:
             handle = ctypes.CDLL(path)
         except OSError as e:
             raise KernelError(f"cannot load the kernel library {path}: {e}") from None
-        handle.llb_last_error.restype = ctypes.c_char_p
-        handle.llb_launch_count.restype = ctypes.c_ulonglong
-        handle.llb_attention_smem_bytes.restype = ctypes.c_longlong
-        handle.llb_attention_scratch_floats.restype = ctypes.c_longlong
+        _declare_signatures(handle)
         if handle.llb_abi_version() != ABI_VERSION:
             raise KernelError(f"{path} has ABI version {handle.llb_abi_version()}, expected {ABI_VERSION}")
         _lib = handle
     return _lib
+
+
+_C_TYPES = {"int": ctypes.c_int, "float": ctypes.c_float, "long long": ctypes.c_longlong,
+            "unsigned long long": ctypes.c_ulonglong, "cudaStream_t": ctypes.c_void_p, "const char*": ctypes.c_char_p}
+
+
+def _declare_signatures(handle: ctypes.CDLL) -> None:
+    """Argument and result types of every entry point, read from the ``LLB_EXPORT`` definitions in the
+    sources the library was built from: pointers are passed as plain integers, without a ctypes
+    object per argument."""
+    pattern = re.compile(r"LLB_EXPORT\s+([\w\s\*]+?)\s*\b(llb_\w+)\s*\(([^)]*)\)\s*\{")
+
+    def ctype(decl: str):
+        decl = " ".join(decl.split())
+        if decl in _C_TYPES:
+            return _C_TYPES[decl]
+        if decl.endswith("*"):
+            return ctypes.c_void_p
+        raise KernelError(f"kernel library: no ctypes type for the C type {decl!r}")
+
+    for name in _build.sources():
+        with open(os.path.join(_build.CSRC_DIR, name)) as f:
+            text = f.read()
+        for ret, fn, args in pattern.findall(text):
+            func = getattr(handle, fn)
+            func.restype = ctype(ret)
+            func.argtypes = [ctype(re.sub(r"\s*\w+$", "", a.strip())) for a in args.split(",") if a.strip() not in ("", "void")]
 
 
 def _check(rc: int) -> None:
@@ -56,24 +82,45 @@ def _dt(t: torch.Tensor) -> int:
     raise KernelError(f"unsupported dtype {t.dtype}; the kernels take float32 and bfloat16")
 
 
-def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    """Device address of a tensor (None: a null pointer)."""
     if t is None:
-        return ctypes.c_void_p(0)
+        return None
     if not t.is_cuda:
         raise KernelError("tensor is not on a CUDA device; there is no CPU path")
     if not t.is_contiguous():
         raise KernelError(f"tensor of shape {tuple(t.shape)} must be contiguous")
-    return ctypes.c_void_p(t.data_ptr())
+    return t.data_ptr()
 
 
-def _i32(t: Optional[torch.Tensor], what: str) -> ctypes.c_void_p:
+def _i32(t: Optional[torch.Tensor], what: str) -> Optional[int]:
     if t is not None and t.dtype != torch.int32:
         raise KernelError(f"{what} must be int32, got {t.dtype}")
     return _ptr(t)
 
 
-def _stream() -> ctypes.c_void_p:
-    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+_scoped_stream: Optional[int] = None
+
+
+class stream_scope:
+    """Within the scope every launch goes to the stream that was current on entry, without asking torch
+    again for each kernel.  The stream must not be switched inside the scope."""
+
+    def __enter__(self):
+        global _scoped_stream
+        self._outer = _scoped_stream
+        _scoped_stream = torch.cuda.current_stream().cuda_stream
+        return self
+
+    def __exit__(self, *exc):
+        global _scoped_stream
+        _scoped_stream = self._outer
+        return False
+
+
+def _stream() -> int:
+    s = _scoped_stream
+    return s if s is not None else torch.cuda.current_stream().cuda_stream
 
 
 def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, err: Optional[torch.Tensor] = None) -> None:

@@ -69,10 +69,32 @@ class StepContext:
         self.err: Optional[torch.Tensor] = None
         self._tiles: Dict[int, Any] = {}
         self.memo: Dict[Any, Any] = {}          # per-step values that parts share (e.g. rotary tables)
+        # Index arrays that parts derive from the batch (tiles, work items) travel with the step's other
+        # metadata when they are made before it is copied (in the parts' ``prepare``): ``_staging`` is
+        # ``[host int32 array, device int32 tensor, next word, end]`` while that is possible.
+        self._staging: Optional[list] = None
+        self.staged_words = 0
+        self.late_uploads = False               # an array was made after the copy and went up on its own
+        self.shape_key: List[Any] = []          # what the step's launches depend on beyond its counts
 
     @property
     def num_spans(self) -> int:
         return len(self.spans)
+
+    def stage(self, arr: np.ndarray) -> torch.Tensor:
+        """The int32 array on the device.  Inside ``prepare`` it is written behind the step's metadata
+        and shares their one copy; its address then depends only on the sizes staged before it."""
+        arr = np.ascontiguousarray(arr, dtype=np.int32)
+        st = self._staging
+        if st is not None and st[2] + arr.size <= st[3]:
+            host, dev, at = st[0], st[1], st[2]
+            host[at: at + arr.size] = arr.reshape(-1)
+            st[2] = at + arr.size
+            self.staged_words += arr.size
+            self.shape_key.append(arr.shape)
+            return dev[at: at + arr.size].view(arr.shape)
+        self.late_uploads = True
+        return torch.from_numpy(arr).to(self.device, non_blocking=False)
 
     def tiles(self, bq: int, min_len: int = 1, max_len: Optional[int] = None):
         """Tiles of ``bq`` query rows, none crossing a span, over the spans whose length lies in
@@ -94,8 +116,9 @@ class StepContext:
                 for q0 in range(0, s.length, bq):
                     ts.append(i)
                     tq.append(q0)
-            arr = torch.from_numpy(np.asarray([ts, tq], dtype=np.int32)).to(self.device, non_blocking=False)
+            arr = self.stage(np.asarray([ts, tq], dtype=np.int32))
             hit = (arr[0], arr[1], len(ts))
+        self.shape_key.append(("tiles", key, hit[2]))
         self._tiles[key] = hit
         return hit
 
@@ -131,10 +154,11 @@ class StepContext:
         if not items:
             hit = (self.iota, self.zeros, 0, None)
         else:
-            arr = torch.from_numpy(np.asarray([t[1:] for t in items], dtype=np.int32).T.copy()).to(self.device)
+            arr = self.stage(np.asarray([t[1:] for t in items], dtype=np.int32).T)
+            self.shape_key.append(("parts", parts))
             cut = None
             if merges:
-                m = torch.from_numpy(np.asarray(merges, dtype=np.int32).T.copy()).to(self.device)
+                m = self.stage(np.asarray(merges, dtype=np.int32).T)
                 cut = (arr[2], arr[3], arr[4], parts, m[0], m[1], m[2], m[3], len(merges))
             else:
                 cut = (arr[2], arr[3], arr[4], 0, None, None, None, None, 0)

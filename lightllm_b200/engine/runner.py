@@ -45,6 +45,8 @@ class ModelRunner:
         # offsets that depend only on its counts, so equal counts give equal addresses.
         S, T, G, P = self.max_spans, self.max_batch_tokens, self.ngroups, self.max_pages
         off = 6 * S + G * S * P + T + 2 * T + G * T
+        self._fixed_words = off
+        off += 8 * T + 64 * S + 4096         # room for the index arrays that parts stage (tiles, work items)
         self._words = off
         self._host = [torch.zeros(off, dtype=torch.int32).pin_memory() for _ in range(2)]
         self._host_done = [None, None]
@@ -63,8 +65,9 @@ class ModelRunner:
             self.views.append(CacheView(ref.group, k, v, st, ref.owns))
         self.last_h2d_bytes = 0
         self._nvtx = os.environ.get("LLB_NVTX", "") not in ("", "0")
-        # Decode-only steps are launch-bound, so they are captured into CUDA graphs: one per
-        # (requests, wanted rows, block-table width), captured the second time a shape is seen.
+        # Steps are launch-bound on the host, so they are captured into CUDA graphs: one per shape (counts of
+        # tokens, requests, wanted rows, block-table width, sizes of the staged index arrays), captured the
+        # second time a shape is seen.
         self.use_cuda_graphs = bool(use_cuda_graphs) and model.graph_safe()
         self.max_graphs = max_graphs
         self._graphs: Dict[tuple, tuple] = {}
@@ -153,12 +156,6 @@ class ModelRunner:
                 sm[s.row: s.row + s.length] = rows * ps + p % ps
         host[o["want_rows"]: o["want_rows"] + R] = want
 
-        self._dev[:words].copy_(self._host[turn][:words], non_blocking=True)
-        ev = torch.cuda.Event()
-        ev.record()
-        self._host_done[turn] = ev
-        self.last_h2d_bytes = words * 4
-
         d = self._dev
         ctx = StepContext()
         ctx.T, ctx.spans = T, spans
@@ -180,12 +177,28 @@ class ModelRunner:
         ctx.max_context = max_context
         ctx.dtype, ctx.device = self.model.dtype, self.device
         ctx.cache, ctx.err = cache, self.err
+
+        # The parts make their index arrays now, behind the fixed fields, so that one copy brings everything.
+        ctx._staging = [host, d, words, self._words]
+        self.model.prepare(ctx, self.views)
+        words = ctx._staging[2]
+        ctx._staging = None
+        self._dev[:words].copy_(self._host[turn][:words], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._host_done[turn] = ev
+        self.last_h2d_bytes = words * 4
         return ctx
 
     def forward(self, ctx: StepContext) -> Optional[torch.Tensor]:
         """Run the layers over the batch that ``ctx`` describes; logits float32 [R, V] or None.
         With ``LLB_NVTX=1`` in the environment every run entry is an NVTX range (the reference only has
         ``printf`` timings, src/engine/batch_loop.cpp:99-102)."""
+        from ..csrc import ops
+        with ops.stream_scope():           # every kernel of the step goes to the stream that is current now
+            return self._forward(ctx)
+
+    def _forward(self, ctx: StepContext) -> Optional[torch.Tensor]:
         m = self.model
         residual = m.embedding.forward(ctx.token_ids, ctx)
         for i, (entry, view) in enumerate(zip(m.run, self.views)):
@@ -205,7 +218,7 @@ class ModelRunner:
         each entry's ``want``, as a float32 ``[wanted, vocab]`` tensor on the device (``None`` if
         nothing is wanted).  Afterwards every request holds its new tokens."""
         ctx = self._build_context(entries)
-        if self.use_cuda_graphs and ctx.decode_only:
+        if self.use_cuda_graphs and not ctx.late_uploads:
             logits = self._forward_graphed(ctx)
         else:
             logits = self.forward(ctx)
@@ -214,11 +227,12 @@ class ModelRunner:
         return logits
 
     def _forward_graphed(self, ctx: StepContext) -> Optional[torch.Tensor]:
-        """A decode-only step through a CUDA graph.  The metadata buffer has equal addresses for equal
-        counts, so a graph captured for (requests, wanted rows, block-table width) serves every later
-        step of that shape; only the metadata copy stays outside."""
+        """A step through a CUDA graph.  The metadata buffer has equal addresses for equal counts, so a
+        graph captured for (tokens, requests, wanted rows, block-table width, sizes of the staged index
+        arrays and what else the parts named) serves every later step of that shape; only the metadata
+        copy stays outside."""
         from ..csrc import ops
-        key = (ctx.num_spans, ctx.num_want, ctx.max_pages)
+        key = (ctx.T, ctx.num_spans, ctx.num_want, ctx.max_pages, ctx.decode_only, tuple(ctx.shape_key))
         hit = self._graphs.get(key)
         if hit is None:
             seen = self._graph_seen.get(key, 0) + 1

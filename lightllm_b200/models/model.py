@@ -58,6 +58,15 @@ class Model:
             if not isinstance(p, Block):
                 p.bind(tensors, dtype, device)
 
+    def prepare(self, ctx, views) -> None:
+        """Every part's ``prepare`` for this step, run entry by run entry (before the metadata copy)."""
+        for entry, view in zip(self.run, views):
+            self.layers[entry.layer].prepare(ctx, view)
+        for part in (self.embedding, self.final_norm, self.head):
+            hook = getattr(part, "prepare", None)
+            if hook is not None:
+                hook(ctx)
+
     def graph_safe(self) -> bool:
         """Whether every part's forward only launches kernels whose arguments are fixed by the step's
         counts (no host-side branching on the batch's contents), so a step can be captured in a CUDA graph."""

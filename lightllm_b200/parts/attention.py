@@ -182,41 +182,65 @@ class AttentionMixer(Mixer):
             f"attention with {group} query heads per kv head and head_dim {self.head_dim} does not fit "
             f"in shared memory even with one query row per block")
 
+    def _plan(self, ctx, dtype):
+        """Which kernels this step's attention takes and over which tiles: made once per step (in
+        ``prepare`` when the engine runs it, so that the index arrays travel with the step's metadata)."""
+        window = self.window or 0
+        key = ("attention_plan", self.num_heads, self.num_kv_heads, self.head_dim, window, dtype)
+        plan = ctx.memo.get(key)
+        if plan is not None:
+            return plan
+        bf16 = dtype == torch.bfloat16
+        if ctx.decode_only:
+            S = ctx.num_spans
+            bound = ctx.max_pages * ctx.page_size          # the same for every step of this shape
+            span = bound if window == 0 else min(bound, window)
+            want = max(1, -(-2 * L.num_sms(ctx.device) // (S * self.num_kv_heads)))       # blocks to fill the SMs twice
+            nsplit = max(1, min(want, -(-span // 128)))
+            mma = bf16 and ops.paged_decode_mma_supports(self.num_heads, self.num_kv_heads, self.head_dim)
+            plan = ("decode_mma" if mma else "decode_simt", ctx.tiles(1), nsplit)
+        else:
+            items, short_max = None, None
+            if (bf16 and ops.attention_tcgen05_supports(self.head_dim, ctx.page_size)
+                    and max(s.length for s in ctx.spans) >= TENSOR_CORE_MIN_ROWS):
+                # long portions go to the tensor cores in tiles of 128 rows; short ones stay on CUDA cores
+                items = ctx.attention_items(TENSOR_CORE_MIN_ROWS, window)
+                short_max = TENSOR_CORE_MIN_ROWS - 1
+            bq = self.tile_height()
+            plan = ("prefill", items, ctx.tiles(bq, max_len=short_max), bq)
+        ctx.memo[key] = plan
+        return plan
+
+    def prepare(self, ctx, cache=None) -> None:
+        self._plan(ctx, ctx.dtype)
+        if hasattr(self.position, "prepare"):
+            self.position.prepare(ctx)
+
     def attend(self, q, cache: CacheView, ctx, out) -> None:
         """out[t] = attention of query row t over positions <= its own (within the window)."""
         g = cache.group
         window = self.window or 0
         common = (ctx.span_row, ctx.span_len, ctx.span_pos, ctx.block_tables[g], ctx.max_pages, ctx.page_size,
                   self.num_heads, self.num_kv_heads, self.head_dim, window, self.scale)
-        if ctx.decode_only:
-            S = ctx.num_spans
-            bound = ctx.max_pages * ctx.page_size          # the same for every step of this shape
-            span = bound if window == 0 else min(bound, window)
-            want = max(1, -(-2 * L.num_sms(q.device) // (S * self.num_kv_heads)))       # blocks to fill the SMs twice
-            nsplit = max(1, min(want, -(-span // 128)))
-            if q.dtype == torch.bfloat16 and ops.paged_decode_mma_supports(self.num_heads, self.num_kv_heads, self.head_dim):
-                tile_span, tile_q0, ntiles = ctx.tiles(1)
-                scratch = None
-                if nsplit > 1:
-                    scratch = torch.empty(ops.attention_scratch_floats(ntiles, self.num_heads, self.head_dim, 1, nsplit),
-                                          dtype=torch.float32, device=q.device)
-                ops.paged_decode_mma(q, cache.k, cache.v, out, tile_span, tile_q0, ntiles, ctx.span_row, ctx.span_pos,
-                                     ctx.block_tables[g], ctx.max_pages, ctx.page_size, self.num_heads,
-                                     self.num_kv_heads, self.head_dim, window, self.scale, nsplit, scratch)
-            else:
-                self._simt(q, cache, out, ctx.tiles(1), common, 1, nsplit)
-            return
-        short_max = None
-        if (q.dtype == torch.bfloat16 and ops.attention_tcgen05_supports(self.head_dim, ctx.page_size)
-                and max(s.length for s in ctx.spans) >= TENSOR_CORE_MIN_ROWS):
-            # long portions go to the tensor cores in tiles of 128 rows; short ones stay on CUDA cores
-            tile_span, tile_q0, ntiles, cut = ctx.attention_items(TENSOR_CORE_MIN_ROWS, window)
-            ops.paged_attention_tcgen05(q, cache.k, cache.v, out, tile_span, tile_q0, ntiles, *common, cut=cut)
-            short_max = TENSOR_CORE_MIN_ROWS - 1
-        bq = self.tile_height()
-        tiles = ctx.tiles(bq, max_len=short_max)
-        if tiles[2] > 0:
-            self._simt(q, cache, out, tiles, common, bq, 1)
+        plan = self._plan(ctx, q.dtype)
+        if plan[0] == "decode_mma":
+            (tile_span, tile_q0, ntiles), nsplit = plan[1], plan[2]
+            scratch = None
+            if nsplit > 1:
+                scratch = torch.empty(ops.attention_scratch_floats(ntiles, self.num_heads, self.head_dim, 1, nsplit),
+                                      dtype=torch.float32, device=q.device)
+            ops.paged_decode_mma(q, cache.k, cache.v, out, tile_span, tile_q0, ntiles, ctx.span_row, ctx.span_pos,
+                                 ctx.block_tables[g], ctx.max_pages, ctx.page_size, self.num_heads,
+                                 self.num_kv_heads, self.head_dim, window, self.scale, nsplit, scratch)
+        elif plan[0] == "decode_simt":
+            self._simt(q, cache, out, plan[1], common, 1, plan[2])
+        else:
+            _, items, tiles, bq = plan
+            if items is not None:
+                tile_span, tile_q0, ntiles, cut = items
+                ops.paged_attention_tcgen05(q, cache.k, cache.v, out, tile_span, tile_q0, ntiles, *common, cut=cut)
+            if tiles[2] > 0:
+                self._simt(q, cache, out, tiles, common, bq, 1)
 
     def _simt(self, q, cache, out, tiles, common, bq, nsplit) -> None:
         tile_span, tile_q0, ntiles = tiles

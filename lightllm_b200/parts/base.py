@@ -49,6 +49,11 @@ class Part:
     def children(self) -> List["Part"]:
         return []
 
+    def prepare(self, ctx, cache=None) -> None:
+        """Called for every run entry before the step's metadata is copied to the device: the place to make
+        index arrays with ``ctx.stage`` / ``ctx.tiles`` so that they share that copy (and, for CUDA graphs,
+        to append to ``ctx.shape_key`` whatever else the launches will depend on)."""
+
 
 class LazyNorm:
     """The normalised input of a mixer, feed-forward or head, not yet computed.

@@ -38,6 +38,15 @@ class Block(Part):
             return LazyNorm(residual, norm, ctx)
         return norm.forward(residual, ctx)
 
+    def prepare(self, ctx, cache=None) -> None:
+        for part in (self.norm1, self.norm2, self.ffn):
+            hook = getattr(part, "prepare", None)
+            if hook is not None:
+                hook(ctx)
+        hook = getattr(self.mixer, "prepare", None)
+        if hook is not None:
+            hook(ctx, cache)
+
     def forward(self, residual, ctx, cache) -> None:
         if self.arrangement == "pre_norm":
             self.mixer.forward(self._normed(self.mixer, self.norm1, residual, ctx), residual, ctx, cache)
