@@ -7,8 +7,10 @@
 // while this one is computed), ldmatrix reads them as MMA fragments (K as is, V transposed), scores
 // and the online softmax stay in registers in float (src/kv_cache/paged_attention.cu:153-163, with
 // this library's departures: -inf start, exact acc / l, the token's own key visible).  The four warps
-// of a block are merged through shared memory; with nsplit > 1 the blocks' partial (acc, m, l) go to
-// scratch and a second kernel merges them (paged_attention.cu:476-532 does the same for 4 fixed splits).
+// of a block are merged through shared memory.  With 2 to 16 splits the blocks of one (request, kv head)
+// form a thread-block cluster and merge their partial (acc, m, l) through distributed shared memory, in
+// the same kernel; with more splits the partials go to scratch and a second kernel merges them
+// (paged_attention.cu:476-532 does the same for 4 fixed splits).
 //
 // Both kernels are programmatic dependent launches: everything that does not depend on the previous
 // kernel (block tables, positions, ranges) is read before griddepcontrol.wait.
@@ -21,6 +23,7 @@ namespace {
 constexpr int BK = 32;          // keys per tile
 constexpr int NWARPS = 4;
 constexpr int MERGE_MAX_SPLITS = 256;
+constexpr int CLUSTER_MAX_SPLITS = 16;      // beyond the portable 8 the kernel opts in to larger clusters
 
 struct DecodeParams {
     const __nv_bfloat16* q;        // [T, Hq, HD]
@@ -61,6 +64,21 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// Distributed shared memory: the float at `local_addr` (a shared-memory address of this block) in the block of
+// rank `rank` of the cluster.
+__device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+// Every thread of every block of the cluster arrives and waits (a hardware barrier: it has no time limit, so no
+// block may leave the kernel or skip it on any path).
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -78,7 +96,7 @@ __device__ __forceinline__ uint32_t tile_addr(uint32_t base, int row, int chunk)
     return base + (uint32_t)row * (HD * 2) + (uint32_t)((chunk ^ (row & 7)) * 16);
 }
 
-template <int HD>
+template <int HD, bool CLUSTER>
 __global__ void __launch_bounds__(NWARPS * 32) paged_decode_mma_kernel(DecodeParams p) {
     constexpr int CH = HD / 8;                 // 16-byte chunks per row
     constexpr int TILE_BYTES = BK * HD * 2;
@@ -277,7 +295,14 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_decode_mma_kernel(DecodePar
                 a += e * wacc[(size_t)(w * 16 + g) * HD + d];
             }
         }
-        if (p.nsplit == 1) {
+        if (CLUSTER) {
+            float* pacc = wml + NWARPS * 16 * 2;      // [16][HD], then (m, l) [16][2]
+            pacc[g * HD + d] = a;
+            if (d == 0) {
+                pacc[16 * HD + g * 2] = M;
+                pacc[16 * HD + g * 2 + 1] = L;
+            }
+        } else if (p.nsplit == 1) {
             p.out[((size_t)row0 * p.Hq + kvh * G + g) * HD + d] = __float2bfloat16_rn(a / L);
         } else {
             p.part_acc[(base + g) * HD + d] = a;
@@ -286,6 +311,30 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_decode_mma_kernel(DecodePar
                 p.part_ml[(base + g) * 2 + 1] = L;
             }
         }
+    }
+    if (CLUSTER) {
+        // The splits of this (request, kv head) are the blocks of one cluster (rank = split).  Each block takes a
+        // share of the outputs and reads every block's partial through distributed shared memory:
+        // out = sum_s 2^(m_s - M) acc_s / sum_s 2^(m_s - M) l_s.
+        cluster_sync_all();
+        const uint32_t pacc_addr = smem_u32(wml + NWARPS * 16 * 2);
+        const uint32_t pml_addr = pacc_addr + 16 * HD * 4;
+        for (int i = split * blockDim.x + threadIdx.x; i < G * HD; i += p.nsplit * blockDim.x) {
+            const int g = i / HD, d = i - g * HD;
+            float M = -INFINITY;
+            for (int sp = 0; sp < p.nsplit; ++sp) M = fmaxf(M, ld_cluster_f32(pml_addr + g * 8, sp));
+            float L = 0.0f, a = 0.0f;
+            for (int sp = 0; sp < p.nsplit; ++sp) {
+                const float ms = ld_cluster_f32(pml_addr + g * 8, sp);
+                if (ms != -INFINITY) {
+                    const float e = fast_exp2(ms - M);
+                    L += e * ld_cluster_f32(pml_addr + g * 8 + 4, sp);
+                    a += e * ld_cluster_f32(pacc_addr + (g * HD + d) * 4, sp);
+                }
+            }
+            p.out[((size_t)row0 * p.Hq + kvh * G + g) * HD + d] = __float2bfloat16_rn(a / L);
+        }
+        cluster_sync_all();        // no block leaves while another may still read its shared memory
     }
 }
 
@@ -337,23 +386,58 @@ cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
     return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
+// Launch as a programmatic dependent launch whose grid.z is one thread-block cluster.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                               Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 1;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = grid.z;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 template <int HD>
 int launch(const DecodeParams& p, int num_tiles, cudaStream_t stream) {
-    constexpr size_t smem = (size_t)NWARPS * 4 * BK * HD * 2;      // also covers the merge: 4 x 16 x HD floats + m, l
-    static_assert(smem >= (size_t)NWARPS * 16 * HD * 4 + NWARPS * 16 * 2 * 4, "merge area does not fit");
+    constexpr size_t smem = (size_t)NWARPS * 4 * BK * HD * 2;      // also covers the merges: 4 x 16 x HD floats + m, l,
+                                                                   // and the block's own 16 x HD floats + m, l
+    static_assert(smem >= (size_t)(NWARPS + 1) * (16 * HD * 4 + 16 * 2 * 4), "merge area does not fit");
     static bool configured = false;
-    if (!configured && smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(paged_decode_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return llb_fail("decode attention: cannot opt in to %zu bytes of shared memory: %s", smem,
-                                              cudaGetErrorString(e));
+    if (!configured) {
+        cudaError_t e = cudaSuccess;
+        if (smem > 48 * 1024) {
+            e = cudaFuncSetAttribute(paged_decode_mma_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e == cudaSuccess)
+                e = cudaFuncSetAttribute(paged_decode_mma_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        }
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(paged_decode_mma_kernel<HD, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        if (e != cudaSuccess) return llb_fail("decode attention: cannot set the kernel's attributes (%zu bytes of shared "
+                                              "memory, clusters of %d): %s", smem, CLUSTER_MAX_SPLITS, cudaGetErrorString(e));
         configured = true;
     }
-    cudaError_t e = launch_pdl(paged_decode_mma_kernel<HD>, dim3(num_tiles, p.Hkv, p.nsplit), dim3(NWARPS * 32), smem,
+    const bool cluster = p.nsplit > 1 && p.nsplit <= CLUSTER_MAX_SPLITS;
+    cudaError_t e;
+    if (cluster)
+        e = launch_pdl_cluster(paged_decode_mma_kernel<HD, true>, dim3(num_tiles, p.Hkv, p.nsplit), dim3(NWARPS * 32), smem,
                                stream, p);
+    else
+        e = launch_pdl(paged_decode_mma_kernel<HD, false>, dim3(num_tiles, p.Hkv, p.nsplit), dim3(NWARPS * 32), smem,
+                       stream, p);
     if (e != cudaSuccess) return llb_fail("decode attention: launch failed: %s", cudaGetErrorString(e));
     int rc = llb_check_launch("paged_decode_mma");
     if (rc) return rc;
-    if (p.nsplit > 1) {
+    if (p.nsplit > 1 && !cluster) {
         e = launch_pdl(decode_merge_kernel, dim3(num_tiles, p.Hq), dim3(32), 0, stream, p, HD);
         if (e != cudaSuccess) return llb_fail("decode merge: launch failed: %s", cudaGetErrorString(e));
         rc = llb_check_launch("decode_merge");
@@ -368,9 +452,12 @@ LLB_EXPORT int llb_paged_decode_mma_supports(int Hq, int Hkv, int hd) {
     return Hkv > 0 && Hq % Hkv == 0 && Hq / Hkv <= 16 && (hd == 64 || hd == 128);
 }
 
+// The largest split count that is merged inside the attention kernel, through a thread-block cluster.
+LLB_EXPORT int llb_paged_decode_mma_cluster_splits() { return CLUSTER_MAX_SPLITS; }
+
 // One query row per tile: q, out [T, Hq, hd] bf16 (row = span_row[tile_span[t]] + tile_q0[t], position
 // span_pos + tile_q0); caches [slots, Hkv, hd] bf16; block_table [S, max_pages].  scratch: num_tiles * Hq *
-// nsplit * (hd + 2) floats when nsplit > 1.
+// nsplit * (hd + 2) floats when nsplit > llb_paged_decode_mma_cluster_splits() (fewer splits merge inside the kernel).
 LLB_EXPORT int llb_paged_decode_mma(const void* q, const void* k_cache, const void* v_cache, void* out,
                                     const int* tile_span, const int* tile_q0, int num_tiles, const int* span_row,
                                     const int* span_pos, const int* block_table, int max_pages, int page_size,
@@ -379,7 +466,7 @@ LLB_EXPORT int llb_paged_decode_mma(const void* q, const void* k_cache, const vo
     if (num_tiles == 0) return 0;
     LLB_REQUIRE(llb_paged_decode_mma_supports(Hq, Hkv, hd), "decode attention: %d/%d heads of size %d are not supported "
                 "(groups of at most 16, head size 64 or 128)", Hq, Hkv, hd);
-    LLB_REQUIRE(nsplit >= 1 && nsplit <= MERGE_MAX_SPLITS && (nsplit == 1 || scratch != nullptr),
+    LLB_REQUIRE(nsplit >= 1 && nsplit <= MERGE_MAX_SPLITS && (nsplit <= CLUSTER_MAX_SPLITS || scratch != nullptr),
                 "decode attention: split count %d is outside 1..%d or scratch is missing", nsplit, MERGE_MAX_SPLITS);
     LLB_REQUIRE(page_size > 0 && max_pages > 0 && Hkv <= 65535, "decode attention: bad sizes");
     LLB_REQUIRE(((uintptr_t)q % 16 == 0) && ((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0),

@@ -145,7 +145,10 @@ struct GemmParams {
     const float* bias;      // [N] or null
     int M, N, K;
     int num_kb;             // K blocks in all
-    int kb_per_split;       // K blocks per grid.z slice
+    int kb_per_split;       // K blocks per grid.z slice (per split of the persistent kernel)
+    int splits;             // persistent kernel: work items per tile along K
+    float* partials;        // [items, tile width, 128] float: the splits' accumulators meet here
+    int* counters;          // [tiles, 8] zero before and after: arrivals per warp region of a tile
     int* error_flag;        // raised when a wait ran out of time
     // rotary epilogue of the q/k/v projection (heads of 64, NeoX pairs, whole head rotated)
     const float2* rope_table;   // [M, 32] of (cos, sin)
@@ -458,6 +461,8 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
     const int n_tiles = (p.N + P_BN - 1) / P_BN;
     const int num_tiles = m_tiles * n_tiles;
     const int nkb = p.num_kb;
+    const int splits = p.splits;
+    const int num_items = num_tiles * splits;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < P_STAGES; ++s) {
@@ -485,10 +490,12 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
     if (warp == 0) {
         if (lane == 0) {
             int it = 0;                                  // k-blocks issued so far, over all tiles
-            for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+            for (int w = blockIdx.x; w < num_items; w += gridDim.x) {
+                const int t = w / splits, ks = w - t * splits;
                 const int a_row0 = (t % m_tiles) * TILE_M, b_row0 = (t / m_tiles) * P_BN;
+                const int kb0 = ks * p.kb_per_split, kb1 = min(nkb, kb0 + p.kb_per_split);
                 bool ok = true;
-                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % P_STAGES;
                     ok = mbar_wait(&empty_bar[s], ((it / P_STAGES) & 1) ^ 1, abort_flag);
                     if (!ok) break;
@@ -504,12 +511,14 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
             constexpr uint32_t idesc = umma_idesc(TILE_M, P_BN);
             int it = 0, local = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
+            for (int w = blockIdx.x; w < num_items && ok; w += gridDim.x, ++local) {
+                const int ks = w % splits;
+                const int kb0 = ks * p.kb_per_split, kb1 = min(nkb, kb0 + p.kb_per_split);
                 const int buf = local & 1;
                 ok = mbar_wait(&acc_empty[buf], ((local >> 1) & 1) ^ 1, abort_flag);   // the epilogue has drained it
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % P_STAGES;
                     ok = mbar_wait(&full_bar[s], (it / P_STAGES) & 1, abort_flag);
                     if (!ok) break;
@@ -519,7 +528,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
 #pragma unroll
                     for (int k = 0; k < TILE_K / UMMA_K; ++k)
                         umma_bf16(tmem_base + buf * P_BN, umma_desc(a_addr + k * UMMA_K * 2),
-                                  umma_desc(b_addr + k * UMMA_K * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                                  umma_desc(b_addr + k * UMMA_K * 2), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
                     umma_commit(&empty_bar[s]);
                 }
                 if (ok) umma_commit(&acc_full[buf]);
@@ -530,11 +539,55 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
         const int half = (warp - 2) >> 2;             // which half of the tile's columns it drains
         const int row = quarter * 32 + lane;
         int local = 0;
-        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++local) {
+        for (int w = blockIdx.x; w < num_items; w += gridDim.x, ++local) {
+            const int t = w / splits;
             const int buf = local & 1;
             const int a_row0 = (t % m_tiles) * TILE_M, b_row0 = (t / m_tiles) * P_BN;
             if (!mbar_wait(&acc_full[buf], (local >> 1) & 1, abort_flag)) break;      // uniform over the warp
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (splits > 1) {
+                // This split's accumulator goes to the meeting place; the warp that arrives last at its
+                // region of the tile (32 rows x half the columns) adds the splits up in their order, so the
+                // sum does not depend on who came last, and runs the epilogue.
+                // Layout [item][column][row]: the 32 lanes of a warp (32 rows) write and read 128 contiguous bytes.
+                float* mine = p.partials + (size_t)w * TILE_M * P_BN + row;
+#pragma unroll 1
+                for (int c0 = half * (P_BN / 2); c0 < (half + 1) * (P_BN / 2); c0 += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * P_BN + c0), r);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) mine[(size_t)(c0 + j) * TILE_M] = __uint_as_float(r[j]);
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __threadfence();
+                __syncwarp();
+                int last = 0;
+                if (lane == 0) {
+                    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[buf])) : "memory");
+                    last = atomicAdd(&p.counters[t * 8 + (warp - 2)], 1) == splits - 1;
+                }
+                last = __shfl_sync(0xffffffffu, last, 0);
+                if (last) {
+                    __threadfence();
+                    const float* first = p.partials + (size_t)(t * splits) * TILE_M * P_BN + row;
+#pragma unroll 1
+                    for (int c0 = half * (P_BN / 2); c0 < (half + 1) * (P_BN / 2); c0 += 32) {
+                        float acc[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) acc[j] = 0.0f;
+                        for (int i = 0; i < splits; ++i) {
+                            const float* src = first + ((size_t)i * P_BN + c0) * TILE_M;
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) acc[j] += __ldcg(src + (size_t)j * TILE_M);
+                        }
+                        epilogue_row<(EPI == EPI_ROPE64 ? LLB_EPI_STORE : EPI), 32>(
+                            p, a_row0 + row, b_row0 + c0, *reinterpret_cast<const uint32_t(*)[32]>(&acc[0]));
+                    }
+                    if (lane == 0) p.counters[t * 8 + (warp - 2)] = 0;
+                }
+                continue;
+            }
             if (EPI == EPI_ROPE64) {
                 // one head (64 columns) at a time, so that both members of every rotary pair are in registers
 #pragma unroll 1
@@ -668,7 +721,7 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const GemmPa
         cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
         configured = true;
     }
-    const int tiles = llb_ceil_div(p.M, TILE_M) * llb_ceil_div(p.N, P_BN);
+    const int tiles = llb_ceil_div(p.M, TILE_M) * llb_ceil_div(p.N, P_BN) * p.splits;
     const int grid = tiles < num_sms ? tiles : num_sms;
     gemm_tcgen05_persistent_kernel<EPI, P_BN><<<grid, P_THREADS, smem, stream>>>(ma, mb, p);
     return llb_check_launch("gemm_tcgen05_persistent");
@@ -700,11 +753,15 @@ int dispatch_epi(int epi, const CUtensorMap& ma, const CUtensorMap& mb, const Ge
 
 // A [M,K] bf16, W [N,K] bf16, both row-major with K a multiple of 8 and 16-byte aligned bases;
 // bias [N] float or null.  `out`: [M,N] bf16 (STORE), [M,N] float (STORE_F32), [M,N/2] bf16 (SWIGLU, N even);
-// `residual`: [M,N] float (RESIDUAL).  split_k > 1 is allowed for RESIDUAL only.  error_flag: one int
-// that the kernel raises if a wait inside it ran out of time (the result is then invalid), or null.
+// `residual`: [M,N] float (RESIDUAL).  split_k > 1 cuts K into that many pieces.  Up to 128 rows this is for
+// RESIDUAL only (atomic adds).  Beyond, any epilogue may be split: the pieces meet in `partials` (at least
+// llb_gemm_tcgen05_partial_floats(M, N, split_k) floats) and `counters` (8 ints per tile of 128 rows x 256 (N > 128)
+// or 128 features, zero before the call and zero again after it), and the piece that arrives last adds them up
+// in their order, so the result does not depend on the order of arrival.  error_flag: one int that the kernel
+// raises if a wait inside it ran out of time (the result is then invalid), or null.
 LLB_EXPORT int llb_gemm_tcgen05(const void* A, const void* W, const float* bias, void* out, float* residual,
-                                int epilogue, int M, int N, int K, int split_k, int* error_flag,
-                                cudaStream_t stream) {
+                                int epilogue, int M, int N, int K, int split_k, float* partials, int* counters,
+                                int* error_flag, cudaStream_t stream) {
     if (M == 0) return 0;
     LLB_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tcgen05: bad sizes M=%d N=%d K=%d", M, N, K);
     LLB_REQUIRE(K % 8 == 0, "gemm_tcgen05: K=%d is not a multiple of 8 (rows must be 16-byte multiples for TMA)", K);
@@ -712,9 +769,12 @@ LLB_EXPORT int llb_gemm_tcgen05(const void* A, const void* W, const float* bias,
     LLB_REQUIRE(epilogue != LLB_EPI_SWIGLU || N % 2 == 0, "gemm_tcgen05: SwiGLU epilogue needs an even N, got %d", N);
     LLB_REQUIRE(epilogue != LLB_EPI_RESIDUAL || residual != nullptr, "gemm_tcgen05: residual epilogue without residual");
     LLB_REQUIRE(epilogue == LLB_EPI_RESIDUAL || out != nullptr, "gemm_tcgen05: output pointer is null");
-    LLB_REQUIRE(split_k >= 1 && (split_k == 1 || epilogue == LLB_EPI_RESIDUAL),
-                "gemm_tcgen05: split_k=%d needs the residual epilogue", split_k);
-    GemmParams p;
+    LLB_REQUIRE(split_k >= 1 && (split_k == 1 || epilogue == LLB_EPI_RESIDUAL || M > 128),
+                "gemm_tcgen05: split_k=%d with up to 128 rows needs the residual epilogue", split_k);
+    LLB_REQUIRE(split_k == 1 || M <= 128 || (partials && counters),
+                "gemm_tcgen05: split_k=%d beyond 128 rows needs the meeting place", split_k);
+    GemmParams p = {};
+    p.splits = 1;
     p.out = out; p.residual = residual; p.bias = bias; p.M = M; p.N = N; p.K = K;
     p.num_kb = llb_ceil_div(K, TILE_K);
     if (split_k > p.num_kb) split_k = p.num_kb;
@@ -738,15 +798,29 @@ LLB_EXPORT int llb_gemm_tcgen05(const void* A, const void* W, const float* bias,
     }
     constexpr int BN = 128;
     if ((rc = make_map(A, M, K, TILE_M, &ma))) return rc;
-    if (split_k == 1 && N >= 2048) {       // wide tiles where their padding of N costs little
+    p.splits = split_k;
+    p.partials = partials;
+    p.counters = counters;
+    // A tensor-core instruction over 128 features takes as long as one over 256, so the wide tile wins wherever
+    // its padding of N costs little, and always when K is split (few tiles are what splitting is for).
+    if (N >= 2048 || (split_k > 1 && N > 128)) {
         if ((rc = make_map(W, N, K, 256, &mb))) return rc;
         return dispatch_persistent<256>(epilogue, ma, mb, p, stream);
     }
     if ((rc = make_map(W, N, K, BN, &mb))) return rc;
-    if (split_k == 1) return dispatch_persistent<128>(epilogue, ma, mb, p, stream);
-    dim3 grid(llb_ceil_div(M, TILE_M), llb_ceil_div(N, BN), split_k);
-    LLB_REQUIRE(grid.y <= 65535, "gemm_tcgen05: N=%d is too large for one launch", N);
-    return dispatch_epi<BN, false>(epilogue, ma, mb, p, grid, stream);
+    return dispatch_persistent<128>(epilogue, ma, mb, p, stream);
+}
+
+// Floats of the meeting place that llb_gemm_tcgen05 needs beyond 128 rows with K cut into split_k pieces.
+LLB_EXPORT long long llb_gemm_tcgen05_partial_floats(int M, int N, int split_k) {
+    if (split_k <= 1 || M <= 128) return 0;
+    const int bn = N > 128 ? 256 : 128;
+    return (long long)llb_ceil_div(M, TILE_M) * llb_ceil_div(N, bn) * split_k * TILE_M * bn;
+}
+// Counters (ints) of that meeting place.
+LLB_EXPORT long long llb_gemm_tcgen05_counters(int M, int N, int split_k) {
+    if (split_k <= 1 || M <= 128) return 0;
+    return (long long)llb_ceil_div(M, TILE_M) * llb_ceil_div(N, N > 128 ? 256 : 128) * 8;
 }
 
 // The q/k/v projection of a prompt portion with its whole epilogue on the tensor-core kernel: bias, NeoX rotation
@@ -763,6 +837,7 @@ LLB_EXPORT int llb_gemm_tcgen05_rope64(const void* A, const void* W, const float
                 ((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0) && ((uintptr_t)rope_table % 8 == 0),
                 "gemm_tcgen05_rope64: operands must be 16-byte aligned");
     GemmParams p = {};
+    p.splits = 1;
     p.bias = bias; p.M = M; p.N = N; p.K = K;
     p.num_kb = llb_ceil_div(K, TILE_K);
     p.kb_per_split = p.num_kb;

@@ -17,7 +17,7 @@ from . import build as _build
 
 F32, BF16 = 0, 1
 EPI_STORE, EPI_STORE_F32, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
-ABI_VERSION = 11
+ABI_VERSION = 13
 
 _lib: Optional[ctypes.CDLL] = None
 
@@ -353,16 +353,29 @@ def paged_decode_mma_supports(num_heads: int, num_kv_heads: int, head_dim: int) 
     return bool(lib().llb_paged_decode_mma_supports(num_heads, num_kv_heads, head_dim))
 
 
+_cluster_splits: Optional[int] = None
+
+
+def decode_mma_cluster_splits() -> int:
+    """Up to this many splits the decode attention merges inside the kernel (a thread-block cluster); more
+    need scratch and the merge kernel."""
+    global _cluster_splits
+    if _cluster_splits is None:
+        _cluster_splits = int(lib().llb_paged_decode_mma_cluster_splits())
+    return _cluster_splits
+
+
 def paged_decode_mma(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                      tile_span: torch.Tensor, tile_q0: torch.Tensor, num_tiles: int, span_row: torch.Tensor,
                      span_pos: torch.Tensor, block_table: torch.Tensor, max_pages: int, page_size: int,
                      num_heads: int, num_kv_heads: int, head_dim: int, window: int, scale: float,
                      nsplit: int = 1, scratch: Optional[torch.Tensor] = None) -> None:
-    """Tensor-core decode attention: one query row per tile over its request's pages; bf16."""
+    """Tensor-core decode attention: one query row per tile over its request's pages; bf16.  ``nsplit`` cuts
+    each request's keys; up to :func:`decode_mma_cluster_splits` the pieces are merged inside the kernel."""
     for t in (q, k_cache, v_cache, out):
         if t.dtype != torch.bfloat16:
             raise KernelError("paged_decode_mma takes bfloat16 tensors")
-    if nsplit > 1:
+    if nsplit > decode_mma_cluster_splits():
         need = attention_scratch_floats(num_tiles, num_heads, head_dim, 1, nsplit)
         if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
             raise KernelError(f"decode attention: nsplit={nsplit} needs {need} floats of scratch")
@@ -429,10 +442,18 @@ def check_async_errors(device: torch.device) -> None:
         raise KernelError("a tensor-core kernel gave up waiting on a barrier; its results are invalid")
 
 
+_meet_counters = {}
+_MEET_COUNTERS = 1 << 16
+
+
 def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], epilogue: int,
                  out: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
                  split_k: int = 1) -> None:
-    """Tensor-core contraction a[M,K] @ w[N,K]^T (bf16, K a multiple of 8) with a fused epilogue."""
+    """Tensor-core contraction a[M,K] @ w[N,K]^T (bf16, K a multiple of 8) with a fused epilogue.
+
+    ``split_k`` > 1 cuts K into pieces that run as separate work items: up to 128 rows for the residual
+    epilogue only (atomic adds); beyond, for every epilogue, through a meeting place in which the piece that
+    arrives last adds all pieces in their order (the result does not depend on who arrives last)."""
     M, K = a.shape
     N, K2 = w.shape
     if K != K2:
@@ -440,8 +461,20 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError("gemm_tcgen05 takes bfloat16 operands")
     _check_epilogue_args(a, N, M, bias, epilogue, out, residual)
+    partials = counters = None
+    if split_k > 1 and M > 128:
+        need = lib().llb_gemm_tcgen05_counters(M, N, split_k)
+        if need > _MEET_COUNTERS:
+            split_k = 1
+        else:
+            key = a.device.index or 0
+            counters = _meet_counters.get(key)
+            if counters is None:
+                counters = _meet_counters[key] = torch.zeros(_MEET_COUNTERS, dtype=torch.int32, device=a.device)
+            partials = torch.empty(lib().llb_gemm_tcgen05_partial_floats(M, N, split_k), dtype=torch.float32,
+                                   device=a.device)
     _check(lib().llb_gemm_tcgen05(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), _ptr(residual), epilogue, M, N, K,
-                                  split_k, _ptr(async_error_flag(a.device)), _stream()))
+                                  split_k, _ptr(partials), _ptr(counters), _ptr(async_error_flag(a.device)), _stream()))
 
 
 def gemm_tcgen05_rope64(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], rope_table: torch.Tensor,

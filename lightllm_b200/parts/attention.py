@@ -19,6 +19,8 @@ _SMEM_LIMIT = 200 * 1024
 # Portions of at least this many rows run on the tensor-core attention kernel (tiles of 128 rows).
 TENSOR_CORE_MIN_ROWS = 32
 FUSED_ROPE_MAX_ROWS = 16
+# Up to this many keys per request the decode attention's pieces are merged inside the kernel.
+CLUSTER_MERGE_MAX_KEYS = 8192
 # From this many rows on, heads of 64 get their rotation and cache write in the projection's tensor-core epilogue.
 PREFILL_ROPE_MIN_ROWS = 128
 
@@ -198,6 +200,12 @@ class AttentionMixer(Mixer):
             want = max(1, -(-2 * L.num_sms(ctx.device) // (S * self.num_kv_heads)))       # blocks to fill the SMs twice
             nsplit = max(1, min(want, -(-span // 128)))
             mma = bf16 and ops.paged_decode_mma_supports(self.num_heads, self.num_kv_heads, self.head_dim)
+            if mma and span <= CLUSTER_MERGE_MAX_KEYS:
+                # Pieces that one thread-block cluster merges inside the kernel, which saves the merge kernel's
+                # round trip: at most 8 (larger clusters start more slowly), and no more blocks than are resident
+                # at once (three per SM).
+                resident = 3 * L.num_sms(ctx.device) // (S * self.num_kv_heads)
+                nsplit = max(1, min(8, ops.decode_mma_cluster_splits(), resident, -(-span // 128)))
             plan = ("decode_mma" if mma else "decode_simt", ctx.tiles(1), nsplit)
         else:
             items, short_max = None, None
@@ -226,7 +234,7 @@ class AttentionMixer(Mixer):
         if plan[0] == "decode_mma":
             (tile_span, tile_q0, ntiles), nsplit = plan[1], plan[2]
             scratch = None
-            if nsplit > 1:
+            if nsplit > ops.decode_mma_cluster_splits():
                 scratch = torch.empty(ops.attention_scratch_floats(ntiles, self.num_heads, self.head_dim, 1, nsplit),
                                       dtype=torch.float32, device=q.device)
             ops.paged_decode_mma(q, cache.k, cache.v, out, tile_span, tile_q0, ntiles, ctx.span_row, ctx.span_pos,

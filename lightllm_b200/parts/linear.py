@@ -66,6 +66,17 @@ def split_k_fused(M: int, N: int, K: int) -> int:
     return max(1, min(kblocks, num_sms() // tiles))
 
 
+def split_k_wide(M: int, N: int, K: int) -> int:
+    """Splits for a contraction of more than 128 rows.  A block's time is its number of tensor-core
+    instructions (K/16 per tile, whatever the tile's width), so when the tiles of 128 rows x 256 features
+    leave half of the SMs idle, K is cut until they do not.  The pieces meet through memory, which costs about
+    as much as 16 blocks of 64 along K: shorter pieces do not pay."""
+    tiles = -(-M // 128) * -(-N // (256 if N > 128 else 128))
+    if tiles * 2 > num_sms():
+        return 1
+    return max(1, min(num_sms() // tiles, -(-K // 64) // 16))
+
+
 def reserve_fused_scratch(device: torch.device, N: int) -> None:
     """Called when a part with a fused decode contraction of N output features is bound."""
     if torch.device(device).type == "cuda":
@@ -95,7 +106,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
             split_k = split_k_fused(M, N, x.shape[1])
         ops.gemm_decode(w, _DECODE_EPI[epilogue], M, a=x, bias=bias, out=out, residual=residual, split_k=split_k)
     elif tensor_core_eligible(x, w):
-        split_k = split_k_for(M, N, x.shape[1]) if (epilogue == RESIDUAL and M <= 128) else 1
+        if M > 128:
+            split_k = split_k_wide(M, N, x.shape[1])
+        else:
+            split_k = split_k_for(M, N, x.shape[1]) if epilogue == RESIDUAL else 1
         ops.gemm_tcgen05(x, w, bias, epilogue, out, residual, split_k)
     else:
         ops.gemm_simt(x, w, bias, epilogue, out, residual)

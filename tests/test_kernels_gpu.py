@@ -120,9 +120,10 @@ def test_gemm_tcgen05(ops, M, N, K, epi):
     if N > 100000 and epi != 1:
         pytest.skip("the vocabulary-sized case is the head's: float output only")
     a, w = rnd((M, K), torch.bfloat16, 40), rnd((N, K), torch.bfloat16, 41, 0.2)
-    for bias, split_k in ((None, 1), (rnd((N,), torch.float32, 42), 1), (rnd((N,), torch.float32, 42), 5)):
-        if split_k > 1 and epi != 2:
-            continue
+    for bias, split_k in ((None, 1), (rnd((N,), torch.float32, 42), 1), (rnd((N,), torch.float32, 42), 5),
+                          (None, 2)):
+        if split_k > 1 and epi != 2 and M <= 128:
+            continue        # few rows: only the residual epilogue can be split (atomic adds)
         residual = rnd((M, N), torch.float32, 43)
         res0 = residual.clone()
         out = None
@@ -138,6 +139,13 @@ def test_gemm_tcgen05(ops, M, N, K, epi):
         tol = 1e-5 * math.sqrt(K) if epi in (1, 2) else 1e-2
         scale = max(1.0, float(ref.abs().max()))
         assert torch.allclose(got, ref, atol=tol * scale, rtol=0), f"max diff {float((got - ref).abs().max())}"
+        if split_k > 1 and M > 128:
+            # the pieces are added in their order, whoever arrives last: a second run gives the same bits,
+            # and the meeting place's counters are zero again
+            again = res0.clone() if epi == 2 else torch.empty_like(out)
+            ops.gemm_tcgen05(a, w, bias, epi, None if epi == 2 else again, again if epi == 2 else None, split_k)
+            assert torch.equal(again, residual if epi == 2 else out)
+            assert int(ops._meet_counters[dev().index or 0].abs().max()) == 0
 
 
 DECODE_SHAPES = [(1, 1152, 896), (8, 9728, 896), (13, 896, 4864), (16, 130, 64), (17, 200, 136), (40, 1000, 96),
@@ -524,7 +532,7 @@ MMA_DECODE_CASES = [
 
 
 @pytest.mark.parametrize("case", MMA_DECODE_CASES)
-@pytest.mark.parametrize("nsplit", [1, 3, 16])
+@pytest.mark.parametrize("nsplit", [1, 3, 8, 16, 20])      # up to 16 merged inside the kernel, beyond by the merge kernel
 @pytest.mark.parametrize("spike", [False, True])
 def test_paged_decode_mma(ops, case, nsplit, spike):
     Hq, Hkv, hd, page, starts, window = case
@@ -535,7 +543,9 @@ def test_paged_decode_mma(ops, case, nsplit, spike):
     s["vc"] = torch.nan_to_num(s["vc"], nan=-7.0)
     ts, tq, nt = tiles_for(lens, 1)
     out = torch.full((s["rows"], Hq * hd), float("nan"), dtype=torch.bfloat16, device=dev())
-    scratch = torch.empty(max(1, ops.attention_scratch_floats(nt, Hq, hd, 1, nsplit)), dtype=torch.float32, device=dev())
+    scratch = None
+    if nsplit > ops.decode_mma_cluster_splits():
+        scratch = torch.empty(ops.attention_scratch_floats(nt, Hq, hd, 1, nsplit), dtype=torch.float32, device=dev())
     ops.paged_decode_mma(s["q"], s["kc"], s["vc"], out, ts, tq, nt, s["span_row"], s["span_pos"], s["bt"],
                          s["max_pages"], page, Hq, Hkv, hd, window or 0, 1.0 / math.sqrt(hd), nsplit, scratch)
     ref = attention_reference(s["full"], lens, starts, hd, window).reshape(s["rows"], Hq * hd)
