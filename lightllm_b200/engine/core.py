@@ -77,8 +77,8 @@ class EngineCore:
     def is_open(self, seq_id: Hashable) -> bool:
         return seq_id in self.cache.seqs
 
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
-        return self.runner.step(entries)
+    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+        return self.runner.step(entries, device_tokens)
 
     def launch_count(self) -> int:
         """Kernels of the engine's own library launched so far in this process."""

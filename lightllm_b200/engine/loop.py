@@ -12,6 +12,8 @@ import time
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence
 
+import torch
+
 from ..sampling import Sampler, SamplingParams
 from .batch import StepEntry
 from .core import EngineCore
@@ -69,9 +71,24 @@ def percentile(values: Sequence[float], p: float) -> float:
     return v[lo] + (v[hi] - v[lo]) * (rank - lo)
 
 
+class _InFlight:
+    """A step that has been launched and whose sampled ids are on their way to the host."""
+
+    __slots__ = ("sched", "wanting", "tokens_dev", "tokens_host", "ready")
+
+    def __init__(self, sched, wanting, tokens_dev, tokens_host, ready):
+        self.sched, self.wanting, self.tokens_dev, self.tokens_host, self.ready = sched, wanting, tokens_dev, tokens_host, ready
+
+
 class BatchMainLoop:
+    """While every running request is decoding and nothing waits, one step is kept in flight: the next step is
+    launched with the ids that the last one sampled still on the device, and the host reads those ids (ends
+    requests on an end-of-sequence id, keeps the metrics) while the GPU already runs the next step.  A request that
+    ends this way has computed one token too many, which is dropped.  ``decode_ahead=False`` launches and reads
+    back step by step, as the reference does."""
+
     def __init__(self, engine: EngineCore, chunk_size: int = 16, max_batch_tokens: int = 256,
-                 max_prefill_entries: int = 999):
+                 max_prefill_entries: int = 999, decode_ahead: bool = True):
         self.engine = engine
         max_batch_tokens = min(max_batch_tokens, engine.runner.max_batch_tokens)
         self.scheduler = Scheduler(engine.cache, chunk_size, max_batch_tokens, max_prefill_entries)
@@ -83,6 +100,11 @@ class BatchMainLoop:
         self._next_id = 0
         self.total_steps = 0
         self._epoch = time.perf_counter()
+        self.decode_ahead = decode_ahead
+        self._inflight: Optional[_InFlight] = None
+        self._pinned = [torch.empty(engine.runner.max_spans, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._pin_turn = 0
+        self.steps_ahead = 0             # steps that were launched before their predecessor's ids were read
 
     def wall_clock(self) -> float:
         return time.perf_counter() - self._epoch
@@ -118,29 +140,71 @@ class BatchMainLoop:
 
     def step(self) -> bool:
         """One scheduler decision run through the engine.  False when there was nothing to do."""
+        prev = self._inflight
+        if prev is not None:
+            self._inflight = None
+            nxt = None
+            if self.decode_ahead and self.scheduler.can_decode_ahead(prev.sched):
+                sched = self.scheduler.step()
+                if (not sched.preempted and len(sched.entries) == len(prev.wanting)
+                        and all(e.request is r and not e.is_prefill for e, r in zip(sched.entries, prev.wanting))):
+                    entries = [StepEntry(r.id, (0,), (0,)) for r in prev.wanting]
+                    nxt = self._launch(sched, entries, prev.wanting, device_tokens=prev.tokens_dev)
+                    self.steps_ahead += 1
+                else:       # cannot happen after can_decode_ahead; the decision is taken again below
+                    raise RuntimeError("the scheduler changed its mind about a step it had declared predictable")
+            self._commit(prev)
+            if nxt is not None:
+                self._inflight = nxt
+                return True
         sched: ScheduleStep = self.scheduler.step()
         for r in list(self.scheduler.finished.values()):
             if not self._metrics[r.id].finished:
                 self._record_finish(r)
         if sched.empty():
-            return False
+            return prev is not None
         entries, wanting = [], []
         for e in sched.entries:
             toks = e.request.tokens_at(e.start_pos, e.num_tokens)
             entries.append(StepEntry(e.request.id, toks, [e.num_tokens - 1] if e.wants_logits else []))
             if e.wants_logits:
                 wanting.append(e.request)
-        logits = self.engine.step(entries)
+        flight = self._launch(sched, entries, wanting)
+        decode_only = all(not e.is_prefill and e.wants_logits for e in sched.entries)
+        if self.decode_ahead and decode_only and not sched.preempted:
+            self._inflight = flight           # read back at the next call, after the next step has been launched
+        else:
+            self._commit(flight)
+        return True
+
+    def _launch(self, sched: ScheduleStep, entries, wanting, device_tokens=None) -> _InFlight:
+        """Run the step and sample; the ids start their way to the host.  The scheduler's first half of the
+        accounting (the tokens are in the cache) is done here."""
+        logits = self.engine.step(entries, device_tokens) if device_tokens is not None else self.engine.step(entries)
+        tokens_dev = tokens_host = ready = None
+        if wanting:
+            tokens_dev = self.sampler.sample_device(logits, [r.id for r in wanting], [r.sampling for r in wanting])
+            tokens_host = self._pinned[self._pin_turn][: len(wanting)]
+            self._pin_turn ^= 1
+            tokens_host.copy_(tokens_dev, non_blocking=True)
+            ready = torch.cuda.Event()
+            ready.record()
+        self.scheduler.advance(sched)
+        return _InFlight(sched, wanting, tokens_dev, tokens_host, ready)
+
+    def _commit(self, flight: _InFlight) -> None:
+        """The sampled ids are read; requests get their tokens, finish, and the metrics are kept."""
+        sched, wanting = flight.sched, flight.wanting
         sampled: Dict[int, int] = {}
         if wanting:
-            toks = self.sampler.sample(logits, [r.id for r in wanting], [r.sampling for r in wanting])
-            sampled = {r.id: t for r, t in zip(wanting, toks)}
+            flight.ready.synchronize()
+            sampled = {r.id: t for r, t in zip(wanting, flight.tokens_host.tolist())}
         now = self.wall_clock()
         for r in wanting:
             m = self._metrics[r.id]
             if not m.first_token_recorded:
                 m.first_token_recorded, m.first_token_time_sec = True, now
-        for r in self.scheduler.on_step_done(sched, sampled):
+        for r in self.scheduler.commit(sched, sampled):
             self._record_finish(r)
         self.total_steps += 1
         pre = [e for e in sched.entries if e.is_prefill]
@@ -148,12 +212,18 @@ class BatchMainLoop:
             self.total_steps, now, sched.total_tokens(), sum(e.num_tokens for e in pre),
             len(sched.entries) - len(pre), len(sched.entries), len(pre), len(sched.entries) - len(pre),
             self.scheduler.num_active(), len(sched.preempted)))
-        return True
+
+    def flush(self) -> None:
+        """Read back the step that is still in flight, if any."""
+        if self._inflight is not None:
+            flight, self._inflight = self._inflight, None
+            self._commit(flight)
 
     def run(self) -> None:
         while self.has_active():
             if not self.step() and self.has_active():
                 raise RuntimeError("the scheduler has active requests but schedules nothing")
+        self.flush()
 
     def _record_finish(self, r: Request) -> None:
         m = self._metrics[r.id]
@@ -163,9 +233,11 @@ class BatchMainLoop:
 
     # ---- results and metrics ---------------------------------------------------------------------
     def generated_tokens(self, request_id: int) -> List[int]:
+        self.flush()
         return list(self._requests[request_id].output_tokens)
 
     def finish_reason(self, request_id: int) -> Optional[str]:
+        self.flush()
         return self._requests[request_id].finish_reason
 
     def metrics(self, request_id: int) -> BatchMetrics:
@@ -175,6 +247,7 @@ class BatchMainLoop:
         return list(self._metrics.values())
 
     def total_tokens_generated(self) -> int:
+        self.flush()
         return sum(len(r.output_tokens) for r in self._requests.values())
 
     def _finished(self) -> List[BatchMetrics]:

@@ -77,7 +77,7 @@ class ModelRunner:
         self.graph_launches = 0          # kernels launched through graph replays
 
     # ------------------------------------------------------------------------------------------
-    def _build_context(self, entries: Sequence[StepEntry]) -> StepContext:
+    def _build_context(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> StepContext:
         cache = self.cache
         vocab = self.model.spec.vocab_size
         if not entries:
@@ -188,6 +188,11 @@ class ModelRunner:
         ev.record()
         self._host_done[turn] = ev
         self.last_h2d_bytes = words * 4
+        if device_tokens is not None:
+            # the tokens of this step are still on the device (the ids the last step sampled)
+            if device_tokens.dtype != torch.int32 or device_tokens.numel() != T or not device_tokens.is_cuda:
+                raise StepError(f"device tokens must be {T} int32 values on the device")
+            ctx.token_ids.copy_(device_tokens.reshape(-1))
         return ctx
 
     def forward(self, ctx: StepContext) -> Optional[torch.Tensor]:
@@ -213,11 +218,13 @@ class ModelRunner:
             return m.head.forward(LazyNorm(residual, m.final_norm, ctx, rows=ctx.want_rows), ctx)
         return m.head.forward(m.final_norm.forward_rows(residual, ctx.want_rows, ctx), ctx)
 
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """One step.  Returns the logits at the wanted places, in the order of the entries and of
         each entry's ``want``, as a float32 ``[wanted, vocab]`` tensor on the device (``None`` if
-        nothing is wanted).  Afterwards every request holds its new tokens."""
-        ctx = self._build_context(entries)
+        nothing is wanted).  Afterwards every request holds its new tokens.  With ``device_tokens`` (int32,
+        one per token of the step, on the device) the entries' own token ids only give the counts: the step
+        reads its ids from that tensor, so ids that were sampled on the device need not visit the host."""
+        ctx = self._build_context(entries, device_tokens)
         if self.use_cuda_graphs and not ctx.late_uploads:
             logits = self._forward_graphed(ctx)
         else:

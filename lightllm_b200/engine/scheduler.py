@@ -238,15 +238,29 @@ class Scheduler:
     def on_step_done(self, step: ScheduleStep, sampled: Dict[int, int]) -> List[Request]:
         """Account for a step that ran: ``sampled`` maps a request id to its next token for the
         entries that wanted logits.  Returns the requests that finished."""
-        done = []
+        self.advance(step)
+        return self.commit(step, sampled)
+
+    def advance(self, step: ScheduleStep) -> None:
+        """First half of the accounting, possible as soon as the step has been launched: its tokens are in
+        the cache.  A request whose last token was in the step is decoding from now on, although the
+        token it sampled is not known yet, so the next step can be decided before ``commit``."""
         for e in step.entries:
             r = e.request
             r.num_computed += e.num_tokens
-            if not e.wants_logits:
+            if e.wants_logits and r.state != FINISHED:
+                r.state = DECODING
+
+    def commit(self, step: ScheduleStep, sampled: Dict[int, int]) -> List[Request]:
+        """Second half: the sampled tokens are known.  Requests that finished meanwhile (their token of a
+        step that was launched ahead is dropped) are skipped.  Returns the requests that finish now."""
+        done = []
+        for e in step.entries:
+            r = e.request
+            if not e.wants_logits or r.state == FINISHED:
                 continue
             tok = sampled[r.id]
             r.output_tokens.append(tok)
-            r.state = DECODING
             reason = None
             if tok == r.eos_token_id:
                 reason = "eos"
@@ -259,6 +273,19 @@ class Scheduler:
                 self._finish(r, reason)
                 done.append(r)
         return done
+
+    def can_decode_ahead(self, step: ScheduleStep) -> bool:
+        """Whether the step after ``step`` (launched, advanced, not yet committed) can be decided now: ``step``
+        gave every running request one decode token, nothing waits, none of them can end with the token it is
+        sampling other than by an end-of-sequence id, and every one finds room for one more token."""
+        if self.waiting or step.preempted or len(step.entries) != len(self.running):
+            return False
+        for e, r in zip(step.entries, self.running):
+            if e.request is not r or e.is_prefill or not e.wants_logits or r.state != DECODING:
+                return False
+            if len(r.output_tokens) + 2 > r.max_new_tokens or r.total_len() + 2 > self.cache.max_seq_len:
+                return False
+        return self.cache.can_reserve_all([(r.id, 1) for r in self.running])
 
     # ---- internals ---------------------------------------------------------------------------------
     def _release(self, r: Request) -> None:

@@ -21,17 +21,20 @@ class Engine:
 
     ``model_dir`` holds ``config.json`` and ``model.safetensors``; the architecture is chosen by
     ``config.json``.  ``dtype`` is ``"bfloat16"`` (serving) or ``"float32"`` (true 32-bit
-    everywhere).  ``max_seq_len`` <= 0 means the model's own limit."""
+    everywhere).  ``max_seq_len`` <= 0 means the model's own limit.  ``decode_ahead`` lets the serve loop
+    launch a decode step before the ids of the step before it have reached the host."""
 
     def __init__(self, model_dir: str, dtype: str = "bfloat16", max_seq_len: int = 0, max_batch_tokens: int = 256,
                  kv_cache_mb: Optional[float] = None, page_size: int = 16, num_pages: Optional[int] = None,
-                 max_seqs: int = 64, chunk_size: int = 16, max_prefill_entries: int = 999, device: str = "cuda:0"):
+                 max_seqs: int = 64, chunk_size: int = 16, max_prefill_entries: int = 999, device: str = "cuda:0",
+                 decode_ahead: bool = True):
         self.core = EngineCore(model_dir, EngineOptions(
             dtype=dtype, max_seq_len=max_seq_len, max_batch_tokens=max_batch_tokens, page_size=page_size,
             num_pages=num_pages, kv_cache_mb=kv_cache_mb, max_seqs=max_seqs, device=device))
         self.chunk_size = chunk_size
         self.max_batch_tokens = max_batch_tokens
         self.max_prefill_entries = max_prefill_entries
+        self.decode_ahead = decode_ahead
 
     @property
     def vocab_size(self) -> int:
@@ -39,7 +42,8 @@ class Engine:
 
     def new_loop(self) -> BatchMainLoop:
         """A serve loop over this engine (submit / step / run), for callers that stream."""
-        return BatchMainLoop(self.core, self.chunk_size, self.max_batch_tokens, self.max_prefill_entries)
+        return BatchMainLoop(self.core, self.chunk_size, self.max_batch_tokens, self.max_prefill_entries,
+                             self.decode_ahead)
 
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int = 64, temperature: float = 1.0,
                  top_k: int = 0, top_p: float = 1.0, min_p: float = 0.0, seed: int = 42,

@@ -77,6 +77,45 @@ def test_greedy_generation_through_the_entry_point(tmp_path, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decoding_ahead_gives_the_same_tokens(tmp_path, dtype):
+    """The serve loop that launches a decode step before it has read the last step's ids gives what the
+    step-by-step loop gives: with requests of different lengths, requests that arrive while others decode,
+    and requests that end on an end-of-sequence id after their next step has already been launched."""
+    d = model_dir(tmp_path, "A", store="float32" if dtype == "float32" else "bfloat16")
+    cfg, _ = P.read_model_dir(d)
+    rng = random.Random(5)
+    prompts = [[rng.randrange(cfg["vocab_size"]) for _ in range(n)] for n in (3, 20, 11, 7)]
+    kw = dict(dtype=dtype, max_seq_len=128, max_batch_tokens=32, page_size=PAGE_SIZE["A"], num_pages=40, max_seqs=4,
+              chunk_size=16)
+    slow = Engine(d, decode_ahead=False, **kw)
+    base = slow.generate(prompts, max_new_tokens=24, temperature=0.0, eos_token_id=-1)
+    # an id that request 1 produces in mid-stream becomes the end-of-sequence id
+    eos = base[1][9]
+    results = {}
+    for ahead in (False, True):
+        eng = Engine(d, decode_ahead=ahead, **kw)
+        loop = eng.new_loop()
+        ids = [loop.submit(p, max_new_tokens=n, eos_token_id=eos, temperature=0.0)
+               for p, n in zip(prompts[:3], (24, 24, 5))]
+        for _ in range(6):
+            loop.step()
+        ids.append(loop.submit(prompts[3], max_new_tokens=9, eos_token_id=eos, temperature=0.0))
+        loop.run()
+        results[ahead] = ([loop.generated_tokens(i) for i in ids], [loop.finish_reason(i) for i in ids])
+        if ahead:
+            assert loop.steps_ahead > 5
+        eng.core.cache.check()
+        assert eng.core.cache.free_pages() == 40
+    assert results[True] == results[False]
+    assert "eos" in results[True][1] and "length" in results[True][1]
+    sampled = {}
+    for ahead in (False, True):
+        eng = Engine(d, decode_ahead=ahead, **kw)
+        sampled[ahead] = eng.generate(prompts, max_new_tokens=12, temperature=0.9, top_k=40, seed=3, eos_token_id=-1)
+    assert sampled[True] == sampled[False]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding_and_first_tokens(tmp_path, dtype):
     d = model_dir(tmp_path, "B", store="float32" if dtype == "float32" else "bfloat16")
     cfg, w = P.read_model_dir(d)
