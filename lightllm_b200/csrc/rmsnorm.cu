@@ -4,6 +4,8 @@
 // y_d = x_d * inv * w_d, then the cast (:50-54).  One block per row; the reference uses two
 // launches and a global buffer for ss, here the row stays in registers between the passes
 // when it fits.
+#include <type_traits>
+
 #include "common.cuh"
 
 // Launch with the programmatic-stream-serialization attribute (the kernel calls griddepcontrol.wait itself).
@@ -72,12 +74,68 @@ __global__ void rmsnorm_kernel(const TI* __restrict__ x, const TW* __restrict__ 
     }
 }
 
+// Four consecutive elements as one 16-byte (float) or 8-byte (bf16) access.
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+}
+
+// One warp per row of a float input whose width is a multiple of 4 and at most 128 * NV: the row stays in
+// registers as NV float4 per lane, the sum needs shuffles only, loads and stores are 16 / 8 bytes wide.
+template <typename TW, typename TO, int NV>
+__global__ void __launch_bounds__(256) rmsnorm_warp_kernel(const float* __restrict__ x, const TW* __restrict__ w,
+                                                           TO* __restrict__ out, const int* __restrict__ rows, int R,
+                                                           int D, float eps) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= R) return;
+    const float* xr = x + (size_t)(rows ? rows[r] : r) * D;
+    float4 v[NV];
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int d = (i * 32 + lane) * 4;
+        v[i] = d < D ? *reinterpret_cast<const float4*>(xr + d) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+    }
+    ss = llb_warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)D + eps);
+    TO* o = out + (size_t)r * D;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int d = (i * 32 + lane) * 4;
+        if (d < D) {
+            const float4 g = load4(w + d);
+            store4(o + d, make_float4(v[i].x * inv * g.x, v[i].y * inv * g.y, v[i].z * inv * g.z, v[i].w * inv * g.w));
+        }
+    }
+}
+
 template <typename TI, typename TW, typename TO>
 static int launch_rmsnorm(const void* x, const void* w, void* out, const int* rows, int R, int D, float eps,
                           cudaStream_t stream) {
     const int threads = 256;
     cudaError_t e;
-    if (D <= threads * 4)
+    if (std::is_same<TI, float>::value && D % 4 == 0 && D <= 128 * 16 && (uintptr_t)x % 16 == 0 &&
+        (uintptr_t)w % 16 == 0 && (uintptr_t)out % 16 == 0 && R >= 8) {
+        const dim3 grid((R + 7) / 8);
+        if (D <= 128 * 8)
+            e = launch_pdl(rmsnorm_warp_kernel<TW, TO, 8>, grid, dim3(threads), stream, (const float*)x, (const TW*)w,
+                           (TO*)out, rows, R, D, eps);
+        else
+            e = launch_pdl(rmsnorm_warp_kernel<TW, TO, 16>, grid, dim3(threads), stream, (const float*)x, (const TW*)w,
+                           (TO*)out, rows, R, D, eps);
+    } else if (D <= threads * 4)
         e = launch_pdl(rmsnorm_kernel<TI, TW, TO, 4>, dim3(R), dim3(threads), stream, (const TI*)x, (const TW*)w, (TO*)out, rows, D, eps);
     else if (D <= threads * 16)
         e = launch_pdl(rmsnorm_kernel<TI, TW, TO, 16>, dim3(R), dim3(threads), stream, (const TI*)x, (const TW*)w, (TO*)out, rows, D, eps);

@@ -64,6 +64,17 @@ def test_rmsnorm(ops, D, out_dtype, w_dtype):
     ops.rmsnorm(x, w, 1e-6, out, rows=rows)
     ref = plain_rmsnorm(x.cpu()[[6, 0, 3]], w.float().cpu(), 1e-6)
     assert torch.allclose(out.float().cpu(), ref, atol=2e-2 if out_dtype == torch.bfloat16 else 1e-5, rtol=2e-2)
+    # many rows (widths that are multiples of 4 take the warp-per-row kernel from 8 rows on), also through a row list
+    xm = rnd((61, D), torch.float32, 4, 3.0)
+    out = torch.full((61, D), float("nan"), dtype=out_dtype, device=dev())
+    ops.rmsnorm(xm, w, 1e-5, out)
+    ref = plain_rmsnorm(xm.cpu(), w.float().cpu(), 1e-5)
+    tol = 1e-5 if out_dtype == torch.float32 else 2e-2
+    assert torch.allclose(out.float().cpu(), ref, atol=tol, rtol=tol)
+    pick = torch.arange(60, -1, -3, dtype=torch.int32, device=dev())
+    out = torch.full((pick.numel(), D), float("nan"), dtype=out_dtype, device=dev())
+    ops.rmsnorm(xm, w, 1e-5, out, rows=pick)
+    assert torch.allclose(out.float().cpu(), ref[pick.cpu().long()], atol=tol, rtol=tol)
 
 
 GEMM_SHAPES = [(1, 50, 37), (3, 127, 172), (8, 64, 896), (9, 66, 45), (70, 130, 172), (129, 1000, 96), (5, 2, 8)]
