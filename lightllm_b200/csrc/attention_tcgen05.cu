@@ -294,6 +294,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
+    // Programmatic dependent launch: set-up is done; from here on global memory is touched, so the kernel before
+    // this one must have completed.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int total = p.num_items;
     const int group = p.Hq / p.Hkv;
     constexpr uint32_t IDESC_S = idesc_bf16(BQ, BKV, 0);
@@ -512,6 +515,8 @@ struct MergeParams {
 __global__ void __launch_bounds__(256) attention_tcgen05_merge_kernel(MergeParams p) {
     // A group of HD/4 threads takes one row (four dimensions each, so a row's loads are contiguous); the
     // blocks of grid.z share the tile's rows.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int mt = blockIdx.x, head = blockIdx.y;
     const int span = p.merge_span[mt], q0 = p.merge_q0[mt];
     const int nrows = min(BQ, p.span_len[span] - q0);
@@ -605,7 +610,18 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
     pp.num_items = num_tiles * p.Hq;
     const int resident = (HD <= 64 ? 2 : 1) * num_sms;       // persistent blocks: as many as stay on the device
     const int grid = pp.num_items < resident ? pp.num_items : resident;
-    attention_tcgen05_kernel<HD><<<grid, NUM_THREADS, smem, stream>>>(mq, mk, mv, pp);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, attention_tcgen05_kernel<HD>, mq, mk, mv, pp);
+    if (e != cudaSuccess) return llb_fail("attention_tcgen05: launch failed: %s", cudaGetErrorString(e));
     return llb_check_launch("attention_tcgen05");
 }
 
@@ -667,6 +683,16 @@ LLB_EXPORT int llb_attention_tcgen05_merge(void* out, const int* merge_span, con
     p.out = (__nv_bfloat16*)out; p.merge_span = merge_span; p.merge_q0 = merge_q0; p.merge_first = merge_first;
     p.merge_count = merge_count; p.span_row = span_row; p.span_len = span_len; p.part_o = part_scratch;
     p.part_ml = part_scratch + (size_t)num_parts * Hq * BQ * hd; p.Hq = Hq; p.HD = hd;
-    attention_tcgen05_merge_kernel<<<dim3(num_merge, Hq, BQ / (256 / (hd / 4))), 256, 0, stream>>>(p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(num_merge, Hq, BQ / (256 / (hd / 4)));
+    cfg.blockDim = dim3(256);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, attention_tcgen05_merge_kernel, p);
+    if (e != cudaSuccess) return llb_fail("attention_tcgen05_merge: launch failed: %s", cudaGetErrorString(e));
     return llb_check_launch("attention_tcgen05_merge");
 }

@@ -486,9 +486,12 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_slot_s;
+    // Programmatic dependent launch: the kernel after this one may start its own set-up as blocks of this one leave;
+    // nothing here reads or writes global memory before the kernel before this one has completed.
 
     if (warp == 0) {
         if (lane == 0) {
+            asm volatile("griddepcontrol.wait;" ::: "memory");
             int it = 0;                                  // k-blocks issued so far, over all tiles
             for (int w = blockIdx.x; w < num_items; w += gridDim.x) {
                 const int t = w / splits, ks = w - t * splits;
@@ -539,6 +542,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
         const int half = (warp - 2) >> 2;             // which half of the tile's columns it drains
         const int row = quarter * 32 + lane;
         int local = 0;
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         for (int w = blockIdx.x; w < num_items; w += gridDim.x, ++local) {
             const int t = w / splits;
             const int buf = local & 1;
@@ -723,7 +727,18 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const GemmPa
     }
     const int tiles = llb_ceil_div(p.M, TILE_M) * llb_ceil_div(p.N, P_BN) * p.splits;
     const int grid = tiles < num_sms ? tiles : num_sms;
-    gemm_tcgen05_persistent_kernel<EPI, P_BN><<<grid, P_THREADS, smem, stream>>>(ma, mb, p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(P_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_persistent_kernel<EPI, P_BN>, ma, mb, p);
+    if (e != cudaSuccess) return llb_fail("gemm_tcgen05: launch failed: %s", cudaGetErrorString(e));
     return llb_check_launch("gemm_tcgen05_persistent");
 }
 
