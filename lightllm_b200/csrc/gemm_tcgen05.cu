@@ -549,6 +549,69 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
             const int a_row0 = (t % m_tiles) * TILE_M, b_row0 = (t / m_tiles) * P_BN;
             if (!mbar_wait(&acc_full[buf], (local >> 1) & 1, abort_flag)) break;      // uniform over the warp
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (splits == 2) {
+                // Two pieces: each finishes one half of the tile's columns.  The warps whose half belongs to the other
+                // piece first give their part of the accumulator away through memory and raise a flag; giving never
+                // waits.  Then every warp takes a share of the block's own half: it waits for the other piece's part,
+                // adds it to its own (a + b, whichever piece it is) and runs the epilogue.  The two pieces are
+                // neighbours in the list of work items and every block of the grid is resident, so the wait ends; it
+                // is bounded all the same.  The flag counts the two warps that have yet to read.
+                const int ks = w - t * 2;
+                constexpr int HALF_COLS = P_BN / 2;
+                const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * P_BN);
+                if (half != ks) {
+                    float* dst = p.partials + (size_t)w * TILE_M * HALF_COLS + row;      // [column][row]
+#pragma unroll 1
+                    for (int c0 = 0; c0 < HALF_COLS; c0 += 32) {
+                        uint32_t r[32];
+                        tmem_ld32(lane_base + half * HALF_COLS + c0, r);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) dst[(size_t)(c0 + j) * TILE_M] = __uint_as_float(r[j]);
+                    }
+                    __threadfence();
+                    __syncwarp();
+                    if (lane == 0) atomicExch(&p.counters[t * 8 + ks * 4 + quarter], 2);
+                }
+                int* flag = &p.counters[t * 8 + (1 - ks) * 4 + quarter];
+                int there = 0;
+                if (lane == 0) {
+                    const long long t0 = clock64();
+                    for (unsigned spins = 0;; ++spins) {
+                        if (atomicAdd(flag, 0) != 0) { there = 1; break; }
+                        if ((spins & 63u) == 63u && (*abort_flag || clock64() - t0 > WAIT_LIMIT_CYCLES)) {
+                            *abort_flag = 1;
+                            break;
+                        }
+                        __nanosleep(40);
+                    }
+                }
+                there = __shfl_sync(0xffffffffu, there, 0);
+                __threadfence();
+                const float* src = p.partials + (size_t)(t * 2 + 1 - ks) * TILE_M * HALF_COLS + row;
+                const int share0 = (half == ks) ? 0 : HALF_COLS / 2;          // the warp's columns of the block's own half
+#pragma unroll 1
+                for (int c0 = share0; c0 < share0 + HALF_COLS / 2; c0 += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(lane_base + ks * HALF_COLS + c0, r);
+                    float other[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) other[j] = there ? __ldcg(src + (size_t)(c0 + j) * TILE_M) : 0.0f;
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + other[j]);
+                    if (there)
+                        epilogue_row<(EPI == EPI_ROPE64 ? LLB_EPI_STORE : EPI), 32>(p, a_row0 + row,
+                                                                                   b_row0 + ks * HALF_COLS + c0, r);
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) {
+                    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[buf])) : "memory");
+                    if (there) atomicSub(flag, 1);
+                }
+                continue;
+            }
             if (splits > 1) {
                 // This split's accumulator goes to the meeting place; the warp that arrives last at its
                 // region of the tile (32 rows x half the columns) adds the splits up in their order, so the
