@@ -60,6 +60,40 @@ struct DecodeGemmParams {
     int* error_flag;
 };
 
+// How the rotary epilogue treats one output feature n (row `row` of the block's tile): whether it is rotated, with
+// which row of the tile it pairs, which frequency it uses, and whether it is the pair's first member.
+struct RopeRow {
+    bool rotate, first;
+    int partner, fi;
+};
+__device__ __forceinline__ RopeRow rope_row(const DecodeGemmParams& p, int n, int row) {
+    RopeRow r;
+    const int q_end = p.Hq * p.hd, k_end = q_end + p.Hkv * p.hd;
+    const int head_row = n % p.hd;                    // q, k and v sections are multiples of hd
+    const int half = p.rotary_dim / 2;
+    r.rotate = n < p.N && n < k_end && head_row < p.rotary_dim;
+    r.partner = row;
+    r.fi = 0;
+    r.first = true;
+    if (r.rotate) {
+        if (p.interleaved) { r.first = (head_row & 1) == 0; r.partner = r.first ? row + 1 : row - 1; r.fi = head_row >> 1; }
+        else { r.first = head_row < half; r.partner = r.first ? row + half : row - half; r.fi = r.first ? head_row : head_row - half; }
+    }
+    return r;
+}
+// (cos, sin) and cache rows of tokens m0 .. m0+15 for that feature; the loads do not depend on each other.
+__device__ __forceinline__ void rope_fetch(const DecodeGemmParams& p, const RopeRow& r, int n, int m0, float2 (&cs)[16],
+                                           int (&slot)[16]) {
+    const int half = p.rotary_dim / 2;
+    const bool cached = n < p.N && n >= p.Hq * p.hd && p.slot_mapping != nullptr;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const int m = m0 + j;
+        cs[j] = (r.rotate && m < p.M) ? __ldg(p.rope_table + (size_t)m * half + r.fi) : make_float2(1.0f, 0.0f);
+        slot[j] = (cached && m < p.M) ? __ldg(p.slot_mapping + m) : -1;
+    }
+}
+
 template <int BN, int EPI, bool NORM, int STAGES>
 __global__ void __launch_bounds__(NUM_THREADS)
 gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
@@ -198,10 +232,20 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 fence_async_smem();
                 mbar_arrive(&b_ready_bar);
             }
-            bool ok = mbar_wait(&acc_bar, 0, abort_flag);
-            tc_fence_after();
             const int row = quarter * 32 + lane;     // row of the tile = TMEM lane = output feature
             const int n = n0 + row;
+            // Rotary epilogue: what this output feature needs of the first 16 tokens (their angles' cos and sin,
+            // their cache rows) is asked for now, while the tensor cores still work; loaded one by one inside the
+            // loop over the tokens, each of these reads would be a round trip of its own.
+            RopeRow rr;
+            float2 cs_first[16];
+            int slot_first[16];
+            if (EPI == DEPI_ROPE_KV) {
+                rr = rope_row(p, n, row);
+                rope_fetch(p, rr, n, 0, cs_first, slot_first);
+            }
+            bool ok = mbar_wait(&acc_bar, 0, abort_flag);
+            tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
             const bool meet = (EPI == DEPI_ROPE_KV || EPI == DEPI_SWIGLU) && gridDim.z > 1;
             if (meet) {
@@ -256,33 +300,33 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             }
             if (ok) {
                 if (EPI == DEPI_ROPE_KV) {
-                    // Rotate pairs of rows of one head and scatter to q and the cache pages.
+                    // Rotate pairs of rows of one head and scatter to q and the cache pages, 16 tokens at a time.
                     if (n < p.N) {
                         const int q_end = p.Hq * p.hd, k_end = q_end + p.Hkv * p.hd;
-                        const int head_row = n % p.hd;                    // q, k and v sections are multiples of hd
-                        const bool rotate = n < k_end && head_row < p.rotary_dim;
-                        const int half = p.rotary_dim / 2;
-                        int partner = row, fi = 0;
-                        bool first = true;
-                        if (rotate) {
-                            if (p.interleaved) { first = (head_row & 1) == 0; partner = first ? row + 1 : row - 1; fi = head_row >> 1; }
-                            else { first = head_row < half; partner = first ? row + half : row - half; fi = first ? head_row : head_row - half; }
-                        }
-                        for (int m = 0; m < p.M; ++m) {
-                            float val = stage_f[row * (BN + 1) + m];
-                            if (rotate) {
-                                const float other = stage_f[partner * (BN + 1) + m];
-                                const float2 cs = p.rope_table[m * half + fi];
-                                val = first ? val * cs.x - other * cs.y : val * cs.x + other * cs.y;
+                        for (int m0 = 0; m0 < p.M; m0 += 16) {
+                            float2 cs[16];
+                            int slot[16];
+                            if (m0 == 0) {
+#pragma unroll
+                                for (int j = 0; j < 16; ++j) { cs[j] = cs_first[j]; slot[j] = slot_first[j]; }
+                            } else {
+                                rope_fetch(p, rr, n, m0, cs, slot);
                             }
-                            const __nv_bfloat16 h = __float2bfloat16_rn(val);
-                            if (n < q_end) {
-                                p.q_out[(size_t)m * q_end + n] = h;
-                            } else if (p.slot_mapping) {
-                                const int slot = p.slot_mapping[m];
-                                if (slot >= 0) {
-                                    if (n < k_end) p.k_cache[(size_t)slot * (p.Hkv * p.hd) + (n - q_end)] = h;
-                                    else p.v_cache[(size_t)slot * (p.Hkv * p.hd) + (n - k_end)] = h;
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) {
+                                const int m = m0 + j;
+                                if (m >= p.M) break;
+                                float val = stage_f[row * (BN + 1) + m];
+                                if (rr.rotate) {
+                                    const float other = stage_f[rr.partner * (BN + 1) + m];
+                                    val = rr.first ? val * cs[j].x - other * cs[j].y : val * cs[j].x + other * cs[j].y;
+                                }
+                                const __nv_bfloat16 h = __float2bfloat16_rn(val);
+                                if (n < q_end) {
+                                    p.q_out[(size_t)m * q_end + n] = h;
+                                } else if (slot[j] >= 0) {
+                                    if (n < k_end) p.k_cache[(size_t)slot[j] * (p.Hkv * p.hd) + (n - q_end)] = h;
+                                    else p.v_cache[(size_t)slot[j] * (p.Hkv * p.hd) + (n - k_end)] = h;
                                 }
                             }
                         }

@@ -903,12 +903,12 @@ LLB_EXPORT long long llb_gemm_tcgen05_counters(int M, int N, int split_k) {
 
 // The q/k/v projection of a prompt portion with its whole epilogue on the tensor-core kernel: bias, NeoX rotation
 // of q and k by rope_table [M, 32] of (cos, sin), q to q_out [M, Hq*64], k and v to the cache rows slot_mapping[m].
-// Heads of 64 with the whole head rotated; N = (Hq + 2*Hkv) * 64.  M > 128 (fewer rows take the decode kernel).
+// Heads of 64 with the whole head rotated; N = (Hq + 2*Hkv) * 64.
 LLB_EXPORT int llb_gemm_tcgen05_rope64(const void* A, const void* W, const float* bias, int M, int N, int K,
                                        const float* rope_table, const int* slot_mapping, void* q_out, void* k_cache,
                                        void* v_cache, int Hq, int Hkv, int* error_flag, cudaStream_t stream) {
     if (M == 0) return 0;
-    LLB_REQUIRE(M > 128 && K % 8 == 0 && N == (Hq + 2 * Hkv) * 64 && Hq > 0 && Hkv > 0,
+    LLB_REQUIRE(M > 0 && K % 8 == 0 && N == (Hq + 2 * Hkv) * 64 && Hq > 0 && Hkv > 0,
                 "gemm_tcgen05_rope64: unsupported shape M=%d N=%d K=%d heads %d/%d", M, N, K, Hq, Hkv);
     LLB_REQUIRE(rope_table && q_out && k_cache && v_cache && slot_mapping, "gemm_tcgen05_rope64: null argument");
     LLB_REQUIRE(((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0) && ((uintptr_t)q_out % 16 == 0) &&

@@ -480,7 +480,7 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
 def gemm_tcgen05_rope64(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], rope_table: torch.Tensor,
                         slot_mapping: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor,
                         v_cache: torch.Tensor, num_heads: int, num_kv_heads: int) -> None:
-    """The q/k/v projection of more than 128 rows with heads of 64: a[M,K] @ w[N,K]^T, bias, NeoX rotation of
+    """The q/k/v projection with heads of 64: a[M,K] @ w[N,K]^T, bias, NeoX rotation of
     the whole head by ``rope_table`` [M, 32, 2] (cos, sin), q to ``q_out`` [M, Hq*64], k and v to the cache rows
     ``slot_mapping`` [M] of ``k_cache`` / ``v_cache`` [slots, Hkv, 64] (a negative slot writes nothing)."""
     M, K = a.shape

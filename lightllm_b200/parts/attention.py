@@ -22,7 +22,7 @@ FUSED_ROPE_MAX_ROWS = 16
 # Up to this many keys per request the decode attention's pieces are merged inside the kernel.
 CLUSTER_MERGE_MAX_KEYS = 8192
 # From this many rows on, heads of 64 get their rotation and cache write in the projection's tensor-core epilogue.
-PREFILL_ROPE_MIN_ROWS = 128
+PREFILL_ROPE_MIN_ROWS = 16
 
 
 class AttentionMixer(Mixer):

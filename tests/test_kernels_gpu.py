@@ -265,7 +265,7 @@ def test_gemm_decode_rope_kv(ops, M, hd, rd, inter, Hq, Hkv, norm):
     sc = ops.splitk_scratch(dev())
     assert float(sc[0].abs().max()) == 0.0 and int(sc[1].abs().max()) == 0       # the meeting place is left clean
 
-@pytest.mark.parametrize("M", [129, 300, 1000])
+@pytest.mark.parametrize("M", [17, 64, 129, 300, 1000])
 @pytest.mark.parametrize("Hq,Hkv,K,bias_on", [(14, 2, 896, True), (3, 1, 72, False), (5, 5, 200, True)])
 def test_gemm_tcgen05_rope64(ops, M, Hq, Hkv, K, bias_on):
     """q/k/v projection of a long portion with bias, rotation and the cache write in the tensor-core
@@ -307,9 +307,6 @@ def test_gemm_tcgen05_rope64(ops, M, Hq, Hkv, K, bias_on):
             kexp[sl], vexp[sl] = kr[t], vr[t]
     assert torch.allclose(kc.float().cpu().reshape(-1, Hkv, hd), kexp, atol=tol, rtol=0)
     assert torch.allclose(vc.float().cpu().reshape(-1, Hkv, hd), vexp, atol=tol, rtol=0)
-    with pytest.raises(ops.KernelError):
-        ops.gemm_tcgen05_rope64(a[:100].contiguous(), w, bias, table[:100].contiguous(), slots[:100].to(dev()),
-                                q[:100].contiguous(), kc, vc, Hq, Hkv)
 
 
 @pytest.mark.parametrize("dtype", DT)
