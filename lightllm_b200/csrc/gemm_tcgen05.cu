@@ -105,6 +105,30 @@ __host__ __device__ constexpr uint32_t umma_idesc(int m, int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+__device__ __forceinline__ bool mbar_try_wait_addr(uint32_t bar_addr, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(bar_addr), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_addr(uint32_t bar_addr, uint32_t parity, volatile int* abort_flag) {
+    const long long t0 = clock64();
+    for (unsigned spins = 1;; ++spins) {
+        if (mbar_try_wait_addr(bar_addr, parity)) return true;
+        if ((spins & 255u) == 0u) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+}
 __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t acc) {
     asm volatile(
         "{\n.reg .pred p;\n"
@@ -112,6 +136,26 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t da, uint64_t
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
         ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(acc)
         : "memory");
+}
+// The same with the accumulate flag fixed: no register feeds the predicate, so the instruction does not wait for one.
+__device__ __forceinline__ void umma_bf16_acc(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.eq.u32 p, 0, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc)
+        : "memory");
+}
+__device__ __forceinline__ void umma_bf16_first(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.u32 p, 0, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit_addr(uint32_t bar_addr) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_addr) : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
@@ -149,6 +193,7 @@ struct GemmParams {
     int splits;             // persistent kernel: work items per tile along K
     float* partials;        // [items, tile width, 128] float: the splits' accumulators meet here
     int* counters;          // [tiles, 8] zero before and after: arrivals per warp region of a tile
+    int tma_out;            // the epilogue leaves through shared memory and TMA stores (map_out is valid)
     int* error_flag;        // raised when a wait ran out of time
     // rotary epilogue of the q/k/v projection (heads of 64, NeoX pairs, whole head rotated)
     const float2* rope_table;   // [M, 32] of (cos, sin)
@@ -434,12 +479,98 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 // Tile width P_BN = 128 (6 stages) or 256 (4 stages): the wide tile re-uses each activation tile for twice as
 // many output features, which matters because the main loop is bound by the bytes an SM can pull from L2.
 
+// ---- Epilogue through shared memory and TMA ---------------------------------------------------------
+// A thread owns one row of the tile, so its direct stores are 16-byte pieces of 32 different rows per warp
+// instruction, which costs the memory system dearly (a third of o_proj's time).  Instead each epilogue warp owns a
+// 4 KB staging tile (32 rows x 128 bytes, 128-byte swizzle), fills it from its accumulator chunks and hands it to
+// the TMA engine, which writes whole rows (and clips at the matrix's edge): a store for out, a reduce-add for the
+// residual stream.  One row of the staging tile takes 32 float outputs (one accumulator chunk), 64 bf16 outputs
+// (two chunks) or 64 SiLU*mul outputs (four chunks).
+template <int EPI> struct StagedOut {
+    static constexpr int PIECES = (EPI == LLB_EPI_STORE) ? 2 : (EPI == LLB_EPI_SWIGLU) ? 4 : 1;   // chunks per staged row
+};
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t smem_addr, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(smem_addr), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, uint32_t smem_addr, int x, int y) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(smem_addr), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+// One accumulator chunk (32 columns starting at output feature nb, this lane's row) goes into the warp's staging
+// tile as piece `piece` of the row; with the row's last piece the tile is handed to TMA at (row0, the row's first
+// feature).  Whole-warp call.
+template <int EPI>
+__device__ __forceinline__ void staged_chunk(const GemmParams& p, const CUtensorMap* map_out, uint8_t* stage, int lane,
+                                             int row0, int nb, int piece, const uint32_t (&r)[32]) {
+    constexpr int PIECES = StagedOut<EPI>::PIECES;
+    constexpr int CHUNKS = 8 / PIECES;               // 16-byte chunks of the 128-byte row that one piece fills
+    if (piece == 0) {                                // the tile's last store must have read it
+        if (lane == 0) tma_store_wait_read();
+        __syncwarp();
+    }
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+    if (p.bias) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (nb + j < p.N) v[j] += p.bias[nb + j];
+    }
+    uint8_t* row = stage + lane * 128;
+    if (EPI == LLB_EPI_STORE_F32 || EPI == LLB_EPI_RESIDUAL) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+            *reinterpret_cast<float4*>(row + ((c ^ (lane & 7)) * 16)) = make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+    } else if (EPI == LLB_EPI_STORE) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * c + 2 * e], v[8 * c + 2 * e + 1]);
+                w[e] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+            *reinterpret_cast<uint4*>(row + (((piece * CHUNKS + c) ^ (lane & 7)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    } else {      // SiLU(gate) * up on interleaved features: 32 accumulator columns give 16 outputs
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int j = 16 * c + 4 * e;
+                const __nv_bfloat162 h = __floats2bfloat162_rn(silu_fast(v[j]) * v[j + 1], silu_fast(v[j + 2]) * v[j + 3]);
+                w[e] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+            *reinterpret_cast<uint4*>(row + (((piece * CHUNKS + c) ^ (lane & 7)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    }
+    if (piece == PIECES - 1) {
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+            const int first = nb - (PIECES - 1) * 32;                     // first accumulator column of the staged row
+            const int x = (EPI == LLB_EPI_SWIGLU) ? first / 2 : first;
+            if (row0 < p.M && first < p.N) {         // a box that lies wholly outside the matrix is not issued
+                if (EPI == LLB_EPI_RESIDUAL) tma_reduce_add_2d(map_out, smem_u32(stage), x, row0);
+                else tma_store_2d(map_out, smem_u32(stage), x, row0);
+                tma_store_commit();
+            }
+        }
+    }
+}
+
 constexpr int P_THREADS = 64 + 256;      // TMA warp, MMA warp, eight epilogue warps (two per TMEM lane quarter)
 
 template <int EPI, int P_BN>
 __global__ void __launch_bounds__(P_THREADS, 1)
 gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                               const GemmParams p) {
+                               const __grid_constant__ CUtensorMap map_out, const GemmParams p) {
     constexpr int P_STAGES = P_BN == 256 ? 4 : 6;
     constexpr uint32_t A_BYTES = TILE_M * TILE_K * 2;
     constexpr uint32_t B_BYTES = P_BN * TILE_K * 2;
@@ -454,6 +585,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* a_tiles = smem;
     uint8_t* b_tiles = smem + P_STAGES * A_BYTES;
+    uint8_t* out_tiles = b_tiles + P_STAGES * B_BYTES;       // eight staging tiles of 4 KB, one per epilogue warp
     volatile int* abort_flag = &abort_s;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -511,8 +643,18 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
         }
     } else if (warp == 1) {
         if (lane == 0) {
+            // One thread issues every MMA, and a lone thread runs its scalar instructions one after the other at
+            // their full latency: a few dozen of them per block of K cost more than the four MMAs themselves.  So
+            // the loop carries what it needs in registers: the stage's two operand descriptors (advanced by
+            // constants; the address field of a descriptor is the shared-memory address / 16), the addresses of its
+            // barriers, its phase bit.
             constexpr uint32_t idesc = umma_idesc(TILE_M, P_BN);
-            int it = 0, local = 0;
+            constexpr uint64_t A_STEP = A_BYTES >> 4, B_STEP = B_BYTES >> 4, K_STEP = (UMMA_K * 2) >> 4;
+            const uint64_t da0 = umma_desc(smem_u32(a_tiles)), db0 = umma_desc(smem_u32(b_tiles));
+            const uint32_t full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]);
+            uint64_t da = da0, db = db0;
+            uint32_t full = full0, empty = empty0, phase = 0;
+            int s = 0, local = 0;
             bool ok = true;
             for (int w = blockIdx.x; w < num_items && ok; w += gridDim.x, ++local) {
                 const int ks = w % splits;
@@ -521,18 +663,23 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
                 ok = mbar_wait(&acc_empty[buf], ((local >> 1) & 1) ^ 1, abort_flag);   // the epilogue has drained it
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                for (int kb = kb0; kb < kb1; ++kb, ++it) {
-                    const int s = it % P_STAGES;
-                    ok = mbar_wait(&full_bar[s], (it / P_STAGES) & 1, abort_flag);
-                    if (!ok) break;
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t a_addr = smem_u32(a_tiles + s * A_BYTES);
-                    const uint32_t b_addr = smem_u32(b_tiles + s * B_BYTES);
-#pragma unroll
-                    for (int k = 0; k < TILE_K / UMMA_K; ++k)
-                        umma_bf16(tmem_base + buf * P_BN, umma_desc(a_addr + k * UMMA_K * 2),
-                                  umma_desc(b_addr + k * UMMA_K * 2), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
-                    umma_commit(&empty_bar[s]);
+                const uint32_t acc = tmem_base + buf * P_BN;
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!mbar_try_wait_addr(full, phase)) {
+                        ok = mbar_wait_addr(full, phase, abort_flag);
+                        if (!ok) break;
+                    }
+                    if (kb == kb0) umma_bf16_first(acc, da, db, idesc);
+                    else umma_bf16_acc(acc, da, db, idesc);
+                    umma_bf16_acc(acc, da + K_STEP, db + K_STEP, idesc);
+                    umma_bf16_acc(acc, da + 2 * K_STEP, db + 2 * K_STEP, idesc);
+                    umma_bf16_acc(acc, da + 3 * K_STEP, db + 3 * K_STEP, idesc);
+                    umma_commit_addr(empty);
+                    if (++s == P_STAGES) {
+                        s = 0; da = da0; db = db0; full = full0; empty = empty0; phase ^= 1;
+                    } else {
+                        da += A_STEP; db += B_STEP; full += 8; empty += 8;
+                    }
                 }
                 if (ok) umma_commit(&acc_full[buf]);
             }
@@ -542,6 +689,10 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
         const int half = (warp - 2) >> 2;             // which half of the tile's columns it drains
         const int row = quarter * 32 + lane;
         int local = 0;
+        constexpr int SEPI = (EPI == EPI_ROPE64) ? LLB_EPI_STORE : EPI;
+        // the SiLU*mul row of 64 outputs needs 128 accumulator columns per warp, which only the wide tile has
+        const bool staged = p.tma_out != 0 && EPI != EPI_ROPE64 && (EPI != LLB_EPI_SWIGLU || P_BN == 256);
+        uint8_t* my_stage = out_tiles + (warp - 2) * 4096;
         asm volatile("griddepcontrol.wait;" ::: "memory");
         for (int w = blockIdx.x; w < num_items; w += gridDim.x, ++local) {
             const int t = w / splits;
@@ -600,9 +751,13 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                     for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + other[j]);
-                    if (there)
-                        epilogue_row<(EPI == EPI_ROPE64 ? LLB_EPI_STORE : EPI), 32>(p, a_row0 + row,
-                                                                                   b_row0 + ks * HALF_COLS + c0, r);
+                    if (there) {
+                        if (staged && (HALF_COLS / 2) % (StagedOut<SEPI>::PIECES * 32) == 0)
+                            staged_chunk<SEPI>(p, &map_out, my_stage, lane, a_row0 + quarter * 32, b_row0 + ks * HALF_COLS + c0,
+                                               ((c0 - share0) >> 5) % StagedOut<SEPI>::PIECES, r);
+                        else
+                            epilogue_row<SEPI, 32>(p, a_row0 + row, b_row0 + ks * HALF_COLS + c0, r);
+                    }
                 }
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
@@ -672,7 +827,11 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
                     uint32_t r[32];
                     tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * P_BN + c0), r);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    epilogue_row<(EPI == EPI_ROPE64 ? LLB_EPI_STORE : EPI), 32>(p, a_row0 + row, b_row0 + c0, r);
+                    if (staged)
+                        staged_chunk<SEPI>(p, &map_out, my_stage, lane, a_row0 + quarter * 32, b_row0 + c0,
+                                           ((c0 - half * (P_BN / 2)) >> 5) % StagedOut<SEPI>::PIECES, r);
+                    else
+                        epilogue_row<SEPI, 32>(p, a_row0 + row, b_row0 + c0, r);
                 }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -683,6 +842,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
         }
     }
 
+    if (warp >= 2 && lane == 0) tma_store_wait_all();       // this warp's TMA stores have been written
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (abort_s && threadIdx.x == 0 && p.error_flag) atomicExch(p.error_flag, 5);
@@ -773,9 +933,10 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, di
 }
 
 template <int EPI, int P_BN>
-int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t stream) {
+int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const GemmParams& p,
+                      cudaStream_t stream) {
     constexpr int P_STAGES = P_BN == 256 ? 4 : 6;
-    constexpr size_t smem = (size_t)P_STAGES * (TILE_M * TILE_K * 2 + P_BN * TILE_K * 2) + 1024;
+    constexpr size_t smem = (size_t)P_STAGES * (TILE_M * TILE_K * 2 + P_BN * TILE_K * 2) + 8 * 4096 + 1024;
     static bool configured = false;
     static int num_sms = 0;
     if (!configured) {
@@ -800,18 +961,40 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const GemmPa
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_persistent_kernel<EPI, P_BN>, ma, mb, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_persistent_kernel<EPI, P_BN>, ma, mb, mo, p);
     if (e != cudaSuccess) return llb_fail("gemm_tcgen05: launch failed: %s", cudaGetErrorString(e));
     return llb_check_launch("gemm_tcgen05_persistent");
 }
 
 template <int P_BN>
-int dispatch_persistent(int epi, const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t s) {
+int dispatch_persistent(int epi, const CUtensorMap& ma, const CUtensorMap& mb, GemmParams p, cudaStream_t s) {
+    // The output's tensor map for the staged epilogue: rows of 128 bytes (32 floats or 64 bf16) x 32 rows, 128-byte
+    // swizzle.  Outputs whose base or row pitch is not a multiple of 16 bytes keep the direct stores.
+    CUtensorMap mo = ma;
+    {
+        const bool f32 = epi == LLB_EPI_STORE_F32 || epi == LLB_EPI_RESIDUAL;
+        const void* base = epi == LLB_EPI_RESIDUAL ? (const void*)p.residual : (const void*)p.out;
+        const long long cols = epi == LLB_EPI_SWIGLU ? p.N / 2 : p.N;
+        const long long pitch = cols * (f32 ? 4 : 2);
+        EncodeTiledFn fn = encode_tiled_fn();
+        if (fn && ((uintptr_t)base % 16 == 0) && pitch % 16 == 0 && (epi != LLB_EPI_SWIGLU || p.N % 2 == 0)) {
+            cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)p.M};
+            cuuint64_t strides[1] = {(cuuint64_t)pitch};
+            cuuint32_t box[2] = {f32 ? 32u : 64u, 32u};
+            cuuint32_t estr[2] = {1, 1};
+            CUresult r = fn(&mo, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                            const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) return llb_fail("gemm_tcgen05: cuTensorMapEncodeTiled (output) failed with code %d", (int)r);
+            p.tma_out = 1;
+        }
+    }
     switch (epi) {
-        case LLB_EPI_STORE: return launch_persistent<LLB_EPI_STORE, P_BN>(ma, mb, p, s);
-        case LLB_EPI_STORE_F32: return launch_persistent<LLB_EPI_STORE_F32, P_BN>(ma, mb, p, s);
-        case LLB_EPI_RESIDUAL: return launch_persistent<LLB_EPI_RESIDUAL, P_BN>(ma, mb, p, s);
-        case LLB_EPI_SWIGLU: return launch_persistent<LLB_EPI_SWIGLU, P_BN>(ma, mb, p, s);
+        case LLB_EPI_STORE: return launch_persistent<LLB_EPI_STORE, P_BN>(ma, mb, mo, p, s);
+        case LLB_EPI_STORE_F32: return launch_persistent<LLB_EPI_STORE_F32, P_BN>(ma, mb, mo, p, s);
+        case LLB_EPI_RESIDUAL: return launch_persistent<LLB_EPI_RESIDUAL, P_BN>(ma, mb, mo, p, s);
+        case LLB_EPI_SWIGLU: return launch_persistent<LLB_EPI_SWIGLU, P_BN>(ma, mb, mo, p, s);
     }
     return llb_fail("gemm_tcgen05: unknown epilogue %d", epi);
 }
@@ -927,5 +1110,5 @@ LLB_EXPORT int llb_gemm_tcgen05_rope64(const void* A, const void* W, const float
     int rc;
     if ((rc = make_map(A, M, K, TILE_M, &ma))) return rc;
     if ((rc = make_map(W, N, K, 128, &mb))) return rc;
-    return launch_persistent<EPI_ROPE64, 128>(ma, mb, p, stream);
+    return launch_persistent<EPI_ROPE64, 128>(ma, mb, ma, p, stream);
 }
