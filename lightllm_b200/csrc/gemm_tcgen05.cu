@@ -196,7 +196,7 @@ struct GemmParams {
     int tma_out;            // the epilogue leaves through shared memory and TMA stores (map_out is valid)
     int* error_flag;        // raised when a wait ran out of time
     // rotary epilogue of the q/k/v projection (heads of 64, NeoX pairs, whole head rotated)
-    const float2* rope_table;   // [M, 32] of (cos, sin)
+    const float2* rope_table;   // [32, M] of (cos, sin): pair-major, so that a warp's rows read neighbouring entries
     const int* slot_mapping;    // [M] cache row of each token, negative: not written
     __nv_bfloat16* q_out;       // [M, Hq * 64]
     __nv_bfloat16* k_cache;     // [slots, Hkv, 64]
@@ -290,53 +290,6 @@ __device__ __forceinline__ void epilogue_row(const GemmParams& p, int m, int nb,
 }
 
 constexpr int EPI_ROPE64 = 4;     // q/k/v projection of heads of 64: bias, NeoX rotation, q store, K/V page write
-
-// Rotary epilogue of one thread: token row m and the 64 output features nb .. nb+63, i.e. one whole head of q, k
-// or v (src/ops/rope.cu:54-59 on every pair; cache rows as src/kv_cache/paged_attention.cu:1150-1163).
-__device__ __forceinline__ void epilogue_rope64_row(const GemmParams& p, int m, int nb, const uint32_t (&r0)[32],
-                                                    const uint32_t (&r1)[32]) {
-    if (m >= p.M || nb >= p.N) return;
-    const int q_end = p.Hq * 64, k_end = q_end + p.Hkv * 64;
-    float a[32], b[32];
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-        a[j] = __uint_as_float(r0[j]);
-        b[j] = __uint_as_float(r1[j]);
-        if (p.bias) { a[j] += p.bias[nb + j]; b[j] += p.bias[nb + 32 + j]; }
-    }
-    if (nb < k_end) {
-        const float2* cs = p.rope_table + (size_t)m * 32;
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-            const float2 t = cs[j];
-            const float x = a[j], y = b[j];
-            a[j] = x * t.x - y * t.y;
-            b[j] = y * t.x + x * t.y;
-        }
-    }
-    __nv_bfloat16* dst;
-    if (nb < q_end) {
-        dst = p.q_out + (size_t)m * q_end + nb;
-    } else {
-        const int slot = p.slot_mapping ? p.slot_mapping[m] : -1;
-        if (slot < 0) return;
-        dst = nb < k_end ? p.k_cache + (size_t)slot * (p.Hkv * 64) + (nb - q_end)
-                         : p.v_cache + (size_t)slot * (p.Hkv * 64) + (nb - k_end);
-    }
-#pragma unroll
-    for (int j = 0; j < 32; j += 8) {
-        uint32_t w[4], x[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const __nv_bfloat162 h = __floats2bfloat162_rn(a[j + 2 * e], a[j + 2 * e + 1]);
-            const __nv_bfloat162 g = __floats2bfloat162_rn(b[j + 2 * e], b[j + 2 * e + 1]);
-            w[e] = *reinterpret_cast<const uint32_t*>(&h);
-            x[e] = *reinterpret_cast<const uint32_t*>(&g);
-        }
-        *reinterpret_cast<uint4*>(dst + j) = make_uint4(w[0], w[1], w[2], w[3]);
-        *reinterpret_cast<uint4*>(dst + 32 + j) = make_uint4(x[0], x[1], x[2], x[3]);
-    }
-}
 
 template <int BN, int EPI, bool SWAP>
 __global__ void __launch_bounds__(NUM_THREADS, 2)
@@ -562,6 +515,77 @@ __device__ __forceinline__ void staged_chunk(const GemmParams& p, const CUtensor
                 tma_store_commit();
             }
         }
+    }
+}
+
+// Rotary epilogue of one warp: token rows row0 .. row0+31 (one per lane) and the 64 output features nb .. nb+63, i.e.
+// one whole head of q, k or v (src/ops/rope.cu:54-59 on every pair; cache rows as src/kv_cache/paged_attention.cu:1150-1163).
+// The (cos, sin) table is laid out [pair][token], so the lanes of a warp read neighbouring entries.  A head of q
+// leaves through the warp's staging tile and one TMA store (64 bf16 are one 128-byte row of it) when `staged`;
+// k and v go straight to their cache rows, which lie wherever the pages are.
+__device__ __forceinline__ void epilogue_rope64_warp(const GemmParams& p, const CUtensorMap* map_q, uint8_t* stage,
+                                                     bool staged, int lane, int row0, int nb, const uint32_t (&r0)[32],
+                                                     const uint32_t (&r1)[32]) {
+    if (nb >= p.N) return;                       // uniform over the warp
+    const int m = row0 + lane;
+    const bool in_m = m < p.M;
+    const int q_end = p.Hq * 64, k_end = q_end + p.Hkv * 64;
+    float a[32], b[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        a[j] = __uint_as_float(r0[j]);
+        b[j] = __uint_as_float(r1[j]);
+        if (p.bias) { a[j] += p.bias[nb + j]; b[j] += p.bias[nb + 32 + j]; }
+    }
+    if (nb < k_end && in_m) {
+        const float2* cs = p.rope_table + m;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const float2 t = cs[(size_t)j * p.M];
+            const float x = a[j], y = b[j];
+            a[j] = x * t.x - y * t.y;
+            b[j] = y * t.x + x * t.y;
+        }
+    }
+    uint32_t wa[16], wb[16];
+#pragma unroll
+    for (int e = 0; e < 16; ++e) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(a[2 * e], a[2 * e + 1]);
+        const __nv_bfloat162 g = __floats2bfloat162_rn(b[2 * e], b[2 * e + 1]);
+        wa[e] = *reinterpret_cast<const uint32_t*>(&h);
+        wb[e] = *reinterpret_cast<const uint32_t*>(&g);
+    }
+    if (nb < q_end && staged) {
+        if (lane == 0) tma_store_wait_read();
+        __syncwarp();
+        uint8_t* row = stage + lane * 128;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            *reinterpret_cast<uint4*>(row + ((c ^ (lane & 7)) * 16)) = make_uint4(wa[4 * c], wa[4 * c + 1], wa[4 * c + 2], wa[4 * c + 3]);
+            *reinterpret_cast<uint4*>(row + (((4 + c) ^ (lane & 7)) * 16)) = make_uint4(wb[4 * c], wb[4 * c + 1], wb[4 * c + 2], wb[4 * c + 3]);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0 && row0 < p.M) {
+            tma_store_2d(map_q, smem_u32(stage), nb, row0);
+            tma_store_commit();
+        }
+        return;
+    }
+    if (!in_m) return;
+    __nv_bfloat16* dst;
+    if (nb < q_end) {
+        dst = p.q_out + (size_t)m * q_end + nb;
+    } else {
+        const int slot = p.slot_mapping ? p.slot_mapping[m] : -1;
+        if (slot < 0) return;
+        dst = nb < k_end ? p.k_cache + (size_t)slot * (p.Hkv * 64) + (nb - q_end)
+                         : p.v_cache + (size_t)slot * (p.Hkv * 64) + (nb - k_end);
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        *reinterpret_cast<uint4*>(dst + 8 * c) = make_uint4(wa[4 * c], wa[4 * c + 1], wa[4 * c + 2], wa[4 * c + 3]);
+        *reinterpret_cast<uint4*>(dst + 32 + 8 * c) = make_uint4(wb[4 * c], wb[4 * c + 1], wb[4 * c + 2], wb[4 * c + 3]);
     }
 }
 
@@ -819,7 +843,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
                     tmem_ld32(ta, r0);
                     tmem_ld32(ta + 32, r1);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    epilogue_rope64_row(p, a_row0 + row, b_row0 + c0, r0, r1);
+                    epilogue_rope64_warp(p, &map_out, my_stage, p.tma_out != 0, lane, a_row0 + quarter * 32, b_row0 + c0, r0, r1);
                 }
             } else {
 #pragma unroll 1
@@ -1085,7 +1109,8 @@ LLB_EXPORT long long llb_gemm_tcgen05_counters(int M, int N, int split_k) {
 }
 
 // The q/k/v projection of a prompt portion with its whole epilogue on the tensor-core kernel: bias, NeoX rotation
-// of q and k by rope_table [M, 32] of (cos, sin), q to q_out [M, Hq*64], k and v to the cache rows slot_mapping[m].
+// of q and k by rope_table [32, M] of (cos, sin) (pair-major: llb_rope_table with transposed = 1), q to q_out
+// [M, Hq*64], k and v to the cache rows slot_mapping[m].
 // Heads of 64 with the whole head rotated; N = (Hq + 2*Hkv) * 64.
 LLB_EXPORT int llb_gemm_tcgen05_rope64(const void* A, const void* W, const float* bias, int M, int N, int K,
                                        const float* rope_table, const int* slot_mapping, void* q_out, void* k_cache,
@@ -1110,5 +1135,20 @@ LLB_EXPORT int llb_gemm_tcgen05_rope64(const void* A, const void* W, const float
     int rc;
     if ((rc = make_map(A, M, K, TILE_M, &ma))) return rc;
     if ((rc = make_map(W, N, K, 128, &mb))) return rc;
-    return launch_persistent<EPI_ROPE64, 128>(ma, mb, ma, p, stream);
+    // q leaves through TMA stores of 64 bf16 x 32 rows when its row pitch allows (always: Hq * 128 bytes)
+    CUtensorMap mq = ma;
+    {
+        EncodeTiledFn fn = encode_tiled_fn();
+        if (!fn) return llb_fail("gemm_tcgen05_rope64: cuTensorMapEncodeTiled is not available from the driver");
+        cuuint64_t dims[2] = {(cuuint64_t)Hq * 64, (cuuint64_t)M};
+        cuuint64_t strides[1] = {(cuuint64_t)Hq * 128};
+        cuuint32_t box[2] = {64u, 32u};
+        cuuint32_t estr[2] = {1, 1};
+        CUresult r = fn(&mq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, q_out, dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return llb_fail("gemm_tcgen05_rope64: cuTensorMapEncodeTiled (q) failed with code %d", (int)r);
+        p.tma_out = 1;
+    }
+    return launch_persistent<EPI_ROPE64, 128>(ma, mb, mq, p, stream);
 }

@@ -17,7 +17,7 @@ from . import build as _build
 
 F32, BF16 = 0, 1
 EPI_STORE, EPI_STORE_F32, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
-ABI_VERSION = 13
+ABI_VERSION = 14
 
 _lib: Optional[ctypes.CDLL] = None
 
@@ -226,11 +226,14 @@ def paged_attention_simt(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
 DEPI_STORE_F32, DEPI_RESIDUAL, DEPI_SWIGLU, DEPI_ROPE_KV = 1, 2, 3, 4
 
 
-def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
-    """(cos, sin) of ``positions[t] * inv_freq[i]`` as float32 ``[T, len(inv_freq), 2]``."""
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, transposed: bool = False) -> torch.Tensor:
+    """(cos, sin) of ``positions[t] * inv_freq[i]`` as float32 ``[T, len(inv_freq), 2]``, or pair-major
+    ``[len(inv_freq), T, 2]`` with ``transposed``."""
     T, half = positions.numel(), inv_freq.numel()
-    out = torch.empty((T, half, 2), dtype=torch.float32, device=positions.device)
-    _check(lib().llb_rope_table(_i32(positions, "positions"), _ptr(inv_freq), _ptr(out), T, half, _stream()))
+    shape = (half, T, 2) if transposed else (T, half, 2)
+    out = torch.empty(shape, dtype=torch.float32, device=positions.device)
+    _check(lib().llb_rope_table(_i32(positions, "positions"), _ptr(inv_freq), _ptr(out), T, half,
+                                1 if transposed else 0, _stream()))
     return out
 
 
@@ -481,7 +484,7 @@ def gemm_tcgen05_rope64(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.T
                         slot_mapping: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor,
                         v_cache: torch.Tensor, num_heads: int, num_kv_heads: int) -> None:
     """The q/k/v projection with heads of 64: a[M,K] @ w[N,K]^T, bias, NeoX rotation of
-    the whole head by ``rope_table`` [M, 32, 2] (cos, sin), q to ``q_out`` [M, Hq*64], k and v to the cache rows
+    the whole head by ``rope_table`` [32, M, 2] (cos, sin; pair-major), q to ``q_out`` [M, Hq*64], k and v to the cache rows
     ``slot_mapping`` [M] of ``k_cache`` / ``v_cache`` [slots, Hkv, 64] (a negative slot writes nothing)."""
     M, K = a.shape
     N, K2 = w.shape
@@ -493,7 +496,7 @@ def gemm_tcgen05_rope64(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.T
     if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N):
         raise KernelError("gemm_tcgen05_rope64: bias must be float32 of length N")
     if rope_table.dtype != torch.float32 or rope_table.numel() != M * 64 or not rope_table.is_contiguous():
-        raise KernelError("gemm_tcgen05_rope64: rope_table must be float32 [M, 32, 2]")
+        raise KernelError("gemm_tcgen05_rope64: rope_table must be float32 [32, M, 2]")
     if slot_mapping.dtype != torch.int32 or slot_mapping.numel() != M:
         raise KernelError("gemm_tcgen05_rope64: slot_mapping must be int32 [M]")
     if tuple(q_out.shape) != (M, num_heads * 64) or k_cache.shape[-1] != 64 or k_cache.shape[-2] != num_kv_heads \

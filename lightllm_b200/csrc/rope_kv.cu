@@ -89,20 +89,23 @@ LLB_EXPORT int llb_rope_kv_write(const void* qkv, int dtype, const int* position
 // cos and sin of pos * inv_freq for every token of a step and every rotary pair, computed once per
 // step (the reference recomputes them on the host for every layer, src/engine/engine_server.cpp:1553-1589).
 __global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
-                                  float2* __restrict__ table, int T, int half) {
+                                  float2* __restrict__ table, int T, int half, int transposed) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= T * half) return;
-    const int t = i / half, f = i - t * half;
+    // token-major [T, half], or pair-major [half, T] (consecutive threads then walk along the tokens)
+    const int t = transposed ? i % T : i / half;
+    const int f = transposed ? i / T : i - t * half;
     const float angle = (float)positions[t] * inv_freq[f];
     table[i] = make_float2(cosf(angle), sinf(angle));
 }
 
-// table [T, half] of (cos, sin) pairs as float2.
+// table [T, half] of (cos, sin) pairs as float2, or [half, T] with transposed != 0.
 LLB_EXPORT int llb_rope_table(const int* positions, const float* inv_freq, float* table, int T, int half,
-                              cudaStream_t stream) {
+                              int transposed, cudaStream_t stream) {
     if (T == 0 || half == 0) return 0;
     LLB_REQUIRE(T > 0 && half > 0 && positions && inv_freq && table, "rope_table: bad arguments");
     const int n = T * half;
-    rope_table_kernel<<<llb_ceil_div(n, 256), 256, 0, stream>>>(positions, inv_freq, (float2*)table, T, half);
+    rope_table_kernel<<<llb_ceil_div(n, 256), 256, 0, stream>>>(positions, inv_freq, (float2*)table, T, half,
+                                                                transposed ? 1 : 0);
     return llb_check_launch("rope_table");
 }

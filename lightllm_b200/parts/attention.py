@@ -133,7 +133,8 @@ class AttentionMixer(Mixer):
         if rotary_dim != 64 or interleaved:
             return None
         q = torch.empty((T, self.num_heads * 64), dtype=torch.bfloat16, device=x.device)
-        ops.gemm_tcgen05_rope64(x, self.w_qkv, self.b_qkv, self.position.step_table(ctx), ctx.slot_mapping[cache.group],
+        ops.gemm_tcgen05_rope64(x, self.w_qkv, self.b_qkv, self.position.step_table(ctx, transposed=True),
+                                ctx.slot_mapping[cache.group],
                                 q, cache.k, cache.v, self.num_heads, self.num_kv_heads)
         return q
 

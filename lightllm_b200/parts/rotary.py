@@ -40,14 +40,14 @@ class RotaryEmbedding(PositionEncoding):
     def rotary_table(self):
         return self.inv_freq, self.rotary_dim, self.style == "interleaved"
 
-    def step_table(self, ctx):
+    def step_table(self, ctx, transposed: bool = False):
         """(cos, sin) of every token of the step, computed once per step and shared by all layers
-        whose encoding has the same frequencies."""
+        whose encoding has the same frequencies: ``[T, pairs, 2]``, or ``[pairs, T, 2]`` with ``transposed``."""
         from ..csrc import ops
-        key = ("rope_table", self.rotary_dim, self.theta)
+        key = ("rope_table", self.rotary_dim, self.theta, transposed)
         hit = ctx.memo.get(key)
         if hit is None:
-            hit = ctx.memo[key] = ops.rope_table(ctx.positions, self.inv_freq)
+            hit = ctx.memo[key] = ops.rope_table(ctx.positions, self.inv_freq, transposed)
         return hit
 
 

@@ -287,7 +287,8 @@ def test_gemm_tcgen05_rope64(ops, M, Hq, Hkv, K, bias_on):
     kc = torch.full((npages, page, Hkv, hd), 77.0, dtype=torch.bfloat16, device=dev())
     vc = torch.full((npages, page, Hkv, hd), 77.0, dtype=torch.bfloat16, device=dev())
     q = torch.full((M, Hq * hd), float("nan"), dtype=torch.bfloat16, device=dev())
-    table = ops.rope_table(pos.to(dev()), inv)
+    table = ops.rope_table(pos.to(dev()), inv, transposed=True)
+    assert torch.equal(table.transpose(0, 1), ops.rope_table(pos.to(dev()), inv))
     ops.gemm_tcgen05_rope64(a, w, bias, table, slots.to(dev()), q, kc, vc, Hq, Hkv)
     ops.check_async_errors(dev())
     y = a.double().cpu() @ w.double().cpu().t()
