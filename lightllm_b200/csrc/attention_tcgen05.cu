@@ -42,6 +42,9 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
@@ -265,9 +268,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     uint8_t* v_s = k_s + 2 * KB * TILE_BYTES;         // 2 stages x KB tiles
     uint8_t* p_s = v_s + 2 * KB * TILE_BYTES;         // 2 tiles (keys 0..63, 64..127)
     uint64_t* bar_q_full = &bars[0];
-    uint64_t* bar_q_free = &bars[1];                  // the item's last S = Q K^T has been computed
+    uint64_t* bar_q_free = &bars[1];                  // the item's last S = Q K^T has been computed (a softmax thread arrives)
     uint64_t* bar_kv_full = &bars[2];                 // [2]
-    uint64_t* bar_kv_free = &bars[4];                 // [2] the tile's P V has been computed
+    uint64_t* bar_kv_free = &bars[4];                 // [2] the tile's P V has been computed (a softmax thread arrives)
     uint64_t* bar_s = &bars[6];
     uint64_t* bar_pv = &bars[7];
     uint32_t* tmem_slot = &tmem_slot_s;
@@ -347,7 +350,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         // ---- tensor-core instructions ----------------------------------------------------------------
         bool ok = true;
         uint32_t n_kv = 0, n_item = 0;
-        auto issue_s = [&](int st, bool last) {
+        // A tcgen05.commit is dear (the tensor pipe takes one about every 470 cycles, more than this kernel's
+        // MMAs of a tile need), so there is one per tile: behind P V of tile j and S of tile j+1 together, plus one
+        // behind the first S of an item.  The barriers that only say "this buffer may be overwritten" are arrived
+        // at by a softmax thread once it has seen that commit.
+        auto issue_s = [&](int st) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
             for (int kb = 0; kb < KB; ++kb)
@@ -356,8 +363,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     umma_bf16(tmem_base, desc_kmajor(smem_u32(q_s + kb * TILE_BYTES) + k * 32),
                               desc_kmajor(smem_u32(k_s + (st * KB + kb) * TILE_BYTES) + k * 32), IDESC_S,
                               (kb > 0 || k > 0) ? 1u : 0u);
-            umma_commit(bar_s);
-            if (last) umma_commit(bar_q_free);
         };
         for (int idx = blockIdx.x; idx < total; idx += gridDim.x) {
             const Item it = make_item(p, idx);
@@ -367,7 +372,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 const int st = n_kv & 1;
                 if (j == 0) {
                     ok = mbar_wait(&bar_kv_full[st], (n_kv >> 1) & 1, abort_flag) && ok;
-                    if (lane == 0 && ok) issue_s(st, it.ntiles == 1);
+                    if (lane == 0 && ok) {
+                        issue_s(st);
+                        umma_commit(bar_s);
+                    }
                     __syncwarp();
                 }
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -380,17 +388,17 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                         umma_bf16(tmem_base + 128, desc_kmajor(smem_u32(p_s + (k >> 2) * TILE_BYTES) + (k & 3) * 32),
                                   desc_mnmajor(smem_u32(v_s + st * KB * TILE_BYTES) + k * 16 * 128, TILE_BYTES), IDESC_PV,
                                   k > 0 ? 1u : 0u);
-                    umma_commit(bar_pv);
-                    umma_commit(&bar_kv_free[st]);
                 }
                 __syncwarp();
                 if (j + 1 < it.ntiles) {
-                    // S of the next tile runs under the softmax threads' read of this tile's P V
+                    // S of the next tile follows at once; it is complete when the softmax threads have read P V
                     const uint32_t n2 = n_kv + 1;
                     ok = mbar_wait(&bar_kv_full[n2 & 1], (n2 >> 1) & 1, abort_flag) && ok;
-                    if (lane == 0 && ok) issue_s(n2 & 1, j + 2 == it.ntiles);
+                    if (lane == 0 && ok) issue_s(n2 & 1);
                     __syncwarp();
                 }
+                if (lane == 0 && ok) umma_commit(bar_pv);     // P V of this tile and S of the next
+                __syncwarp();
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 named_barrier(BAR_TILE_END, NUM_SOFTMAX + 32);
             }
@@ -404,7 +412,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         const int r = threadIdx.x & (BQ - 1);       // query row of this thread = TMEM lane
         constexpr int HO = HD / 2;                  // output dimensions of this thread
         bool ok = true;
-        uint32_t n_s = 0;
+        uint32_t n_s = 0, n_item = 0;
         for (int idx = blockIdx.x; idx < total; idx += gridDim.x) {
             const Item it = make_item(p, idx);
             if (it.ntiles <= 0) continue;
@@ -418,7 +426,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             float m_run = -INFINITY, l_run = 0.0f;
             for (int j = 0; j < it.ntiles; ++j, ++n_s) {
                 const int kt = it.kt0 + j * BKV;
-                ok = mbar_wait(bar_s, n_s & 1, abort_flag) && ok;
+                if (j == 0) {      // later tiles' S came with the commit behind the tile before them
+                    ok = mbar_wait(bar_s, n_item & 1, abort_flag) && ok;
+                    if (threadIdx.x == 0 && it.ntiles == 1) mbar_arrive(bar_q_free);     // the item's last S has read Q
+                }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 // Softmax of this thread's row over its 64 keys of the tile, in two passes over tensor memory
                 // (maximum first, then the probabilities), 32 columns at a time.  Tiles that lie wholly below
@@ -444,6 +455,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 named_barrier(BAR_P_READY, NUM_SOFTMAX + 32);
                 ok = mbar_wait(bar_pv, n_s & 1, abort_flag) && ok;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (threadIdx.x == 0) {
+                    mbar_arrive(&bar_kv_free[n_s & 1]);                       // this tile's K and V have been read
+                    if (j + 2 == it.ntiles) mbar_arrive(bar_q_free);           // and so has Q, by the item's last S
+                }
 #pragma unroll
                 for (int c = 0; c < HO / 32; ++c) {
                     float t[32];
@@ -486,6 +501,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     *reinterpret_cast<uint4*>(dst + d) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
             }
+            ++n_item;
         }
     }
 
