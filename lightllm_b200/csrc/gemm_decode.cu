@@ -183,6 +183,62 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             griddep_wait();
             if (NORM) {
                 // B operand = RMSNorm(x) * w for all K, as bf16 in the swizzled K-major tiles.  One warp per row.
+                if (p.K <= 1024 && p.M <= 8) {
+                    // Few short rows: a warp asks for both of its rows at once and keeps them in registers (8 float4
+                    // per lane and row), so the statistics and the scaled copy cost one trip to memory, not four.
+                    const int ra = warp - 2, rb = warp + 2;
+                    const bool has_a = ra < p.M, has_b = rb < p.M;
+                    const float* xa = p.x + (size_t)(has_a ? (p.x_rows ? p.x_rows[ra] : ra) : 0) * p.K;
+                    const float* xb = p.x + (size_t)(has_b ? (p.x_rows ? p.x_rows[rb] : rb) : 0) * p.K;
+                    float4 va[8], vb[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int k = (i * 32 + lane) * 4;
+                        const bool in_k = k < p.K;
+                        va[i] = (has_a && in_k) ? *reinterpret_cast<const float4*>(xa + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        vb[i] = (has_b && in_k) ? *reinterpret_cast<const float4*>(xb + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+                    float sa = 0.0f, sb = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        sa += va[i].x * va[i].x + va[i].y * va[i].y + va[i].z * va[i].z + va[i].w * va[i].w;
+                        sb += vb[i].x * vb[i].x + vb[i].y * vb[i].y + vb[i].z * vb[i].z + vb[i].w * vb[i].w;
+                    }
+                    sa = llb_warp_sum(sa);
+                    sb = llb_warp_sum(sb);
+                    const float inva = 1.0f / sqrtf(sa / (float)p.K + p.eps), invb = 1.0f / sqrtf(sb / (float)p.K + p.eps);
+                    // rows of the tile beyond M stay as they are: what the MMA makes of them is never read
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int k = (i * 32 + lane) * 4;       // 4 elements = half of a 16-byte chunk of the tile row
+                        if (k >= p.K || (k >> 6) < kb_begin || (k >> 6) >= kb_end) continue;
+                        float nw[4];
+                        if (p.norm_w_bf16) {
+                            const uint2 u = *reinterpret_cast<const uint2*>((const __nv_bfloat16*)p.norm_w + k);
+                            const float2 f0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+                            const float2 f1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+                            nw[0] = f0.x; nw[1] = f0.y; nw[2] = f1.x; nw[3] = f1.y;
+                        } else {
+                            const float4 c0 = *reinterpret_cast<const float4*>((const float*)p.norm_w + k);
+                            nw[0] = c0.x; nw[1] = c0.y; nw[2] = c0.z; nw[3] = c0.w;
+                        }
+                        const int kb = k >> 6, q = (k & 63) >> 3, sub = (k & 7) * 2;       // tile, chunk, byte offset in it
+                        if (has_a) {
+                            const __nv_bfloat162 h0 = __floats2bfloat162_rn(va[i].x * inva * nw[0], va[i].y * inva * nw[1]);
+                            const __nv_bfloat162 h1 = __floats2bfloat162_rn(va[i].z * inva * nw[2], va[i].w * inva * nw[3]);
+                            uint8_t* dst = b_tiles + (size_t)kb * B_BYTES + (uint32_t)ra * 128 + ((q ^ (ra & 7)) * 16) + sub;
+                            *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<const uint32_t*>(&h0),
+                                                                        *reinterpret_cast<const uint32_t*>(&h1));
+                        }
+                        if (has_b) {
+                            const __nv_bfloat162 h0 = __floats2bfloat162_rn(vb[i].x * invb * nw[0], vb[i].y * invb * nw[1]);
+                            const __nv_bfloat162 h1 = __floats2bfloat162_rn(vb[i].z * invb * nw[2], vb[i].w * invb * nw[3]);
+                            uint8_t* dst = b_tiles + (size_t)kb * B_BYTES + (uint32_t)rb * 128 + ((q ^ (rb & 7)) * 16) + sub;
+                            *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<const uint32_t*>(&h0),
+                                                                        *reinterpret_cast<const uint32_t*>(&h1));
+                        }
+                    }
+                } else
                 for (int r = warp - 2; r < BN; r += 4) {
                     const bool real = r < p.M;
                     const float* xr = p.x + (size_t)(real ? (p.x_rows ? p.x_rows[r] : r) : 0) * p.K;

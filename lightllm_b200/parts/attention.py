@@ -96,7 +96,8 @@ class AttentionMixer(Mixer):
         table = self.position.rotary_table()
         if table is None or self.w_qkv.dtype != torch.bfloat16 or not hasattr(self.position, "step_table"):
             return None
-        if isinstance(x, LazyNorm) and not (x.fusable() is not None and x.num_rows <= L.FUSE_NORM_MAX_ROWS):
+        if isinstance(x, LazyNorm) and not (x.fusable() is not None and x.num_rows <= L.FUSE_NORM_MAX_ROWS
+                                           and self.w_qkv.shape[1] <= L.FUSE_NORM_MAX_COLS):
             x = x.materialize()
         lazy = isinstance(x, LazyNorm)
         rms = x.fusable() if lazy else None

@@ -40,9 +40,12 @@ def tensor_core_eligible(x: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 DECODE_ROWS = 64     # steps of at most this many rows use the fused decode contraction
-# Rows up to which the norm is folded into the contraction's prologue.  Measured on B200 at Qwen2.5-0.5B sizes
-# the separate norm kernel (2 us) beats the prologue (5 us at 8 rows, 30 us at 64), so it is off.
+# Rows up to which the norm is folded into the contraction's prologue.  Measured on B200 at Qwen2.5-0.5B sizes the
+# separate norm kernel wins at every size: at 8 rows the prologue (each block reads the rows, one trip to memory
+# before its first MMA) makes gate/up 10.2 us against 7.5 + 1.7, and the decode step 0.95 ms against 0.89.  So it is
+# off; the prologue stays built and tested.
 FUSE_NORM_MAX_ROWS = 0
+FUSE_NORM_MAX_COLS = 1024
 
 
 def decode_eligible(M: int, w: torch.Tensor, act_dtype: torch.dtype, norm: bool, epilogue: int, head_dim: int = 0) -> bool:
@@ -120,7 +123,7 @@ def linear_normed(lazy, w: torch.Tensor, bias: Optional[torch.Tensor], epilogue:
     """``linear`` on a LazyNorm input: the norm runs inside the contraction when the shape allows."""
     M, N = lazy.num_rows, w.shape[0]
     rms = lazy.fusable()
-    if rms is not None and epilogue in _DECODE_EPI and 0 < M <= FUSE_NORM_MAX_ROWS and \
+    if rms is not None and epilogue in _DECODE_EPI and 0 < M <= FUSE_NORM_MAX_ROWS and w.shape[1] <= FUSE_NORM_MAX_COLS and \
             decode_eligible(M, w, lazy.norm.out_dtype, True, _DECODE_EPI[epilogue]):
         cols = N // 2 if epilogue == SWIGLU else N
         out = torch.empty((M, cols), dtype=torch.float32 if epilogue == STORE_F32 else torch.bfloat16,
