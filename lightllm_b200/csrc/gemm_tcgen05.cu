@@ -22,9 +22,11 @@
 #include <mutex>
 #include <unordered_map>
 
-#include "common.cuh"
+#include "tcgen05_common.cuh"
 
 namespace {
+
+using namespace t5;
 
 // SiLU for the bf16 epilogues: the fast exponential and division are far inside bf16's rounding.
 __device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
@@ -34,145 +36,6 @@ constexpr int TILE_K = 64;        // bf16 elements per stage row = 128 bytes = o
 constexpr int UMMA_K = 16;
 constexpr int STAGES = 3;
 constexpr int NUM_THREADS = 192;
-constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;   // about 2 s of SM cycles
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ unsigned long long globaltimer_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait: false when the time limit ran out (or another role already gave up).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-    if (mbar_try_wait(bar, parity)) return true;
-    // The time limit is checked once every 256 failed attempts, on the SM's own cycle counter: reading a
-    // timer inside the loop would add its latency to every wake-up.
-    const long long t0 = clock64();
-    for (unsigned spins = 1;; ++spins) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((spins & 255u) == 0u) {
-            if (*abort_flag) return false;
-            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
-                *abort_flag = 1;
-                return false;
-            }
-        }
-    }
-}
-
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
-        : "memory");
-}
-
-// Shared memory matrix descriptor of a K-major tile with 128-byte rows and the 128-byte swizzle:
-// start address >> 4 | leading offset (unused in this mode, 1) | stride offset = 8 rows * 128 B |
-// descriptor version 1 (sm_100) | layout type 2 (128-byte swizzle).
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
-    d |= (uint64_t)1 << 16;
-    d |= (uint64_t)(1024 >> 4) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
-    return d;
-}
-
-// Instruction descriptor of kind::f16: D float (1 << 4), A and B bf16 (1 << 7, 1 << 10), both K-major,
-// N >> 3 at bit 17, M >> 4 at bit 24.
-__host__ __device__ constexpr uint32_t umma_idesc(int m, int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-
-__device__ __forceinline__ bool mbar_try_wait_addr(uint32_t bar_addr, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(ok)
-        : "r"(bar_addr), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait_addr(uint32_t bar_addr, uint32_t parity, volatile int* abort_flag) {
-    const long long t0 = clock64();
-    for (unsigned spins = 1;; ++spins) {
-        if (mbar_try_wait_addr(bar_addr, parity)) return true;
-        if ((spins & 255u) == 0u) {
-            if (*abort_flag) return false;
-            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
-                *abort_flag = 1;
-                return false;
-            }
-        }
-    }
-}
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t acc) {
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "setp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(acc)
-        : "memory");
-}
-// The same with the accumulate flag fixed: no register feeds the predicate, so the instruction does not wait for one.
-__device__ __forceinline__ void umma_bf16_acc(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc) {
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "setp.eq.u32 p, 0, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc)
-        : "memory");
-}
-__device__ __forceinline__ void umma_bf16_first(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc) {
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "setp.ne.u32 p, 0, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc)
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit_addr(uint32_t bar_addr) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_addr) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-}
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
@@ -350,7 +213,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
         } else if (warp == 1) {
             if (lane == 0) {
-                constexpr uint32_t idesc = umma_idesc(TILE_M, BN);
+                constexpr uint32_t idesc = idesc_bf16(TILE_M, BN);
                 bool ok = true;
                 for (int i = 0; i < nkb && ok; ++i) {
                     const int s = i % STAGES;
@@ -362,7 +225,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const uint32_t b_addr = smem_u32(b_tiles + s * B_BYTES);
 #pragma unroll
                     for (int k = 0; k < TILE_K / UMMA_K; ++k) {
-                        umma_bf16(tmem_base, umma_desc(a_addr + k * UMMA_K * 2), umma_desc(b_addr + k * UMMA_K * 2),
+                        umma_bf16(tmem_base, desc_kmajor(a_addr + k * UMMA_K * 2), desc_kmajor(b_addr + k * UMMA_K * 2),
                                   idesc, (i > 0 || k > 0) ? 1u : 0u);
                     }
                     umma_commit(&empty_bar[s]);      // frees the stage when these MMAs have read it
@@ -381,7 +244,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 for (int c0 = 0; c0 < BN; c0 += CHUNK) {
                     uint32_t r[32];
                     const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
-                    if (CHUNK == 32) tmem_ld32(taddr, r); else tmem_ld16(taddr, r);
+                    if (CHUNK == 32) tmem_ld32_nowait(taddr, r); else tmem_ld16(taddr, r);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                     if (!SWAP) {
                         // row = token m, columns = output features n: 32 consecutive columns per thread
@@ -442,18 +305,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 template <int EPI> struct StagedOut {
     static constexpr int PIECES = (EPI == LLB_EPI_STORE) ? 2 : (EPI == LLB_EPI_SWIGLU) ? 4 : 1;   // chunks per staged row
 };
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t smem_addr, int x, int y) {
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
-                 ::"l"(map), "r"(smem_addr), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, uint32_t smem_addr, int x, int y) {
-    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
-                 ::"l"(map), "r"(smem_addr), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-
 // One accumulator chunk (32 columns starting at output feature nb, this lane's row) goes into the warp's staging
 // tile as piece `piece` of the row; with the row's last piece the tile is handed to TMA at (row0, the row's first
 // feature).  Whole-warp call.
@@ -672,9 +523,9 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
             // the loop carries what it needs in registers: the stage's two operand descriptors (advanced by
             // constants; the address field of a descriptor is the shared-memory address / 16), the addresses of its
             // barriers, its phase bit.
-            constexpr uint32_t idesc = umma_idesc(TILE_M, P_BN);
+            constexpr uint32_t idesc = idesc_bf16(TILE_M, P_BN);
             constexpr uint64_t A_STEP = A_BYTES >> 4, B_STEP = B_BYTES >> 4, K_STEP = (UMMA_K * 2) >> 4;
-            const uint64_t da0 = umma_desc(smem_u32(a_tiles)), db0 = umma_desc(smem_u32(b_tiles));
+            const uint64_t da0 = desc_kmajor(smem_u32(a_tiles)), db0 = desc_kmajor(smem_u32(b_tiles));
             const uint32_t full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]);
             uint64_t da = da0, db = db0;
             uint32_t full = full0, empty = empty0, phase = 0;
@@ -739,7 +590,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
 #pragma unroll 1
                     for (int c0 = 0; c0 < HALF_COLS; c0 += 32) {
                         uint32_t r[32];
-                        tmem_ld32(lane_base + half * HALF_COLS + c0, r);
+                        tmem_ld32_nowait(lane_base + half * HALF_COLS + c0, r);
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                         for (int j = 0; j < 32; ++j) dst[(size_t)(c0 + j) * TILE_M] = __uint_as_float(r[j]);
@@ -768,7 +619,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
 #pragma unroll 1
                 for (int c0 = share0; c0 < share0 + HALF_COLS / 2; c0 += 32) {
                     uint32_t r[32];
-                    tmem_ld32(lane_base + ks * HALF_COLS + c0, r);
+                    tmem_ld32_nowait(lane_base + ks * HALF_COLS + c0, r);
                     float other[32];
 #pragma unroll
                     for (int j = 0; j < 32; ++j) other[j] = there ? __ldcg(src + (size_t)(c0 + j) * TILE_M) : 0.0f;
@@ -800,7 +651,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
 #pragma unroll 1
                 for (int c0 = half * (P_BN / 2); c0 < (half + 1) * (P_BN / 2); c0 += 32) {
                     uint32_t r[32];
-                    tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * P_BN + c0), r);
+                    tmem_ld32_nowait(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * P_BN + c0), r);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                     for (int j = 0; j < 32; ++j) mine[(size_t)(c0 + j) * TILE_M] = __uint_as_float(r[j]);
@@ -840,8 +691,8 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
                 for (int c0 = half * (P_BN / 2); c0 < (half + 1) * (P_BN / 2); c0 += 64) {
                     uint32_t r0[32], r1[32];
                     const uint32_t ta = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * P_BN + c0);
-                    tmem_ld32(ta, r0);
-                    tmem_ld32(ta + 32, r1);
+                    tmem_ld32_nowait(ta, r0);
+                    tmem_ld32_nowait(ta + 32, r1);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                     epilogue_rope64_warp(p, &map_out, my_stage, p.tma_out != 0, lane, a_row0 + quarter * 32, b_row0 + c0, r0, r1);
                 }
@@ -849,7 +700,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
 #pragma unroll 1
                 for (int c0 = half * (P_BN / 2); c0 < (half + 1) * (P_BN / 2); c0 += 32) {
                     uint32_t r[32];
-                    tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * P_BN + c0), r);
+                    tmem_ld32_nowait(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * P_BN + c0), r);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                     if (staged)
                         staged_chunk<SEPI>(p, &map_out, my_stage, lane, a_row0 + quarter * 32, b_row0 + c0,
@@ -879,23 +730,6 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
 // ---------------------------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* sym = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)sym;
-    });
-    return fn;
-}
-
 struct MapKey {
     const void* ptr;
     int rows, K, box_rows;
@@ -920,7 +754,7 @@ int make_map(const void* ptr, int rows, int K, int box_rows, CUtensorMap* out) {
             return 0;
         }
     }
-    EncodeTiledFn fn = encode_tiled_fn();
+    t5::EncodeTiledFn fn = t5::encode_tiled_fn();
     if (!fn) return llb_fail("gemm_tcgen05: cuTensorMapEncodeTiled is not available from the driver");
     cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)K * 2};
@@ -1000,7 +834,7 @@ int dispatch_persistent(int epi, const CUtensorMap& ma, const CUtensorMap& mb, G
         const void* base = epi == LLB_EPI_RESIDUAL ? (const void*)p.residual : (const void*)p.out;
         const long long cols = epi == LLB_EPI_SWIGLU ? p.N / 2 : p.N;
         const long long pitch = cols * (f32 ? 4 : 2);
-        EncodeTiledFn fn = encode_tiled_fn();
+        t5::EncodeTiledFn fn = t5::encode_tiled_fn();
         if (fn && ((uintptr_t)base % 16 == 0) && pitch % 16 == 0 && (epi != LLB_EPI_SWIGLU || p.N % 2 == 0)) {
             cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)p.M};
             cuuint64_t strides[1] = {(cuuint64_t)pitch};
@@ -1138,7 +972,7 @@ LLB_EXPORT int llb_gemm_tcgen05_rope64(const void* A, const void* W, const float
     // q leaves through TMA stores of 64 bf16 x 32 rows when its row pitch allows (always: Hq * 128 bytes)
     CUtensorMap mq = ma;
     {
-        EncodeTiledFn fn = encode_tiled_fn();
+        t5::EncodeTiledFn fn = t5::encode_tiled_fn();
         if (!fn) return llb_fail("gemm_tcgen05_rope64: cuTensorMapEncodeTiled is not available from the driver");
         cuuint64_t dims[2] = {(cuuint64_t)Hq * 64, (cuuint64_t)M};
         cuuint64_t strides[1] = {(cuuint64_t)Hq * 128};
