@@ -241,11 +241,17 @@ class ModelRunner:
         from ..csrc import ops
         key = (ctx.T, ctx.num_spans, ctx.num_want, ctx.max_pages, ctx.decode_only, tuple(ctx.shape_key))
         hit = self._graphs.get(key)
-        if hit is None:
+        if hit is not None:
+            self._graphs[key] = self._graphs.pop(key)          # most recently used last
+        else:
             seen = self._graph_seen.get(key, 0) + 1
             self._graph_seen[key] = seen
-            if seen < 2 or len(self._graphs) >= self.max_graphs:
-                return self.forward(ctx)          # first sight of a shape (also the warm-up), or no room left
+            if len(self._graph_seen) > 4096:              # shapes seen once and never again
+                self._graph_seen.clear()
+            if seen < 2:
+                return self.forward(ctx)          # first sight of a shape (also the warm-up)
+            if len(self._graphs) >= self.max_graphs:      # the least recently used graph makes room
+                del self._graphs[next(iter(self._graphs))]
             before = ops.launch_count()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, pool=self._graph_pool):

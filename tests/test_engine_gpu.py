@@ -77,6 +77,45 @@ def test_greedy_generation_through_the_entry_point(tmp_path, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_replayed_from_graphs_match_steps_launched_one_by_one(tmp_path, dtype):
+    """Step shapes that repeat (prompt portions of equal length at equal positions, mixed steps, decode steps) are
+    captured in CUDA graphs at their second appearance; with room for two graphs only, graphs are dropped and
+    captured again.  The logits are those of a runner that launches every kernel itself."""
+    d = model_dir(tmp_path, "A", store="float32" if dtype == "float32" else "bfloat16")
+    cfg, _ = P.read_model_dir(d)
+    rng = random.Random(11)
+    V = cfg["vocab_size"]
+    toks = {k: [rng.randrange(V) for _ in range(70)] for k in "abc"}
+    outs = {}
+    for graphs in (False, True):
+        core = core_for(d, dtype, page=PAGE_SIZE["A"], pages=40)
+        core.runner.use_cuda_graphs = graphs and core.runner.use_cuda_graphs
+        core.runner.max_graphs = 2
+        got = []
+        for rnd_ in range(4):                       # the same schedule four times: every shape comes back
+            for k in "abc":
+                core.open(k)
+            got.append(core.step([StepEntry("a", toks["a"][:40], [39])]))
+            got.append(core.step([StepEntry("b", toks["b"][:40], [39])]))                       # same shape as the last
+            got.append(core.step([StepEntry("a", toks["a"][40:41], [0]), StepEntry("c", toks["c"][:33], [32])]))
+            got.append(core.step([StepEntry("a", toks["a"][41:42], [0]), StepEntry("b", toks["b"][40:41], [0]),
+                                  StepEntry("c", toks["c"][33:34], [0])]))
+            got.append(core.step([StepEntry("a", toks["a"][42:43], [0]), StepEntry("b", toks["b"][41:42], [0]),
+                                  StepEntry("c", toks["c"][34:35], [0])]))
+            for k in "abc":
+                core.close(k)
+        outs[graphs] = [g.float().cpu() for g in got]
+        if graphs:
+            assert core.runner.graph_replays >= 8 and len(core.runner._graphs) <= 2
+        core.runner.check_device_errors()
+    worst = max(float((a - b).abs().max()) for a, b in zip(outs[False], outs[True]))
+    print("largest difference between replayed and launched steps:", worst)
+    # the same kernels on the same inputs: equal bits in float32; in bfloat16 the decode contractions add their
+    # pieces with float atomics, whose order is free, so the last bits of the float32 sums may differ
+    assert worst == 0.0 if dtype == "float32" else worst < 1e-3
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_decoding_ahead_gives_the_same_tokens(tmp_path, dtype):
     """The serve loop that launches a decode step before it has read the last step's ids gives what the
     step-by-step loop gives: with requests of different lengths, requests that arrive while others decode,
