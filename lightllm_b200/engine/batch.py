@@ -122,15 +122,30 @@ class StepContext:
         self._tiles[key] = hit
         return hit
 
-    def attention_items(self, min_len: int, window: int, chunk_tiles: int = 4):
+    def attention_items(self, min_len: int, window: int, chunk_tiles: Optional[int] = 4, heads: int = 1,
+                        slots: int = 1):
         """Work items of the tensor-core attention kernel for the spans of at least ``min_len`` rows: tiles
         of 128 query rows whose key range (in tiles of 128 keys) is cut into pieces of ``chunk_tiles``, longest
-        first, so that a long prompt's last rows do not set the kernel's time.  Returns ``(tile_span, tile_q0,
-        count, cut)`` with ``cut`` as ``ops.paged_attention_tcgen05`` takes it."""
-        key = ("items", min_len, window, chunk_tiles)
+        first, so that a long prompt's last rows do not set the kernel's time.  With ``chunk_tiles=None`` the
+        piece is as long as the work allows: the tiles of all ``heads`` spread over ``slots`` resident blocks give
+        each block so many tiles anyway, and shorter pieces would only add partial results to merge (between 4
+        and 16).  Returns ``(tile_span, tile_q0, count, cut)`` with ``cut`` as ``ops.paged_attention_tcgen05``
+        takes it."""
+        key = ("items", min_len, window, chunk_tiles, heads, slots)
         hit = self._tiles.get(key)
         if hit is not None:
             return hit
+        if chunk_tiles is None:
+            total = 0
+            for s in self.spans:
+                if s.length < min_len:
+                    continue
+                for q0 in range(0, s.length, 128):
+                    pos0 = s.start + q0
+                    hi = pos0 + min(128, s.length - q0)
+                    lo = max(0, pos0 - window + 1) if window > 0 else 0
+                    total += -(-(hi - (lo // 128) * 128) // 128)
+            chunk_tiles = min(16, max(4, -(-total * heads // max(1, slots))))
         items, merges, parts = [], [], 0
         for i, s in enumerate(self.spans):
             if s.length < min_len:

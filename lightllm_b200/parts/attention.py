@@ -214,7 +214,9 @@ class AttentionMixer(Mixer):
             if (bf16 and ops.attention_tcgen05_supports(self.head_dim, ctx.page_size)
                     and max(s.length for s in ctx.spans) >= TENSOR_CORE_MIN_ROWS):
                 # long portions go to the tensor cores in tiles of 128 rows; short ones stay on CUDA cores
-                items = ctx.attention_items(TENSOR_CORE_MIN_ROWS, window)
+                blocks_per_sm = 2 if self.head_dim <= 64 else 1
+                items = ctx.attention_items(TENSOR_CORE_MIN_ROWS, window, None, self.num_heads,
+                                            blocks_per_sm * L.num_sms(ctx.device))
                 short_max = TENSOR_CORE_MIN_ROWS - 1
             bq = self.tile_height()
             plan = ("prefill", items, ctx.tiles(bq, max_len=short_max), bq)
