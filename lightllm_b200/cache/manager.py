@@ -67,6 +67,22 @@ class PagePool:
         self._owner[page] = owner
         return page
 
+    def take_many(self, owner: Hashable, n: int) -> List[int]:
+        """``n`` pages at once, in the order ``take`` would give them."""
+        if owner is None:
+            raise CacheError("a page needs an owner")
+        if n > len(self._free):
+            raise OutOfPages(f"{n} pages asked for, {len(self._free)} free")
+        if n <= 0:
+            return []
+        pages = self._free[-n:][::-1]
+        del self._free[-n:]
+        for page in pages:
+            if self._owner[page] is not None:
+                raise CacheError(f"page {page} on the free list is owned by {self._owner[page]!r}")
+            self._owner[page] = owner
+        return pages
+
     def give(self, page: int, owner: Hashable) -> None:
         if not 0 <= page < self.num_pages:
             raise CacheError(f"page {page} is outside the pool of {self.num_pages}")
@@ -176,9 +192,8 @@ class CacheManager:
             if need > pool.free_count:
                 raise OutOfPages(f"group {g}: {need} pages needed, {pool.free_count} free")
         for g, (need, pool) in enumerate(zip(needs, self.pools)):
-            for _ in range(need):
-                seq.tables[g].append(pool.take(seq_id))
             if need:
+                seq.tables[g].extend(pool.take_many(seq_id, need))
                 seq.version += 1
 
     def can_reserve_all(self, asks) -> bool:

@@ -38,6 +38,7 @@ class Model:
             [self.layers[e.layer].mixer.cache_spec() for e in self.run], [e.cache_of for e in self.run])
         self.dtype: Optional[torch.dtype] = None
         self.device: Optional[torch.device] = None
+        self._prepare_hooks = None
 
     def parts(self) -> List[Part]:
         out: List[Part] = []
@@ -60,12 +61,30 @@ class Model:
 
     def prepare(self, ctx, views) -> None:
         """Every part's ``prepare`` for this step, run entry by run entry (before the metadata copy)."""
-        for entry, view in zip(self.run, views):
-            self.layers[entry.layer].prepare(ctx, view)
-        for part in (self.embedding, self.final_norm, self.head):
-            hook = getattr(part, "prepare", None)
-            if hook is not None:
+        hooks = self._prepare_hooks
+        if hooks is None:
+            # the parts that have something to prepare (most do not override the hook), found once
+            from ..parts.base import Part
+            def own(part):
+                hook = getattr(part, "prepare", None)
+                return hook if hook is not None and getattr(type(part), "prepare", None) is not Part.prepare else None
+            hooks = []
+            for i, entry in enumerate(self.run):
+                block = self.layers[entry.layer]
+                for part in (block.norm1, block.norm2, block.ffn):
+                    if own(part):
+                        hooks.append((own(part), None))
+                if own(block.mixer):
+                    hooks.append((own(block.mixer), i))
+            for part in (self.embedding, self.final_norm, self.head):
+                if own(part):
+                    hooks.append((own(part), None))
+            self._prepare_hooks = hooks
+        for hook, run_index in hooks:
+            if run_index is None:
                 hook(ctx)
+            else:
+                hook(ctx, views[run_index])
 
     def graph_safe(self) -> bool:
         """Whether every part's forward only launches kernels whose arguments are fixed by the step's
