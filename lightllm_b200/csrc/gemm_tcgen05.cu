@@ -19,6 +19,8 @@
 // exit, frees its TMEM and returns; the host reports the flag as an error.
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include <mutex>
 #include <unordered_map>
 
@@ -442,13 +444,22 @@ __device__ __forceinline__ void epilogue_rope64_warp(const GemmParams& p, const 
 
 constexpr int P_THREADS = 64 + 256;      // TMA warp, MMA warp, eight epilogue warps (two per TMEM lane quarter)
 
-template <int EPI, int P_BN>
+// PAIR: two CTAs (a cluster of two) share a tile of 256 rows x 256 features: each loads its 128 rows of A and its half
+// of B, the first CTA issues tcgen05.mma.cta_group::2 over both, and each drains its own 128 x 256 accumulator.  A block of
+// K then costs a CTA 32 KB of operands for 512 cycles of tensor work, the 64 bytes per cycle an SM gets from L2, where
+// the single-CTA wide tile needs 96.
+template <int EPI, int P_BN, bool PAIR>
 __global__ void __launch_bounds__(P_THREADS, 1)
 gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                                const __grid_constant__ CUtensorMap map_out, const GemmParams p) {
-    constexpr int P_STAGES = P_BN == 256 ? 4 : 6;
+    static_assert(!PAIR || P_BN == 256, "a pair's tile is 256 features wide");
+    // KPS blocks of K share a stage (and a commit): the hand-over of a stage between the loading and the issuing thread
+    // costs about 150 cycles beyond the MMAs of one block of K, which a pair's smaller stages leave room to halve.
+    constexpr int KPS = PAIR ? 2 : 1;
+    constexpr int P_STAGES = PAIR ? 3 : (P_BN == 256 ? 4 : 6);
+    constexpr int ROWS_PER_TILE = PAIR ? 2 * TILE_M : TILE_M;
     constexpr uint32_t A_BYTES = TILE_M * TILE_K * 2;
-    constexpr uint32_t B_BYTES = P_BN * TILE_K * 2;
+    constexpr uint32_t B_BYTES = (PAIR ? P_BN / 2 : P_BN) * TILE_K * 2;
     constexpr uint32_t TMEM_COLS = 2 * P_BN;
     __shared__ __align__(8) uint64_t full_bar[P_STAGES];
     __shared__ __align__(8) uint64_t empty_bar[P_STAGES];
@@ -459,12 +470,15 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* a_tiles = smem;
-    uint8_t* b_tiles = smem + P_STAGES * A_BYTES;
-    uint8_t* out_tiles = b_tiles + P_STAGES * B_BYTES;       // eight staging tiles of 4 KB, one per epilogue warp
+    uint8_t* b_tiles = smem + P_STAGES * KPS * A_BYTES;
+    uint8_t* out_tiles = b_tiles + P_STAGES * KPS * B_BYTES;       // eight staging tiles of 4 KB, one per epilogue warp
     volatile int* abort_flag = &abort_s;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m_tiles = (p.M + TILE_M - 1) / TILE_M;
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0u;            // which CTA of the pair
+    const int first_item = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+    const int item_stride = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+    const int m_tiles = (p.M + ROWS_PER_TILE - 1) / ROWS_PER_TILE;
     const int n_tiles = (p.N + P_BN - 1) / P_BN;
     const int num_tiles = m_tiles * n_tiles;
     const int nkb = p.num_kb;
@@ -478,19 +492,18 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&acc_full[b], 1);
-            mbar_init(&acc_empty[b], 8);        // one arrival per epilogue warp
+            mbar_init(&acc_empty[b], PAIR ? 16 : 8);        // one arrival per epilogue warp (of both CTAs of a pair)
         }
         abort_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot_s)),
-                     "r"(TMEM_COLS)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (PAIR) tmem_alloc2(&tmem_slot_s, TMEM_COLS);
+        else tmem_alloc(&tmem_slot_s, TMEM_COLS);
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if (PAIR) cluster_sync_all();       // both CTAs' barriers exist before either signals the other's
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_slot_s;
     // Programmatic dependent launch: the kernel after this one may start its own set-up as blocks of this one leave;
@@ -500,30 +513,42 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
         if (lane == 0) {
             asm volatile("griddepcontrol.wait;" ::: "memory");
             int it = 0;                                  // k-blocks issued so far, over all tiles
-            for (int w = blockIdx.x; w < num_items; w += gridDim.x) {
+            // pair: both CTAs' loads complete on the first CTA's barrier, which that CTA arms for both
+            const uint32_t full_of_first = PAIR ? mapa_u32(smem_u32(&full_bar[0]), 0) : 0u;
+            for (int w = first_item; w < num_items; w += item_stride) {
                 const int t = w / splits, ks = w - t * splits;
-                const int a_row0 = (t % m_tiles) * TILE_M, b_row0 = (t / m_tiles) * P_BN;
+                const int a_row0 = (t % m_tiles) * ROWS_PER_TILE + (int)rank * TILE_M;
+                const int b_row0 = (t / m_tiles) * P_BN + (PAIR ? (int)rank * (P_BN / 2) : 0);
                 const int kb0 = ks * p.kb_per_split, kb1 = min(nkb, kb0 + p.kb_per_split);
                 bool ok = true;
-                for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                for (int kb = kb0; kb < kb1; kb += KPS, ++it) {
                     const int s = it % P_STAGES;
                     ok = mbar_wait(&empty_bar[s], ((it / P_STAGES) & 1) ^ 1, abort_flag);
                     if (!ok) break;
-                    mbar_expect_tx(&full_bar[s], A_BYTES + B_BYTES);
-                    tma_load_2d(a_tiles + s * A_BYTES, &map_a, kb * TILE_K, a_row0, &full_bar[s]);
-                    tma_load_2d(b_tiles + s * B_BYTES, &map_b, kb * TILE_K, b_row0, &full_bar[s]);
+                    if (PAIR) {
+                        const int nk = min(KPS, kb1 - kb);
+                        if (rank == 0) mbar_expect_tx(&full_bar[s], nk * 2 * (A_BYTES + B_BYTES));
+                        for (int j = 0; j < nk; ++j) {
+                            tma_load_2d_pair(a_tiles + (s * KPS + j) * A_BYTES, &map_a, (kb + j) * TILE_K, a_row0, full_of_first + s * 8);
+                            tma_load_2d_pair(b_tiles + (s * KPS + j) * B_BYTES, &map_b, (kb + j) * TILE_K, b_row0, full_of_first + s * 8);
+                        }
+                    } else {
+                        mbar_expect_tx(&full_bar[s], A_BYTES + B_BYTES);
+                        tma_load_2d(a_tiles + s * A_BYTES, &map_a, kb * TILE_K, a_row0, &full_bar[s]);
+                        tma_load_2d(b_tiles + s * B_BYTES, &map_b, kb * TILE_K, b_row0, &full_bar[s]);
+                    }
                 }
                 if (!ok) break;
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
+        if (lane == 0 && rank == 0) {
             // One thread issues every MMA, and a lone thread runs its scalar instructions one after the other at
             // their full latency: a few dozen of them per block of K cost more than the four MMAs themselves.  So
             // the loop carries what it needs in registers: the stage's two operand descriptors (advanced by
             // constants; the address field of a descriptor is the shared-memory address / 16), the addresses of its
             // barriers, its phase bit.
-            constexpr uint32_t idesc = idesc_bf16(TILE_M, P_BN);
+            constexpr uint32_t idesc = idesc_bf16(ROWS_PER_TILE, P_BN);
             constexpr uint64_t A_STEP = A_BYTES >> 4, B_STEP = B_BYTES >> 4, K_STEP = (UMMA_K * 2) >> 4;
             const uint64_t da0 = desc_kmajor(smem_u32(a_tiles)), db0 = desc_kmajor(smem_u32(b_tiles));
             const uint32_t full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]);
@@ -531,7 +556,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
             uint32_t full = full0, empty = empty0, phase = 0;
             int s = 0, local = 0;
             bool ok = true;
-            for (int w = blockIdx.x; w < num_items && ok; w += gridDim.x, ++local) {
+            for (int w = first_item; w < num_items && ok; w += item_stride, ++local) {
                 const int ks = w % splits;
                 const int kb0 = ks * p.kb_per_split, kb1 = min(nkb, kb0 + p.kb_per_split);
                 const int buf = local & 1;
@@ -539,24 +564,40 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t acc = tmem_base + buf * P_BN;
-                for (int kb = kb0; kb < kb1; ++kb) {
+                for (int kb = kb0; kb < kb1; kb += KPS) {
                     if (!mbar_try_wait_addr(full, phase)) {
                         ok = mbar_wait_addr(full, phase, abort_flag);
                         if (!ok) break;
                     }
-                    if (kb == kb0) umma_bf16_first(acc, da, db, idesc);
-                    else umma_bf16_acc(acc, da, db, idesc);
-                    umma_bf16_acc(acc, da + K_STEP, db + K_STEP, idesc);
-                    umma_bf16_acc(acc, da + 2 * K_STEP, db + 2 * K_STEP, idesc);
-                    umma_bf16_acc(acc, da + 3 * K_STEP, db + 3 * K_STEP, idesc);
-                    umma_commit_addr(empty);
+                    if (PAIR) {
+                        const int nk = min(KPS, kb1 - kb);
+                        for (int j = 0; j < nk; ++j) {
+                            const uint64_t ja = da + j * A_STEP, jb = db + j * B_STEP;
+                            if (kb == kb0 && j == 0) umma2_bf16_first(acc, ja, jb, idesc);
+                            else umma2_bf16_acc(acc, ja, jb, idesc);
+                            umma2_bf16_acc(acc, ja + K_STEP, jb + K_STEP, idesc);
+                            umma2_bf16_acc(acc, ja + 2 * K_STEP, jb + 2 * K_STEP, idesc);
+                            umma2_bf16_acc(acc, ja + 3 * K_STEP, jb + 3 * K_STEP, idesc);
+                        }
+                        umma2_commit_both(empty);            // frees the stage in both CTAs
+                    } else {
+                        if (kb == kb0) umma_bf16_first(acc, da, db, idesc);
+                        else umma_bf16_acc(acc, da, db, idesc);
+                        umma_bf16_acc(acc, da + K_STEP, db + K_STEP, idesc);
+                        umma_bf16_acc(acc, da + 2 * K_STEP, db + 2 * K_STEP, idesc);
+                        umma_bf16_acc(acc, da + 3 * K_STEP, db + 3 * K_STEP, idesc);
+                        umma_commit_addr(empty);
+                    }
                     if (++s == P_STAGES) {
                         s = 0; da = da0; db = db0; full = full0; empty = empty0; phase ^= 1;
                     } else {
-                        da += A_STEP; db += B_STEP; full += 8; empty += 8;
+                        da += KPS * A_STEP; db += KPS * B_STEP; full += 8; empty += 8;
                     }
                 }
-                if (ok) umma_commit(&acc_full[buf]);
+                if (ok) {
+                    if (PAIR) umma2_commit_both(smem_u32(&acc_full[buf]));
+                    else umma_commit(&acc_full[buf]);
+                }
             }
         }
     } else {
@@ -569,10 +610,11 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
         const bool staged = p.tma_out != 0 && EPI != EPI_ROPE64 && (EPI != LLB_EPI_SWIGLU || P_BN == 256);
         uint8_t* my_stage = out_tiles + (warp - 2) * 4096;
         asm volatile("griddepcontrol.wait;" ::: "memory");
-        for (int w = blockIdx.x; w < num_items; w += gridDim.x, ++local) {
+        const uint32_t acc_empty_of_first = PAIR ? mapa_u32(smem_u32(&acc_empty[0]), 0) : 0u;
+        for (int w = first_item; w < num_items; w += item_stride, ++local) {
             const int t = w / splits;
             const int buf = local & 1;
-            const int a_row0 = (t % m_tiles) * TILE_M, b_row0 = (t / m_tiles) * P_BN;
+            const int a_row0 = (t % m_tiles) * ROWS_PER_TILE + (int)rank * TILE_M, b_row0 = (t / m_tiles) * P_BN;
             if (!mbar_wait(&acc_full[buf], (local >> 1) & 1, abort_flag)) break;      // uniform over the warp
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             if (splits == 2) {
@@ -712,7 +754,8 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) {
-                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[buf])) : "memory");
+                if (PAIR) mbar_arrive_cluster(acc_empty_of_first + buf * 8);      // the pair's accumulators are drained together
+                else asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[buf])) : "memory");
             }
         }
     }
@@ -720,10 +763,12 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
     if (warp >= 2 && lane == 0) tma_store_wait_all();       // this warp's TMA stores have been written
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if (PAIR) cluster_sync_all();       // neither CTA leaves (or frees tensor memory) while the other may still use it
     if (abort_s && threadIdx.x == 0 && p.error_flag) atomicExch(p.error_flag, 5);
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        if (PAIR) tmem_dealloc2(tmem_base, TMEM_COLS);
+        else tmem_dealloc(tmem_base, TMEM_COLS);
     }
 }
 
@@ -790,15 +835,16 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, di
     return llb_check_launch("gemm_tcgen05");
 }
 
-template <int EPI, int P_BN>
+template <int EPI, int P_BN, bool PAIR = false>
 int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const GemmParams& p,
                       cudaStream_t stream) {
-    constexpr int P_STAGES = P_BN == 256 ? 4 : 6;
-    constexpr size_t smem = (size_t)P_STAGES * (TILE_M * TILE_K * 2 + P_BN * TILE_K * 2) + 8 * 4096 + 1024;
+    constexpr int KPS = PAIR ? 2 : 1;
+    constexpr int P_STAGES = PAIR ? 3 : (P_BN == 256 ? 4 : 6);
+    constexpr size_t smem = (size_t)P_STAGES * KPS * (TILE_M * TILE_K * 2 + (PAIR ? P_BN / 2 : P_BN) * TILE_K * 2) + 8 * 4096 + 1024;
     static bool configured = false;
     static int num_sms = 0;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<EPI, P_BN>,
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<EPI, P_BN, PAIR>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return llb_fail("gemm_tcgen05: cannot opt in to %zu bytes of shared memory: %s", smem,
                                               cudaGetErrorString(e));
@@ -807,24 +853,39 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const CUtens
         cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
         configured = true;
     }
-    const int tiles = llb_ceil_div(p.M, TILE_M) * llb_ceil_div(p.N, P_BN) * p.splits;
-    const int grid = tiles < num_sms ? tiles : num_sms;
+    const int tiles = llb_ceil_div(p.M, PAIR ? 2 * TILE_M : TILE_M) * llb_ceil_div(p.N, P_BN) * p.splits;
+    const int units = PAIR ? num_sms / 2 : num_sms;              // blocks, or pairs of blocks
+    const int grid = (tiles < units ? tiles : units) * (PAIR ? 2 : 1);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(P_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 2;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_persistent_kernel<EPI, P_BN>, ma, mb, mo, p);
+    cfg.numAttrs = PAIR ? 2 : 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_persistent_kernel<EPI, P_BN, PAIR>, ma, mb, mo, p);
     if (e != cudaSuccess) return llb_fail("gemm_tcgen05: launch failed: %s", cudaGetErrorString(e));
     return llb_check_launch("gemm_tcgen05_persistent");
 }
 
-template <int P_BN>
+// LLB_GEMM_PAIR=0 in the environment keeps the single-CTA tiles (for comparisons).
+bool pair_tiles_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("LLB_GEMM_PAIR");
+        on = (e && e[0] == '0') ? 0 : 1;
+    }
+    return on == 1;
+}
+
+template <int P_BN, bool PAIR = false>
 int dispatch_persistent(int epi, const CUtensorMap& ma, const CUtensorMap& mb, GemmParams p, cudaStream_t s) {
     // The output's tensor map for the staged epilogue: rows of 128 bytes (32 floats or 64 bf16) x 32 rows, 128-byte
     // swizzle.  Outputs whose base or row pitch is not a multiple of 16 bytes keep the direct stores.
@@ -849,10 +910,10 @@ int dispatch_persistent(int epi, const CUtensorMap& ma, const CUtensorMap& mb, G
         }
     }
     switch (epi) {
-        case LLB_EPI_STORE: return launch_persistent<LLB_EPI_STORE, P_BN>(ma, mb, mo, p, s);
-        case LLB_EPI_STORE_F32: return launch_persistent<LLB_EPI_STORE_F32, P_BN>(ma, mb, mo, p, s);
-        case LLB_EPI_RESIDUAL: return launch_persistent<LLB_EPI_RESIDUAL, P_BN>(ma, mb, mo, p, s);
-        case LLB_EPI_SWIGLU: return launch_persistent<LLB_EPI_SWIGLU, P_BN>(ma, mb, mo, p, s);
+        case LLB_EPI_STORE: return launch_persistent<LLB_EPI_STORE, P_BN, PAIR>(ma, mb, mo, p, s);
+        case LLB_EPI_STORE_F32: return launch_persistent<LLB_EPI_STORE_F32, P_BN, PAIR>(ma, mb, mo, p, s);
+        case LLB_EPI_RESIDUAL: return launch_persistent<LLB_EPI_RESIDUAL, P_BN, PAIR>(ma, mb, mo, p, s);
+        case LLB_EPI_SWIGLU: return launch_persistent<LLB_EPI_SWIGLU, P_BN, PAIR>(ma, mb, mo, p, s);
     }
     return llb_fail("gemm_tcgen05: unknown epilogue %d", epi);
 }
@@ -920,8 +981,14 @@ LLB_EXPORT int llb_gemm_tcgen05(const void* A, const void* W, const float* bias,
     p.splits = split_k;
     p.partials = partials;
     p.counters = counters;
-    // A tensor-core instruction over 128 features takes as long as one over 256, so the wide tile wins wherever
-    // its padding of N costs little, and always when K is split (few tiles are what splitting is for).
+    // Many rows and many features: pairs of CTAs on tiles of 256 x 256, each CTA loading its own rows and half of
+    // the weights' tile.
+    if (split_k == 1 && N >= 2048 && M >= 512 && pair_tiles_enabled()) {
+        if ((rc = make_map(W, N, K, 128, &mb))) return rc;
+        return dispatch_persistent<256, true>(epilogue, ma, mb, p, stream);
+    }
+    // The wide tile wins wherever its padding of N costs little, and always when K is split (few tiles are what
+    // splitting is for).
     if (N >= 2048 || (split_k > 1 && N > 128)) {
         if ((rc = make_map(W, N, K, 256, &mb))) return rc;
         return dispatch_persistent<256>(epilogue, ma, mb, p, stream);

@@ -196,6 +196,67 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&r)[32]) {
     tmem_wait_ld();
 }
 
+// ---- A pair of CTAs (a cluster of two) working on one tile: tcgen05 with cta_group::2 ----------------------------
+// The MMA is issued by one thread of the pair's first CTA and reads each CTA's own A rows and each CTA's half of B
+// from the same shared-memory offsets; each CTA's accumulator rows land in its own tensor memory (allocated by a warp
+// of each CTA together, at the same address).  TMA loads of either CTA may complete on a barrier of the other.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// The shared::cluster address of `local_addr` (a shared-memory address of this CTA) in the CTA of rank `rank`.
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t local_addr, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    return remote;
+}
+// Every thread of every CTA of the cluster arrives and waits (a hardware barrier without a time limit: every path
+// through a kernel passes it the same number of times).
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// A TMA tile load into this CTA's shared memory that completes on a barrier given by its shared::cluster address
+// (this CTA's or its peer's).  No multicast.
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int x, int y, uint32_t bar_cluster_addr) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster_addr), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void umma2_bf16_acc(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.eq.u32 p, 0, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc)
+        : "memory");
+}
+__device__ __forceinline__ void umma2_bf16_first(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.u32 p, 0, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc)
+        : "memory");
+}
+// The commit arrives on the barrier at this shared-memory offset in both CTAs of the pair.
+__device__ __forceinline__ void umma2_commit_both(uint32_t bar_addr) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar_addr), "h"((unsigned short)3) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t* slot, uint32_t cols) {       // by one warp of each CTA of the pair
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t base, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(cols) : "memory");
+}
+
 // Programmatic dependent launch.  wait: all grids this one depends on have completed and their writes
 // are visible.  launch_dependents: the next grid of the stream may start its own preamble.
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
