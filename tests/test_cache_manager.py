@@ -136,3 +136,17 @@ def test_random_orders_of_requests_keep_the_invariants(seed):
     m.check()
     assert m.free_pages(0) == 24 and m.free_pages(1) == 9 and m.free_slots == 4
     assert slots_seen <= {0, 1, 2, 3} and next_id > 4          # slots were used again
+
+
+def test_pages_taken_in_one_slice_come_in_the_order_of_single_takes():
+    a, b = PagePool(10), PagePool(10)
+    a.take("w"), b.take("w")
+    singles = [a.take("x") for _ in range(4)]
+    assert b.take_many("x", 4) == singles and b.take_many("x", 0) == []
+    assert a.free_count == b.free_count == 5
+    with pytest.raises(OutOfPages):
+        b.take_many("y", 6)
+    assert b.free_count == 5                       # nothing was taken
+    for page in singles:
+        b.give(page, "x")
+    b.check()

@@ -174,3 +174,47 @@ def test_random_workloads_finish_and_leak_nothing(seed):
         assert r.state == FINISHED and r.finish_reason in ("length", "too_long", "out_of_pages")
         if r.finish_reason == "length":
             assert len(r.output_tokens) == r.max_new_tokens
+
+
+def test_a_step_can_be_decided_before_the_last_one_is_read():
+    """The accounting in two halves: after ``advance`` (tokens in the cache) the next decode step can be decided,
+    ``commit`` adds the sampled tokens later; a request that ends on an end-of-sequence id drops the token of the
+    step that was launched ahead; steps that could end a request by length are never launched ahead."""
+    m = manager(50)
+    s = Scheduler(m, 16, 64)
+    s.add_request(Request(0, [1] * 5, max_new_tokens=6, eos_token_id=99))
+    s.add_request(Request(1, [2] * 7, max_new_tokens=20, eos_token_id=99))
+
+    def launch():
+        st = s.step()
+        s.cache.reserve_all((e.request.id, e.num_tokens) for e in st.entries)
+        for e in st.entries:
+            s.cache.advance(e.request.id, e.num_tokens)
+        s.advance(st)
+        return st
+
+    first = launch()                                     # both prompts whole, both want logits
+    assert not s.can_decode_ahead(first)                 # a prompt step is read at once
+    assert s.commit(first, {0: 10, 1: 11}) == []
+    st1 = launch()                                       # decode step 1
+    assert s.can_decode_ahead(st1)
+    st2 = launch()                                       # decided and launched before st1's tokens are known
+    assert [e.start_pos for e in st2.entries] == [e.start_pos + 1 for e in st1.entries]
+    assert s.commit(st1, {0: 12, 1: 99}) != []           # request 1 ends on its end-of-sequence id ...
+    assert s.finished[1].output_tokens == [11, 99]
+    assert not s.can_decode_ahead(st2)                   # ... so the batch has changed
+    assert s.commit(st2, {0: 13, 1: 55}) == []           # its token of the step launched ahead is dropped
+    assert s.finished[1].output_tokens == [11, 99] and s.running[0].output_tokens == [10, 12, 13]
+    st3 = launch()
+    assert s.can_decode_ahead(st3)                       # it samples the 4th of 6 tokens: one more step is safe
+    st4 = launch()
+    s.commit(st3, {0: 14})
+    assert s.can_decode_ahead(st4)                       # the 5th; the step after it samples the last
+    st5 = launch()
+    s.commit(st4, {0: 15})
+    assert not s.can_decode_ahead(st5)                   # the request ends by length with st5's token
+    done = s.commit(st5, {0: 16})
+    assert [r.id for r in done] == [0] and s.finished[0].finish_reason == "length"
+    assert s.finished[0].output_tokens == [10, 12, 13, 14, 15, 16]
+    assert m.free_pages() == 50
+    m.check()

@@ -1,0 +1,73 @@
+"""The step context on the host (no GPU): index arrays staged behind the step's metadata, tiles, and the work items
+of the tensor-core attention with their adaptive piece length."""
+import numpy as np
+import torch
+
+from lightllm_b200.engine.batch import Span, StepContext
+
+
+def context(spans, staging_words=0):
+    ctx = StepContext()
+    ctx.device = torch.device("cpu")
+    ctx.spans = [Span(i, i, start, length, row) for i, (start, length, row) in enumerate(spans)]
+    n = len(spans)
+    ctx.iota = torch.arange(n, dtype=torch.int32)
+    ctx.zeros = torch.zeros(n, dtype=torch.int32)
+    if staging_words:
+        host = np.zeros(staging_words + 7, dtype=np.int32)
+        dev = torch.from_numpy(host)                 # on the CPU the "copy" is the same memory
+        ctx._staging = [host, dev, 7, staging_words + 7]
+        ctx._host, ctx._dev = host, dev
+    return ctx
+
+
+def test_staged_arrays_lie_behind_each_other_and_name_their_shapes():
+    ctx = context([(0, 5, 0)], staging_words=20)
+    a = ctx.stage(np.arange(6, dtype=np.int32).reshape(2, 3))
+    b = ctx.stage(np.asarray([9, 8, 7], dtype=np.int32))
+    assert a.shape == (2, 3) and a.data_ptr() == ctx._dev.data_ptr() + 7 * 4 and b.data_ptr() == ctx._dev.data_ptr() + 13 * 4
+    assert ctx._host[7:16].tolist() == [0, 1, 2, 3, 4, 5, 9, 8, 7] and ctx.staged_words == 9
+    assert ctx.shape_key == [(2, 3), (3,)] and not ctx.late_uploads
+    big = ctx.stage(np.zeros(30, dtype=np.int32))           # no room left: it goes up on its own
+    assert ctx.late_uploads and big.numel() == 30 and ctx._staging[2] == 16
+    late = context([(0, 5, 0)])                              # after the copy (no staging): the same
+    assert late.stage(np.ones(3, dtype=np.int32)).tolist() == [1, 1, 1] and late.late_uploads
+
+
+def test_tiles_do_not_cross_spans():
+    ctx = context([(0, 5, 0), (10, 1, 5), (3, 40, 6)], staging_words=200)
+    ts, tq, n = ctx.tiles(16)
+    assert n == 5 and ts.tolist() == [0, 1, 2, 2, 2] and tq.tolist() == [0, 0, 0, 16, 32]
+    ts, tq, n = ctx.tiles(16, max_len=5)
+    assert n == 2 and ts.tolist() == [0, 1]
+    assert ctx.tiles(64)[2] == 3 and ctx.tiles(64)[0] is ctx.iota          # one tile per span: the ready-made arrays
+    assert ctx.tiles(16, min_len=100)[2] == 0
+
+
+def test_attention_items_cover_every_key_tile_once():
+    ctx = context([(0, 1000, 0), (700, 40, 1000), (3, 20, 1040)], staging_words=4000)
+    for window, chunk in ((0, 1), (0, 2), (0, 4), (300, 2), (0, None)):
+        ts, tq, n, cut = ctx.attention_items(32, window, chunk, heads=6, slots=8)
+        k0, nk, part, nparts = cut[0], cut[1], cut[2], cut[3]
+        seen = {}
+        for i in range(n):
+            key = (int(ts[i]), int(tq[i]))
+            seen.setdefault(key, []).append((int(k0[i]), int(nk[i]), int(part[i])))
+        for (span, q0), pieces in seen.items():
+            s = ctx.spans[span]
+            assert s.length >= 32
+            pos0 = s.start + q0
+            hi = pos0 + min(128, s.length - q0)
+            lo = max(0, pos0 - window + 1) if window else 0
+            want = -(-(hi - (lo // 128) * 128) // 128)
+            pieces.sort()
+            assert pieces[0][0] == 0 and sum(p[1] for p in pieces) == want
+            for (a, an, _), (b, _, _) in zip(pieces, pieces[1:]):
+                assert a + an == b
+            assert (len(pieces) == 1) == (pieces[0][2] == -1)          # only cut rows have partial results
+        assert sorted(seen) == sorted((i, q0) for i, s in enumerate(ctx.spans) if s.length >= 32
+                                      for q0 in range(0, s.length, 128))
+        assert nparts == sum(len(p) for p in seen.values() if len(p) > 1)
+    # the adaptive piece: 6 heads x 43 tiles over 8 resident blocks is 33 tiles each, so pieces of the cap, 16
+    ts, tq, n, cut = ctx.attention_items(32, 0, None, heads=6, slots=8)
+    assert int(cut[1].max()) <= 16 and n == len(set(zip(ts.tolist(), tq.tolist(), cut[0].tolist())))
