@@ -152,8 +152,8 @@ __device__ __forceinline__ void named_barrier(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
-// A persistent block: it takes the work items blockIdx.x, blockIdx.x + gridDim.x, ... (item = query tile x head,
-// heads fastest, so that neighbouring blocks read the same keys) and keeps three roles busy:
+// A persistent block: it takes one work item of every round of gridDim.x items (item = query tile x head, heads
+// fastest, so that neighbouring blocks read the same keys) and keeps three roles busy:
 //   warp 9   loader: Q of the next item and the key/value tiles, two stages ahead, across item boundaries
 //   warp 8   issues the tensor-core instructions: S of tile j+1 right after P V of tile j
 //   warps 0-7  softmax, two threads per query row
@@ -216,6 +216,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     // this one must have completed.
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int total = p.num_items;
+    // The items come longest first.  Dealt round-robin, the blocks that got the longest items of one round would also
+    // get the longest of the next; so every other round is dealt backwards, and a block's load stays near the mean.
+    auto item_index = [&](int round) {
+        return round * (int)gridDim.x + ((round & 1) ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x);
+    };
     const int group = p.Hq / p.Hkv;
     constexpr uint32_t IDESC_S = idesc_bf16(BQ, BKV, 0);
     constexpr uint32_t IDESC_PV = idesc_bf16(BQ, HD, 1);
@@ -225,7 +230,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         // ---- loader ------------------------------------------------------------------------------
         bool ok = true;
         uint32_t n_kv = 0, n_item = 0;
-        for (int idx = blockIdx.x; idx < total; idx += gridDim.x) {
+        for (int round = 0; round * (int)gridDim.x < total; ++round) {
+            const int idx = item_index(round);
+            if (idx >= total) continue;
             const Item it = make_item(p, idx);
             if (it.ntiles <= 0) continue;        // cannot happen with the lists the engine makes; every role skips it alike
             const int kvh = it.head / group;
@@ -279,7 +286,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                               desc_kmajor(smem_u32(k_s + (st * KB + kb) * TILE_BYTES) + k * 32), IDESC_S,
                               (kb > 0 || k > 0) ? 1u : 0u);
         };
-        for (int idx = blockIdx.x; idx < total; idx += gridDim.x) {
+        for (int round = 0; round * (int)gridDim.x < total; ++round) {
+            const int idx = item_index(round);
+            if (idx >= total) continue;
             const Item it = make_item(p, idx);
             if (it.ntiles <= 0) continue;
             ok = mbar_wait(bar_q_full, n_item & 1, abort_flag) && ok;
@@ -328,7 +337,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         constexpr int HO = HD / 2;                  // output dimensions of this thread
         bool ok = true;
         uint32_t n_s = 0, n_item = 0;
-        for (int idx = blockIdx.x; idx < total; idx += gridDim.x) {
+        for (int round = 0; round * (int)gridDim.x < total; ++round) {
+            const int idx = item_index(round);
+            if (idx >= total) continue;
             const Item it = make_item(p, idx);
             if (it.ntiles <= 0) continue;
             const int qpos = it.pos0 + r;
