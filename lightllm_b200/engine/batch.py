@@ -135,36 +135,30 @@ class StepContext:
         hit = self._tiles.get(key)
         if hit is not None:
             return hit
-        if chunk_tiles is None:
-            total = 0
-            for s in self.spans:
-                if s.length < min_len:
-                    continue
-                for q0 in range(0, s.length, 128):
-                    pos0 = s.start + q0
-                    hi = pos0 + min(128, s.length - q0)
-                    lo = max(0, pos0 - window + 1) if window > 0 else 0
-                    total += -(-(hi - (lo // 128) * 128) // 128)
-            chunk_tiles = min(16, max(4, -(-total * heads // max(1, slots))))
-        items, merges, parts = [], [], 0
+        # the row tiles (span, first row, key tiles) of the spans that take part
+        rows = []
         for i, s in enumerate(self.spans):
             if s.length < min_len:
                 continue
             for q0 in range(0, s.length, 128):
-                nrows = min(128, s.length - q0)
                 pos0 = s.start + q0
-                hi = pos0 + nrows
-                lo = max(0, pos0 - window + 1) if window > 0 else 0
-                ntiles = -(-(hi - (lo // 128) * 128) // 128)
-                if ntiles <= chunk_tiles + 1:
-                    items.append((ntiles, i, q0, 0, ntiles, -1))
-                    continue
-                nchunks = -(-ntiles // chunk_tiles)
-                merges.append((i, q0, parts, nchunks))
-                for c in range(nchunks):
-                    nk = min(chunk_tiles, ntiles - c * chunk_tiles)
-                    items.append((nk, i, q0, c * chunk_tiles, nk, parts + c))
-                parts += nchunks
+                hi = pos0 + 128 if q0 + 128 <= s.length else s.start + s.length
+                lo = pos0 - window + 1 if window > 0 and pos0 >= window else 0
+                rows.append((i, q0, -(-(hi - (lo // 128) * 128) // 128)))
+        if chunk_tiles is None:
+            total = sum(r[2] for r in rows)
+            chunk_tiles = min(16, max(4, -(-total * heads // max(1, slots))))
+        items, merges, parts = [], [], 0
+        for i, q0, ntiles in rows:
+            if ntiles <= chunk_tiles + 1:
+                items.append((ntiles, i, q0, 0, ntiles, -1))
+                continue
+            nchunks = -(-ntiles // chunk_tiles)
+            merges.append((i, q0, parts, nchunks))
+            for c in range(nchunks):
+                nk = min(chunk_tiles, ntiles - c * chunk_tiles)
+                items.append((nk, i, q0, c * chunk_tiles, nk, parts + c))
+            parts += nchunks
         items.sort(key=lambda t: -t[0])
         if not items:
             hit = (self.iota, self.zeros, 0, None)

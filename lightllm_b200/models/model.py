@@ -68,17 +68,21 @@ class Model:
             def own(part):
                 hook = getattr(part, "prepare", None)
                 return hook if hook is not None and getattr(type(part), "prepare", None) is not Part.prepare else None
-            hooks = []
+            hooks, keys = [], set()
+
+            def add(part, run_index):
+                key = getattr(part, "prepare_key", None)
+                if own(part) and (key is None or key not in keys):
+                    hooks.append((own(part), run_index))
+                    if key is not None:
+                        keys.add(key)         # parts with equal keys prepare the same things: once is enough
             for i, entry in enumerate(self.run):
                 block = self.layers[entry.layer]
                 for part in (block.norm1, block.norm2, block.ffn):
-                    if own(part):
-                        hooks.append((own(part), None))
-                if own(block.mixer):
-                    hooks.append((own(block.mixer), i))
+                    add(part, None)
+                add(block.mixer, i)
             for part in (self.embedding, self.final_norm, self.head):
-                if own(part):
-                    hooks.append((own(part), None))
+                add(part, None)
             self._prepare_hooks = hooks
         for hook, run_index in hooks:
             if run_index is None:

@@ -11,7 +11,7 @@ from ..config import PartSpec, part_class, register_part
 from ..csrc import ops
 from ..weights import WeightSpec
 from . import linear as L
-from .base import CacheView, LazyNorm, Mixer
+from .base import CacheView, LazyNorm, Mixer, Part
 
 # Shared memory budget per block used to pick the tile height of the CUDA-core kernel.
 _SMEM_BUDGET = 100 * 1024
@@ -222,6 +222,17 @@ class AttentionMixer(Mixer):
             plan = ("prefill", items, ctx.tiles(bq, max_len=short_max), bq)
         ctx.memo[key] = plan
         return plan
+
+    @property
+    def prepare_key(self):
+        """What the step's plan and rotary table depend on; attention layers that agree in it prepare once."""
+        pos_key = ()
+        if getattr(type(self.position), "prepare", None) is not Part.prepare:
+            # a position encoding with a preparation of its own must say what it depends on, or runs every time
+            pos_key = getattr(self.position, "prepare_key", None)
+            if pos_key is None:
+                return None
+        return ("attention", self.num_heads, self.num_kv_heads, self.head_dim, self.window or 0, pos_key)
 
     def prepare(self, ctx, cache=None) -> None:
         self._plan(ctx, ctx.dtype)

@@ -52,7 +52,13 @@ class Part:
     def prepare(self, ctx, cache=None) -> None:
         """Called for every run entry before the step's metadata is copied to the device: the place to make
         index arrays with ``ctx.stage`` / ``ctx.tiles`` so that they share that copy (and, for CUDA graphs,
-        to append to ``ctx.shape_key`` whatever else the launches will depend on)."""
+        to append to ``ctx.shape_key`` whatever else the launches will depend on).
+
+        A part whose preparation only depends on its own constants (not on its cache planes) may set
+        ``prepare_key`` to a hashable value of them: of the parts of a model with equal keys only the first is
+        called in a step."""
+
+    prepare_key = None
 
 
 class LazyNorm:

@@ -71,3 +71,22 @@ def test_attention_items_cover_every_key_tile_once():
     # the adaptive piece: 6 heads x 43 tiles over 8 resident blocks is 33 tiles each, so pieces of the cap, 16
     ts, tq, n, cut = ctx.attention_items(32, 0, None, heads=6, slots=8)
     assert int(cut[1].max()) <= 16 and n == len(set(zip(ts.tolist(), tq.tolist(), cut[0].tolist())))
+
+
+def test_layers_that_prepare_the_same_things_prepare_once(tmp_path):
+    """Attention layers with equal heads, window and position encoding share one plan per step: only the first of
+    them is called.  Tiny C has a full layer and two windowed ones, so two calls; tiny A one."""
+    import json
+    from lightllm_b200.config import load_config, model_spec_for
+    from lightllm_b200.models.model import Model
+    from tests.tiny_configs import config
+    for name, want in (("A", 1), ("C", 2)):
+        d = tmp_path / name
+        d.mkdir()
+        (d / "config.json").write_text(json.dumps(config(name)))
+        model = Model(model_spec_for(load_config(str(d))))
+        ctx = context([(0, 5, 0), (7, 1, 5)], staging_words=400)
+        ctx.dtype, ctx.page_size, ctx.max_pages, ctx.decode_only, ctx.T = torch.float32, 16, 32, False, 6
+        model.prepare(ctx, [None] * len(model.run))
+        assert len(model._prepare_hooks) == want
+        assert len([k for k in ctx.memo if k[0] == "attention_plan"]) == want
