@@ -17,7 +17,7 @@ from . import build as _build
 
 F32, BF16 = 0, 1
 EPI_STORE, EPI_STORE_F32, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
-ABI_VERSION = 14
+ABI_VERSION = 15
 
 _lib: Optional[ctypes.CDLL] = None
 
@@ -389,6 +389,11 @@ def paged_decode_mma(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
         _ptr(scratch), _stream()))
 
 
+# Where the blocks that share a long row of logits meet (a 64-bit slot and a counter per row), per device.
+_ARGMAX_ROWS = 4096
+_argmax_scratch = {}
+
+
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
     """out[r] = first index of the largest logit of row r.  logits float32 [R,V]."""
     R, V = logits.shape
@@ -396,8 +401,12 @@ def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
         raise KernelError("argmax: logits must be float32 with unit inner stride")
     if not logits.is_cuda:
         raise KernelError("argmax: logits are not on a CUDA device; there is no CPU path")
+    key = logits.device.index or 0
+    scratch = _argmax_scratch.get(key)
+    if scratch is None:          # zero once: every launch leaves it zero
+        scratch = _argmax_scratch[key] = torch.zeros(3 * _ARGMAX_ROWS, dtype=torch.int32, device=logits.device)
     _check(lib().llb_argmax(ctypes.c_void_p(logits.data_ptr()), R, V, ctypes.c_longlong(logits.stride(0)),
-                            _i32(out, "out"), _stream()))
+                            _i32(out, "out"), _ptr(scratch), _ARGMAX_ROWS, _stream()))
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: Optional[torch.Tensor],

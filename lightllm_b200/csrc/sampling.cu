@@ -57,7 +57,8 @@ __device__ float block_max(float v, float* sh) {
 }
 
 // First index of the largest value of a row.
-__device__ int block_argmax(const float* x, int V, float* shf, int* shi) {
+// ``none`` is what a row without any value above -inf (or with NaNs only) gives.
+__device__ int block_argmax(const float* x, int V, float* shf, int* shi, int none = 0) {
     float best = -INFINITY;
     int bi = 0x7fffffff;
     for (int i = threadIdx.x; i < V; i += blockDim.x) {
@@ -83,7 +84,7 @@ __device__ int block_argmax(const float* x, int V, float* shf, int* shi) {
             const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
             if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
         }
-        if (lane == 0) shi[32] = (bi == 0x7fffffff) ? 0 : bi;
+        if (lane == 0) shi[32] = (bi == 0x7fffffff) ? none : bi;
     }
     __syncthreads();
     return shi[32];
@@ -96,6 +97,40 @@ __global__ void __launch_bounds__(THREADS) argmax_kernel(const float* __restrict
     const int r = blockIdx.x;
     const int idx = block_argmax(logits + (size_t)r * stride, V, shf, shi);
     if (threadIdx.x == 0) out[r] = idx;
+}
+
+// The same over a long row, by many blocks: block (s, r) takes the s-th piece of row r and offers its first maximum to
+// the row's slot as one 64-bit number (the value's ordered key above, 2^32 - 1 - index below: the larger value wins,
+// among equal values the smaller index) with an atomic maximum.  The block that counts itself last on the row's
+// counter writes the index and leaves slot and counter zero for the next launch.  A row without any value above
+// -inf offers nothing and gets index 0, as in the one-block kernel.
+constexpr int SPLIT_THREADS = 256;
+constexpr int SPLIT_ELEMS = 4096;            // elements of a row per block
+
+__global__ void __launch_bounds__(SPLIT_THREADS) argmax_split_kernel(const float* __restrict__ logits, int V, long long stride,
+                                                                     unsigned long long* __restrict__ slots,
+                                                                     int* __restrict__ counters, int* __restrict__ out) {
+    __shared__ float shf[33];
+    __shared__ int shi[33];
+    const int r = blockIdx.y;
+    const int begin = blockIdx.x * SPLIT_ELEMS;
+    const int n = min(SPLIT_ELEMS, V - begin);
+    const int idx = block_argmax(logits + (size_t)r * stride + begin, n, shf, shi, /*none=*/-1);
+    if (threadIdx.x == 0) {
+        if (idx >= 0) {
+            const float v = logits[(size_t)r * stride + begin + idx] + 0.0f;        // -0 counts as +0
+            const unsigned long long offer = ((unsigned long long)ordered_key(v) << 32) |
+                                             (unsigned long long)(0xffffffffu - (unsigned)(begin + idx));
+            atomicMax(slots + r, offer);
+        }
+        __threadfence();
+        if (atomicAdd(counters + r, 1) == (int)gridDim.x - 1) {
+            __threadfence();
+            const unsigned long long best = atomicExch(slots + r, 0ull);
+            out[r] = best == 0ull ? 0 : (int)(0xffffffffu - (unsigned)(best & 0xffffffffull));
+            atomicExch(counters + r, 0);
+        }
+    }
 }
 
 // params per row: temperature, top_p, min_p, uniform; top_k per row as int.
@@ -219,10 +254,19 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict
 
 }  // namespace
 
-// logits [R, V] float with row stride `stride` elements; out [R] int32.
-LLB_EXPORT int llb_argmax(const float* logits, int R, int V, long long stride, int* out, cudaStream_t stream) {
+// logits [R, V] float with row stride `stride` elements; out [R] int32.  scratch (or null): 3 * scratch_rows ints,
+// 8-byte aligned, zero on entry and left zero; with it, rows of 4 * 4096 elements or more are shared among blocks.
+LLB_EXPORT int llb_argmax(const float* logits, int R, int V, long long stride, int* out, int* scratch, int scratch_rows,
+                          cudaStream_t stream) {
     if (R == 0) return 0;
     LLB_REQUIRE(R > 0 && V > 0 && stride >= V, "argmax: bad sizes R=%d V=%d stride=%lld", R, V, stride);
+    if (scratch && R <= scratch_rows && R <= 65535 && V >= 4 * SPLIT_ELEMS && (uintptr_t)scratch % 8 == 0) {
+        unsigned long long* slots = (unsigned long long*)scratch;
+        int* counters = scratch + 2 * (size_t)scratch_rows;
+        argmax_split_kernel<<<dim3(llb_ceil_div(V, SPLIT_ELEMS), R), SPLIT_THREADS, 0, stream>>>(logits, V, stride, slots,
+                                                                                               counters, out);
+        return llb_check_launch("argmax");
+    }
     argmax_kernel<<<R, THREADS, 0, stream>>>(logits, V, stride, out);
     return llb_check_launch("argmax");
 }

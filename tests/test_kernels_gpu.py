@@ -565,17 +565,31 @@ def test_paged_decode_mma(ops, case, nsplit, spike):
     assert torch.allclose(got, ref, atol=2e-2, rtol=2e-2), f"max diff {float((got - ref).abs().max())}"
 
 
-def test_argmax_lowest_index_on_ties(ops):
-    V = 151937
-    x = rnd((5, V), torch.float32, 30)
-    x[0, 100] = x[0, 9000] = 50.0
+@pytest.mark.parametrize("V", [151937, 16384, 1003])      # long rows are shared among blocks, short ones are not
+def test_argmax_lowest_index_on_ties(ops, V):
+    x = rnd((9, V), torch.float32, 30)
+    x[0, 100] = x[0, 900] = 50.0
     x[1, V - 1] = 60.0
     x[2, :] = 1.0
-    out = torch.empty(5, dtype=torch.int32, device=dev())
-    ops.argmax(x, out)
-    ref = [int(np.argmax(r)) for r in x.cpu().numpy()]
-    assert out.cpu().tolist() == ref
-    assert out[0].item() == 100 and out[2].item() == 0
+    x[3, :] = float("-inf")                      # nothing above -inf: index 0
+    x[4, :] = -3.0
+    x[4, V // 2] = -0.0                          # the zeros are equal: the first of them
+    x[4, V - 7] = 0.0
+    x[5, :] = float("-inf")
+    x[5, V - 2] = -1e30
+    x[6, V // 3] = float("nan")                  # a NaN is never the largest
+    if V > 4096:
+        x[7, 4095] = x[7, 4096] = 70.0           # a tie across two blocks' pieces
+    out = torch.full((9,), -1, dtype=torch.int32, device=dev())
+    for _ in range(2):                           # the second run finds the meeting place clean
+        ops.argmax(x, out)
+        got = out.cpu().tolist()
+        ref = [int(np.argmax(np.nan_to_num(r, nan=-np.inf))) for r in x.cpu().numpy()]
+        assert got == ref
+        assert got[0] == 100 and got[2] == 0 and got[3] == 0 and got[4] == V // 2 and got[5] == V - 2
+        out.fill_(-1)
+    scratch = ops._argmax_scratch.get(dev().index or 0)
+    assert scratch is None or int(scratch.abs().max()) == 0
 
 
 @pytest.mark.parametrize("temperature,top_k,top_p,min_p", [(1.0, 0, 1.0, 0.0), (0.7, 40, 1.0, 0.0),
