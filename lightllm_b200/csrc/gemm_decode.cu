@@ -211,14 +211,16 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         const int k = (i * 32 + lane) * 4;       // 4 elements = half of a 16-byte chunk of the tile row
-                        if (k >= p.K || (k >> 6) < kb_begin || (k >> 6) >= kb_end) continue;
-                        float nw[4];
-                        if (p.norm_w_bf16) {
+                        if ((k >> 6) < kb_begin || (k >> 6) >= kb_end) continue;
+                        // columns from K to the end of the last tile are written as zeros: the weights there are the
+                        // copy's zero fill, but zero times whatever the shared memory held before need not be zero
+                        float nw[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                        if (k < p.K && p.norm_w_bf16) {
                             const uint2 u = *reinterpret_cast<const uint2*>((const __nv_bfloat16*)p.norm_w + k);
                             const float2 f0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
                             const float2 f1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
                             nw[0] = f0.x; nw[1] = f0.y; nw[2] = f1.x; nw[3] = f1.y;
-                        } else {
+                        } else if (k < p.K) {
                             const float4 c0 = *reinterpret_cast<const float4*>((const float*)p.norm_w + k);
                             nw[0] = c0.x; nw[1] = c0.y; nw[2] = c0.z; nw[3] = c0.w;
                         }
