@@ -96,16 +96,16 @@ class StepContext:
         self.late_uploads = True
         return torch.from_numpy(arr).to(self.device, non_blocking=False)
 
-    def tiles(self, bq: int, min_len: int = 1, max_len: Optional[int] = None):
+    def tiles(self, bq: int, min_len: int = 1, max_len: Optional[int] = None, select: Optional[tuple] = None):
         """Tiles of ``bq`` query rows, none crossing a span, over the spans whose length lies in
-        ``[min_len, max_len]``: ``(tile_span, tile_q0, count)`` as device int32 arrays.  Built once
-        per step for each choice."""
-        key = (bq, min_len, max_len)
+        ``[min_len, max_len]`` (of the spans ``select`` names by index, if given): ``(tile_span, tile_q0,
+        count)`` as device int32 arrays.  Built once per step for each choice."""
+        key = (bq, min_len, max_len, select)
         hit = self._tiles.get(key)
         if hit is not None:
             return hit
-        chosen = [(i, s) for i, s in enumerate(self.spans)
-                  if s.length >= min_len and (max_len is None or s.length <= max_len)]
+        chosen = [(i, self.spans[i]) for i in (range(len(self.spans)) if select is None else select)
+                  if self.spans[i].length >= min_len and (max_len is None or self.spans[i].length <= max_len)]
         if len(chosen) == len(self.spans) and bq >= max(s.length for s in self.spans):
             hit = (self.iota, self.zeros, len(self.spans))
         elif not chosen:
@@ -123,21 +123,22 @@ class StepContext:
         return hit
 
     def attention_items(self, min_len: int, window: int, chunk_tiles: Optional[int] = 4, heads: int = 1,
-                        slots: int = 1):
+                        slots: int = 1, select: Optional[tuple] = None):
         """Work items of the tensor-core attention kernel for the spans of at least ``min_len`` rows: tiles
         of 128 query rows whose key range (in tiles of 128 keys) is cut into pieces of ``chunk_tiles``, longest
         first, so that a long prompt's last rows do not set the kernel's time.  With ``chunk_tiles=None`` the
         piece is as long as the work allows: the tiles of all ``heads`` spread over ``slots`` resident blocks give
         each block so many tiles anyway, and shorter pieces would only add partial results to merge (between 4
-        and 16).  Returns ``(tile_span, tile_q0, count, cut)`` with ``cut`` as ``ops.paged_attention_tcgen05``
-        takes it."""
-        key = ("items", min_len, window, chunk_tiles, heads, slots)
+        and 16).  ``select`` names the spans by index instead of all of at least ``min_len`` rows.  Returns
+        ``(tile_span, tile_q0, count, cut)`` with ``cut`` as ``ops.paged_attention_tcgen05`` takes it."""
+        key = ("items", min_len, window, chunk_tiles, heads, slots, select)
         hit = self._tiles.get(key)
         if hit is not None:
             return hit
         # the row tiles (span, first row, key tiles) of the spans that take part
         rows = []
-        for i, s in enumerate(self.spans):
+        for i in (range(len(self.spans)) if select is None else select):
+            s = self.spans[i]
             if s.length < min_len:
                 continue
             for q0 in range(0, s.length, 128):

@@ -19,6 +19,9 @@ _SMEM_LIMIT = 200 * 1024
 # Portions of at least this many rows run on the tensor-core attention kernel (tiles of 128 rows).
 TENSOR_CORE_MIN_ROWS = 32
 FUSED_ROPE_MAX_ROWS = 16
+# From this many keys on, a portion of fewer than TENSOR_CORE_MIN_ROWS rows is better served by the tensor-core kernel
+# (or, without it, by the CUDA-core kernel row by row with the keys in pieces) than by one block walking all keys.
+MANY_KEYS = 512
 # Up to this many keys per request the decode attention's pieces are merged inside the kernel.
 CLUSTER_MERGE_MAX_KEYS = 8192
 # From this many rows on, heads of 64 get their rotation and cache write in the projection's tensor-core epilogue.
@@ -210,18 +213,51 @@ class AttentionMixer(Mixer):
                 nsplit = max(1, min(8, ops.decode_mma_cluster_splits(), resident, -(-span // 128)))
             plan = ("decode_mma" if mma else "decode_simt", ctx.tiles(1), nsplit)
         else:
-            items, short_max = None, None
-            if (bf16 and ops.attention_tcgen05_supports(self.head_dim, ctx.page_size)
-                    and max(s.length for s in ctx.spans) >= TENSOR_CORE_MIN_ROWS):
-                # long portions go to the tensor cores in tiles of 128 rows; short ones stay on CUDA cores
-                blocks_per_sm = 2 if self.head_dim <= 64 else 1
-                items = ctx.attention_items(TENSOR_CORE_MIN_ROWS, window, None, self.num_heads,
-                                            blocks_per_sm * L.num_sms(ctx.device))
-                short_max = TENSOR_CORE_MIN_ROWS - 1
-            bq = self.tile_height()
-            plan = ("prefill", items, ctx.tiles(bq, max_len=short_max), bq)
+            plan = self._plan_mixed(ctx, bf16, window)
         ctx.memo[key] = plan
         return plan
+
+    def _plan_mixed(self, ctx, bf16: bool, window: int):
+        """A step with portions of prompts, maybe beside decoded tokens.  Each span goes where its shape is served best:
+        portions of 32 rows or more, and shorter ones over many keys, to the tensor-core kernel in tiles of 128 rows;
+        single tokens to the decode kernel (its pieces along the keys merged in a cluster); the rest (everything in
+        float32) to the CUDA-core kernel, in tiles of rows, or row by row with the keys in pieces for few rows over many
+        keys."""
+        tc_ok = bf16 and ops.attention_tcgen05_supports(self.head_dim, ctx.page_size)
+        mma_ok = bf16 and ops.paged_decode_mma_supports(self.num_heads, self.num_kv_heads, self.head_dim)
+        tensor, single, rows, rest = [], [], [], []
+        rows_keys = 0
+        for i, s in enumerate(ctx.spans):
+            keys = s.start + s.length if window == 0 else min(s.start + s.length, window + s.length)
+            few = s.length < TENSOR_CORE_MIN_ROWS
+            if tc_ok and (not few or (s.length >= 2 and keys >= MANY_KEYS)):
+                tensor.append(i)
+            elif mma_ok and s.length == 1:
+                single.append(i)
+            elif few and keys >= MANY_KEYS:
+                rows.append(i)
+                rows_keys = max(rows_keys, keys)
+            else:
+                rest.append(i)
+        items = None
+        if tensor:
+            blocks_per_sm = 2 if self.head_dim <= 64 else 1
+            items = ctx.attention_items(1, window, None, self.num_heads, blocks_per_sm * L.num_sms(ctx.device),
+                                        select=tuple(tensor))
+        decode = None
+        if single:
+            bound = ctx.max_pages * ctx.page_size
+            span = bound if window == 0 else min(bound, window)
+            resident = 3 * L.num_sms(ctx.device) // (len(single) * self.num_kv_heads)
+            nsplit = max(1, min(8, ops.decode_mma_cluster_splits(), resident, -(-span // 128)))
+            decode = (ctx.tiles(1, select=tuple(single)), nsplit)
+        simt = []
+        if rows:         # few rows over many keys: row by row, each row's keys in pieces
+            simt.append((ctx.tiles(1, select=tuple(rows)), 1, max(2, min(16, -(-rows_keys // 256)))))
+        if rest:
+            bq = self.tile_height()
+            simt.append((ctx.tiles(bq, select=tuple(rest)), bq, 1))
+        return ("mixed", items, decode, simt)
 
     @property
     def prepare_key(self):
@@ -258,12 +294,17 @@ class AttentionMixer(Mixer):
         elif plan[0] == "decode_simt":
             self._simt(q, cache, out, plan[1], common, 1, plan[2])
         else:
-            _, items, tiles, bq = plan
+            _, items, decode, simt = plan
             if items is not None:
                 tile_span, tile_q0, ntiles, cut = items
                 ops.paged_attention_tcgen05(q, cache.k, cache.v, out, tile_span, tile_q0, ntiles, *common, cut=cut)
-            if tiles[2] > 0:
-                self._simt(q, cache, out, tiles, common, bq, 1)
+            if decode is not None:
+                (tile_span, tile_q0, ntiles), nsplit = decode
+                ops.paged_decode_mma(q, cache.k, cache.v, out, tile_span, tile_q0, ntiles, ctx.span_row, ctx.span_pos,
+                                     ctx.block_tables[g], ctx.max_pages, ctx.page_size, self.num_heads,
+                                     self.num_kv_heads, self.head_dim, window, self.scale, nsplit, None)
+            for tiles, bq, nsplit in simt:
+                self._simt(q, cache, out, tiles, common, bq, nsplit)
 
     def _simt(self, q, cache, out, tiles, common, bq, nsplit) -> None:
         tile_span, tile_q0, ntiles = tiles

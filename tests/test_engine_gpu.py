@@ -175,6 +175,39 @@ def test_long_decoding_and_first_tokens(tmp_path, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_step_with_every_kind_of_span(tmp_path, dtype):
+    """One step holds a decoded token over 700 keys, five rows of a prompt over 600 keys, a portion of 100 rows from
+    the start and a short new prompt: in bfloat16 they go to the decode kernel, to the tensor-core kernel (the five
+    rows too, where all keys are visible; to the CUDA-core kernel in the layer with the window of 150), and to the
+    CUDA-core kernel; in float32 the few rows over many keys are walked row by row in pieces.  Sharp attention, so a
+    key lost by any of them shows."""
+    d = model_dir(tmp_path, "D", seed=12, store="float32" if dtype == "float32" else "bfloat16", edit=sharpen(6.0))
+    cfg, w = P.read_model_dir(d)
+    V = cfg["vocab_size"]
+    rng = random.Random(13)
+    seqs = {n: [rng.randrange(V) for _ in range(L)] for n, L in (("a", 702), ("b", 640), ("c", 100), ("d", 7))}
+    ref = {n: P.plain_forward(cfg, w, s) for n, s in seqs.items()}
+    core = core_for(d, dtype, page=16, pages=120, max_seqs=4, max_tokens=1024)
+    for n in seqs:
+        core.open(n)
+    core.step([StepEntry("a", seqs["a"][:700], [])])
+    core.step([StepEntry("b", seqs["b"][:600], [])])
+    steps = [
+        [("a", 700, 1), ("b", 600, 5), ("c", 0, 100), ("d", 0, 7)],
+        [("a", 701, 1), ("b", 605, 35)],
+    ]
+    for step in steps:
+        lg = core.step([StepEntry(n, seqs[n][at: at + c], list(range(c))) for n, at, c in step]).float().cpu()
+        row = 0
+        for n, at, c in step:
+            err = (lg[row: row + c] - ref[n][at: at + c]).abs().max(dim=1).values
+            assert float(err.max()) <= ATOL[dtype], \
+                f"{dtype}: request {n}: first wrong position {at + int((err > ATOL[dtype]).nonzero()[0])}"
+            row += c
+    core.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "C"])
 def test_sharp_attention_over_far_keys_page_edges_and_reused_pages(tmp_path, name, dtype):
     d = model_dir(tmp_path, name, seed=8, store="float32" if dtype == "float32" else "bfloat16",
