@@ -30,6 +30,9 @@ class StepError(ValueError):
 class ModelRunner:
     """Owns the device-side step metadata and runs the model over a batch."""
 
+    # A mixed step's shape is captured into a graph when it comes for this many-th time.
+    MIXED_CAPTURE_AFTER = 6
+
     def __init__(self, model: Model, cache: CacheManager, max_batch_tokens: int, max_spans: Optional[int] = None,
                  use_cuda_graphs: bool = True, max_graphs: int = 64):
         if model.device is None or model.device.type != "cuda":
@@ -251,8 +254,12 @@ class ModelRunner:
             self._graph_seen[key] = seen
             if len(self._graph_seen) > 4096:              # shapes seen once and never again
                 self._graph_seen.clear()
-            if seen < 2:
-                return self.forward(ctx)          # first sight of a shape (also the warm-up)
+            # A capture costs the host about as much as four steps launched one by one.  The shapes of decoding
+            # batches and of a lone portion come again hundreds of times; a step that mixes several portions and
+            # tokens rarely meets its shape again, so such a shape must have come more often before it is captured.
+            settled = ctx.decode_only or ctx.num_spans == 1
+            if seen < (2 if settled else self.MIXED_CAPTURE_AFTER):
+                return self.forward(ctx)          # the first sights of a shape (also the warm-up)
             if len(self._graphs) >= self.max_graphs:      # the least recently used graph makes room
                 del self._graphs[next(iter(self._graphs))]
             before = ops.launch_count()

@@ -16,11 +16,14 @@ from .base import CacheView, LazyNorm, Mixer, Part
 # Shared memory budget per block used to pick the tile height of the CUDA-core kernel.
 _SMEM_BUDGET = 100 * 1024
 _SMEM_LIMIT = 200 * 1024
-# Portions of at least this many rows run on the tensor-core attention kernel (tiles of 128 rows).
-TENSOR_CORE_MIN_ROWS = 32
+# Portions of at least this many rows run on the tensor-core attention kernel (tiles of 128 rows, the rows beyond the
+# portion masked): one block of the CUDA-core kernel walking a portion's keys takes hundreds of microseconds from a
+# few hundred keys on, an item of the tensor-core kernel about two per 128 keys.
+TENSOR_CORE_MIN_ROWS = 2
 FUSED_ROPE_MAX_ROWS = 16
-# From this many keys on, a portion of fewer than TENSOR_CORE_MIN_ROWS rows is better served by the tensor-core kernel
-# (or, without it, by the CUDA-core kernel row by row with the keys in pieces) than by one block walking all keys.
+# Where the tensor-core kernels do not apply (float32, other head sizes): a portion of fewer than FEW_ROWS rows over
+# MANY_KEYS keys or more is walked row by row with each row's keys in pieces, not by one block per tile of rows.
+FEW_ROWS = 32
 MANY_KEYS = 512
 # Up to this many keys per request the decode attention's pieces are merged inside the kernel.
 CLUSTER_MERGE_MAX_KEYS = 8192
@@ -219,7 +222,7 @@ class AttentionMixer(Mixer):
 
     def _plan_mixed(self, ctx, bf16: bool, window: int):
         """A step with portions of prompts, maybe beside decoded tokens.  Each span goes where its shape is served best:
-        portions of 32 rows or more, and shorter ones over many keys, to the tensor-core kernel in tiles of 128 rows;
+        portions of two rows or more to the tensor-core kernel in tiles of 128 rows;
         single tokens to the decode kernel (its pieces along the keys merged in a cluster); the rest (everything in
         float32) to the CUDA-core kernel, in tiles of rows, or row by row with the keys in pieces for few rows over many
         keys."""
@@ -229,12 +232,11 @@ class AttentionMixer(Mixer):
         rows_keys = 0
         for i, s in enumerate(ctx.spans):
             keys = s.start + s.length if window == 0 else min(s.start + s.length, window + s.length)
-            few = s.length < TENSOR_CORE_MIN_ROWS
-            if tc_ok and (not few or (s.length >= 2 and keys >= MANY_KEYS)):
+            if tc_ok and s.length >= TENSOR_CORE_MIN_ROWS:
                 tensor.append(i)
             elif mma_ok and s.length == 1:
                 single.append(i)
-            elif few and keys >= MANY_KEYS:
+            elif s.length < FEW_ROWS and keys >= MANY_KEYS:
                 rows.append(i)
                 rows_keys = max(rows_keys, keys)
             else:

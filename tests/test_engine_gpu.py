@@ -92,6 +92,7 @@ def test_steps_replayed_from_graphs_match_steps_launched_one_by_one(tmp_path, dt
         core = core_for(d, dtype, page=PAGE_SIZE["A"], pages=40)
         core.runner.use_cuda_graphs = graphs and core.runner.use_cuda_graphs
         core.runner.max_graphs = 2
+        core.runner.MIXED_CAPTURE_AFTER = 2         # mixed shapes too at their second appearance (by default later)
         got = []
         for rnd_ in range(4):                       # the same schedule four times: every shape comes back
             for k in "abc":
