@@ -90,3 +90,40 @@ def test_layers_that_prepare_the_same_things_prepare_once(tmp_path):
         model.prepare(ctx, [None] * len(model.run))
         assert len(model._prepare_hooks) == want
         assert len([k for k in ctx.memo if k[0] == "attention_plan"]) == want
+
+
+def test_every_span_of_a_mixed_step_goes_to_the_kernel_for_its_shape(tmp_path, monkeypatch):
+    """The attention's plan for a step that mixes portions and tokens (no GPU: the kernels' own answers about what they
+    support are asked, the device's SM count is given).  In bfloat16 with heads of 64: single tokens to the decode
+    kernel, portions of two rows or more to the tensor-core kernel.  In float32: tiles of rows on CUDA cores, but few
+    rows over many keys row by row with the keys in pieces."""
+    import json
+    from lightllm_b200.config import load_config, model_spec_for
+    from lightllm_b200.csrc import ops
+    from lightllm_b200.models.model import Model
+    from lightllm_b200.parts import linear
+    from tests.tiny_configs import config
+    monkeypatch.setattr(linear, "num_sms", lambda device=None: 148)
+    monkeypatch.setattr(ops, "decode_mma_cluster_splits", lambda: 16)
+    d = tmp_path / "D"
+    d.mkdir()
+    (d / "config.json").write_text(json.dumps(config("D")))
+    mixer = Model(model_spec_for(load_config(str(d)))).layers[0].mixer          # layer 0 of D sees all keys
+    spans = [(700, 1, 0), (600, 5, 1), (0, 100, 6), (0, 7, 106), (40, 1, 113)]
+
+    def plan(dtype):
+        ctx = context(spans, staging_words=4000)
+        ctx.dtype, ctx.page_size, ctx.max_pages, ctx.decode_only, ctx.T = dtype, 16, 64, False, 114
+        return mixer._plan(ctx, dtype)
+
+    kind, items, decode, simt = plan(torch.bfloat16)
+    assert kind == "mixed" and simt == []
+    assert sorted(set(items[0].tolist())) == [1, 2, 3]                   # the portions, as items of the tensor-core kernel
+    (tile_span, tile_q0, n), nsplit = decode
+    assert tile_span.tolist() == [0, 4] and n == 2 and 1 <= nsplit <= 8  # the tokens, each request's keys in pieces
+    kind, items, decode, simt = plan(torch.float32)
+    assert items is None and decode is None and len(simt) == 2
+    (rows_span, rows_q0, rows_n), bq, nsplit = simt[0]                   # few rows over many keys: row by row, in pieces
+    assert bq == 1 and nsplit >= 2 and rows_span.tolist() == [0, 1, 1, 1, 1, 1] and rows_q0.tolist() == [0, 0, 1, 2, 3, 4]
+    (tile_span, _, _), bq, nsplit = simt[1]                              # the rest in tiles of rows
+    assert bq >= 1 and nsplit == 1 and sorted(set(tile_span.tolist())) == [2, 3, 4]
