@@ -35,7 +35,7 @@ def main(argv=None) -> int:
     V = spec.vocab_size
     users = [([1, 2, 3, 4, 5], 15), (list(range(10, 30)), 10), ([7 * i % V for i in range(1, 41)], 20)]
     loop = eng.new_loop()
-    ids = [loop.submit([t % V for t in p], max_new_tokens=n, eos_token_id=151643, temperature=args.temperature)
+    ids = [loop.submit([t % V for t in p], max_new_tokens=n, temperature=args.temperature)
            for p, n in users]
     t0 = time.perf_counter()
     while loop.has_active():

@@ -15,7 +15,8 @@ def main(argv=None) -> int:
     ap.add_argument("--top-p", type=float, default=0.9)
     ap.add_argument("--min-p", type=float, default=0.0)
     ap.add_argument("--seed", type=int, default=42)
-    ap.add_argument("--eos-token-id", type=int, default=151643)
+    ap.add_argument("--eos-token-id", type=int, default=None,
+                    help="default: eos_token_id of the model's config.json (the reference fixes 151643, scheduler.h:29)")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--max-seq-len", type=int, default=2048)
     args = ap.parse_args(argv)

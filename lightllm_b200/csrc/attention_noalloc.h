@@ -13,14 +13,16 @@
 //
 // How: the scratch is one file-scope `static __device__` array of LLB_NOALLOC_SCRATCH_FLOATS
 // floats (8 MiB), aligned to 256 bytes.  Every GPU on which the library's module gets loaded
-// holds these 8 MiB until the process exits.  The first call on a device looks up the array's
-// device address (cudaGetSymbolAddress) and remembers it; make that first call before any
-// stream capture begins.  No call allocates or frees anything, on the device or through any
+// holds these 8 MiB until the process exits.  The first call with nsplit > 1 on a device looks up
+// the array's device address (cudaGetSymbolAddress) and remembers it; make that first call before
+// any stream capture begins.  No call allocates or frees anything, on the device or through any
 // library.
 //
 // Limits and rules:
-//   * num_tiles * Hq * BQ * nsplit * (hd + 2) must not exceed LLB_NOALLOC_SCRATCH_FLOATS, else
-//     the call fails with a message that states both numbers and launches nothing;
+//   * with nsplit > 1, num_tiles * Hq * BQ * nsplit * (hd + 2) must not exceed
+//     LLB_NOALLOC_SCRATCH_FLOATS, else the call fails with a message that states both numbers
+//     and launches nothing.  A call with nsplit == 1 never touches the array: it has no size
+//     limit and does not look up the array's address;
 //   * all calls share the one array, and it keeps what the last call left there.  Nothing in it
 //     has to start at zero: every split writes its whole partial (an empty split writes
 //     m = -inf, l = 0) before the merge reads it;

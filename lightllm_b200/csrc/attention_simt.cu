@@ -594,14 +594,17 @@ LLB_EXPORT int llb_paged_attention_noalloc(const void* q, const void* k_cache, c
                                            int hd, int window, float scale, int BQ, int nsplit, cudaStream_t stream) {
     if (num_tiles == 0) return 0;
     LLB_REQUIRE(num_tiles > 0 && Hq > 0 && hd > 0 && BQ > 0 && nsplit >= 1, "attention_noalloc: bad sizes");
-    const long long need = llb_attention_scratch_floats(num_tiles, Hq, hd, BQ, nsplit);
-    LLB_REQUIRE(need <= (long long)LLB_NOALLOC_SCRATCH_FLOATS,
-                "attention_noalloc: %d tiles x %d heads x %d rows x %d splits x (head_dim %d + 2) needs %lld floats of "
-                "scratch; the built-in scratch holds %lld. Use fewer splits or the entry point that takes scratch",
-                num_tiles, Hq, BQ, nsplit, hd, need, (long long)LLB_NOALLOC_SCRATCH_FLOATS);
+    // Without splits nothing is written to the scratch: such a call has no size limit and needs no address.
     float* scratch = nullptr;
-    int rc = noalloc_scratch(&scratch);
-    if (rc) return rc;
+    if (nsplit > 1) {
+        const long long need = llb_attention_scratch_floats(num_tiles, Hq, hd, BQ, nsplit);
+        LLB_REQUIRE(need <= (long long)LLB_NOALLOC_SCRATCH_FLOATS,
+                    "attention_noalloc: %d tiles x %d heads x %d rows x %d splits x (head_dim %d + 2) needs %lld floats of "
+                    "scratch; the built-in scratch holds %lld. Use fewer splits or the entry point that takes scratch",
+                    num_tiles, Hq, BQ, nsplit, hd, need, (long long)LLB_NOALLOC_SCRATCH_FLOATS);
+        int rc = noalloc_scratch(&scratch);
+        if (rc) return rc;
+    }
     return llb_paged_attention(q, k_cache, v_cache, out, dtype, tile_span, tile_q0, num_tiles, span_row, span_len,
                                span_pos, block_table, max_pages, page_size, Hq, Hkv, hd, window, scale, BQ, nsplit,
                                scratch, stream);

@@ -250,7 +250,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 // page numbers first: their latency then lies under the wait for the stage
                 const int ppt = BKV / p.page_size;
                 const int lp = kt / p.page_size + lane;
-                const int page = (lane < ppt && lp < p.max_pages) ? bt[lp] : -1;
+                // only pages that hold keys of [lo, hi): what lies beyond the request's own keys is never read
+                const bool holds_keys = lp * p.page_size < it.hi && (lp + 1) * p.page_size > it.lo;
+                const int page = (lane < ppt && lp < p.max_pages && holds_keys) ? bt[lp] : -1;
                 if (n_kv >= 2) ok = mbar_wait(&bar_kv_free[st], ((n_kv >> 1) - 1) & 1, abort_flag) && ok;
                 if (!ok) continue;
                 if (lane == 0) mbar_expect_tx(&bar_kv_full[st], 2 * KB * TILE_BYTES);
@@ -357,6 +359,18 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     if (threadIdx.x == 0 && it.ntiles == 1) mbar_arrive(bar_q_free);     // the item's last S has read Q
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (kt + BKV > it.hi && kt + r >= it.hi) {
+                    // The span's last page may hold rows that no token has written yet (what an earlier owner left
+                    // there).  Their probabilities are exact zeros, but zero times anything must stay zero: the V
+                    // rows of the keys from `hi` on are cleared before P V reads them.  (S is complete, so the tile's
+                    // copies have landed; a row is 128 bytes in every 64-column tile, each half-thread clears 64.)
+#pragma unroll
+                    for (int kb = 0; kb < KB; ++kb) {
+                        uint4* vrow = reinterpret_cast<uint4*>(v_s + ((n_s & 1) * KB + kb) * TILE_BYTES + (uint32_t)r * 128 + half * 64);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) vrow[q] = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                }
                 // Softmax of this thread's row over its 64 keys of the tile, in two passes over tensor memory
                 // (maximum first, then the probabilities), 32 columns at a time.  Tiles that lie wholly below
                 // the diagonal and inside the window of every row of the block skip the masking.

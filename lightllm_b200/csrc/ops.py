@@ -17,7 +17,7 @@ from . import build as _build
 
 F32, BF16 = 0, 1
 EPI_STORE, EPI_STORE_F32, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
-ABI_VERSION = 15
+ABI_VERSION = 16
 
 _lib: Optional[ctypes.CDLL] = None
 
@@ -132,6 +132,13 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, err: Op
                                _i32(err, "err"), _stream()))
 
 
+def cast_add(src: torch.Tensor, dst: torch.Tensor, accumulate: bool = False) -> None:
+    """dst = src (converted to dst's dtype), or dst += src with ``accumulate``; float32 or bfloat16 on either side."""
+    if src.numel() != dst.numel():
+        raise KernelError(f"cast_add: {tuple(src.shape)} does not fit {tuple(dst.shape)}")
+    _check(lib().llb_cast_add(_ptr(src), _dt(src), _ptr(dst), _dt(dst), src.numel(), 1 if accumulate else 0, _stream()))
+
+
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
             rows: Optional[torch.Tensor] = None) -> None:
     """out[r,:] = rmsnorm(x[rows[r],:]) * weight (rows = None: row r of x)."""
@@ -238,16 +245,21 @@ def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, transposed: bool
 
 
 _splitk = {}
+_splitk_retired = []     # meeting places that a larger one replaced: CUDA graphs captured earlier still use them
 
 
 def reserve_splitk_scratch(device: torch.device, floats: int, tiles: int) -> None:
     """Make sure the device has a zeroed meeting place of ``floats`` floats and ``tiles`` counters for
-    split-K contractions with fused epilogues.  Call it when a model is bound, never inside a step."""
+    split-K contractions with fused epilogues.  Call it when a model is bound, never inside a step.
+    A meeting place that a larger one replaces is kept alive (and zero, as every launch leaves it): a graph
+    captured while it was current goes on adding into it."""
     key = torch.device(device).index or 0
     have = _splitk.get(key)
     if have is None or have[0].numel() < floats or have[1].numel() < tiles:
         floats = max(floats, have[0].numel() if have else 0)
         tiles = max(tiles, have[1].numel() if have else 0)
+        if have is not None:
+            _splitk_retired.append(have)
         _splitk[key] = (torch.zeros(floats, dtype=torch.float32, device=device),
                         torch.zeros(tiles, dtype=torch.int32, device=device))
 
@@ -452,6 +464,14 @@ def check_async_errors(device: torch.device) -> None:
     if int(t.item()) != 0:
         t.zero_()
         raise KernelError("a tensor-core kernel gave up waiting on a barrier; its results are invalid")
+
+
+def selftest_wait_expires(device: torch.device, limit_cycles: int = 1_000_000) -> torch.Tensor:
+    """Run the library's self-test block whose waits nothing ever satisfies (csrc/selftest.cu): afterwards
+    :func:`check_async_errors` raises.  Returns the two roles' outcomes (2 = left its wait unsatisfied)."""
+    trace = torch.zeros(2, dtype=torch.int32, device=device)
+    _check(lib().llb_selftest_wait_expires(_ptr(async_error_flag(device)), _ptr(trace), limit_cycles, _stream()))
+    return trace
 
 
 _meet_counters = {}

@@ -41,7 +41,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait: false when the time limit ran out or another role of the block already gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, volatile int* abort_flag, long long limit) {
     if (mbar_try_wait(bar, parity)) return true;
     // The time limit is checked once every 256 failed attempts, on the SM's own cycle counter: reading a
     // timer inside the loop would add its latency to every wake-up.
@@ -50,12 +50,15 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
         if (mbar_try_wait(bar, parity)) return true;
         if ((spins & 255u) == 0u) {
             if (*abort_flag) return false;
-            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+            if (clock64() - t0 > limit) {
                 *abort_flag = 1;
                 return false;
             }
         }
     }
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    return mbar_wait_limit(bar, parity, abort_flag, WAIT_LIMIT_CYCLES);
 }
 // The same on a barrier given by its shared-memory address (for loops that carry the address in a register).
 __device__ __forceinline__ bool mbar_try_wait_addr(uint32_t bar_addr, uint32_t parity) {

@@ -26,7 +26,8 @@ class EngineOptions:
 
     ``max_seq_len`` <= 0 means the model's ``max_position_embeddings`` (engine_server.cpp:412-415).
     The pool has ``num_pages`` pages per cache group if given, else as many as ``kv_cache_mb``
-    megabytes hold, else enough for ``max_seqs`` requests of ``max_seq_len`` tokens."""
+    megabytes hold, else enough for ``max_seqs`` requests of ``max_seq_len`` tokens or what fits in 85 % of
+    the device memory that is free after the weights are loaded, whichever is less."""
 
     dtype: str = "bfloat16"
     max_seq_len: int = 0
@@ -61,7 +62,17 @@ class EngineCore:
             n = int(opt.kv_cache_mb * 1024 * 1024 // max(1, per_page))
             num_pages = [max(1, n)] * len(layout.groups)
         else:
-            num_pages = [pages_per_seq * opt.max_seqs] * len(layout.groups)
+            # Room for max_seqs requests of max_seq_len tokens, but no more than most of the memory that is free
+            # now that the weights are loaded (a model with 131,072 positions would ask for more than the device has).
+            per_page = sum(layout.bytes_per_page(g, opt.page_size, esize) for g in range(len(layout.groups)))
+            want = pages_per_seq * opt.max_seqs
+            free_bytes = torch.cuda.mem_get_info(self.device)[0]
+            fit = int(free_bytes * 0.85 // max(1, per_page))
+            if fit < pages_per_seq:
+                raise RuntimeError(
+                    f"the cache of one request of {self.max_seq_len} tokens needs {pages_per_seq * per_page} bytes, but "
+                    f"only {free_bytes} bytes of device memory are free: give max_seq_len, num_pages or kv_cache_mb")
+            num_pages = [min(want, fit)] * len(layout.groups)
         self.cache = CacheManager(layout, opt.page_size, num_pages, opt.max_seqs, self.max_seq_len,
                                   self.dtype, self.device)
         self.runner = ModelRunner(self.model, self.cache, opt.max_batch_tokens, opt.max_seqs, opt.use_cuda_graphs)
@@ -88,3 +99,9 @@ class EngineCore:
     @property
     def vocab_size(self) -> int:
         return self.model.spec.vocab_size
+
+    @property
+    def eos_token_ids(self) -> tuple:
+        """The end-of-sequence ids that the model's config.json names (empty if it names none)."""
+        config = getattr(self.model, "config", None)
+        return tuple(config.eos_token_ids) if config is not None else ()

@@ -109,11 +109,13 @@ class BatchMainLoop:
     def wall_clock(self) -> float:
         return time.perf_counter() - self._epoch
 
-    def submit(self, prompt_tokens: Sequence[int], max_new_tokens: int = 64, eos_token_id: int = 151643,
+    def submit(self, prompt_tokens: Sequence[int], max_new_tokens: int = 64, eos_token_id=None,
                temperature: float = 1.0, top_k: int = 0, top_p: float = 1.0, min_p: float = 0.0,
                seed: int = 42) -> int:
         params = SamplingParams(temperature, top_k, top_p, min_p, seed)
         params.validate()
+        if eos_token_id is None:        # the model's own end-of-sequence ids (config.json), none if it names none
+            eos_token_id = tuple(getattr(self.engine, "eos_token_ids", ())) or -1
         vocab = self.engine.vocab_size
         for t in prompt_tokens:
             if not 0 <= int(t) < vocab:

@@ -10,6 +10,7 @@ one host-to-device copy of the step's metadata, no synchronisation, and the step
 """
 from __future__ import annotations
 
+import logging
 import os
 from typing import Dict, Hashable, List, Optional, Sequence
 
@@ -67,11 +68,17 @@ class ModelRunner:
             st = cache.state[ref.state_plane] if ref.state_plane is not None else None
             self.views.append(CacheView(ref.group, k, v, st, ref.owns))
         self.last_h2d_bytes = 0
+        self.last_ctx: Optional[StepContext] = None
         self._nvtx = os.environ.get("LLB_NVTX", "") not in ("", "0")
         # Steps are launch-bound on the host, so they are captured into CUDA graphs: one per shape (counts of
         # tokens, requests, wanted rows, block-table width, sizes of the staged index arrays), captured the
         # second time a shape is seen.
-        self.use_cuda_graphs = bool(use_cuda_graphs) and model.graph_safe()
+        self.graph_blockers = model.graph_blockers()      # the parts (by class name) that keep steps out of graphs
+        self.use_cuda_graphs = bool(use_cuda_graphs) and not self.graph_blockers
+        if use_cuda_graphs and self.graph_blockers:
+            logging.getLogger("lightllm_b200").info(
+                "steps run launch by launch, not from CUDA graphs: %s do(es) not declare graph_safe",
+                ", ".join(self.graph_blockers))
         self.max_graphs = max_graphs
         self._graphs: Dict[tuple, tuple] = {}
         self._graph_seen: Dict[tuple, int] = {}
@@ -159,6 +166,7 @@ class ModelRunner:
             for i, s in enumerate(spans):
                 table = cache.block_table_array(s.seq_id, g)
                 bt[i, : len(table)] = table[:P]
+                bt[i, len(table):] = -1          # "no page": what an earlier step left in the buffer is never an id
                 p = pos[s.row: s.row + s.length]
                 rows = table[p // ps]
                 if rows.min() < 0:
@@ -231,6 +239,7 @@ class ModelRunner:
         one per token of the step, on the device) the entries' own token ids only give the counts: the step
         reads its ids from that tensor, so ids that were sampled on the device need not visit the host."""
         ctx = self._build_context(entries, device_tokens)
+        self.last_ctx = ctx          # kept for inspection (which kernels the step's plan chose)
         if self.use_cuda_graphs and not ctx.late_uploads:
             logits = self._forward_graphed(ctx)
         else:

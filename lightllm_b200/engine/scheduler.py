@@ -41,7 +41,9 @@ class Request:
     output_tokens: List[int] = field(default_factory=list)
     num_computed: int = 0            # tokens of prompt + output whose keys and values are cached
     max_new_tokens: int = 64
-    eos_token_id: int = 151643
+    # The ids that end the sequence: an integer or a collection of them; -1 (no token) means none.  The scheduler
+    # knows no vocabulary: callers take the ids from the model's configuration (``eos_token_id`` of config.json).
+    eos_token_id: object = -1
     sampling: SamplingParams = field(default_factory=SamplingParams)
     state: str = WAITING
     finish_reason: Optional[str] = None
@@ -262,7 +264,8 @@ class Scheduler:
             tok = sampled[r.id]
             r.output_tokens.append(tok)
             reason = None
-            if tok == r.eos_token_id:
+            eos = r.eos_token_id
+            if tok == eos if isinstance(eos, int) else (eos is not None and tok in eos):
                 reason = "eos"
             elif len(r.output_tokens) >= r.max_new_tokens:
                 reason = "length"

@@ -47,9 +47,10 @@ class Engine:
 
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int = 64, temperature: float = 1.0,
                  top_k: int = 0, top_p: float = 1.0, min_p: float = 0.0, seed: int = 42,
-                 eos_token_id: int = 151643, return_reasons: bool = False):
+                 eos_token_id=None, return_reasons: bool = False):
         """Continue every prompt (token ids in, token ids out) with continuous batching.
-        ``temperature=0`` is greedy.  Request ``i`` draws from its own stream seeded ``seed + i``
+        ``temperature=0`` is greedy.  ``eos_token_id``: an id or several that end a sequence; ``None`` takes them
+        from the model's config.json, ``-1`` means none.  Request ``i`` draws from its own stream seeded ``seed + i``
         (as the reference's ``sample_batch``, src/ops/sampling.cpp:341-359)."""
         loop = self.new_loop()
         ids = [loop.submit(p, max_new_tokens, eos_token_id, temperature, top_k, top_p, min_p, seed + i)

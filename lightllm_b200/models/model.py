@@ -10,9 +10,6 @@ from ..config import ModelConfig, ModelSpec, load_config, model_spec_for
 from ..parts import Block, Part, build_part
 from ..weights import WeightSpec, dedup_specs, load_checkpoint_tensors
 
-# Tensor-name endings that a checkpoint may carry without the model reading them.
-IGNORED_SUFFIXES = ("rotary_emb.inv_freq",)
-
 
 def _walk(part: Part):
     yield part
@@ -34,8 +31,9 @@ class Model:
         self.final_norm = build_part("norm", spec.final_norm)
         self.head = build_part("head", spec.head)
         self.run = list(spec.run)
+        mixers = [self.layers[e.layer].mixer for e in self.run]
         self.cache_layout = CacheLayout.build(
-            [self.layers[e.layer].mixer.cache_spec() for e in self.run], [e.cache_of for e in self.run])
+            [m.cache_spec() if m is not None else None for m in mixers], [e.cache_of for e in self.run])
         self.dtype: Optional[torch.dtype] = None
         self.device: Optional[torch.device] = None
         self._prepare_hooks = None
@@ -77,10 +75,9 @@ class Model:
                     if key is not None:
                         keys.add(key)         # parts with equal keys prepare the same things: once is enough
             for i, entry in enumerate(self.run):
-                block = self.layers[entry.layer]
-                for part in (block.norm1, block.norm2, block.ffn):
-                    add(part, None)
-                add(block.mixer, i)
+                for sb in self.layers[entry.layer].subs:
+                    for part in sb.parts():
+                        add(part, i if part is sb.part and sb.role == "mixer" else None)
             for part in (self.embedding, self.final_norm, self.head):
                 add(part, None)
             self._prepare_hooks = hooks
@@ -90,10 +87,15 @@ class Model:
             else:
                 hook(ctx, views[run_index])
 
+    def graph_blockers(self) -> List[str]:
+        """The parts that keep this model's steps out of CUDA graphs: those that do not declare that their
+        forward only launches kernels whose arguments are fixed by the step's counts."""
+        return sorted({type(p).__name__ for p in self.parts()
+                       if not isinstance(p, Block) and not getattr(p, "graph_safe", False)})
+
     def graph_safe(self) -> bool:
-        """Whether every part's forward only launches kernels whose arguments are fixed by the step's
-        counts (no host-side branching on the batch's contents), so a step can be captured in a CUDA graph."""
-        return all(getattr(p, "graph_safe", False) for p in self.parts() if not isinstance(p, Block))
+        """Whether a step of this model can be captured in a CUDA graph (no part blocks it)."""
+        return not self.graph_blockers()
 
     def weight_bytes(self) -> int:
         """Bytes of the tensors a step reads (a tied table counts once)."""
@@ -127,6 +129,6 @@ def load_model(model_dir: str, dtype, device: torch.device) -> Model:
     model = Model(model_spec_for(config))
     model.config = config
     dt = compute_dtype(dtype)
-    tensors = load_checkpoint_tensors(model_dir, model.weight_specs(), dt, device, IGNORED_SUFFIXES)
+    tensors = load_checkpoint_tensors(model_dir, model.weight_specs(), dt, device, tuple(model.spec.ignored_suffixes))
     model.bind(tensors, dt, device)
     return model

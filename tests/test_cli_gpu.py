@@ -1,0 +1,80 @@
+"""The command lines run as a user runs them (``python -m lightllm_b200.cli...``), on a tiny model, and what they
+print is checked against the plain implementation: the reference's tools drive its engine the same way
+(tools/bench_server.cpp:158-245, tests/test_generate.cpp:284-290)."""
+import os
+import re
+import subprocess
+import sys
+
+import pytest
+
+from lightllm_b200.weights import write_random_model
+from tests.plain import qwen2_plain as P
+from tests.tiny_configs import config
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def run_cli(module, *args):
+    env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    proc = subprocess.run([sys.executable, "-m", module, *map(str, args)], stdout=subprocess.PIPE, stderr=subprocess.PIPE,
+                          text=True, env=env, timeout=600, cwd=ROOT)
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    return proc.stdout
+
+
+@pytest.fixture(scope="module")
+def tiny_a(tmp_path_factory):
+    d = str(tmp_path_factory.mktemp("cli_model"))
+    write_random_model(config("A"), seed=3, out_dir=d, store_dtype="float32")
+    return d, *P.read_model_dir(d)
+
+
+def test_generate_prints_the_plain_greedy_continuation(tiny_a):
+    d, cfg, w = tiny_a
+    prompt = [5, 17, 3, 99, 250, 7]
+    out = run_cli("lightllm_b200.cli.generate", d, *prompt, "--temperature", 0, "--max-new-tokens", 9, "--dtype", "float32",
+                  "--max-seq-len", 64)
+    got = re.search(r"generated:\s*([\d ]+)\((\w+)\)", out)
+    assert got, out
+    assert [int(t) for t in got.group(1).split()] == P.plain_greedy(cfg, w, prompt, 9)
+    assert got.group(2) == "length"
+    assert re.search(r"prompt:\s*5 17 3 99 250 7", out)
+
+
+def test_generate_samples_the_same_tokens_for_the_same_seed(tiny_a):
+    d, _, _ = tiny_a
+    a = run_cli("lightllm_b200.cli.generate", d, 1, 2, 3, "--seed", 5, "--max-seq-len", 64)
+    b = run_cli("lightllm_b200.cli.generate", d, 1, 2, 3, "--seed", 5, "--max-seq-len", 64)
+    c = run_cli("lightllm_b200.cli.generate", d, 1, 2, 3, "--seed", 6, "--max-seq-len", 64)
+    pick = lambda s: re.search(r"generated:\s*([\d ]+)", s).group(1)
+    assert pick(a) == pick(b) != pick(c)
+    assert len(pick(a).split()) == 12            # the reference's 12 new tokens (tests/test_generate.cpp:148-149)
+
+
+def test_bench_server_runs_its_three_users_to_the_plain_tokens(tiny_a):
+    d, cfg, w = tiny_a
+    out = run_cli("lightllm_b200.cli.bench_server", d, 128, 64, "--dtype", "float32")
+    V = cfg["vocab_size"]
+    users = [([1, 2, 3, 4, 5], 15), (list(range(10, 30)), 10), ([7 * i % V for i in range(1, 41)], 20)]
+    for i, (prompt, n) in enumerate(users):
+        line = re.search(rf"\[user {i}\] \[([\d, ]+)\] \((\w+)\)", out)
+        assert line, out
+        assert [int(t) for t in line.group(1).split(",")] == P.plain_greedy(cfg, w, [t % V for t in prompt], n)
+        assert line.group(2) == "length"
+    assert re.search(r"Total tokens: 45 ", out) and "steps/s" in out
+    steps = re.findall(r"\[step\s+\d+\] tokens=\s*(\d+) prefill=\s*(\d+) decode=\s*(\d+)", out)
+    assert steps and all(int(t) == int(p) + int(dd) and int(t) <= 64 for t, p, dd in steps)
+
+
+def test_random_model_writes_a_folder_the_engine_loads(tmp_path):
+    import json
+    cfg_path = str(tmp_path / "config.json")
+    with open(cfg_path, "w") as f:
+        json.dump(config("B"), f)
+    out_dir = str(tmp_path / "made")
+    run_cli("lightllm_b200.cli.random_model", cfg_path, out_dir, 4)
+    assert sorted(os.listdir(out_dir)) == ["config.json", "model.safetensors"]
+    text = run_cli("lightllm_b200.cli.generate", out_dir, 1, 2, 3, "--temperature", 0, "--max-new-tokens", 3, "--max-seq-len", 64)
+    assert re.search(r"generated:\s*\d+ \d+ \d+", text)

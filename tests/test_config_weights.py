@@ -5,7 +5,8 @@ import os
 import pytest
 import torch
 
-from lightllm_b200.config import (ConfigError, Qwen2Config, config_from_dict, known_architectures, load_config,
+from lightllm_b200.models.qwen2 import Qwen2Config
+from lightllm_b200.config import (ConfigError, config_from_dict, known_architectures, load_config,
                                   model_spec_for)
 from lightllm_b200.models import Model, weight_specs_of
 from lightllm_b200.weights import (Checkpoint, SafetensorsError, WeightError, check_against, load_checkpoint_tensors,
@@ -149,3 +150,34 @@ def test_safetensors_errors(tmp_path):
     with pytest.raises(SafetensorsError, match="tensor not found: nope"):
         f.read("nope")
     f.close()
+
+
+def test_a_layer_is_a_list_of_sub_blocks():
+    from lightllm_b200.config import LayerSpec, PartSpec, SubBlock
+    n, m, f = PartSpec("rmsnorm"), PartSpec("attention"), PartSpec("gated_mlp")
+    short = LayerSpec(n, m, n, f, arrangement="pre_norm")
+    assert short.arrangement == "sequential" and [sb.role for sb in short.sub_blocks] == ["mixer", "ffn"]
+    assert short.sub_blocks[0].norm_before is n and short.sub_blocks[1].norm_after is None
+    lone = LayerSpec(sub_blocks=[SubBlock("mixer", m)])
+    assert len(lone.sub_blocks) == 1 and lone.sub_blocks[0].norm_before is None
+    with pytest.raises(ValueError, match="at most one mixer"):
+        LayerSpec(sub_blocks=[SubBlock("mixer", m), SubBlock("mixer", m)])
+    with pytest.raises(ValueError, match="at least one"):
+        LayerSpec()
+    with pytest.raises(ValueError, match="not both"):
+        LayerSpec(n, m, sub_blocks=[SubBlock("ffn", f)])
+    with pytest.raises(ValueError, match="role"):
+        LayerSpec(sub_blocks=[SubBlock("norm", n)])
+    with pytest.raises(ValueError, match="parallel"):
+        LayerSpec(sub_blocks=[SubBlock("ffn", f, n, n, after="stream")], arrangement="parallel")
+    with pytest.raises(ValueError, match="arrangement"):
+        LayerSpec(n, m, n, f, arrangement="sandwich")
+
+
+def test_end_of_sequence_ids_come_from_the_configuration():
+    base = config("A")
+    assert config_from_dict(base).eos_token_ids == ()
+    assert config_from_dict({**base, "eos_token_id": 7}).eos_token_ids == (7,)
+    assert config_from_dict({**base, "eos_token_id": [7, 9]}).eos_token_ids == (7, 9)
+    with pytest.raises(ConfigError, match="eos_token_id"):
+        config_from_dict({**base, "eos_token_id": "end"}).eos_token_ids

@@ -97,3 +97,63 @@ def test_plain_sampler_against_the_reference_sampler():
     # the draw: first index whose cumulative mass reaches u
     p = np.array([0.0, 0.25, 0.0, 0.5, 0.25])
     assert [P.plain_draw(p, u) for u in (0.0, 0.2, 0.25, 0.26, 0.75, 0.76, 0.999)] == [1, 1, 1, 3, 3, 4, 4]
+
+
+# ---------------------------------------------------------------------------------------------
+# The plain attention and contraction against the reference's own CPU oracles
+# ---------------------------------------------------------------------------------------------
+ATTENTION_GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "attention_golden.json")
+
+
+class _GoldenInputs:
+    """The generator of tests/golden/golden_attention.cu (xorshift, 24 bits to a float in [-1, 1), times a scale in
+    float32), so that the inputs need not be stored."""
+
+    def __init__(self):
+        self.state = 88172645463325252
+        self.mask = (1 << 64) - 1
+
+    def draw(self, n, scale):
+        out = np.empty(n, dtype=np.float32)
+        s = self.state
+        for i in range(n):
+            s ^= (s << 13) & self.mask
+            s ^= s >> 7
+            s ^= (s << 17) & self.mask
+            out[i] = np.float32(((s >> 40) & 0xFFFFFF) / 8388608.0 - 1.0) * np.float32(scale)
+        self.state = s
+        return torch.from_numpy(out)
+
+
+def test_plain_attention_and_head_agree_with_the_references_cpu_oracles():
+    """``cpu_attention`` (tests/test_paged_attention_v2.cu:111-156: the query rows see every key),
+    ``cpu_prefill_attention_causal`` (tests/test_paged_prefill.cu:164-215: the rows are the last positions, causal,
+    ``acc / (l + 1e-8)``) and ``cpu_lm_head`` (tests/test_lm_head.cu:50-61), run once from the reference's own test
+    programs (tests/golden/golden_attention.cu): grouped heads (``h // (Hq / Hkv)``), one kv head for all, the
+    ``1 / sqrt(D)`` scale, the causal rule by absolute position and the ``x W^T`` head are theirs, not a reading."""
+    with open(ATTENTION_GOLDEN) as f:
+        golden = json.load(f)
+    gen = _GoldenInputs()
+    for case in golden["attention"]:
+        T, Hq, Hkv, D, S = case["T"], case["Hq"], case["Hkv"], case["D"], case["seq_len"]
+        q = gen.draw(T * Hq * D, 1.5).reshape(T, Hq, D)
+        k = gen.draw(S * Hkv * D, 1.5).reshape(S, Hkv, D)
+        v = gen.draw(S * Hkv * D, 1.0).reshape(S, Hkv, D)
+        # the plain function takes whole sequences: the T query rows are the last T positions of S
+        q_full = torch.zeros(S, Hq, D)
+        q_full[S - T:] = q
+        causal = P.plain_attention(q_full, k, v, 1.0 / math.sqrt(D))[S - T:]
+        want = torch.tensor(case["causal"]).reshape(T, Hq, D)
+        assert float((causal - want).abs().max()) < 2e-6, (T, Hq, Hkv, D, S)
+        # every query row over every key is what the last position sees
+        for t in range(T):
+            q_last = torch.zeros(S, Hq, D)
+            q_last[S - 1] = q[t]
+            every = P.plain_attention(q_last, k, v, 1.0 / math.sqrt(D))[S - 1]
+            want = torch.tensor(case["every_key"]).reshape(T, Hq, D)[t]
+            assert float((every - want).abs().max()) < 2e-6, (T, Hq, Hkv, D, S, t)
+    head = golden["lm_head"]
+    hidden = gen.draw(head["D"], 1.0)
+    embed = gen.draw(head["V"] * head["D"], 0.5).reshape(head["V"], head["D"])
+    got = P.plain_linear(hidden[None, :], embed)[0]
+    assert float((got - torch.tensor(head["logits"])).abs().max()) < 2e-6

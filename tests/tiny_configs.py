@@ -31,8 +31,17 @@ TINY_D = {
     "tie_word_embeddings": True, "max_position_embeddings": 1024, "use_sliding_window": True,
     "sliding_window": 150, "max_window_layers": 1, "hidden_act": "silu",
 }
-PAGE_SIZE = {"A": 16, "B": 8, "C": 16, "D": 16}
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
+# E has heads of 128 (the head size of the larger checkpoints of the family), given by its own key since it is not
+# hidden / heads, an untied head and no window.
+TINY_E = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 2, "hidden_size": 256, "num_attention_heads": 4, "num_key_value_heads": 2,
+    "head_dim": 128, "intermediate_size": 520, "vocab_size": 2003, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
+    "tie_word_embeddings": False, "max_position_embeddings": 1024, "use_sliding_window": False,
+    "hidden_act": "silu",
+}
+PAGE_SIZE = {"A": 16, "B": 8, "C": 16, "D": 16, "E": 16}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
 
 
 def config(name):
