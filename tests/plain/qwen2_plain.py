@@ -3,12 +3,26 @@
 
 It shares no code with the engine: it has its own safetensors reader, its own configuration
 reading and its own formulas, written from the reference's files (cited per function; paths are
-relative to the reference project).  The reference's own model code cannot be built on a
-machine without a GPU (every tensor it touches is a CUDA tensor, src/tensor.cpp:62-72, and the
-build needs the absent third_party/xgrammar), so this file rests on the formulas, with the
-reference's known deviations from the architecture left out on purpose: the q/k/v biases are
-added, every rotary pair is rotated, a token sees its own key, and the output head follows
-``tie_word_embeddings``.
+relative to the reference project).  The reference's whole model cannot be run on a machine
+without a GPU (every tensor it touches is a CUDA tensor, src/tensor.cpp:62-72, and the build of
+its engine needs the absent third_party/xgrammar), and its engine departs from the architecture
+in known places, which are left out here on purpose: the q/k/v biases are added, every rotary
+pair is rotated, a token sees its own key, and the output head follows ``tie_word_embeddings``.
+
+What pins each formula to the reference's own code rather than to a reading of it
+(tests/test_plain.py, golden files under tests/golden/ made by the scripts beside them):
+
+* ``plain_attention``: the reference's CPU oracles ``cpu_attention`` (tests/test_paged_attention_v2.cu:111-156)
+  and ``cpu_prefill_attention_causal`` (tests/test_paged_prefill.cu:164-215), compiled from its test
+  programs: head grouping ``h // (Hq / Hkv)``, one kv head for all, the ``1/sqrt(D)`` scale, softmax,
+  the causal rule by absolute position;
+* ``plain_linear`` as the output head: ``cpu_lm_head`` (tests/test_lm_head.cu:50-61);
+* ``plain_rmsnorm``, ``plain_silu``, ``plain_embedding``: the reference's own kernels ``rms_norm``,
+  ``silu`` and ``embedding`` (src/ops/norm.cu, elementwise.cu, embedding.cu), run once on a B200;
+* ``plain_sampling_probs`` / ``plain_draw``: the reference's ``sample()`` (src/ops/sampling.cpp);
+* the rotation, the window rule, the q/k/v biases and the block's order of operations rest on the
+  formulas cited at each function (the reference's rotation kernel turns one pair per head and its
+  engine has no window), checked against loops and float64 in tests/test_plain.py.
 """
 from __future__ import annotations
 

@@ -157,3 +157,21 @@ def test_plain_attention_and_head_agree_with_the_references_cpu_oracles():
     embed = gen.draw(head["V"] * head["D"], 0.5).reshape(head["V"], head["D"])
     got = P.plain_linear(hidden[None, :], embed)[0]
     assert float((got - torch.tensor(head["logits"])).abs().max()) < 2e-6
+
+
+def test_plain_norm_silu_and_embedding_agree_with_the_references_own_kernels():
+    """``rms_norm`` (src/ops/norm.cu:11-75), ``silu`` (src/ops/elementwise.cu:27-33) and ``embedding``
+    (src/ops/embedding.cu:9-30) of the reference, run once on a B200 from its own sources
+    (tests/golden/golden_ops.cu, make_golden_gpu.sh); the inputs are drawn again here with the same generator."""
+    with open(os.path.join(os.path.dirname(__file__), "golden", "ops_golden.json")) as f:
+        golden = json.load(f)
+    gen = _GoldenInputs()
+    R, D = golden["rows"], golden["width"]
+    x, w = gen.draw(R * D, 3.0).reshape(R, D), gen.draw(D, 1.0)
+    want = torch.tensor(golden["rms_norm"]).reshape(R, D)
+    assert float((P.plain_rmsnorm(x, w, golden["eps"]) - want).abs().max()) < 2e-6
+    s = gen.draw(golden["silu_n"], 6.0)
+    assert float((P.plain_silu(s) - torch.tensor(golden["silu"])).abs().max()) < 2e-6
+    table = gen.draw(golden["vocab"] * golden["embed_width"], 1.0).reshape(golden["vocab"], golden["embed_width"])
+    got = P.plain_embedding(torch.tensor(golden["ids"]), table)
+    assert torch.equal(got, torch.tensor(golden["embedding"]).reshape(len(golden["ids"]), golden["embed_width"]))
