@@ -17,7 +17,7 @@ from . import build as _build
 
 F32, BF16 = 0, 1
 EPI_STORE, EPI_STORE_F32, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
-ABI_VERSION = 16
+ABI_VERSION = 17
 
 _lib: Optional[ctypes.CDLL] = None
 
@@ -458,12 +458,84 @@ def async_error_flag(device: torch.device) -> torch.Tensor:
     return t
 
 
+_reset_on_error = []      # counters that a kernel leaves in an unknown state when it gives up; cleared with the flag
+
+
 def check_async_errors(device: torch.device) -> None:
     """Synchronises and raises if a kernel gave up on a wait (its output is then invalid)."""
     t = async_error_flag(device)
-    if int(t.item()) != 0:
+    code = int(t.item())
+    if code != 0:
         t.zero_()
-        raise KernelError("a tensor-core kernel gave up waiting on a barrier; its results are invalid")
+        for counters in _reset_on_error:
+            if counters.device == t.device:
+                counters.zero_()
+        raise KernelError(f"a tensor-core kernel gave up waiting on a barrier (code {code}); its results are invalid")
+
+
+# ---- the layers of a decode step as one persistent kernel (csrc/decode_layers.cu) -----------------------------------
+MAX_FUSED_GROUPS = 4
+MAX_FUSED_SPLITS = 32
+
+
+def decode_layers_supports(M: int, D: int, Hq: int, Hkv: int, hd: int, I: int, rotary_dim: int) -> bool:
+    return bool(lib().llb_decode_layers_supports(M, D, Hq, Hkv, hd, I, rotary_dim))
+
+
+def decode_layers_descriptors(layers, D: int, Hq: int, Hkv: int, hd: int, I: int, device) -> torch.Tensor:
+    """The device array of layer descriptors for :func:`decode_layers`.  ``layers``: one dict per layer with the
+    tensors ``w_qkv``, ``w_o``, ``w_gate_up``, ``w_down``, ``b_qkv`` (or None), ``norm1_w``, ``norm2_w``, ``k_cache``,
+    ``v_cache`` and the numbers ``eps1``, ``eps2``, ``window`` (0: none), ``group``.  The tensors must stay alive and
+    in place as long as the descriptors are used."""
+    import numpy as np
+    size = int(lib().llb_decode_layers_desc_bytes())
+    host = np.zeros(len(layers) * size, dtype=np.uint8)
+    for i, d in enumerate(layers):
+        for name in ("w_qkv", "w_o", "w_gate_up", "w_down"):
+            if d[name].dtype != torch.bfloat16:
+                raise KernelError(f"decode_layers: {name} must be bfloat16")
+        if d["norm1_w"].dtype != d["norm2_w"].dtype or d["norm1_w"].dtype not in (torch.bfloat16, torch.float32):
+            raise KernelError("decode_layers: the two norm weights must share a dtype (bfloat16 or float32)")
+        if d["k_cache"].dtype != torch.bfloat16 or (d["b_qkv"] is not None and d["b_qkv"].dtype != torch.float32):
+            raise KernelError("decode_layers: the cache must be bfloat16 and the bias float32")
+        _check(lib().llb_decode_layers_describe(
+            host.ctypes.data + i * size, _ptr(d["w_qkv"]), _ptr(d["w_o"]), _ptr(d["w_gate_up"]), _ptr(d["w_down"]),
+            _ptr(d["b_qkv"]), _ptr(d["norm1_w"]), _ptr(d["norm2_w"]), 1 if d["norm1_w"].dtype == torch.bfloat16 else 0,
+            ctypes.c_float(d["eps1"]), ctypes.c_float(d["eps2"]), _ptr(d["k_cache"]), _ptr(d["v_cache"]),
+            int(d["window"] or 0), int(d["group"]), D, Hq, Hkv, hd, I))
+    return torch.from_numpy(host).to(device)
+
+
+def decode_layers_scratch_floats(M: int, Hq: int, Hkv: int, hd: int, I: int, nsplit: int) -> int:
+    return int(lib().llb_decode_layers_scratch_floats(M, Hq, Hkv, hd, I, nsplit))
+
+
+def decode_layers_counters(device) -> torch.Tensor:
+    """The two counters on which the blocks of :func:`decode_layers` meet (zero between launches)."""
+    t = torch.zeros(2, dtype=torch.int32, device=device)
+    _reset_on_error.append(t)
+    return t
+
+
+def decode_layers(descriptors: torch.Tensor, num_layers: int, residual: torch.Tensor, D: int, Hq: int, Hkv: int, hd: int,
+                  I: int, rotary_dim: int, interleaved: bool, scale: float, rope_table: Optional[torch.Tensor],
+                  span_pos: torch.Tensor, block_tables, slot_mappings, max_pages: int, page_size: int, nsplit: int,
+                  scratch: torch.Tensor, counters: torch.Tensor) -> None:
+    """All layers of a decode step (one token per request, at most 64) in one persistent kernel, in place on the
+    float32 ``residual`` [M, D].  ``block_tables`` / ``slot_mappings``: one int32 tensor per cache group (up to 4)."""
+    M = residual.shape[0]
+    if residual.dtype != torch.float32 or tuple(residual.shape) != (M, D):
+        raise KernelError(f"decode_layers: residual must be float32 [{M},{D}]")
+    if len(block_tables) > MAX_FUSED_GROUPS or len(block_tables) != len(slot_mappings):
+        raise KernelError(f"decode_layers: at most {MAX_FUSED_GROUPS} cache groups")
+    bts = [_i32(t, "block_table") for t in block_tables] + [None] * (MAX_FUSED_GROUPS - len(block_tables))
+    sms = [_i32(t, "slot_mapping") for t in slot_mappings] + [None] * (MAX_FUSED_GROUPS - len(slot_mappings))
+    if scratch.dtype != torch.float32:
+        raise KernelError("decode_layers: scratch must be float32")
+    _check(lib().llb_decode_layers(
+        _ptr(descriptors), num_layers, _ptr(residual), M, D, Hq, Hkv, hd, I, rotary_dim, 1 if interleaved else 0,
+        ctypes.c_float(scale), _ptr(rope_table), _i32(span_pos, "span_pos"), *bts, *sms, max_pages, page_size, nsplit,
+        _ptr(scratch), scratch.numel(), _ptr(counters), _ptr(async_error_flag(residual.device)), _stream()))
 
 
 def selftest_wait_expires(device: torch.device, limit_cycles: int = 1_000_000) -> torch.Tensor:

@@ -22,6 +22,7 @@ from ..models import Model
 from ..parts import CacheView
 from ..parts.base import LazyNorm
 from .batch import Span, StepContext, StepEntry
+from .fused_decode import FusedDecode
 
 
 class StepError(ValueError):
@@ -85,6 +86,8 @@ class ModelRunner:
         self._graph_pool = None
         self.graph_replays = 0
         self.graph_launches = 0          # kernels launched through graph replays
+        # Decode steps run the common layers as one persistent kernel per segment of the run list.
+        self.fused = FusedDecode(model, self.views, self.device)
 
     # ------------------------------------------------------------------------------------------
     def _build_context(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> StepContext:
@@ -220,10 +223,18 @@ class ModelRunner:
     def _forward(self, ctx: StepContext) -> Optional[torch.Tensor]:
         m = self.model
         residual = m.embedding.forward(ctx.token_ids, ctx)
-        for i, (entry, view) in enumerate(zip(m.run, self.views)):
+        fused = self.fused if self.fused.takes(ctx) else None
+        i = 0
+        while i < len(m.run):
+            segment = fused.segment_at(i) if fused is not None else None
             if self._nvtx:
-                torch.cuda.nvtx.range_push(f"run{i}:layer{entry.layer}")
-            m.layers[entry.layer].forward(residual, ctx, view)
+                torch.cuda.nvtx.range_push(f"run{i}:" + (f"fused to {segment.end}" if segment else f"layer{m.run[i].layer}"))
+            if segment is not None:
+                segment.run(residual, ctx)
+                i = segment.end
+            else:
+                m.layers[m.run[i].layer].forward(residual, ctx, self.views[i])
+                i += 1
             if self._nvtx:
                 torch.cuda.nvtx.range_pop()
         if ctx.num_want == 0:

@@ -662,3 +662,140 @@ def test_a_wait_that_runs_out_is_reported_and_the_library_goes_on(ops):
     ops.check_async_errors(dev())
     ref = a.float().cpu() @ w.float().cpu().t()
     assert torch.allclose(out.cpu(), ref, atol=2e-2, rtol=2e-2)
+
+
+# ---------------------------------------------------------------------------------------------
+# The layers of a decode step as one persistent kernel
+# ---------------------------------------------------------------------------------------------
+FUSED_CASES = [
+    # D, Hq, Hkv, hd, I, page, rotary_dim, interleaved, bias, norm dtype, window, layers, contexts (keys before the new token)
+    (136, 6, 2, 64, 344, 16, 64, False, True, torch.bfloat16, None, 2, [0, 1, 15, 16, 17, 300, 700]),
+    (256, 4, 2, 128, 520, 8, 128, False, True, torch.bfloat16, 150, 2, [5, 149, 150, 151, 400]),
+    (192, 3, 1, 64, 136, 32, 32, True, False, torch.float32, None, 3, [0, 2100]),
+    (128, 16, 1, 64, 256, 16, 64, False, True, torch.bfloat16, None, 1, list(range(0, 64 * 9, 9))),        # 64 rows
+    (128, 2, 2, 128, 64, 16, 0, False, False, torch.bfloat16, 40, 2, [33 * i for i in range(20)]),          # 20 rows, no positions
+]
+
+
+def fused_reference(h, layers, ctx_k, ctx_v, positions, Hq, Hkv, hd, rotary_dim, interleaved, theta, window):
+    """Plain float64 layers on the new tokens: h [M, D]; ctx_k/ctx_v[l][r]: the cached keys and values of request r."""
+    from tests.plain import qwen2_plain as P
+    M = h.shape[0]
+    new_k = [[None] * M for _ in layers]
+    new_v = [[None] * M for _ in layers]
+    for li, w in enumerate(layers):
+        x = P.plain_rmsnorm(h, w["n1"], w["eps1"])
+        qkv = P.plain_linear(x, w["w_qkv"], w["b_qkv"])
+        q = qkv[:, : Hq * hd].reshape(M, Hq, hd)
+        k = qkv[:, Hq * hd: (Hq + Hkv) * hd].reshape(M, Hkv, hd)
+        v = qkv[:, (Hq + Hkv) * hd:].reshape(M, Hkv, hd)
+        if rotary_dim:
+            q = P.plain_rope(q, positions, theta, rotary_dim, interleaved=interleaved)
+            k = P.plain_rope(k, positions, theta, rotary_dim, interleaved=interleaved)
+        att = torch.zeros(M, Hq * hd, dtype=h.dtype)
+        for r in range(M):
+            kk = torch.cat([ctx_k[li][r], k[r: r + 1]])
+            vv = torch.cat([ctx_v[li][r], v[r: r + 1]])
+            qq = torch.zeros(kk.shape[0], Hq, hd, dtype=h.dtype)
+            qq[-1] = q[r]
+            att[r] = P.plain_attention(qq, kk, vv, 1.0 / math.sqrt(hd), window)[-1].reshape(-1)
+            new_k[li][r], new_v[li][r] = k[r], v[r]
+        h = h + P.plain_linear(att, w["w_o"])
+        x = P.plain_rmsnorm(h, w["n2"], w["eps2"])
+        h = h + P.plain_swiglu(x, w["w_gate"], w["w_up"], w["w_down"])
+    return h, new_k, new_v
+
+
+@pytest.mark.parametrize("case", FUSED_CASES)
+def test_decode_layers_against_plain_layers(ops, case):
+    """The persistent kernel on its own, at sizes the engine's tests do not have: first tokens, page edges, a window's
+    edge, 64 rows, groups of 16, partial and interleaved rotation, float32 norm weights, no bias, no positions.  The
+    residual after the layers and the keys and values it wrote are compared with plain float64 layers.  Run twice:
+    the second launch finds the scratch and the counters as the first left them."""
+    D, Hq, Hkv, hd, I, page, rotary_dim, interleaved, bias, norm_dt, window, nl, contexts = case
+    M = len(contexts)
+    assert ops.decode_layers_supports(M, D, Hq, Hkv, hd, I, rotary_dim)
+    g = torch.Generator().manual_seed(50 + D)
+    bf = lambda t: t.to(torch.bfloat16)
+    rn = lambda *shape, s=1.0: torch.randn(*shape, generator=g) * s
+    theta = 10000.0
+    Nqkv = (Hq + 2 * Hkv) * hd
+    total_pages = sum(-(-(c + 1) // page) for c in contexts) + 2
+    perm = torch.randperm(total_pages, generator=g).tolist()
+    max_pages = max(-(-(c + 1) // page) for c in contexts) + 1
+    bt = torch.full((M, max_pages), -1, dtype=torch.int32)
+    for r, c in enumerate(contexts):
+        for lp in range(-(-(c + 1) // page)):
+            bt[r, lp] = perm.pop()
+    slot = torch.tensor([int(bt[r, c // page]) * page + c % page for r, c in enumerate(contexts)], dtype=torch.int32)
+    layers, ref_layers, caches, ctx_k, ctx_v = [], [], [], [], []
+    for li in range(nl):
+        w = dict(w_qkv=bf(rn(Nqkv, D, s=D ** -0.5)), w_o=bf(rn(D, Hq * hd, s=(Hq * hd) ** -0.5)),
+                 w_gate=bf(rn(I, D, s=D ** -0.5)), w_up=bf(rn(I, D, s=D ** -0.5)), w_down=bf(rn(D, I, s=I ** -0.5)),
+                 b_qkv=rn(Nqkv, s=0.3) if bias else None, n1=(1 + rn(D, s=0.1)).to(norm_dt), n2=(1 + rn(D, s=0.1)).to(norm_dt),
+                 eps1=1e-5, eps2=3e-6)
+        kc = torch.full((total_pages * page, Hkv, hd), float("nan"))       # rows that no request owns stay NaN
+        vc = torch.full((total_pages * page, Hkv, hd), float("nan"))
+        ks, vs = [], []
+        for r, c in enumerate(contexts):
+            k, v = bf(rn(c, Hkv, hd)).float(), bf(rn(c, Hkv, hd)).float()
+            if c > 3:           # a far key that matters: a piece that is lost or weighted wrongly shows
+                k[2] = 0.0
+                k[2, :, 0] = 6.0
+                v[2] = 4.0
+            for pos in range(c):
+                at = int(bt[r, pos // page]) * page + pos % page
+                kc[at], vc[at] = k[pos], v[pos]
+            ks.append(k.double())
+            vs.append(v.double())
+        ctx_k.append(ks)
+        ctx_v.append(vs)
+        kc, vc = bf(kc).to(dev()), bf(vc).to(dev())
+        caches.append((kc, vc))
+        dw = {k: (v.to(dev()) if isinstance(v, torch.Tensor) else v) for k, v in w.items()}
+        layers.append(dict(w_qkv=dw["w_qkv"], w_o=dw["w_o"],
+                           w_gate_up=torch.stack([dw["w_gate"], dw["w_up"]], dim=1).reshape(2 * I, D).contiguous(),
+                           w_down=dw["w_down"], b_qkv=dw["b_qkv"], norm1_w=dw["n1"], norm2_w=dw["n2"], k_cache=kc, v_cache=vc,
+                           eps1=w["eps1"], eps2=w["eps2"], window=window or 0, group=0))
+        ref_layers.append({k: (v.double() if isinstance(v, torch.Tensor) else v) for k, v in w.items()})
+    h0 = rn(M, D, s=2.0)
+    positions = torch.tensor(contexts, dtype=torch.int32)
+    want, new_k, new_v = fused_reference(h0.double(), ref_layers, ctx_k, ctx_v, positions.long(), Hq, Hkv, hd, rotary_dim,
+                                         interleaved, theta, window)
+    desc = ops.decode_layers_descriptors(layers, D, Hq, Hkv, hd, I, dev())
+    counters = ops.decode_layers_counters(dev())
+    nsplit = 5 if max(contexts) > 256 else 2
+    scratch = torch.full((ops.decode_layers_scratch_floats(M, Hq, Hkv, hd, I, nsplit),), float("nan"), device=dev())
+    table = None
+    if rotary_dim:
+        inv_freq = (1.0 / theta ** (torch.arange(0, rotary_dim, 2, dtype=torch.float64) / rotary_dim)).float().to(dev())
+        table = ops.rope_table(positions.to(dev()), inv_freq)
+    for attempt in range(2):
+        h = h0.clone().to(dev())
+        ops.decode_layers(desc, nl, h, D, Hq, Hkv, hd, I, rotary_dim, interleaved, 1.0 / math.sqrt(hd), table,
+                          positions.to(dev()), [bt.to(dev())], [slot.to(dev())], max_pages, page, nsplit, scratch, counters)
+        ops.check_async_errors(dev())
+        assert counters.cpu().tolist() == [0, 0]
+        got = h.cpu().double()
+        assert not torch.isnan(got).any()
+        scale = float(want.abs().max())
+        err = float((got - want).abs().max())
+        assert err <= 3e-2 * scale, f"attempt {attempt}: residual differs by {err} (largest value {scale})"
+        for li, (kc, vc) in enumerate(caches):
+            for r in range(M):
+                at = int(slot[r])
+                assert torch.allclose(kc[at].cpu().double(), new_k[li][r], atol=3e-2, rtol=3e-2), (li, r)
+                assert torch.allclose(vc[at].cpu().double(), new_v[li][r], atol=3e-2, rtol=3e-2), (li, r)
+
+
+def test_decode_layers_refuses_what_it_cannot_run(ops):
+    assert not ops.decode_layers_supports(65, 128, 2, 2, 64, 64, 64)          # too many rows
+    assert not ops.decode_layers_supports(4, 128, 2, 2, 48, 64, 48)           # a head size without a kernel
+    assert not ops.decode_layers_supports(4, 132, 2, 2, 64, 64, 64)           # a width whose rows are not 16-byte multiples
+    assert not ops.decode_layers_supports(4, 128, 34, 2, 64, 64, 64)          # groups of 17
+    h = torch.zeros((4, 128), dtype=torch.float32, device=dev())
+    i32 = torch.zeros((4, 1), dtype=torch.int32, device=dev())
+    with pytest.raises(ops.KernelError, match="unsupported sizes"):
+        ops.decode_layers(torch.zeros(1024, dtype=torch.uint8, device=dev()), 1, h, 128, 2, 2, 48, 64, 48, False, 1.0, None,
+                          i32.view(-1), [i32], [i32.view(-1)], 1, 16, 1, torch.zeros(8, device=dev()),
+                          ops.decode_layers_counters(dev()))
