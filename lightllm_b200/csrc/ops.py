@@ -520,9 +520,11 @@ def decode_layers_counters(device) -> torch.Tensor:
 def decode_layers(descriptors: torch.Tensor, num_layers: int, residual: torch.Tensor, D: int, Hq: int, Hkv: int, hd: int,
                   I: int, rotary_dim: int, interleaved: bool, scale: float, rope_table: Optional[torch.Tensor],
                   span_pos: torch.Tensor, block_tables, slot_mappings, max_pages: int, page_size: int, nsplit: int,
-                  scratch: torch.Tensor, counters: torch.Tensor) -> None:
+                  scratch: torch.Tensor, counters: torch.Tensor, timeline: Optional[torch.Tensor] = None,
+                  timeline_block: int = 0) -> None:
     """All layers of a decode step (one token per request, at most 64) in one persistent kernel, in place on the
-    float32 ``residual`` [M, D].  ``block_tables`` / ``slot_mappings``: one int32 tensor per cache group (up to 4)."""
+    float32 ``residual`` [M, D].  ``block_tables`` / ``slot_mappings``: one int32 tensor per cache group (up to 4).
+    ``timeline`` (int64, 2 * (2 + 64 * layers) words) receives the milestones of block ``timeline_block`` as (label, SM cycle) pairs."""
     M = residual.shape[0]
     if residual.dtype != torch.float32 or tuple(residual.shape) != (M, D):
         raise KernelError(f"decode_layers: residual must be float32 [{M},{D}]")
@@ -535,7 +537,8 @@ def decode_layers(descriptors: torch.Tensor, num_layers: int, residual: torch.Te
     _check(lib().llb_decode_layers(
         _ptr(descriptors), num_layers, _ptr(residual), M, D, Hq, Hkv, hd, I, rotary_dim, 1 if interleaved else 0,
         ctypes.c_float(scale), _ptr(rope_table), _i32(span_pos, "span_pos"), *bts, *sms, max_pages, page_size, nsplit,
-        _ptr(scratch), scratch.numel(), _ptr(counters), _ptr(async_error_flag(residual.device)), _stream()))
+        _ptr(scratch), scratch.numel(), _ptr(counters), _ptr(async_error_flag(residual.device)), _ptr(timeline),
+        timeline_block, _stream()))
 
 
 def selftest_wait_expires(device: torch.device, limit_cycles: int = 1_000_000) -> torch.Tensor:
