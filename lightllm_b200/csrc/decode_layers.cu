@@ -135,7 +135,7 @@ __device__ __forceinline__ void worker_sync() { asm volatile("bar.sync 1, 256;" 
 // Milestones of block 0 for tuning, in cycles of its SM: label = layer * 100 + stage * 10 + what (1 operands built,
 // 2 drained / items done, 3 past the barrier; 5-7 inside a batch: slots free, operands stored, arrivals made).  Off (a null pointer) in normal use.
 __device__ __forceinline__ void stamp(const FusedParams& p, unsigned& n, int label) {
-    if (p.timeline != nullptr && (int)blockIdx.x == (p.timeline_block & 0xffff) && threadIdx.x == 64) {
+    if (p.timeline != nullptr && (int)blockIdx.x == p.timeline_block && threadIdx.x == 64) {
         p.timeline[2 * n] = (unsigned long long)label;
         p.timeline[2 * n + 1] = (unsigned long long)clock64();
         ++n;
@@ -514,8 +514,10 @@ __device__ __forceinline__ void attention_prefetch(const FusedParams& p, const L
     if (wt >= KV_THREADS) return;
     const int warp = wt >> 5, lane = wt & 31;
     const ItemGeom g = item_geom<BK>(p, L, item);
-    const int kb_first = g.klo + warp * BK;
-    if (kb_first < g.khi) issue_kv_tile<HD>(p, L, g, smem_u32(attn) + warp * 4 * TILE_BYTES, 0, kb_first, lane);
+    const int kb_first = g.klo + warp * BK, kb_second = kb_first + (KV_THREADS / 32) * BK;
+    const uint32_t wbase = smem_u32(attn) + warp * 4 * TILE_BYTES;
+    if (kb_first < g.khi) issue_kv_tile<HD>(p, L, g, wbase, 0, kb_first, lane);
+    if (kb_second < g.khi) issue_kv_tile<HD>(p, L, g, wbase, 1, kb_second, lane);     // both of the warp's buffers
 }
 
 template <int HD>
@@ -617,7 +619,8 @@ __device__ void attention_item(const FusedParams& p, const LayerCache& L, int it
         for (int kb = kb_first; kb < khi; kb += KVW * BK) {
             const int kb_next = kb + KVW * BK;
             if (kb_next < khi) {
-                issue_kv_tile<HD>(p, L, geo, wbase, buf ^ 1, kb_next, lane);
+                // (a prefetched item already has its second tile on the way)
+                if (!(prefetched && kb == kb_first)) issue_kv_tile<HD>(p, L, geo, wbase, buf ^ 1, kb_next, lane);
                 cp_async_wait<1>();
             } else {
                 cp_async_wait<0>();
@@ -750,11 +753,16 @@ __device__ void attention_item(const FusedParams& p, const LayerCache& L, int it
 template <int BN, int STAGES, int HD>
 __global__ void __launch_bounds__(NUM_THREADS, 1) decode_layers_kernel(const FusedParams p) {
     constexpr uint32_t B_BYTES = BN * TILE_K * 2;
-    constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+    // Two units are in flight (one being drained): 2 x BN columns of tensor memory.  (Four accumulators per unit, one per
+    // K step, were tried: the instructions are not paced by their dependency on one accumulator, about 170 cycles each
+    // either way.)
+    constexpr int NACC = 1;
+    constexpr uint32_t TMEM_COLS = 2 * NACC * BN < 32 ? 32 : 2 * NACC * BN;
     constexpr int WORKER_WARPS = WORKERS / 32;
     __shared__ __align__(8) uint64_t full_a[STAGES], full_b[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_s;
+    __shared__ volatile int wait_ok[2];   // what the polling worker warp found, for the warps parked meanwhile (used in turn)
     __shared__ BlockPlan plan;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -788,23 +796,41 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) decode_layers_kernel(const Fus
 
     if (warp == 0) {
         // ---- weight tiles, in the order in which the block will use them, as far ahead as the ring allows ----------
+        // A second cursor runs one ring further ahead and only asks for its tiles into L2, so that a slot that comes free
+        // is refilled from there and not from memory.
         if (lane == 0) {
-            uint32_t it = 0;
-            bool ok = true;
-            for (int l = 0; l < p.num_layers && ok; ++l) {
-                const LayerDesc* L = p.layers + l;
-                for (int st = 0; st < 4 && ok; ++st) {
-                    const CUtensorMap* map = stage_map(L, st);
-                    const int NKB = plan.NKB[st];
-                    int nt = plan.nt_first[st], kb = plan.kb_first[st];
-                    for (int i = 0; i < plan.n_tiles[st]; ++i, ++it) {
-                        const int s = it % STAGES;
-                        if (!mbar_wait(&empty_bar[s], ((it / STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
-                        mbar_expect_tx(&full_a[s], A_BYTES);
-                        tma_load_2d(a_tiles + s * A_BYTES, map, kb * TILE_K, nt * TILE_M, &full_a[s]);
-                        if (++kb == NKB) { kb = 0; ++nt; }
+            struct Cursor {
+                int l, st, i, nt, kb;
+                __device__ __forceinline__ bool valid(const FusedParams& p) const { return l < p.num_layers; }
+                __device__ __forceinline__ void settle(const FusedParams& p, const BlockPlan& plan) {     // skip empty stages
+                    while (l < p.num_layers && i >= plan.n_tiles[st]) {
+                        i = 0;
+                        if (++st == 4) { st = 0; ++l; }
+                        nt = plan.nt_first[st]; kb = plan.kb_first[st];
                     }
                 }
+                __device__ __forceinline__ void advance(const FusedParams& p, const BlockPlan& plan) {
+                    ++i;
+                    if (++kb == plan.NKB[st]) { kb = 0; ++nt; }
+                    settle(p, plan);
+                }
+            };
+            Cursor cur = {0, 0, 0, plan.nt_first[0], plan.kb_first[0]}, ahead = cur;
+            cur.settle(p, plan);
+            ahead.settle(p, plan);
+            for (int k = 0; k < STAGES && ahead.valid(p); ++k) ahead.advance(p, plan);
+            uint32_t it = 0;
+            while (cur.valid(p)) {
+                const int s = it % STAGES;
+                if (!mbar_wait_polite(&empty_bar[s], ((it / STAGES) & 1) ^ 1, abort_flag)) break;
+                mbar_expect_tx(&full_a[s], A_BYTES);
+                tma_load_2d(a_tiles + s * A_BYTES, stage_map(p.layers + cur.l, cur.st), cur.kb * TILE_K, cur.nt * TILE_M, &full_a[s]);
+                if (ahead.valid(p)) {
+                    tma_prefetch_2d(stage_map(p.layers + ahead.l, ahead.st), ahead.kb * TILE_K, ahead.nt * TILE_M);
+                    ahead.advance(p, plan);
+                }
+                cur.advance(p, plan);
+                ++it;
             }
         }
     } else if (warp == 1) {
@@ -821,21 +847,21 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) decode_layers_kernel(const Fus
                     for (int i = 0; i < total && ok;) {
                         const int n = min(NKB - kb0, total - i);
                         const int buf = ua & 1;
-                        ok = mbar_wait(&acc_empty[buf], ((ua >> 1) & 1) ^ 1, abort_flag);
+                        ok = mbar_wait_polite(&acc_empty[buf], ((ua >> 1) & 1) ^ 1, abort_flag);
                         for (int k = 0; k < n && ok; ++k, ++it) {
                             const int s = it % STAGES;
-                            ok = mbar_wait(&full_a[s], (it / STAGES) & 1, abort_flag) &&
-                                 mbar_wait(&full_b[s], (it / STAGES) & 1, abort_flag);
+                            ok = mbar_wait_polite(&full_a[s], (it / STAGES) & 1, abort_flag) &&
+                                 mbar_wait_polite(&full_b[s], (it / STAGES) & 1, abort_flag);
                             if (!ok) break;
                             tc_fence_after();
                             const uint64_t da = desc_kmajor(a_base + s * A_BYTES), db = desc_kmajor(b_base + s * B_BYTES);
-                            const uint32_t d = tmem_base + buf * BN;
+                            const uint32_t d = tmem_base + buf * NACC * BN;
                             // the four K steps of a tile: 32 bytes further along the swizzled rows each (2 in descriptor units)
                             if (k == 0) umma_bf16_first(d, da, db, idesc); else umma_bf16_acc(d, da, db, idesc);
                             umma_bf16_acc(d, da + 2, db + 2, idesc);
                             umma_bf16_acc(d, da + 4, db + 4, idesc);
                             umma_bf16_acc(d, da + 6, db + 6, idesc);
-                            umma_commit(&empty_bar[s]);
+                            umma_commit(&empty_bar[s]);          // the slot is free when these four have read it
                         }
                         if (ok) umma_commit(&acc_full[buf]);
                         ++ua;
@@ -852,20 +878,39 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) decode_layers_kernel(const Fus
         const int col_half = (warp - 2) >> 2;    // two warps share a quarter: each drains half of the columns
         uint32_t it = 0, ua = 0;
         unsigned epoch = 0, stamps = 0;
-        int label = 0;
+        int label = 0, wsel = 0;
 
         // Drain accumulator `u` (row tile nt of a stage with N outputs) into target [M, N] by atomic adds.
         auto drain = [&](uint32_t u, int nt, int N, float* target) {
             const int buf = u & 1;
-            const bool ok = __all_sync(0xffffffffu, mbar_wait(&acc_full[buf], (u >> 1) & 1, abort_flag));
+            // One warp polls (on a scheduler that it shares with no other role); the others are parked at the barrier and
+            // take no issue slots from the roles that work meanwhile.
+            if (warp == 2) {
+                const bool done = mbar_wait_polite(&acc_full[buf], (u >> 1) & 1, abort_flag);
+                if (lane == 0) wait_ok[wsel] = done ? 1 : 0;
+            }
+            worker_sync();
+            const bool ok = wait_ok[wsel] != 0;
+            wsel ^= 1;
             tc_fence_after();
             const int n = nt * TILE_M + quarter * 32 + lane;
-            const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
+            const uint32_t taddr = tmem_base + buf * NACC * BN + ((uint32_t)(quarter * 32) << 16);
             float* out = target + n;
+            // the four accumulators of the unit, 16 columns (tokens) at a time
+            auto load_sum = [&](int c0, float (&v)[16]) {
+                float w[16];
+                tmem_ld16(taddr + c0, v);
+#pragma unroll
+                for (int a = 1; a < NACC; ++a) {
+                    tmem_ld16(taddr + a * BN + c0, w);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] += w[j];
+                }
+            };
             if (ok) {      // uniform over the warp: tcgen05.ld is a warp-wide instruction
                 if (BN == 16) {          // one group of 16 columns: each of the two warps adds eight of them
                     float v[16];
-                    tmem_ld16(taddr, v);
+                    load_sum(0, v);
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         const int m = col_half * 8 + j;
@@ -875,7 +920,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) decode_layers_kernel(const Fus
 #pragma unroll 1
                     for (int c0 = col_half * 16; c0 < BN && c0 < p.M; c0 += 32) {
                         float v[16];
-                        tmem_ld16(taddr + c0, v);
+                        load_sum(c0, v);
 #pragma unroll
                         for (int j = 0; j < 16; ++j)
                             if (c0 + j < p.M && n < N) red_add(out + (size_t)(c0 + j) * N, v[j]);
@@ -908,12 +953,18 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) decode_layers_kernel(const Fus
                 // The stage's first tiles find their slots free: every accumulator of the stage before was drained before
                 // the blocks met, so every earlier tensor-core instruction has completed.  Later batches wait (one lane;
                 // the warp follows it).
-                if (lane == 0 && jb > 0)
-                    for (int j = jb; j < je; ++j) {
-                        const uint32_t at = it + j;
-                        live = mbar_wait(&empty_bar[at % STAGES], ((at / STAGES) & 1) ^ 1, abort_flag) && live;
+                if (jb > 0) {
+                    if (warp == 2) {
+                        for (int j = jb; j < je; ++j) {
+                            const uint32_t at = it + j;
+                            live = mbar_wait_polite(&empty_bar[at % STAGES], ((at / STAGES) & 1) ^ 1, abort_flag) && live;
+                        }
+                        if (lane == 0) wait_ok[wsel] = live ? 1 : 0;
                     }
-                live = __shfl_sync(0xffffffffu, live ? 1 : 0, 0) != 0;
+                    worker_sync();
+                    live = wait_ok[wsel] != 0;
+                    wsel ^= 1;
+                }
                 stamp(p, stamps, label + 5);
                 Batch b;
                 if (jb == 0) { b.kb0 = kb_first; b.nt0 = nt_first; }
@@ -934,7 +985,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) decode_layers_kernel(const Fus
             it += n_tiles;
             ua += units;
             stamp(p, stamps, label + 1);
-            for (; next_drain < units; ++next_drain) drain(u0 + next_drain, nt_first + next_drain, si.N, target);
+            for (; next_drain < units; ++next_drain)
+                drain(u0 + next_drain, nt_first + next_drain, si.N, target);
             stamp(p, stamps, label + 2);
         };
         auto zero_range = [&](float* buf, int lo, int hi) {        // this block's part of a scratch array

@@ -60,6 +60,23 @@ __device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, 
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
     return mbar_wait_limit(bar, parity, abort_flag, WAIT_LIMIT_CYCLES);
 }
+// The same for a role that may wait long beside warps that work: between attempts the warp sleeps a few dozen
+// nanoseconds, so that its polling does not take the scheduler's issue slots from the warps it shares it with.
+__device__ __forceinline__ bool mbar_wait_polite(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (unsigned spins = 1;; ++spins) {
+        __nanosleep(32);
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spins & 63u) == 0u) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+}
 // The same on a barrier given by its shared-memory address (for loops that carry the address in a register).
 __device__ __forceinline__ bool mbar_try_wait_addr(uint32_t bar_addr, uint32_t parity) {
     uint32_t ok;
@@ -90,6 +107,10 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
         : "memory");
+}
+// Ask for a tile into L2 only (no shared memory, no barrier): a later load of the same tile finds it there.
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int x, int y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
 }
 // TMA stores from a shared-memory tile (bulk async-group completion): plain, and adding into float global memory.
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t smem_addr, int x, int y) {

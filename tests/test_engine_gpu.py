@@ -351,6 +351,42 @@ def test_decode_over_many_keys_merged_through_scratch(tmp_path, monkeypatch):
     core.runner.check_device_errors()
 
 
+@pytest.mark.parametrize("name,rows", [("D", 3), ("D", 40), ("E", 17)])
+def test_decode_steps_through_the_persistent_kernel(tmp_path, name, rows):
+    """Decode steps of several requests with contexts of different lengths (a first token, page edges, the window's
+    edge on tiny D) run the layers as one persistent kernel; the logits are the plain implementation's.  With 40
+    rows the step is beyond the size up to which the engine chooses that kernel by itself, so the limit is raised."""
+    d = model_dir(tmp_path, name, seed=17, store="bfloat16", edit=sharpen(4.0))
+    cfg, w = P.read_model_dir(d)
+    rng = random.Random(18)
+    V, page = cfg["vocab_size"], PAGE_SIZE[name]
+    lens = [1 + (37 * i) % 200 for i in range(rows)]
+    lens[0], lens[-1] = 1, 2 * page          # a request whose first token is decoded alone; one at a page's edge
+    seqs = {i: [rng.randrange(V) for _ in range(n + 6)] for i, n in enumerate(lens)}
+    ref = {i: P.plain_forward(cfg, w, s) for i, s in seqs.items()}
+    core = EngineCore(d, EngineOptions(dtype="bfloat16", max_seq_len=256, max_batch_tokens=512, page_size=page,
+                                       num_pages=rows * (-(-206 // page) + 1), max_seqs=rows))
+    assert core.runner.fused.enabled and core.runner.fused.segment_at(0).end == cfg["num_hidden_layers"]
+    core.runner.fused.max_rows = 64
+    for i, n in enumerate(lens):
+        core.open(i)
+        if n > 1:
+            core.step([StepEntry(i, seqs[i][: n - 1], [])])
+    before = core.launch_count()
+    tol = atol_for(name, "bfloat16", ref)
+    worst = 0.0
+    for t in range(6):
+        lg = core.step([StepEntry(i, [seqs[i][lens[i] - 1 + t]], [0]) for i in range(rows)]).float().cpu()
+        for i in range(rows):
+            err = float((lg[i] - ref[i][lens[i] - 1 + t]).abs().max())
+            worst = max(worst, err)
+            assert err <= tol, f"tiny {name}: step {t}, request {i} at position {lens[i] - 1 + t}: {err}"
+    record(f"persistent decode tiny {name} {rows} rows", worst, logits_std(ref))
+    # embedding, rotation table, the layers, final norm, head: five launches a step (the first steps are not yet graphs)
+    assert core.launch_count() - before <= 8 * 6
+    core.runner.check_device_errors()
+
+
 def test_temperature_sampling_is_seeded_and_per_request(tmp_path):
     d = model_dir(tmp_path, "A", store="bfloat16")
     eng = Engine(d, dtype="bfloat16", max_seq_len=128, max_batch_tokens=64, num_pages=40, max_seqs=4)
