@@ -15,6 +15,9 @@ FLOAT32_ATOL = 1e-4
 
 # measured worst relative errors (see the docstring); a test prints its own worst so that these can be checked again
 BF16_WORST_REL = {"A": 0.125, "B": 0.125, "C": 0.125, "D": 0.125, "E": 0.125,
+                  # the same models with their q and k projections scaled up (sharp attention: a lost key shows, and
+                  # rounding of the scores weighs more)
+                  "A sharp": 0.125, "C sharp": 0.125, "D sharp": 0.125, "E sharp": 0.125,
                   "toy": 0.125,        # the toy architectures of test_engine_gpu.py
                   "real": 0.125}       # two layers at the 0.5B sizes (test_real_sizes_gpu.py)
 
