@@ -2,6 +2,7 @@
 """Benchmark of the engine on one B200: decode tokens a second at Qwen2.5-0.5B sizes.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L]
+    python bench.py --sizes 1.5b|7b          (the larger sizes of the family: a line of their own)
 
 Prints one JSON line.  ``value`` is decoded tokens a second over K timed decode steps of a
 batch of 8 requests that each hold a 2,048-token prompt (random weights, random token ids),
@@ -32,6 +33,12 @@ QWEN25_05B = {
     "tie_word_embeddings": True, "max_position_embeddings": 32768, "sliding_window": 32768,
     "max_window_layers": 24, "use_sliding_window": False, "hidden_act": "silu",
 }
+# The larger sizes BASELINE.json lists (its configs[3] and configs[4]), measured with `--sizes`.
+QWEN25_15B = dict(QWEN25_05B, num_hidden_layers=28, hidden_size=1536, num_attention_heads=12, num_key_value_heads=2,
+                  head_dim=128, intermediate_size=8960, max_window_layers=28)
+QWEN25_7B = dict(QWEN25_05B, num_hidden_layers=28, hidden_size=3584, num_attention_heads=28, num_key_value_heads=4,
+                 head_dim=128, intermediate_size=18944, vocab_size=152064, tie_word_embeddings=False, max_window_layers=28)
+SIZES = {"0.5b": QWEN25_05B, "1.5b": QWEN25_15B, "7b": QWEN25_7B}
 PROMPT_LEN = 2048
 CONTEXT_LEN = 4096
 PAGE_SIZE = 16
@@ -101,7 +108,7 @@ def make_model_dir(layers: int) -> str:
 def flops_prefill(cfg, layers, T):
     D, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
     Hq, Hkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
-    hd = D // Hq
+    hd = cfg.get("head_dim", D // Hq)
     linear = 2 * T * (D * (Hq + 2 * Hkv) * hd + Hq * hd * D + 3 * D * I)
     attn = 2 * 2 * Hq * hd * T * (T + 1) // 2      # QK^T and PV over the causal half
     return layers * (linear + attn) + 2 * D * V    # head for the last row
@@ -199,6 +206,74 @@ def time_e2e(engine, batch, steps, warmup, rng):
     return batch * steps / dt, h2d, 4 * batch
 
 
+def time_mixed(engine, requests, lo, hi, new_tokens, rng):
+    """BASELINE.json configs[3]'s workload through the serve loop: `requests` prompts with lengths uniform in
+    [lo, hi], all submitted at once, prompt portions under the loop's token budget beside decoded tokens,
+    `new_tokens` tokens each (the reference measures the same way, tools/bench_mixed_lengths.cpp)."""
+    import torch
+    V = engine.vocab_size
+    loop = engine.new_loop()
+    loop.measure_device = True
+    lens = [rng.randint(lo, hi) for _ in range(requests)]
+    for n in lens:
+        loop.submit([rng.randrange(V) for _ in range(n)], max_new_tokens=new_tokens, eos_token_id=-1, temperature=0.0)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    loop.run()
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    busy = loop.device_busy_ms() / 1000.0
+    steps = loop.step_metrics
+    return {"requests": requests, "prompt_tokens": sum(lens), "generated": loop.total_tokens_generated(),
+            "steps": len(steps), "seconds": round(wall, 3),
+            "generated_tok_s": round(loop.total_tokens_generated() / wall, 1),
+            "all_tok_s": round((sum(lens) + loop.total_tokens_generated()) / wall, 1),
+            "ms_per_step": round(1000.0 * wall / max(1, len(steps)), 3),
+            "host_share": round(max(0.0, 1.0 - busy / wall), 3),
+            "ttft_ms_p50": round(loop.stat("ttft", 50), 1), "tpot_ms_p50": round(loop.stat("tpot", 50), 2)}
+
+
+def run_sizes(name: str, steps: int, warmup: int) -> int:
+    """Decode at batch 1 / 8 / 64 and a 2,048-token prefill at one of the larger sizes, with their roofline
+    fractions, and for the 1.5B sizes the mixed workload.  Weights are drawn on the device."""
+    import torch
+    from lightllm_b200 import Engine
+    from lightllm_b200.models import random_model_on_device
+    cfg = SIZES[name]
+    pk = peaks()
+    rng = random.Random(0)
+    device = torch.device("cuda:0")
+    torch.cuda.set_device(device)
+    model = random_model_on_device(dict(cfg), 0, "bfloat16", device)
+    max_batch = 64
+    engine = Engine(None, dtype="bfloat16", max_seq_len=CONTEXT_LEN + 512, max_batch_tokens=4 * PROMPT_LEN, page_size=PAGE_SIZE,
+                    num_pages=max_batch * (PROMPT_LEN + 512) // PAGE_SIZE, max_seqs=max_batch, chunk_size=PROMPT_LEN,
+                    model=model)
+    core = engine.core
+    out = {"sizes": name, "dtype": "bf16", "data": "synthetic: random weights drawn on the device (seed 0)",
+           "config": {"layers": cfg["num_hidden_layers"], "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+                      "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg.get("head_dim", 64),
+                      "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+                      "tied_embeddings": cfg["tie_word_embeddings"], "prompt_len": PROMPT_LEN, "page_size": PAGE_SIZE},
+           "peaks": pk["source"], "decode": {}}
+    for b in (1, 8, 64):
+        ms, _, ctx = time_decode(core, b, steps, warmup, rng)
+        gbs = decode_bytes(core, b, ctx) / (ms * 1e-3) / 1e9
+        out["decode"][f"b{b}"] = {"tok_s": round(b * 1000.0 / ms, 1), "ms_per_step": round(ms, 4), "gb_s": round(gbs, 1),
+                                  "frac_of_hbm": round(gbs / pk["hbm_gbs"], 4)}
+    pre_ms = time_prefill(core, 4, 3, rng)
+    fl = flops_prefill(cfg, cfg["num_hidden_layers"], PROMPT_LEN)
+    out["prefill"] = {"tok_s": round(PROMPT_LEN * 1000.0 / pre_ms, 1), "ms": round(pre_ms, 3),
+                      "frac_of_bf16_peak": round(fl / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+    if name == "1.5b":
+        del engine, core
+        mixed = Engine(None, dtype="bfloat16", max_seq_len=4096 + 128 + 16, max_batch_tokens=2048, page_size=PAGE_SIZE,
+                       num_pages=32 * (4096 + 256) // PAGE_SIZE, max_seqs=32, chunk_size=2048, model=model)
+        out["mixed"] = time_mixed(mixed, 32, 64, 4096, 128, rng)
+    print(json.dumps(out))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -208,6 +283,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=QWEN25_05B["num_hidden_layers"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (for profiling runs)")
+    ap.add_argument("--sizes", choices=["1.5b", "7b"], default=None,
+                    help="measure at the Qwen2.5-1.5B or 7B layer sizes instead (a line of its own, not the bench record)")
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="run one part only and print a short line (for profiling runs, not a bench record)")
     args = ap.parse_args()
@@ -221,6 +298,8 @@ def main() -> int:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     args.warmup = max(3, args.warmup)
+    if args.sizes:
+        return run_sizes(args.sizes, min(args.steps, 64), args.warmup)
 
     import torch
     from lightllm_b200 import Engine

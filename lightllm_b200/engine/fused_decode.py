@@ -28,6 +28,12 @@ MAX_ROWS = 64          # what the kernel takes
 # the 0.5B sizes: 0.72 / 0.77 / 0.88 / 1.12 ms a step at 1 / 8 / 16 / 32 rows against 0.80 / 0.90 / 1.00 / 1.17; at 64 rows
 # 1.66 against 1.54, where the attention's keys and the operands of 64 rows outweigh the saved launches).
 DEFAULT_ROWS = 32
+# The kernel pays where a layer is paced by its chain of stages, not by its bytes: up to this many bytes of weights a
+# layer.  Measured: 30 MB a layer (0.5B sizes) 0.72 ms a step at one row against 0.80 launched kernel by kernel; 93 MB
+# (1.5B) 1.36 against 1.33 at one row and 1.57 against 1.81 at eight; 404 MB (7B) 4.5 against 3.1: there the separate
+# kernels stream their weights at 0.7 of the memory's bandwidth, which one block per multiprocessor walking through
+# build, multiply and drain does not reach.
+MAX_LAYER_BYTES = 128 << 20
 
 
 def _layer_facts(block, view):
@@ -107,7 +113,7 @@ class FusedDecode:
             facts = [None] * len(facts)
         i = 0
         while i < len(facts):
-            if facts[i] is None or not self._sizes_ok(facts[i][0]):
+            if facts[i] is None or not self._sizes_ok(facts[i][0]) or self._layer_bytes(facts[i][1]) > MAX_LAYER_BYTES:
                 i += 1
                 continue
             j = i
@@ -116,6 +122,10 @@ class FusedDecode:
             self.segments[i] = Segment(i, j, facts[i][0], [f[1] for f in facts[i:j]], facts[i][2], device)
             i = j
         self.enabled = any(s is not None for s in self.segments)
+
+    @staticmethod
+    def _layer_bytes(tensors) -> int:
+        return sum(tensors[k].numel() * tensors[k].element_size() for k in ("w_qkv", "w_o", "w_gate_up", "w_down"))
 
     @staticmethod
     def _sizes_ok(sizes) -> bool:

@@ -105,6 +105,8 @@ class BatchMainLoop:
         self._pinned = [torch.empty(engine.runner.max_spans, dtype=torch.int32).pin_memory() for _ in range(2)]
         self._pin_turn = 0
         self.steps_ahead = 0             # steps that were launched before their predecessor's ids were read
+        self.measure_device = False      # with it, every step is bracketed by events: see device_busy_ms()
+        self._device_spans = []
 
     def wall_clock(self) -> float:
         return time.perf_counter() - self._epoch
@@ -182,6 +184,9 @@ class BatchMainLoop:
     def _launch(self, sched: ScheduleStep, entries, wanting, device_tokens=None) -> _InFlight:
         """Run the step and sample; the ids start their way to the host.  The scheduler's first half of the
         accounting (the tokens are in the cache) is done here."""
+        if self.measure_device:
+            begin = torch.cuda.Event(enable_timing=True)
+            begin.record()
         logits = self.engine.step(entries, device_tokens) if device_tokens is not None else self.engine.step(entries)
         tokens_dev = tokens_host = ready = None
         if wanting:
@@ -191,6 +196,10 @@ class BatchMainLoop:
             tokens_host.copy_(tokens_dev, non_blocking=True)
             ready = torch.cuda.Event()
             ready.record()
+        if self.measure_device:
+            end = torch.cuda.Event(enable_timing=True)
+            end.record()
+            self._device_spans.append((begin, end))
         self.scheduler.advance(sched)
         return _InFlight(sched, wanting, tokens_dev, tokens_host, ready)
 
@@ -261,6 +270,12 @@ class BatchMainLoop:
         if not vals:
             return 0.0
         return sum(vals) / len(vals) if p is None else percentile(vals, p)
+
+    def device_busy_ms(self) -> float:
+        """With ``measure_device``: the time the device spent between the first and the last kernel of every step so
+        far, summed; what is missing to the wall clock is the time it waited for the host between steps."""
+        torch.cuda.synchronize()
+        return sum(b.elapsed_time(e) for b, e in self._device_spans)
 
     def throughput_tok_s(self) -> float:
         t = self.wall_clock()

@@ -21,16 +21,17 @@ class Engine:
 
     ``model_dir`` holds ``config.json`` and ``model.safetensors``; the architecture is chosen by
     ``config.json``.  ``dtype`` is ``"bfloat16"`` (serving) or ``"float32"`` (true 32-bit
-    everywhere).  ``max_seq_len`` <= 0 means the model's own limit.  ``decode_ahead`` lets the serve loop
+    everywhere).  ``model``: a model that is already bound on the device (then ``model_dir`` is not read).
+    ``max_seq_len`` <= 0 means the model's own limit.  ``decode_ahead`` lets the serve loop
     launch a decode step before the ids of the step before it have reached the host."""
 
     def __init__(self, model_dir: str, dtype: str = "bfloat16", max_seq_len: int = 0, max_batch_tokens: int = 256,
                  kv_cache_mb: Optional[float] = None, page_size: int = 16, num_pages: Optional[int] = None,
                  max_seqs: int = 64, chunk_size: int = 16, max_prefill_entries: int = 999, device: str = "cuda:0",
-                 decode_ahead: bool = True):
+                 decode_ahead: bool = True, model=None):
         self.core = EngineCore(model_dir, EngineOptions(
             dtype=dtype, max_seq_len=max_seq_len, max_batch_tokens=max_batch_tokens, page_size=page_size,
-            num_pages=num_pages, kv_cache_mb=kv_cache_mb, max_seqs=max_seqs, device=device))
+            num_pages=num_pages, kv_cache_mb=kv_cache_mb, max_seqs=max_seqs, device=device), model=model)
         self.chunk_size = chunk_size
         self.max_batch_tokens = max_batch_tokens
         self.max_prefill_entries = max_prefill_entries

@@ -123,6 +123,37 @@ def compute_dtype(name) -> torch.dtype:
         raise ValueError(f"dtype must be 'float32' or 'bfloat16', got {name!r}") from None
 
 
+def random_model_on_device(config, seed: int, dtype, device: torch.device) -> Model:
+    """A model of ``config`` (a config.json dictionary or its typed form) with random weights drawn on the device:
+    for measurements at sizes whose weights would take minutes to write and read as a folder.  The distributions are
+    those of the random-weights mode (each part's weight list says them); the values are not the folder's."""
+    import hashlib
+    from ..config import config_from_dict
+    if isinstance(config, dict):
+        config = config_from_dict(config, "random-weights configuration")
+    model = Model(model_spec_for(config))
+    model.config = config
+    dt = compute_dtype(dtype)
+    tensors: Dict[str, torch.Tensor] = {}
+    for s in model.weight_specs():
+        g = torch.Generator(device=device)
+        g.manual_seed(int.from_bytes(hashlib.sha256(f"{seed}:{s.name}".encode()).digest()[:8], "little") & 0x7FFF_FFFF_FFFF_FFFF)
+        kind, shape = s.init[0], tuple(s.shape)
+        if kind in ("normal", "one_plus_normal"):
+            t = torch.randn(shape, generator=g, dtype=torch.float32, device=device) * float(s.init[1])
+            if kind == "one_plus_normal":
+                t += 1.0
+        elif kind in ("zeros", "ones"):
+            t = torch.full(shape, 0.0 if kind == "zeros" else 1.0, dtype=torch.float32, device=device)
+        elif kind == "randint":
+            t = torch.randint(int(s.init[1]), int(s.init[2]), shape, generator=g, dtype=torch.int32, device=device)
+        else:
+            raise ValueError(f"unknown init rule {s.init!r} for tensor {s.name!r}")
+        tensors[s.name] = t if s.kind == "int" else t.to(dt)
+    model.bind(tensors, dt, device)
+    return model
+
+
 def load_model(model_dir: str, dtype, device: torch.device) -> Model:
     """Build the model that ``model_dir/config.json`` names and bind ``model.safetensors`` to it."""
     config = load_config(model_dir)

@@ -674,6 +674,10 @@ FUSED_CASES = [
     (192, 3, 1, 64, 136, 32, 32, True, False, torch.float32, None, 3, [0, 2100]),
     (128, 16, 1, 64, 256, 16, 64, False, True, torch.bfloat16, None, 1, list(range(0, 64 * 9, 9))),        # 64 rows
     (128, 2, 2, 128, 64, 16, 0, False, False, torch.bfloat16, 40, 2, [33 * i for i in range(20)]),          # 20 rows, no positions
+    # wide layers: a block owns more tiles of a stage than its ring holds and parts of several row tiles, so operands
+    # are built in several batches and accumulators are drained while later ones are still being fed
+    (2048, 16, 2, 128, 8192, 16, 128, False, True, torch.bfloat16, None, 1, [5, 300, 17]),
+    (1024, 8, 8, 64, 4096, 16, 64, False, True, torch.bfloat16, None, 2, [40 + 3 * i for i in range(40)]),  # the same at 40 rows
 ]
 
 
