@@ -233,13 +233,16 @@ def time_mixed(engine, requests, lo, hi, new_tokens, rng):
             "ttft_ms_p50": round(loop.stat("ttft", 50), 1), "tpot_ms_p50": round(loop.stat("tpot", 50), 2)}
 
 
-def run_sizes(name: str, steps: int, warmup: int) -> int:
+def run_sizes(name: str, steps: int, warmup: int, layers=None, only=None) -> int:
     """Decode at batch 1 / 8 / 64 and a 2,048-token prefill at one of the larger sizes, with their roofline
     fractions, and for the 1.5B sizes the mixed workload.  Weights are drawn on the device."""
     import torch
     from lightllm_b200 import Engine
     from lightllm_b200.models import random_model_on_device
-    cfg = SIZES[name]
+    cfg = dict(SIZES[name])
+    layers_of_config = cfg["num_hidden_layers"]
+    if layers:               # fewer layers of the same sizes (for profiling runs); both numbers are reported
+        cfg["num_hidden_layers"] = cfg["max_window_layers"] = layers
     pk = peaks()
     rng = random.Random(0)
     device = torch.device("cuda:0")
@@ -251,21 +254,25 @@ def run_sizes(name: str, steps: int, warmup: int) -> int:
                     model=model)
     core = engine.core
     out = {"sizes": name, "dtype": "bf16", "data": "synthetic: random weights drawn on the device (seed 0)",
-           "config": {"layers": cfg["num_hidden_layers"], "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+           "config": {"layers": cfg["num_hidden_layers"], "layers_of_config": layers_of_config, "hidden": cfg["hidden_size"],
+                      "heads": cfg["num_attention_heads"],
                       "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg.get("head_dim", 64),
                       "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
                       "tied_embeddings": cfg["tie_word_embeddings"], "prompt_len": PROMPT_LEN, "page_size": PAGE_SIZE},
            "peaks": pk["source"], "decode": {}}
-    for b in (1, 8, 64):
+    for b in (() if only == "prefill" else (1, 8, 64)):
         ms, _, ctx = time_decode(core, b, steps, warmup, rng)
         gbs = decode_bytes(core, b, ctx) / (ms * 1e-3) / 1e9
         out["decode"][f"b{b}"] = {"tok_s": round(b * 1000.0 / ms, 1), "ms_per_step": round(ms, 4), "gb_s": round(gbs, 1),
                                   "frac_of_hbm": round(gbs / pk["hbm_gbs"], 4)}
-    pre_ms = time_prefill(core, 4, 3, rng)
+    if only == "decode":
+        print(json.dumps(out))
+        return 0
+    pre_ms = time_prefill(core, 4 if only is None else steps, 3, rng)
     fl = flops_prefill(cfg, cfg["num_hidden_layers"], PROMPT_LEN)
     out["prefill"] = {"tok_s": round(PROMPT_LEN * 1000.0 / pre_ms, 1), "ms": round(pre_ms, 3),
                       "frac_of_bf16_peak": round(fl / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
-    if name == "1.5b":
+    if name == "1.5b" and only is None:
         del engine, core
         mixed = Engine(None, dtype="bfloat16", max_seq_len=4096 + 128 + 16, max_batch_tokens=2048, page_size=PAGE_SIZE,
                        num_pages=32 * (4096 + 256) // PAGE_SIZE, max_seqs=32, chunk_size=2048, model=model)
@@ -299,7 +306,8 @@ def main() -> int:
         return 2
     args.warmup = max(3, args.warmup)
     if args.sizes:
-        return run_sizes(args.sizes, min(args.steps, 64), args.warmup)
+        return run_sizes(args.sizes, min(args.steps, 64), args.warmup,
+                         args.layers if args.layers != QWEN25_05B["num_hidden_layers"] else None, args.only)
 
     import torch
     from lightllm_b200 import Engine

@@ -1,0 +1,134 @@
+"""``bench_ops [--rows T] [--batch B] [--context C] [--reps N] [--only NAME ...]``: every kernel of the library alone.
+
+The reference times its operators one by one in its test program (tests/test_ops.cu:92-231: add, SiLU, RMSNorm,
+rotation, contractions).  This tool does the same for this library's kernels at the layer sizes of a configuration
+(by default the Qwen2.5-0.5B sizes): each operator runs ``--reps`` times between CUDA events, after a warm-up, with a
+buffer larger than L2 written in between so that every run starts cold, and is reported with the bytes it has to move
+and the bandwidth that makes.  It is also the workload under which the kernels' profiler summaries are taken (one
+operator with ``--only``).
+"""
+import argparse
+import json
+import math
+import sys
+
+SIZES = {"hidden": 896, "heads": 14, "kv_heads": 2, "head_dim": 64, "intermediate": 4864, "vocab": 151936, "page": 16}
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="bench_ops")
+    ap.add_argument("--rows", type=int, default=2048, help="rows of a prompt portion (prefill-shaped operators)")
+    ap.add_argument("--batch", type=int, default=8, help="requests of a decode step (decode-shaped operators)")
+    ap.add_argument("--context", type=int, default=2048, help="keys each request holds (attention operators)")
+    ap.add_argument("--reps", type=int, default=20)
+    ap.add_argument("--only", nargs="*", default=None, help="names of the operators to run (default: all)")
+    for k, v in SIZES.items():
+        ap.add_argument(f"--{k.replace('_', '-')}", type=int, default=v)
+    args = ap.parse_args(argv)
+
+    import torch
+    from lightllm_b200.csrc import ops
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    g = torch.Generator(device=dev).manual_seed(0)
+    rn = lambda *shape, dtype=torch.float32, s=1.0: (torch.randn(*shape, generator=g, device=dev) * s).to(dtype)
+    T, B, C = args.rows, args.batch, args.context
+    D, Hq, Hkv, hd, I, V, page = (args.hidden, args.heads, args.kv_heads, args.head_dim, args.intermediate, args.vocab,
+                                  args.page)
+    Nqkv = (Hq + 2 * Hkv) * hd
+    flush = torch.empty(192 << 20, dtype=torch.uint8, device=dev)          # larger than L2
+    results = []
+
+    def run(name, fn, nbytes, flops=0):
+        if args.only and name not in args.only:
+            return
+        for _ in range(3):
+            fn()
+        times = []
+        for _ in range(args.reps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1) * 1000.0)
+        times.sort()
+        us = times[len(times) // 2]
+        rec = {"op": name, "us": round(us, 2), "MB": round(nbytes / 1e6, 3), "GB/s": round(nbytes / us / 1e3, 1)}
+        if flops:
+            rec["TFLOP/s"] = round(flops / us / 1e6, 2)
+        results.append(rec)
+        print(json.dumps(rec), flush=True)
+
+    # ---- what a prompt portion of T rows runs ---------------------------------------------------------------------------
+    ids = torch.randint(0, V, (T,), generator=g, device=dev, dtype=torch.int32)
+    table = rn(V, D, dtype=torch.bfloat16, s=0.02)
+    resid = torch.empty((T, D), dtype=torch.float32, device=dev)
+    run("embedding", lambda: ops.embedding(ids, table, resid), T * D * (2 + 4))
+    w_norm = torch.ones(D, dtype=torch.bfloat16, device=dev)
+    x_bf = torch.empty((T, D), dtype=torch.bfloat16, device=dev)
+    run("rmsnorm", lambda: ops.rmsnorm(resid, w_norm, 1e-6, x_bf), T * D * (4 + 2))
+    resid32 = rn(T, D)
+    w_norm32 = torch.ones(D, device=dev)
+    x32 = torch.empty((T, D), device=dev)
+    run("rmsnorm_float32", lambda: ops.rmsnorm(resid32, w_norm32, 1e-6, x32), T * D * 8)
+    positions = torch.arange(T, dtype=torch.int32, device=dev)
+    inv_freq = (1.0 / 1e6 ** (torch.arange(0, hd, 2, dtype=torch.float64) / hd)).float().to(dev)
+    run("rope_table", lambda: ops.rope_table(positions, inv_freq), T * hd // 2 * 8)
+    slots = -(-T // page) * page
+    kc = torch.zeros((slots, Hkv, hd), dtype=torch.bfloat16, device=dev)
+    vc = torch.zeros_like(kc)
+    qkv = rn(T, Nqkv, dtype=torch.bfloat16)
+    q_out = torch.empty((T, Hq * hd), dtype=torch.bfloat16, device=dev)
+    run("rope_kv_write", lambda: ops.rope_kv_write(qkv, positions, positions, inv_freq, hd, False, q_out, kc, vc, Hq, Hkv, hd),
+        2 * T * Nqkv * 2)
+    # the 32-bit contraction and attention (the float32 path), at a portion of 256 rows so that a run stays short
+    Ts = min(T, 256)
+    a32, w32 = rn(Ts, D), rn(Nqkv, D, s=D ** -0.5)
+    out32 = torch.empty((Ts, Nqkv), device=dev)
+    run("gemm_simt_float32", lambda: ops.gemm_simt(a32, w32, None, ops.EPI_STORE, out32), (Ts * D + Nqkv * D + Ts * Nqkv) * 4,
+        2 * Ts * D * Nqkv)
+    kc32, vc32 = rn(slots, Hkv, hd), rn(slots, Hkv, hd)
+    q32, o32 = rn(Ts, Hq * hd), torch.empty((Ts, Hq * hd), device=dev)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    bt = torch.arange(slots // page, dtype=torch.int32, device=dev).reshape(1, -1)
+    bq = 16
+    tiles = list(range(0, Ts, bq))
+    run("paged_attention_simt_float32",
+        lambda: ops.paged_attention_simt(q32, kc32, vc32, o32, i32([0] * len(tiles)), i32(tiles), len(tiles), i32([0]), i32([Ts]),
+                                         i32([0]), bt, bt.shape[1], page, Hq, Hkv, hd, 0, 1 / math.sqrt(hd), bq),
+        (2 * Ts * Hq * hd + 2 * Ts * Hkv * hd) * 4, 2 * 2 * Hq * hd * Ts * (Ts + 1) // 2)
+
+    # ---- what a decode step of B requests over C keys runs --------------------------------------------------------------
+    pages_per = -(-(C + 1) // page)
+    kcd = rn(B * pages_per * page, Hkv, hd, dtype=torch.bfloat16)
+    vcd = rn(B * pages_per * page, Hkv, hd, dtype=torch.bfloat16)
+    btd = torch.arange(B * pages_per, dtype=torch.int32, device=dev).reshape(B, pages_per)
+    qd = rn(B, Hq * hd, dtype=torch.bfloat16)
+    od = torch.empty_like(qd)
+    rows, pos, zero = i32(list(range(B))), i32([C] * B), i32([0] * B)
+    kv_bytes = B * (C + 1) * Hkv * hd * 2 * 2
+    if ops.paged_decode_mma_supports(Hq, Hkv, hd):
+        nsplit = max(1, min(8, 3 * 148 // (B * Hkv), -(-(C + 1) // 128)))
+        run("paged_decode_mma", lambda: ops.paged_decode_mma(qd, kcd, vcd, od, rows, zero, B, rows, pos, btd, pages_per, page, Hq,
+                                                             Hkv, hd, 0, 1 / math.sqrt(hd), nsplit, None), kv_bytes)
+        big = 24           # more pieces than a cluster merges: the pieces meet in scratch and a second kernel merges them
+        scratch = torch.empty(ops.attention_scratch_floats(B, Hq, hd, 1, big), device=dev)
+        run("paged_decode_mma_and_merge", lambda: ops.paged_decode_mma(qd, kcd, vcd, od, rows, zero, B, rows, pos, btd, pages_per,
+                                                                       page, Hq, Hkv, hd, 0, 1 / math.sqrt(hd), big, scratch),
+            kv_bytes + 2 * B * Hq * big * (hd + 2) * 4)
+    logits = rn(B, V, s=3.0)
+    tok = torch.empty(B, dtype=torch.int32, device=dev)
+    run("argmax", lambda: ops.argmax(logits, tok), B * V * 4)
+    f = lambda v: torch.full((B,), v, dtype=torch.float32, device=dev)
+    temp, top_p, min_p, u = f(0.8), f(0.9), f(0.0), f(0.5)
+    top_k = torch.full((B,), 40, dtype=torch.int32, device=dev)
+    run("sample_top_k_top_p", lambda: ops.sample(logits, temp, top_k, top_p, min_p, u, tok), B * V * 4)
+    run("sample_temperature_only", lambda: ops.sample(logits, temp, None, None, None, u, tok), B * V * 4)
+    ops.check_async_errors(dev)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

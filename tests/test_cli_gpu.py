@@ -78,3 +78,17 @@ def test_random_model_writes_a_folder_the_engine_loads(tmp_path):
     assert sorted(os.listdir(out_dir)) == ["config.json", "model.safetensors"]
     text = run_cli("lightllm_b200.cli.generate", out_dir, 1, 2, 3, "--temperature", 0, "--max-new-tokens", 3, "--max-seq-len", 64)
     assert re.search(r"generated:\s*\d+ \d+ \d+", text)
+
+
+def test_bench_ops_times_every_operator():
+    """The operator benchmark at small sizes: every operator reports a time and the bytes it moves."""
+    import json
+    out = run_cli("lightllm_b200.cli.bench_ops", "--rows", 64, "--batch", 3, "--context", 200, "--reps", 2, "--hidden", 128,
+                  "--heads", 4, "--kv-heads", 2, "--head-dim", 64, "--intermediate", 256, "--vocab", 9001)
+    recs = [json.loads(line) for line in out.splitlines() if line.startswith("{")]
+    names = [r["op"] for r in recs]
+    for want in ("embedding", "rmsnorm", "rmsnorm_float32", "rope_table", "rope_kv_write", "gemm_simt_float32",
+                 "paged_attention_simt_float32", "paged_decode_mma", "paged_decode_mma_and_merge", "argmax",
+                 "sample_top_k_top_p", "sample_temperature_only"):
+        assert want in names, names
+    assert all(r["us"] > 0 and r["MB"] > 0 for r in recs)
