@@ -61,9 +61,9 @@ struct GemmParams {
     int tma_out;            // the epilogue leaves through shared memory and TMA stores (map_out is valid)
     int* error_flag;        // raised when a wait ran out of time
     // rotary epilogue of the q/k/v projection (heads of 64, NeoX pairs, whole head rotated)
-    const float2* rope_table;   // [32, M] of (cos, sin): pair-major, so that a warp's rows read neighbouring entries
+    const float2* rope_table;   // [hd/2, M] of (cos, sin): pair-major, so that a warp's rows read neighbouring entries
     const int* slot_mapping;    // [M] cache row of each token, negative: not written
-    __nv_bfloat16* q_out;       // [M, Hq * 64]
+    __nv_bfloat16* q_out;       // [M, Hq * hd]
     __nv_bfloat16* k_cache;     // [slots, Hkv, 64]
     __nv_bfloat16* v_cache;
     int Hq, Hkv;
@@ -155,6 +155,8 @@ __device__ __forceinline__ void epilogue_row(const GemmParams& p, int m, int nb,
 }
 
 constexpr int EPI_ROPE64 = 4;     // q/k/v projection of heads of 64: bias, NeoX rotation, q store, K/V page write
+constexpr int EPI_ROPE128 = 5;    // the same with heads of 128 (one head is one tile of 128 columns)
+constexpr bool epi_is_rope(int epi) { return epi == EPI_ROPE64 || epi == EPI_ROPE128; }
 
 template <int BN, int EPI, bool SWAP>
 __global__ void __launch_bounds__(NUM_THREADS, 2)
@@ -371,18 +373,23 @@ __device__ __forceinline__ void staged_chunk(const GemmParams& p, const CUtensor
     }
 }
 
-// Rotary epilogue of one warp: token rows row0 .. row0+31 (one per lane) and the 64 output features nb .. nb+63, i.e.
-// one whole head of q, k or v (src/ops/rope.cu:54-59 on every pair; cache rows as src/kv_cache/paged_attention.cu:1150-1163).
-// The (cos, sin) table is laid out [pair][token], so the lanes of a warp read neighbouring entries.  A head of q
-// leaves through the warp's staging tile and one TMA store (64 bf16 are one 128-byte row of it) when `staged`;
-// k and v go straight to their cache rows, which lie wherever the pages are.
-__device__ __forceinline__ void epilogue_rope64_warp(const GemmParams& p, const CUtensorMap* map_q, uint8_t* stage,
-                                                     bool staged, int lane, int row0, int nb, const uint32_t (&r0)[32],
-                                                     const uint32_t (&r1)[32]) {
+// Rotary epilogue of one warp: token rows row0 .. row0+31 (one per lane) and the 64 output features nb .. nb+63 of q,
+// k or v (src/ops/rope.cu:54-59 on every pair; cache rows as src/kv_cache/paged_attention.cu:1150-1163).  With heads
+// of 64 these are one whole head and both members of every pair (j, j + 32) are here; with heads of 128 they are half
+// of a head, the pairs are (j, j + 64), and the other members come in `p0`, `p1` (the same columns of the head's other
+// half).  The (cos, sin) table is laid out [pair][token], so the lanes of a warp read neighbouring entries.  q leaves
+// through the warp's staging tile and one TMA store (64 bf16 are one 128-byte row of it) when `staged`; k and v go
+// straight to their cache rows, which lie wherever the pages are.
+template <int HD>
+__device__ __forceinline__ void epilogue_rope_warp(const GemmParams& p, const CUtensorMap* map_q, uint8_t* stage,
+                                                   bool staged, int lane, int row0, int nb, const uint32_t (&r0)[32],
+                                                   const uint32_t (&r1)[32], const uint32_t (&p0)[32],
+                                                   const uint32_t (&p1)[32]) {
     if (nb >= p.N) return;                       // uniform over the warp
     const int m = row0 + lane;
     const bool in_m = m < p.M;
-    const int q_end = p.Hq * 64, k_end = q_end + p.Hkv * 64;
+    const int q_end = p.Hq * HD, k_end = q_end + p.Hkv * HD;
+    const bool second_half = HD == 128 && (nb & 64) != 0;      // these columns are the pairs' second members
     float a[32], b[32];
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
@@ -392,12 +399,24 @@ __device__ __forceinline__ void epilogue_rope64_warp(const GemmParams& p, const 
     }
     if (nb < k_end && in_m) {
         const float2* cs = p.rope_table + m;
+        if (HD == 64) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-            const float2 t = cs[(size_t)j * p.M];
-            const float x = a[j], y = b[j];
-            a[j] = x * t.x - y * t.y;
-            b[j] = y * t.x + x * t.y;
+            for (int j = 0; j < 32; ++j) {
+                const float2 t = cs[(size_t)j * p.M];
+                const float x = a[j], y = b[j];
+                a[j] = x * t.x - y * t.y;
+                b[j] = y * t.x + x * t.y;
+            }
+        } else {
+            const int nbp = second_half ? nb - 64 : nb + 64;      // where the partners' bias lies
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                float pa = __uint_as_float(p0[j]), pb = __uint_as_float(p1[j]);
+                if (p.bias) { pa += p.bias[nbp + j]; pb += p.bias[nbp + 32 + j]; }
+                const float2 ta = cs[(size_t)j * p.M], tb = cs[(size_t)(32 + j) * p.M];
+                a[j] = second_half ? a[j] * ta.x + pa * ta.y : a[j] * ta.x - pa * ta.y;
+                b[j] = second_half ? b[j] * tb.x + pb * tb.y : b[j] * tb.x - pb * tb.y;
+            }
         }
     }
     uint32_t wa[16], wb[16];
@@ -432,8 +451,8 @@ __device__ __forceinline__ void epilogue_rope64_warp(const GemmParams& p, const 
     } else {
         const int slot = p.slot_mapping ? p.slot_mapping[m] : -1;
         if (slot < 0) return;
-        dst = nb < k_end ? p.k_cache + (size_t)slot * (p.Hkv * 64) + (nb - q_end)
-                         : p.v_cache + (size_t)slot * (p.Hkv * 64) + (nb - k_end);
+        dst = nb < k_end ? p.k_cache + (size_t)slot * (p.Hkv * HD) + (nb - q_end)
+                         : p.v_cache + (size_t)slot * (p.Hkv * HD) + (nb - k_end);
     }
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
@@ -605,9 +624,9 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
         const int half = (warp - 2) >> 2;             // which half of the tile's columns it drains
         const int row = quarter * 32 + lane;
         int local = 0;
-        constexpr int SEPI = (EPI == EPI_ROPE64) ? LLB_EPI_STORE : EPI;
+        constexpr int SEPI = epi_is_rope(EPI) ? LLB_EPI_STORE : EPI;
         // the SiLU*mul row of 64 outputs needs 128 accumulator columns per warp, which only the wide tile has
-        const bool staged = p.tma_out != 0 && EPI != EPI_ROPE64 && (EPI != LLB_EPI_SWIGLU || P_BN == 256);
+        const bool staged = p.tma_out != 0 && !epi_is_rope(EPI) && (EPI != LLB_EPI_SWIGLU || P_BN == 256);
         uint8_t* my_stage = out_tiles + (warp - 2) * 4096;
         asm volatile("griddepcontrol.wait;" ::: "memory");
         const uint32_t acc_empty_of_first = PAIR ? mapa_u32(smem_u32(&acc_empty[0]), 0) : 0u;
@@ -720,23 +739,34 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
 #pragma unroll
                             for (int j = 0; j < 32; ++j) acc[j] += __ldcg(src + (size_t)j * TILE_M);
                         }
-                        epilogue_row<(EPI == EPI_ROPE64 ? LLB_EPI_STORE : EPI), 32>(
+                        epilogue_row<(epi_is_rope(EPI) ? LLB_EPI_STORE : EPI), 32>(
                             p, a_row0 + row, b_row0 + c0, *reinterpret_cast<const uint32_t(*)[32]>(&acc[0]));
                     }
                     if (lane == 0) p.counters[t * 8 + (warp - 2)] = 0;
                 }
                 continue;
             }
-            if (EPI == EPI_ROPE64) {
-                // one head (64 columns) at a time, so that both members of every rotary pair are in registers
+            if (epi_is_rope(EPI)) {
+                // 64 columns at a time: a head of 64 with both members of every rotary pair, or half of a head of 128
 #pragma unroll 1
                 for (int c0 = half * (P_BN / 2); c0 < (half + 1) * (P_BN / 2); c0 += 64) {
                     uint32_t r0[32], r1[32];
                     const uint32_t ta = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * P_BN + c0);
                     tmem_ld32_nowait(ta, r0);
                     tmem_ld32_nowait(ta + 32, r1);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    epilogue_rope64_warp(p, &map_out, my_stage, p.tma_out != 0, lane, a_row0 + quarter * 32, b_row0 + c0, r0, r1);
+                    if (EPI == EPI_ROPE128) {      // the pairs' other members: the same columns of the head's other half (the tile is one head)
+                        uint32_t p0[32], p1[32];
+                        const uint32_t tp = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * P_BN + (c0 ^ 64));
+                        tmem_ld32_nowait(tp, p0);
+                        tmem_ld32_nowait(tp + 32, p1);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        epilogue_rope_warp<128>(p, &map_out, my_stage, p.tma_out != 0, lane, a_row0 + quarter * 32, b_row0 + c0,
+                                                r0, r1, p0, p1);
+                    } else {
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        epilogue_rope_warp<64>(p, &map_out, my_stage, p.tma_out != 0, lane, a_row0 + quarter * 32, b_row0 + c0,
+                                               r0, r1, r0, r1);
+                    }
                 }
             } else {
 #pragma unroll 1
@@ -1010,19 +1040,19 @@ LLB_EXPORT long long llb_gemm_tcgen05_counters(int M, int N, int split_k) {
 }
 
 // The q/k/v projection of a prompt portion with its whole epilogue on the tensor-core kernel: bias, NeoX rotation
-// of q and k by rope_table [32, M] of (cos, sin) (pair-major: llb_rope_table with transposed = 1), q to q_out
-// [M, Hq*64], k and v to the cache rows slot_mapping[m].
-// Heads of 64 with the whole head rotated; N = (Hq + 2*Hkv) * 64.
-LLB_EXPORT int llb_gemm_tcgen05_rope64(const void* A, const void* W, const float* bias, int M, int N, int K,
-                                       const float* rope_table, const int* slot_mapping, void* q_out, void* k_cache,
-                                       void* v_cache, int Hq, int Hkv, int* error_flag, cudaStream_t stream) {
+// of q and k by rope_table [hd/2, M] of (cos, sin) (pair-major: llb_rope_table with transposed = 1), q to q_out
+// [M, Hq*hd], k and v to the cache rows slot_mapping[m].
+// Heads of 64 or 128 with the whole head rotated; N = (Hq + 2*Hkv) * hd.
+LLB_EXPORT int llb_gemm_tcgen05_rope(const void* A, const void* W, const float* bias, int M, int N, int K,
+                                     const float* rope_table, const int* slot_mapping, void* q_out, void* k_cache,
+                                     void* v_cache, int Hq, int Hkv, int hd, int* error_flag, cudaStream_t stream) {
     if (M == 0) return 0;
-    LLB_REQUIRE(M > 0 && K % 8 == 0 && N == (Hq + 2 * Hkv) * 64 && Hq > 0 && Hkv > 0,
-                "gemm_tcgen05_rope64: unsupported shape M=%d N=%d K=%d heads %d/%d", M, N, K, Hq, Hkv);
-    LLB_REQUIRE(rope_table && q_out && k_cache && v_cache && slot_mapping, "gemm_tcgen05_rope64: null argument");
+    LLB_REQUIRE(M > 0 && K % 8 == 0 && (hd == 64 || hd == 128) && N == (Hq + 2 * Hkv) * hd && Hq > 0 && Hkv > 0,
+                "gemm_tcgen05_rope: unsupported shape M=%d N=%d K=%d heads %d/%d of %d", M, N, K, Hq, Hkv, hd);
+    LLB_REQUIRE(rope_table && q_out && k_cache && v_cache && slot_mapping, "gemm_tcgen05_rope: null argument");
     LLB_REQUIRE(((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0) && ((uintptr_t)q_out % 16 == 0) &&
                 ((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0) && ((uintptr_t)rope_table % 8 == 0),
-                "gemm_tcgen05_rope64: operands must be 16-byte aligned");
+                "gemm_tcgen05_rope: operands must be 16-byte aligned");
     GemmParams p = {};
     p.splits = 1;
     p.bias = bias; p.M = M; p.N = N; p.K = K;
@@ -1036,20 +1066,21 @@ LLB_EXPORT int llb_gemm_tcgen05_rope64(const void* A, const void* W, const float
     int rc;
     if ((rc = make_map(A, M, K, TILE_M, &ma))) return rc;
     if ((rc = make_map(W, N, K, 128, &mb))) return rc;
-    // q leaves through TMA stores of 64 bf16 x 32 rows when its row pitch allows (always: Hq * 128 bytes)
+    // q leaves through TMA stores of 64 bf16 x 32 rows (its row pitch, Hq * hd * 2 bytes, always allows it)
     CUtensorMap mq = ma;
     {
         t5::EncodeTiledFn fn = t5::encode_tiled_fn();
-        if (!fn) return llb_fail("gemm_tcgen05_rope64: cuTensorMapEncodeTiled is not available from the driver");
-        cuuint64_t dims[2] = {(cuuint64_t)Hq * 64, (cuuint64_t)M};
-        cuuint64_t strides[1] = {(cuuint64_t)Hq * 128};
+        if (!fn) return llb_fail("gemm_tcgen05_rope: cuTensorMapEncodeTiled is not available from the driver");
+        cuuint64_t dims[2] = {(cuuint64_t)Hq * hd, (cuuint64_t)M};
+        cuuint64_t strides[1] = {(cuuint64_t)Hq * hd * 2};
         cuuint32_t box[2] = {64u, 32u};
         cuuint32_t estr[2] = {1, 1};
         CUresult r = fn(&mq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, q_out, dims, strides, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r != CUDA_SUCCESS) return llb_fail("gemm_tcgen05_rope64: cuTensorMapEncodeTiled (q) failed with code %d", (int)r);
+        if (r != CUDA_SUCCESS) return llb_fail("gemm_tcgen05_rope: cuTensorMapEncodeTiled (q) failed with code %d", (int)r);
         p.tma_out = 1;
     }
-    return launch_persistent<EPI_ROPE64, 128>(ma, mb, mq, p, stream);
+    return hd == 128 ? launch_persistent<EPI_ROPE128, 128>(ma, mb, mq, p, stream)
+                     : launch_persistent<EPI_ROPE64, 128>(ma, mb, mq, p, stream);
 }

@@ -17,7 +17,7 @@ from . import build as _build
 
 F32, BF16 = 0, 1
 EPI_STORE, EPI_STORE_F32, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
-ABI_VERSION = 17
+ABI_VERSION = 18
 
 _lib: Optional[ctypes.CDLL] = None
 
@@ -584,28 +584,34 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
                                   split_k, _ptr(partials), _ptr(counters), _ptr(async_error_flag(a.device)), _stream()))
 
 
-def gemm_tcgen05_rope64(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], rope_table: torch.Tensor,
-                        slot_mapping: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor,
-                        v_cache: torch.Tensor, num_heads: int, num_kv_heads: int) -> None:
-    """The q/k/v projection with heads of 64: a[M,K] @ w[N,K]^T, bias, NeoX rotation of
-    the whole head by ``rope_table`` [32, M, 2] (cos, sin; pair-major), q to ``q_out`` [M, Hq*64], k and v to the cache rows
-    ``slot_mapping`` [M] of ``k_cache`` / ``v_cache`` [slots, Hkv, 64] (a negative slot writes nothing)."""
+def gemm_tcgen05_rope(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], rope_table: torch.Tensor,
+                      slot_mapping: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor,
+                      v_cache: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int = 64) -> None:
+    """The q/k/v projection with heads of 64 or 128: a[M,K] @ w[N,K]^T, bias, NeoX rotation of the whole head by
+    ``rope_table`` [hd/2, M, 2] (cos, sin; pair-major), q to ``q_out`` [M, Hq*hd], k and v to the cache rows
+    ``slot_mapping`` [M] of ``k_cache`` / ``v_cache`` [slots, Hkv, hd] (a negative slot writes nothing)."""
     M, K = a.shape
     N, K2 = w.shape
-    if K != K2 or N != (num_heads + 2 * num_kv_heads) * 64:
-        raise KernelError(f"gemm_tcgen05_rope64: a {tuple(a.shape)}, w {tuple(w.shape)}, heads {num_heads}/{num_kv_heads}")
+    hd = head_dim
+    if hd not in (64, 128) or K != K2 or N != (num_heads + 2 * num_kv_heads) * hd:
+        raise KernelError(f"gemm_tcgen05_rope: a {tuple(a.shape)}, w {tuple(w.shape)}, heads {num_heads}/{num_kv_heads} of {hd}")
     for t, name in ((a, "a"), (w, "w"), (q_out, "q_out"), (k_cache, "k_cache"), (v_cache, "v_cache")):
         if t.dtype != torch.bfloat16 or not t.is_contiguous():
-            raise KernelError(f"gemm_tcgen05_rope64: {name} must be contiguous bfloat16")
+            raise KernelError(f"gemm_tcgen05_rope: {name} must be contiguous bfloat16")
     if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N):
-        raise KernelError("gemm_tcgen05_rope64: bias must be float32 of length N")
-    if rope_table.dtype != torch.float32 or rope_table.numel() != M * 64 or not rope_table.is_contiguous():
-        raise KernelError("gemm_tcgen05_rope64: rope_table must be float32 [32, M, 2]")
+        raise KernelError("gemm_tcgen05_rope: bias must be float32 of length N")
+    if rope_table.dtype != torch.float32 or rope_table.numel() != M * hd or not rope_table.is_contiguous():
+        raise KernelError("gemm_tcgen05_rope: rope_table must be float32 [hd/2, M, 2]")
     if slot_mapping.dtype != torch.int32 or slot_mapping.numel() != M:
-        raise KernelError("gemm_tcgen05_rope64: slot_mapping must be int32 [M]")
-    if tuple(q_out.shape) != (M, num_heads * 64) or k_cache.shape[-1] != 64 or k_cache.shape[-2] != num_kv_heads \
+        raise KernelError("gemm_tcgen05_rope: slot_mapping must be int32 [M]")
+    if tuple(q_out.shape) != (M, num_heads * hd) or k_cache.shape[-1] != hd or k_cache.shape[-2] != num_kv_heads \
             or v_cache.shape != k_cache.shape:
-        raise KernelError("gemm_tcgen05_rope64: q_out must be [M, Hq*64] and the caches [..., Hkv, 64]")
-    _check(lib().llb_gemm_tcgen05_rope64(_ptr(a), _ptr(w), _ptr(bias), M, N, K, _ptr(rope_table), _ptr(slot_mapping),
-                                         _ptr(q_out), _ptr(k_cache), _ptr(v_cache), num_heads, num_kv_heads,
-                                         _ptr(async_error_flag(a.device)), _stream()))
+        raise KernelError("gemm_tcgen05_rope: q_out must be [M, Hq*hd] and the caches [..., Hkv, hd]")
+    _check(lib().llb_gemm_tcgen05_rope(_ptr(a), _ptr(w), _ptr(bias), M, N, K, _ptr(rope_table), _ptr(slot_mapping),
+                                       _ptr(q_out), _ptr(k_cache), _ptr(v_cache), num_heads, num_kv_heads, hd,
+                                       _ptr(async_error_flag(a.device)), _stream()))
+
+
+def gemm_tcgen05_rope64(a, w, bias, rope_table, slot_mapping, q_out, k_cache, v_cache, num_heads, num_kv_heads) -> None:
+    """:func:`gemm_tcgen05_rope` at heads of 64."""
+    gemm_tcgen05_rope(a, w, bias, rope_table, slot_mapping, q_out, k_cache, v_cache, num_heads, num_kv_heads, 64)

@@ -27,7 +27,7 @@ FEW_ROWS = 32
 MANY_KEYS = 512
 # Up to this many keys per request the decode attention's pieces are merged inside the kernel.
 CLUSTER_MERGE_MAX_KEYS = 8192
-# From this many rows on, heads of 64 get their rotation and cache write in the projection's tensor-core epilogue.
+# From this many rows on, heads of 64 or 128 get their rotation and cache write in the projection's tensor-core epilogue.
 PREFILL_ROPE_MIN_ROWS = 16
 
 
@@ -129,20 +129,20 @@ class AttentionMixer(Mixer):
 
     def _project_prefill_fused(self, x, ctx, cache: CacheView):
         """The projection of a long portion with bias, rotation and the cache write in the epilogue of the
-        tensor-core kernel: bfloat16, heads of 64 rotated whole with NeoX pairs.  Returns q, or None."""
+        tensor-core kernel: bfloat16, heads of 64 or 128 rotated whole with NeoX pairs.  Returns q, or None."""
         T = x.shape[0]
+        hd = self.head_dim
         table = self.position.rotary_table()
-        if (T <= PREFILL_ROPE_MIN_ROWS or table is None or not cache.writes or self.head_dim != 64
+        if (T <= PREFILL_ROPE_MIN_ROWS or table is None or not cache.writes or hd not in (64, 128)
                 or x.dtype != torch.bfloat16 or self.w_qkv.dtype != torch.bfloat16 or self.w_qkv.shape[1] % 8
                 or not hasattr(self.position, "step_table")):
             return None
         _, rotary_dim, interleaved = table
-        if rotary_dim != 64 or interleaved:
+        if rotary_dim != hd or interleaved:
             return None
-        q = torch.empty((T, self.num_heads * 64), dtype=torch.bfloat16, device=x.device)
-        ops.gemm_tcgen05_rope64(x, self.w_qkv, self.b_qkv, self.position.step_table(ctx, transposed=True),
-                                ctx.slot_mapping[cache.group],
-                                q, cache.k, cache.v, self.num_heads, self.num_kv_heads)
+        q = torch.empty((T, self.num_heads * hd), dtype=torch.bfloat16, device=x.device)
+        ops.gemm_tcgen05_rope(x, self.w_qkv, self.b_qkv, self.position.step_table(ctx, transposed=True),
+                              ctx.slot_mapping[cache.group], q, cache.k, cache.v, self.num_heads, self.num_kv_heads, hd)
         return q
 
     def forward(self, x, residual, ctx, cache: CacheView) -> None:

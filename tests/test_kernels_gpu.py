@@ -268,11 +268,13 @@ def test_gemm_decode_rope_kv(ops, M, hd, rd, inter, Hq, Hkv, norm):
     assert float(sc[0].abs().max()) == 0.0 and int(sc[1].abs().max()) == 0       # the meeting place is left clean
 
 @pytest.mark.parametrize("M", [17, 64, 129, 300, 1000])
-@pytest.mark.parametrize("Hq,Hkv,K,bias_on", [(14, 2, 896, True), (3, 1, 72, False), (5, 5, 200, True)])
-def test_gemm_tcgen05_rope64(ops, M, Hq, Hkv, K, bias_on):
+@pytest.mark.parametrize("Hq,Hkv,K,bias_on,hd", [(14, 2, 896, True, 64), (3, 1, 72, False, 64), (5, 5, 200, True, 64),
+                                                 (12, 2, 1536, True, 128), (3, 1, 72, False, 128), (2, 2, 200, True, 128)])
+def test_gemm_tcgen05_rope(ops, M, Hq, Hkv, K, bias_on, hd):
     """q/k/v projection of a long portion with bias, rotation and the cache write in the tensor-core
-    epilogue, against the plain parts."""
-    hd, page = 64, 16
+    epilogue, against the plain parts; heads of 64 (two heads a tile) and of 128 (the pairs' members lie in
+    different halves of the tile)."""
+    page = 16
     npages = -(-M // page) + 3
     N = (Hq + 2 * Hkv) * hd
     w = rnd((N, K), torch.bfloat16, 160, 0.3)
@@ -291,7 +293,7 @@ def test_gemm_tcgen05_rope64(ops, M, Hq, Hkv, K, bias_on):
     q = torch.full((M, Hq * hd), float("nan"), dtype=torch.bfloat16, device=dev())
     table = ops.rope_table(pos.to(dev()), inv, transposed=True)
     assert torch.equal(table.transpose(0, 1), ops.rope_table(pos.to(dev()), inv))
-    ops.gemm_tcgen05_rope64(a, w, bias, table, slots.to(dev()), q, kc, vc, Hq, Hkv)
+    ops.gemm_tcgen05_rope(a, w, bias, table, slots.to(dev()), q, kc, vc, Hq, Hkv, hd)
     ops.check_async_errors(dev())
     y = a.double().cpu() @ w.double().cpu().t()
     if bias_on:

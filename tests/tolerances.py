@@ -13,13 +13,22 @@ import torch
 
 FLOAT32_ATOL = 1e-4
 
-# measured worst relative errors (see the docstring); a test prints its own worst so that these can be checked again
-BF16_WORST_REL = {"A": 0.125, "B": 0.125, "C": 0.125, "D": 0.125, "E": 0.125,
+# measured worst relative errors (see the docstring); a test prints its own worst so that these can be checked again.
+# Each figure is the largest that one recorded run of the GPU tests (LLB_TOLERANCE_RECORD) showed under that key,
+# rounded up in the third decimal.
+BF16_WORST_REL = {"A": 0.014,          # replay 0.0134
+                  "B": 0.017,          # replay 0.0170, long decoding 0.0136
+                  "C": 0.020,          # replay 0.0196
+                  "D": 0.021,          # replay 0.0200
+                  "E": 0.020,          # replay 0.0199
                   # the same models with their q and k projections scaled up (sharp attention: a lost key shows, and
                   # rounding of the scores weighs more)
-                  "A sharp": 0.125, "C sharp": 0.125, "D sharp": 0.125, "E sharp": 0.125,
-                  "toy": 0.125,        # the toy architectures of test_engine_gpu.py
-                  "real": 0.125}       # two layers at the 0.5B sizes (test_real_sizes_gpu.py)
+                  "A sharp": 0.016,    # 0.0157
+                  "C sharp": 0.025,    # 0.0250
+                  "D sharp": 0.053,    # every kind of span 0.0524; persistent decode 0.0191; merge through scratch 0.0111
+                  "E sharp": 0.036,    # persistent decode, 17 rows: 0.0352
+                  "toy": 0.035,        # the toy architectures of test_engine_gpu.py: routed 0.0343, norms 0.0186
+                  "real": 0.033}       # two layers at the 0.5B sizes (test_real_sizes_gpu.py): 0.0323
 
 
 def logits_std(plain_logits) -> float:
