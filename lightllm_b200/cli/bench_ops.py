@@ -100,6 +100,27 @@ def main(argv=None) -> int:
                                          i32([0]), bt, bt.shape[1], page, Hq, Hkv, hd, 0, 1 / math.sqrt(hd), bq),
         (2 * Ts * Hq * hd + 2 * Ts * Hkv * hd) * 4, 2 * 2 * Hq * hd * Ts * (Ts + 1) // 2)
 
+    # the tensor-core attention of the whole portion (a prompt of T rows from position 0), cut into items as the engine does
+    if ops.attention_tcgen05_supports(hd, page):
+        from lightllm_b200.engine.batch import cut_attention_rows
+        from lightllm_b200.parts import linear as L
+        import numpy as np
+        rows_t = [(0, q0, -(-min(q0 + 128, T) // 128)) for q0 in range(0, T, 128)]
+        items, merges, parts = cut_attention_rows(rows_t, None, Hq, (2 if hd <= 64 else 1) * L.num_sms(dev))
+        arr = torch.from_numpy(np.asarray([t[1:] for t in items], dtype=np.int32).T.copy()).to(dev)
+        m = torch.from_numpy(np.asarray(merges, dtype=np.int32).reshape(-1, 4).T.copy()).to(dev)
+        cut = (arr[2], arr[3], arr[4], parts, m[0], m[1], m[2], m[3], len(merges)) if merges else (arr[2], arr[3], arr[4], 0, None, None, None, None, 0)
+        kcp, vcp = rn(slots, Hkv, hd, dtype=torch.bfloat16), rn(slots, Hkv, hd, dtype=torch.bfloat16)
+        qp = rn(T, Hq * hd, dtype=torch.bfloat16)
+        op = torch.empty_like(qp)
+        btp = torch.arange(slots // page, dtype=torch.int32, device=dev).reshape(1, -1)
+        i32p = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+        sr, sl, sp = i32p([0]), i32p([T]), i32p([0])
+        run("paged_attention_tcgen05",
+            lambda: ops.paged_attention_tcgen05(qp, kcp, vcp, op, arr[0].contiguous(), arr[1].contiguous(), len(items), sr, sl, sp, btp,
+                                                btp.shape[1], page, Hq, Hkv, hd, 0, 1 / math.sqrt(hd), cut=cut),
+            (2 * T * Hq * hd + 2 * T * Hkv * hd) * 2, 2 * 2 * Hq * hd * T * (T + 1) // 2)
+
     # ---- what a decode step of B requests over C keys runs --------------------------------------------------------------
     pages_per = -(-(C + 1) // page)
     kcd = rn(B * pages_per * page, Hkv, hd, dtype=torch.bfloat16)
@@ -126,6 +147,16 @@ def main(argv=None) -> int:
     top_k = torch.full((B,), 40, dtype=torch.int32, device=dev)
     run("sample_top_k_top_p", lambda: ops.sample(logits, temp, top_k, top_p, min_p, u, tok), B * V * 4)
     run("sample_temperature_only", lambda: ops.sample(logits, temp, None, None, None, u, tok), B * V * 4)
+    # ---- what issuing tensor-core instructions costs one thread, alone and beside busy warps (cycles, not bytes) -------
+    if not args.only or "mma_issue" in args.only:
+        for n, a_tmem in ((64, False), (128, False), (64, True), (16, False)):
+            for neighbours, kind in ((0, 1), (4, 2), (8, 2), (4, 1), (8, 1)):
+                r = ops.selftest_mma_issue(dev, n, a_tmem, neighbours, kind)
+                torch.cuda.synchronize()
+                rec = {"op": "mma_issue", "n": n, "a_from": "tmem" if a_tmem else "smem", "busy_warps": neighbours,
+                       "busy_kind": ("none" if not neighbours else "fma chains" if kind == 1 else "softmax-like"),
+                       "cycles_per_mma": round(r["cycles_per_mma"], 1), "commit_cycles": r["commit_cycles"]}
+                print(json.dumps(rec), flush=True)
     ops.check_async_errors(dev)
     return 0
 

@@ -49,7 +49,7 @@ def _fingerprint() -> str:
             h.update(name.encode())
             with open(os.path.join(CSRC_DIR, name), "rb") as f:
                 h.update(f.read())
-    h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS).encode())
+    h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS + os.environ.get("LLB_NVCC_EXTRA", "").split()).encode())
     return h.hexdigest()[:16]
 
 

@@ -17,7 +17,7 @@ from . import build as _build
 
 F32, BF16 = 0, 1
 EPI_STORE, EPI_STORE_F32, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
-ABI_VERSION = 18
+ABI_VERSION = 19
 
 _lib: Optional[ctypes.CDLL] = None
 
@@ -547,6 +547,16 @@ def selftest_wait_expires(device: torch.device, limit_cycles: int = 1_000_000) -
     trace = torch.zeros(2, dtype=torch.int32, device=device)
     _check(lib().llb_selftest_wait_expires(_ptr(async_error_flag(device)), _ptr(trace), limit_cycles, _stream()))
     return trace
+
+
+def selftest_mma_issue(device: torch.device, n: int = 64, a_tmem: bool = False, neighbours: int = 0, kind: int = 1,
+                       iters: int = 256) -> dict:
+    """The microbenchmark of csrc/selftest.cu: cycles that one thread needs to issue ``4 * iters`` tcgen05.mma of
+    128 x n x 16 beside ``neighbours`` busy warps (kind 1: FMA chains, 2: softmax-like), and for the commit."""
+    out = torch.zeros(4, dtype=torch.int64, device=device)
+    _check(lib().llb_selftest_mma_issue(_ptr(out), n, int(a_tmem), neighbours, kind, iters, _stream()))
+    issue, commit, arrive, _ = out.tolist()
+    return {"cycles_per_mma": issue / (4 * iters), "commit_cycles": commit, "arrive_cycles": arrive}
 
 
 _meet_counters = {}

@@ -36,6 +36,32 @@ class Span:
     row: int           # first row of the batch that belongs to it
 
 
+def cut_attention_rows(rows, chunk_tiles=None, heads=1, slots=1):
+    """Cuts row tiles ``(span, q0, key tiles)`` into the work items of the tensor-core attention kernel: a tile
+    whose key range is longer than ``chunk_tiles`` (+1) becomes pieces of that many key tiles, which leave partial
+    results for the merge kernel.  With ``chunk_tiles=None`` the piece is as long as the work allows: the tiles of
+    all ``heads`` spread over ``slots`` resident blocks give each block so many tiles anyway, and shorter pieces
+    would only add partial results to merge (between 4 and 16).  Returns ``(items, merges, parts)``: items
+    ``(key tiles, span, q0, first key tile, key tiles, part or -1)`` longest first, merges ``(span, q0, first part,
+    parts)``, and the number of partial results."""
+    if chunk_tiles is None:
+        total = sum(r[2] for r in rows)
+        chunk_tiles = min(16, max(4, -(-total * heads // max(1, slots))))
+    items, merges, parts = [], [], 0
+    for i, q0, ntiles in rows:
+        if ntiles <= chunk_tiles + 1:
+            items.append((ntiles, i, q0, 0, ntiles, -1))
+            continue
+        nchunks = -(-ntiles // chunk_tiles)
+        merges.append((i, q0, parts, nchunks))
+        for c in range(nchunks):
+            nk = min(chunk_tiles, ntiles - c * chunk_tiles)
+            items.append((nk, i, q0, c * chunk_tiles, nk, parts + c))
+        parts += nchunks
+    items.sort(key=lambda t: -t[0])
+    return items, merges, parts
+
+
 class StepContext:
     """Everything a part may read while a step runs.
 
@@ -146,21 +172,7 @@ class StepContext:
                 hi = pos0 + 128 if q0 + 128 <= s.length else s.start + s.length
                 lo = pos0 - window + 1 if window > 0 and pos0 >= window else 0
                 rows.append((i, q0, -(-(hi - (lo // 128) * 128) // 128)))
-        if chunk_tiles is None:
-            total = sum(r[2] for r in rows)
-            chunk_tiles = min(16, max(4, -(-total * heads // max(1, slots))))
-        items, merges, parts = [], [], 0
-        for i, q0, ntiles in rows:
-            if ntiles <= chunk_tiles + 1:
-                items.append((ntiles, i, q0, 0, ntiles, -1))
-                continue
-            nchunks = -(-ntiles // chunk_tiles)
-            merges.append((i, q0, parts, nchunks))
-            for c in range(nchunks):
-                nk = min(chunk_tiles, ntiles - c * chunk_tiles)
-                items.append((nk, i, q0, c * chunk_tiles, nk, parts + c))
-            parts += nchunks
-        items.sort(key=lambda t: -t[0])
+        items, merges, parts = cut_attention_rows(rows, chunk_tiles, heads, slots)
         if not items:
             hit = (self.iota, self.zeros, 0, None)
         else:

@@ -805,3 +805,14 @@ def test_decode_layers_refuses_what_it_cannot_run(ops):
         ops.decode_layers(torch.zeros(1024, dtype=torch.uint8, device=dev()), 1, h, 128, 2, 2, 48, 64, 48, False, 1.0, None,
                           i32.view(-1), [i32], [i32.view(-1)], 1, 16, 1, torch.zeros(8, device=dev()),
                           ops.decode_layers_counters(dev()))
+
+
+@pytest.mark.parametrize("n,a_tmem,neighbours,kind", [(64, False, 0, 1), (128, False, 8, 2), (64, True, 4, 1), (16, False, 8, 1)])
+def test_mma_issue_microbenchmark(ops, n, a_tmem, neighbours, kind):
+    """The issue-cost microbenchmark runs, ends by itself and reports plausible cycle counts (an MMA of this shape
+    keeps the tensor pipe for 32-64 cycles; beside busy warps the issuing thread needs a multiple)."""
+    r = ops.selftest_mma_issue(dev(), n, a_tmem, neighbours, kind, iters=64)
+    torch.cuda.synchronize()
+    ops.check_async_errors(dev())
+    assert 20.0 < r["cycles_per_mma"] < 5000.0 and 0 < r["commit_cycles"] < 100000
+
