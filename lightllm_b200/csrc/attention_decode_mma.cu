@@ -17,8 +17,11 @@
 #include <math.h>
 
 #include "common.cuh"
+#include "warp_mma.cuh"
 
 namespace {
+
+using namespace wm;
 
 constexpr int BK = 32;          // keys per tile
 constexpr int NWARPS = 4;
@@ -41,29 +44,6 @@ struct DecodeParams {
     float* part_ml;                // [tiles, Hkv, nsplit, G, 2]   (m in base-2 units, l)
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
-    const int n = valid ? 16 : 0;     // 0 source bytes: the 16 bytes are zero-filled
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() {
-    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
-}
-__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
-                 "{%0, %1, %2, %3};"
-                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
 // Distributed shared memory: the float at `local_addr` (a shared-memory address of this block) in the block of
 // rank `rank` of the cluster.
 __device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t rank) {
@@ -79,16 +59,6 @@ __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-__device__ __forceinline__ float fast_exp2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
-    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-    return *reinterpret_cast<const uint32_t*>(&h);
-}
-
 // Shared memory tile [32 keys][HD] bf16; the 16-byte chunk c of row r sits at chunk c ^ (r & 7), so that
 // the eight rows an ldmatrix touches fall into different banks.
 template <int HD>
@@ -105,7 +75,7 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_decode_mma_kernel(DecodePar
     extern __shared__ __align__(128) uint8_t smem[];
     // per warp: K[2], V[2]; afterwards reused for the merge of the warps
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t wbase = smem_u32(smem) + warp * 4 * TILE_BYTES;
+    const uint32_t wbase = smem_addr(smem) + warp * 4 * TILE_BYTES;
     const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     const int G = p.Hq / p.Hkv;
 
@@ -317,7 +287,7 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_decode_mma_kernel(DecodePar
         // share of the outputs and reads every block's partial through distributed shared memory:
         // out = sum_s 2^(m_s - M) acc_s / sum_s 2^(m_s - M) l_s.
         cluster_sync_all();
-        const uint32_t pacc_addr = smem_u32(wml + NWARPS * 16 * 2);
+        const uint32_t pacc_addr = smem_addr(wml + NWARPS * 16 * 2);
         const uint32_t pml_addr = pacc_addr + 16 * HD * 4;
         for (int i = split * blockDim.x + threadIdx.x; i < G * HD; i += p.nsplit * blockDim.x) {
             const int g = i / HD, d = i - g * HD;

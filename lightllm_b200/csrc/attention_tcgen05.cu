@@ -25,10 +25,12 @@
 #include <unordered_map>
 
 #include "tcgen05_common.cuh"
+#include "warp_mma.cuh"
 
 namespace {
 
 using namespace t5;
+using wm::fast_exp2;
 
 constexpr int BQ = 128;     // query rows per block = TMEM lanes
 constexpr int BKV = 128;    // keys per tile
@@ -36,11 +38,6 @@ constexpr int NUM_THREADS = 320;   // 8 softmax warps (two threads per query row
                                    // half of the output), the warp that issues tensor-core work, the loader warp
 constexpr int MMA_WARP = 8, LOAD_WARP = 9;
 
-__device__ __forceinline__ float fast_exp2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
 // Masking is a select on the column index, never a branch: columns c_lo .. c_hi of the tile are this row's
 // visible keys (causal, the span's end, the window's start; c_hi < c_lo when none is).
 __device__ __forceinline__ float masked(float s, int col, int c_lo, int c_hi) {

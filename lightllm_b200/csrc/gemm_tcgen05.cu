@@ -38,15 +38,6 @@ constexpr int TILE_K = 64;        // bf16 elements per stage row = 128 bytes = o
 constexpr int UMMA_K = 16;
 constexpr int STAGES = 3;
 constexpr int NUM_THREADS = 192;
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr)
-        : "memory");
-}
 
 struct GemmParams {
     void* out;              // STORE / SWIGLU: bf16; STORE_F32: float
@@ -248,7 +239,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 for (int c0 = 0; c0 < BN; c0 += CHUNK) {
                     uint32_t r[32];
                     const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
-                    if (CHUNK == 32) tmem_ld32_nowait(taddr, r); else tmem_ld16(taddr, r);
+                    if (CHUNK == 32) tmem_ld32_nowait(taddr, r); else tmem_ld16_nowait(taddr, r);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                     if (!SWAP) {
                         // row = token m, columns = output features n: 32 consecutive columns per thread

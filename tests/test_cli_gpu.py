@@ -88,7 +88,8 @@ def test_bench_ops_times_every_operator():
     recs = [json.loads(line) for line in out.splitlines() if line.startswith("{")]
     names = [r["op"] for r in recs]
     for want in ("embedding", "rmsnorm", "rmsnorm_float32", "rope_table", "rope_kv_write", "gemm_simt_float32",
-                 "paged_attention_simt_float32", "paged_decode_mma", "paged_decode_mma_and_merge", "argmax",
-                 "sample_top_k_top_p", "sample_temperature_only"):
+                 "paged_attention_simt_float32", "paged_attention_tcgen05", "paged_decode_mma",
+                 "paged_decode_mma_and_merge", "argmax", "sample_top_k_top_p", "sample_temperature_only", "mma_issue"):
         assert want in names, names
-    assert all(r["us"] > 0 and r["MB"] > 0 for r in recs)
+    assert all(r["us"] > 0 and r["MB"] > 0 for r in recs if r["op"] != "mma_issue")
+    assert all(r["cycles_per_mma"] > 0 for r in recs if r["op"] == "mma_issue")
