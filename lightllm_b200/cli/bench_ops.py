@@ -100,6 +100,29 @@ def main(argv=None) -> int:
                                          i32([0]), bt, bt.shape[1], page, Hq, Hkv, hd, 0, 1 / math.sqrt(hd), bq),
         (2 * Ts * Hq * hd + 2 * Ts * Hkv * hd) * 4, 2 * 2 * Hq * hd * Ts * (Ts + 1) // 2)
 
+    # the four contractions of a layer on the tensor cores, as a portion of T rows runs them (K cut as the engine cuts it)
+    if ops.has_tcgen05() and T > 128:
+        from lightllm_b200.parts import linear as L
+        resid_f = rn(T, D)
+        w_qkv, b_qkv = rn(Nqkv, D, dtype=torch.bfloat16, s=D ** -0.5), rn(Nqkv)
+        w_o = rn(D, Hq * hd, dtype=torch.bfloat16, s=(Hq * hd) ** -0.5)
+        w_gu = rn(2 * I, D, dtype=torch.bfloat16, s=D ** -0.5)
+        w_dn = rn(D, I, dtype=torch.bfloat16, s=I ** -0.5)
+        x_in, attn_o = rn(T, D, dtype=torch.bfloat16), rn(T, Hq * hd, dtype=torch.bfloat16)
+        act = torch.empty((T, I), dtype=torch.bfloat16, device=dev)
+        qkv_out = torch.empty((T, Nqkv), dtype=torch.bfloat16, device=dev)
+        gemm_bytes = lambda M, N, K, out_b: (M * K + N * K) * 2 + M * N * out_b
+        run("gemm_tcgen05_qkv", lambda: L.linear(x_in, w_qkv, b_qkv, L.STORE, qkv_out), gemm_bytes(T, Nqkv, D, 2), 2 * T * Nqkv * D)
+        run("gemm_tcgen05_o_proj_residual", lambda: L.linear(attn_o, w_o, None, L.RESIDUAL, residual=resid_f),
+            gemm_bytes(T, D, Hq * hd, 8), 2 * T * D * Hq * hd)
+        run("gemm_tcgen05_gate_up_swiglu", lambda: L.linear(x_in, w_gu, None, L.SWIGLU, act), gemm_bytes(T, 2 * I, D, 1),
+            2 * T * 2 * I * D)
+        run("gemm_tcgen05_down_residual", lambda: L.linear(act, w_dn, None, L.RESIDUAL, residual=resid_f), gemm_bytes(T, D, I, 8),
+            2 * T * D * I)
+        for sk in (1, 2, 4):
+            run(f"gemm_tcgen05_down_residual_split{sk}", lambda: ops.gemm_tcgen05(act, w_dn, None, ops.EPI_RESIDUAL, None, resid_f, sk),
+                gemm_bytes(T, D, I, 8), 2 * T * D * I)
+
     # the tensor-core attention of the whole portion (a prompt of T rows from position 0), cut into items as the engine does
     if ops.attention_tcgen05_supports(hd, page):
         from lightllm_b200.engine.batch import cut_attention_rows

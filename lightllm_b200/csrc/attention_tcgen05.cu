@@ -210,7 +210,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
     // Programmatic dependent launch: set-up is done; from here on global memory is touched, so the kernel before
-    // this one must have completed.
+    // this one must have completed.  The kernel after this one may start its set-up as blocks of this one leave.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int total = p.num_items;
     // The items come longest first.  Dealt round-robin, the blocks that got the longest items of one round would also

@@ -47,6 +47,8 @@ struct GemmParams {
     int num_kb;             // K blocks in all
     int kb_per_split;       // K blocks per grid.z slice (per split of the persistent kernel)
     int splits;             // persistent kernel: work items per tile along K
+    int direct;             // residual epilogue with splits: every piece adds its part to the residual itself (TMA
+                            // reduce-add), nothing meets in `partials`
     float* partials;        // [items, tile width, 128] float: the splits' accumulators meet here
     int* counters;          // [tiles, 8] zero before and after: arrivals per warp region of a tile
     int tma_out;            // the epilogue leaves through shared memory and TMA stores (map_out is valid)
@@ -516,8 +518,10 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
     if (PAIR) cluster_sync_all();       // both CTAs' barriers exist before either signals the other's
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_slot_s;
-    // Programmatic dependent launch: the kernel after this one may start its own set-up as blocks of this one leave;
-    // nothing here reads or writes global memory before the kernel before this one has completed.
+    // Programmatic dependent launch: the kernel after this one may start its own set-up as blocks of this one leave
+    // (it waits for this kernel's completion itself before it touches global memory); nothing here reads or writes
+    // global memory before the kernel before this one has completed.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == 0) {
         if (lane == 0) {
@@ -627,7 +631,8 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
             const int a_row0 = (t % m_tiles) * ROWS_PER_TILE + (int)rank * TILE_M, b_row0 = (t / m_tiles) * P_BN;
             if (!mbar_wait(&acc_full[buf], (local >> 1) & 1, abort_flag)) break;      // uniform over the warp
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (splits == 2) {
+            const bool direct = EPI == LLB_EPI_RESIDUAL && p.direct != 0;      // uniform over the grid
+            if (splits == 2 && !direct) {
                 // Two pieces: each finishes one half of the tile's columns.  The warps whose half belongs to the other
                 // piece first give their part of the accumulator away through memory and raise a flag; giving never
                 // waits.  Then every warp takes a share of the block's own half: it waits for the other piece's part,
@@ -694,7 +699,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
                 }
                 continue;
             }
-            if (splits > 1) {
+            if (splits > 1 && !direct) {
                 // This split's accumulator goes to the meeting place; the warp that arrives last at its
                 // region of the tile (32 rows x half the columns) adds the splits up in their order, so the
                 // sum does not depend on who came last, and runs the epilogue.
@@ -930,6 +935,10 @@ int dispatch_persistent(int epi, const CUtensorMap& ma, const CUtensorMap& mb, G
             p.tma_out = 1;
         }
     }
+    // Pieces of a residual contraction without bias add their parts through the TMA store path themselves: float adds in
+    // L2 commute up to rounding, and the meeting place (a round trip of every accumulator through memory, and a wait of
+    // one piece for the other) is saved.
+    p.direct = (epi == LLB_EPI_RESIDUAL && p.splits > 1 && p.bias == nullptr && p.tma_out) ? 1 : 0;
     switch (epi) {
         case LLB_EPI_STORE: return launch_persistent<LLB_EPI_STORE, P_BN, PAIR>(ma, mb, mo, p, s);
         case LLB_EPI_STORE_F32: return launch_persistent<LLB_EPI_STORE_F32, P_BN, PAIR>(ma, mb, mo, p, s);
@@ -958,7 +967,9 @@ int dispatch_epi(int epi, const CUtensorMap& ma, const CUtensorMap& mb, const Ge
 // RESIDUAL only (atomic adds).  Beyond, any epilogue may be split: the pieces meet in `partials` (at least
 // llb_gemm_tcgen05_partial_floats(M, N, split_k) floats) and `counters` (8 ints per tile of 128 rows x 256 (N > 128)
 // or 128 features, zero before the call and zero again after it), and the piece that arrives last adds them up
-// in their order, so the result does not depend on the order of arrival.  error_flag: one int that the kernel
+// in their order, so the result does not depend on the order of arrival (except a RESIDUAL contraction without bias
+// whose output row is a multiple of 16 bytes: its pieces add themselves into `residual`, float adds that commute up
+// to rounding, and the meeting place is not touched).  error_flag: one int that the kernel
 // raises if a wait inside it ran out of time (the result is then invalid), or null.
 LLB_EXPORT int llb_gemm_tcgen05(const void* A, const void* W, const float* bias, void* out, float* residual,
                                 int epilogue, int M, int N, int K, int split_k, float* partials, int* counters,

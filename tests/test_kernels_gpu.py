@@ -154,10 +154,14 @@ def test_gemm_tcgen05(ops, M, N, K, epi):
         assert torch.allclose(got, ref, atol=tol * scale, rtol=0), f"max diff {float((got - ref).abs().max())}"
         if split_k > 1 and M > 128:
             # the pieces are added in their order, whoever arrives last: a second run gives the same bits,
-            # and the meeting place's counters are zero again
+            # and the meeting place's counters are zero again.  (A residual contraction without bias adds its pieces
+            # straight into the residual instead: float adds in L2, equal up to the rounding of their order.)
             again = res0.clone() if epi == 2 else torch.empty_like(out)
             ops.gemm_tcgen05(a, w, bias, epi, None if epi == 2 else again, again if epi == 2 else None, split_k)
-            assert torch.equal(again, residual if epi == 2 else out)
+            if epi == 2 and bias is None:
+                assert torch.allclose(again, residual, atol=2e-6 * scale, rtol=0)
+            else:
+                assert torch.equal(again, residual if epi == 2 else out)
             assert int(ops._meet_counters[dev().index or 0].abs().max()) == 0
 
 
