@@ -17,7 +17,7 @@ from . import build as _build
 
 F32, BF16 = 0, 1
 EPI_STORE, EPI_STORE_F32, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
-ABI_VERSION = 19
+ABI_VERSION = 20
 
 _lib: Optional[ctypes.CDLL] = None
 
@@ -54,6 +54,8 @@ def _declare_signatures(handle: ctypes.CDLL) -> None:
 
     def ctype(decl: str):
         decl = " ".join(decl.split())
+        if decl == "void":
+            return None
         if decl in _C_TYPES:
             return _C_TYPES[decl]
         if decl.endswith("*"):
@@ -121,6 +123,11 @@ class stream_scope:
 def _stream() -> int:
     s = _scoped_stream
     return s if s is not None else torch.cuda.current_stream().cuda_stream
+
+
+def current_stream() -> int:
+    """The stream that this module's launches go to right now (see :class:`stream_scope`)."""
+    return _stream()
 
 
 def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, err: Optional[torch.Tensor] = None) -> None:
@@ -563,6 +570,15 @@ _meet_counters = {}
 _MEET_COUNTERS = 1 << 16
 
 
+def meet_counters(device: torch.device) -> torch.Tensor:
+    """The device's counters of wide split contractions (zero before and after every launch), made on first use."""
+    key = torch.device(device).index or 0
+    counters = _meet_counters.get(key)
+    if counters is None:
+        counters = _meet_counters[key] = torch.zeros(_MEET_COUNTERS, dtype=torch.int32, device=device)
+    return counters
+
+
 def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], epilogue: int,
                  out: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
                  split_k: int = 1) -> None:
@@ -584,10 +600,7 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
         if need > _MEET_COUNTERS:
             split_k = 1
         else:
-            key = a.device.index or 0
-            counters = _meet_counters.get(key)
-            if counters is None:
-                counters = _meet_counters[key] = torch.zeros(_MEET_COUNTERS, dtype=torch.int32, device=a.device)
+            counters = meet_counters(a.device)
             partials = torch.empty(lib().llb_gemm_tcgen05_partial_floats(M, N, split_k), dtype=torch.float32,
                                    device=a.device)
     _check(lib().llb_gemm_tcgen05(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), _ptr(residual), epilogue, M, N, K,

@@ -23,6 +23,7 @@ from ..parts import CacheView
 from ..parts.base import LazyNorm
 from .batch import Span, StepContext, StepEntry
 from .fused_decode import FusedDecode
+from .native_step import NativeLayers
 
 
 class StepError(ValueError):
@@ -88,6 +89,8 @@ class ModelRunner:
         self.graph_launches = 0          # kernels launched through graph replays
         # Decode steps run the common layers as one persistent kernel per segment of the run list.
         self.fused = FusedDecode(model, self.views, self.device)
+        # Every other step runs them through the library's step executor: one call for a stretch of run entries.
+        self.native = NativeLayers(model, self.views, self.device)
 
     # ------------------------------------------------------------------------------------------
     def _build_context(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> StepContext:
@@ -232,6 +235,12 @@ class ModelRunner:
             if segment is not None:
                 segment.run(residual, ctx)
                 i = segment.end
+            elif self.native.covers[i]:
+                j = self.native.stretch(i)
+                if fused is not None:           # up to where the next fused segment begins
+                    j = next((k for k in range(i + 1, j) if fused.segment_at(k) is not None), j)
+                self.native.run(residual, ctx, i, j)
+                i = j
             else:
                 m.layers[m.run[i].layer].forward(residual, ctx, self.views[i])
                 i += 1

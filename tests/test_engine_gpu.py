@@ -394,6 +394,67 @@ def test_decode_steps_through_the_persistent_kernel(tmp_path, name, rows):
     core.runner.check_device_errors()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["B", "D", "E"])
+def test_layers_through_the_step_executor_match_the_parts(tmp_path, monkeypatch, name, dtype):
+    """The same steps (a whole prompt, portions beside decoded tokens, decode steps of few and of 40 rows, a step whose
+    portion is long enough for the tensor-core projection) through the library's step executor and through the parts
+    launched one by one: the two issue the same kernels, so the logits agree to the last bits that the order of
+    atomic adds leaves open, and both follow the plain implementation."""
+    d = model_dir(tmp_path, name, seed=23, store="float32" if dtype == "float32" else "bfloat16", edit=sharpen(3.0))
+    cfg, w = P.read_model_dir(d)
+    rng = random.Random(24)
+    V, page = cfg["vocab_size"], PAGE_SIZE[name]
+    nreq = 40
+    lens = [3 + (29 * i) % 90 for i in range(nreq)]
+    seqs = {i: [rng.randrange(V) for _ in range(n + 4)] for i, n in enumerate(lens)}
+    seqs["long"] = [rng.randrange(V) for _ in range(150)]
+    ref = {i: P.plain_forward(cfg, w, s) for i, s in seqs.items()}
+
+    def run(native: bool):
+        monkeypatch.setenv("LLB_NATIVE_STEP", "1" if native else "0")
+        monkeypatch.setenv("LLB_FUSED_DECODE", "0")          # decode steps take the layer-by-layer path as well
+        core = EngineCore(d, EngineOptions(dtype=dtype, max_seq_len=256, max_batch_tokens=2048, page_size=page,
+                                           num_pages=(nreq + 2) * (-(-160 // page) + 1), max_seqs=nreq + 1,
+                                           use_cuda_graphs=False))
+        assert all(core.runner.native.covers) == native
+        out = []
+        for i in range(nreq):
+            core.open(i)
+        core.open("long")
+        # whole prompts of the first requests, one by one and several in a step
+        out.append(core.step([StepEntry(0, seqs[0][: lens[0]], [lens[0] - 1])]))
+        out.append(core.step([StepEntry(i, seqs[i][: lens[i]], [lens[i] - 1]) for i in range(1, 6)]))
+        # portions of the long prompt beside decoded tokens of those, then beside more prompts
+        out.append(core.step([StepEntry("long", seqs["long"][:100], [0, 99])] +
+                             [StepEntry(i, [seqs[i][lens[i]]], [0]) for i in range(0, 6)]))
+        out.append(core.step([StepEntry("long", seqs["long"][100:150], [49])] +
+                             [StepEntry(i, seqs[i][: lens[i]], [lens[i] - 1]) for i in range(6, nreq)]))
+        # decode steps: three rows, then forty
+        out.append(core.step([StepEntry(i, [seqs[i][lens[i] + 1]], [0]) for i in range(0, 3)]))
+        out.append(core.step([StepEntry(i, [seqs[i][lens[i] + (2 if i < 3 else 1 if i < 6 else 0)]], [0]) for i in range(nreq)]))
+        core.runner.check_device_errors()
+        calls = core.runner.native.calls
+        return [o.float().cpu() for o in out], calls
+
+    parts, calls0 = run(False)
+    native, calls1 = run(True)
+    assert calls0 == 0 and calls1 == 6          # one call of the executor per step
+    tol = atol_for({"B": "C sharp"}.get(name, name + " sharp"), dtype, ref)
+    # In bfloat16 the split contractions add their pieces in whatever order they arrive; a float sum that differs in its
+    # last bit can round an activation to the neighbouring bfloat16, so the two runs may differ by a fraction of the
+    # error that either has against the plain implementation (a quarter of the allowance, half of the measured worst).
+    for a, b in zip(parts, native):
+        assert a.shape == b.shape
+        assert float((a - b).abs().max()) <= (1e-5 if dtype == "float32" else 0.25 * tol)
+    # and against the plain implementation: the first and the last step
+    assert float((native[0][0] - ref[0][lens[0] - 1]).abs().max()) <= tol
+    last = native[-1]
+    for i in range(nreq):
+        at = lens[i] + (2 if i < 3 else 1 if i < 6 else 0)
+        assert float((last[i] - ref[i][at]).abs().max()) <= tol, (i, at)
+
+
 def test_temperature_sampling_is_seeded_and_per_request(tmp_path):
     d = model_dir(tmp_path, "A", store="bfloat16")
     eng = Engine(d, dtype="bfloat16", max_seq_len=128, max_batch_tokens=64, num_pages=40, max_seqs=4)
