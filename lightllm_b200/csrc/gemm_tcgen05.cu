@@ -911,6 +911,19 @@ bool pair_tiles_enabled() {
     return on == 1;
 }
 
+// Features from which the pair tiles are used (LLB_GEMM_PAIR_MIN_N in the environment, for comparisons).  Measured at
+// 2,048 rows: 1,536 features (o_proj and down at the 1.5B sizes, which single tiles of 128 x 128 run in two uneven rounds,
+// each waiting for operands) take 6.6 ms a prefill step with pair tiles against 8.1 ms without; 896 features gain nothing.
+int pair_min_features() {
+    static int n = -1;
+    if (n < 0) {
+        const char* e = getenv("LLB_GEMM_PAIR_MIN_N");
+        n = e ? atoi(e) : 1024;
+        if (n < 256) n = 256;
+    }
+    return n;
+}
+
 template <int P_BN, bool PAIR = false>
 int dispatch_persistent(int epi, const CUtensorMap& ma, const CUtensorMap& mb, GemmParams p, cudaStream_t s) {
     // The output's tensor map for the staged epilogue: rows of 128 bytes (32 floats or 64 bf16) x 32 rows, 128-byte
@@ -939,6 +952,7 @@ int dispatch_persistent(int epi, const CUtensorMap& ma, const CUtensorMap& mb, G
     // L2 commute up to rounding, and the meeting place (a round trip of every accumulator through memory, and a wait of
     // one piece for the other) is saved.
     p.direct = (epi == LLB_EPI_RESIDUAL && p.splits > 1 && p.bias == nullptr && p.tma_out) ? 1 : 0;
+    if (PAIR && p.splits > 1 && !p.direct) return llb_fail("gemm_tcgen05: pair tiles cannot meet pieces along K");
     switch (epi) {
         case LLB_EPI_STORE: return launch_persistent<LLB_EPI_STORE, P_BN, PAIR>(ma, mb, mo, p, s);
         case LLB_EPI_STORE_F32: return launch_persistent<LLB_EPI_STORE_F32, P_BN, PAIR>(ma, mb, mo, p, s);
@@ -1015,7 +1029,7 @@ LLB_EXPORT int llb_gemm_tcgen05(const void* A, const void* W, const float* bias,
     p.counters = counters;
     // Many rows and many features: pairs of CTAs on tiles of 256 x 256, each CTA loading its own rows and half of
     // the weights' tile.
-    if (split_k == 1 && N >= 2048 && M >= 512 && pair_tiles_enabled()) {
+    if (split_k == 1 && N >= pair_min_features() && M >= 512 && pair_tiles_enabled()) {
         if ((rc = make_map(W, N, K, 128, &mb))) return rc;
         return dispatch_persistent<256, true>(epilogue, ma, mb, p, stream);
     }

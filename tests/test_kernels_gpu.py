@@ -123,7 +123,7 @@ def test_gemm_simt(ops, M, N, K, epi, dtypes):
 TC_SHAPES = [(9, 50, 40), (16, 128, 64), (17, 130, 64), (33, 1152, 896), (64, 9728, 896), (65, 896, 4864),
              (128, 896, 896), (129, 200, 72), (300, 1000, 96), (2048, 1152, 896), (1000, 896, 4864), (12, 151936, 896),
              # many rows and features: tiles of 256 x 256 on pairs of CTAs (whole pairs, ragged edges, several rounds)
-             (512, 2048, 64), (600, 2304, 136), (1000, 9728, 896), (4100, 2600, 200)]
+             (512, 2048, 64), (600, 2304, 136), (1000, 9728, 896), (4100, 2600, 200), (2048, 1536, 1536), (700, 1030, 264)]
 
 
 @pytest.mark.parametrize("M,N,K", TC_SHAPES)
