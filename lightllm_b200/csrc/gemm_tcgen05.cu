@@ -1097,6 +1097,12 @@ LLB_EXPORT int llb_gemm_tcgen05_rope(const void* A, const void* W, const float* 
         if (r != CUDA_SUCCESS) return llb_fail("gemm_tcgen05_rope: cuTensorMapEncodeTiled (q) failed with code %d", (int)r);
         p.tma_out = 1;
     }
+    // Many rows and features: pair tiles, as the plain contraction takes them (each CTA loads 128 of the tile's 256 weight
+    // rows, which is the box of `mb` already).  Measured at 2,048 rows: 4,608 features (the 7B sizes) 25.0 ms a prefill step
+    // against 26.1; 2,048 features (1.5B) and 1,152 (0.5B) gain nothing, so the rule starts at 4,096.
+    if (M >= 512 && N >= 4 * pair_min_features() && pair_tiles_enabled())
+        return hd == 128 ? launch_persistent<EPI_ROPE128, 256, true>(ma, mb, mq, p, stream)
+                         : launch_persistent<EPI_ROPE64, 256, true>(ma, mb, mq, p, stream);
     return hd == 128 ? launch_persistent<EPI_ROPE128, 128>(ma, mb, mq, p, stream)
                      : launch_persistent<EPI_ROPE64, 128>(ma, mb, mq, p, stream);
 }

@@ -273,7 +273,9 @@ def test_gemm_decode_rope_kv(ops, M, hd, rd, inter, Hq, Hkv, norm):
 
 @pytest.mark.parametrize("M", [17, 64, 129, 300, 1000])
 @pytest.mark.parametrize("Hq,Hkv,K,bias_on,hd", [(14, 2, 896, True, 64), (3, 1, 72, False, 64), (5, 5, 200, True, 64),
-                                                 (12, 2, 1536, True, 128), (3, 1, 72, False, 128), (2, 2, 200, True, 128)])
+                                                 (12, 2, 1536, True, 128), (3, 1, 72, False, 128), (2, 2, 200, True, 128),
+                                                 # 4,608 and 4,224 features: pair tiles of 256 x 256
+                                                 (28, 4, 264, True, 128), (50, 8, 136, False, 64)])
 def test_gemm_tcgen05_rope(ops, M, Hq, Hkv, K, bias_on, hd):
     """q/k/v projection of a long portion with bias, rotation and the cache write in the tensor-core
     epilogue, against the plain parts; heads of 64 (two heads a tile) and of 128 (the pairs' members lie in
