@@ -740,6 +740,12 @@ def toy_spec(cfg: ToyConfig) -> ModelSpec:
                                         SubBlock("ffn", ffn("l1.ffn"), norm("l1.n2"), norm("l1.n2s"), after="stream")]),
                   LayerSpec(sub_blocks=[SubBlock("ffn", ffn("l2.ffn"))])]
         run = [RunEntry(0), RunEntry(1), RunEntry(2)]
+    elif cfg.variant == "reread":
+        # the common block only, so that every run entry goes through the library's step executor: a layer that runs
+        # twice, the second time reading the keys and values its first run wrote (it projects q alone)
+        layers = [LayerSpec(norm("l0.n1"), attn("l0.attn"), norm("l0.n2"), ffn("l0.ffn")),
+                  LayerSpec(norm("l1.n1"), attn("l1.attn"), norm("l1.n2"), ffn("l1.ffn"))]
+        run = [RunEntry(0), RunEntry(1), RunEntry(0, cache_of=0)]
     else:   # "shared": a parallel block, a layer that runs twice, and a run that reads an earlier run's cache
         layers = [LayerSpec(norm("l0.n1"), attn("l0.attn"), norm("l0.n2"), ffn("l0.ffn"), arrangement="parallel"),
                   LayerSpec(norm("l1.n1"), attn("l1.attn"), norm("l1.n2"), ffn("l1.ffn"))]
@@ -812,6 +818,14 @@ def toy_plain(raw, w, ids):
         h = h + torch.stack(outs)
         h = h + ffn("l0.ffn", P.plain_rmsnorm(h, w["l0.n2.weight"], eps))
         h = pre_norm_attn_layer("l1", h)
+    elif raw.get("variant") == "reread":
+        q0, k0, v0 = qkv("l0.attn", P.plain_rmsnorm(h, w["l0.n1.weight"], eps))
+        h = h + attn_out("l0.attn", q0, k0, v0)
+        h = h + ffn("l0.ffn", P.plain_rmsnorm(h, w["l0.n2.weight"], eps))
+        h = pre_norm_attn_layer("l1", h)
+        q2, _, _ = qkv("l0.attn", P.plain_rmsnorm(h, w["l0.n1.weight"], eps))       # keys and values of run entry 0
+        h = h + attn_out("l0.attn", q2, k0, v0)
+        h = h + ffn("l0.ffn", P.plain_rmsnorm(h, w["l0.n2.weight"], eps))
     else:
         x1, x2 = P.plain_rmsnorm(h, w["l0.n1.weight"], eps), P.plain_rmsnorm(h, w["l0.n2.weight"], eps)
         q0, k0, v0 = qkv("l0.attn", x1)
@@ -825,7 +839,7 @@ def toy_plain(raw, w, ids):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("variant", ["state", "shared", "routed", "norms"])
+@pytest.mark.parametrize("variant", ["state", "shared", "routed", "norms", "reread"])
 def test_toy_architecture_registered_from_the_test(tmp_path, variant, dtype):
     """Architectures made of the framework's parts and of parts defined in this file (a mixer with state of its own,
     a feed-forward with routing, a learned position encoding) and of other arrangements of a layer (a mixer alone,
@@ -846,6 +860,8 @@ def test_toy_architecture_registered_from_the_test(tmp_path, variant, dtype):
         assert len(layout.state_planes) == 1 and layout.planes_per_group == [1]
     elif variant == "shared":
         assert layout.planes_per_group == [3] and not layout.refs[3].owns
+    elif variant == "reread":
+        assert layout.planes_per_group == [2] and not layout.refs[2].owns and all(core.runner.native.covers)
     rng = random.Random(10)
     seqs = {n: [rng.randrange(211) for _ in range(L)] for n, L in (("a", 50), ("b", 31), ("c", 44))}
     ref, sure = {}, {}
