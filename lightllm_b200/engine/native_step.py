@@ -15,7 +15,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from typing import Dict, List, Optional
+from typing import List, Optional
 
 import torch
 
@@ -139,7 +139,7 @@ class NativeLayers:
         _check_layout()
         self.device = device
         self.dtype = model.dtype
-        records, self._keep, self._mixers = [], [], []
+        records, self._keep = [], []
         self._plan_keys: List[object] = []          # distinct attention plans of a step, by the mixers' prepare_key
         self._plan_mixer: List[AttentionMixer] = []
         hidden = None
