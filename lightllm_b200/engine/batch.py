@@ -9,6 +9,7 @@ attends wrongly, engine_server.cpp:1603-1612).
 """
 from __future__ import annotations
 
+import math
 from dataclasses import dataclass, field
 from typing import Any, Dict, Hashable, List, Optional, Sequence
 
@@ -36,17 +37,14 @@ class Span:
     row: int           # first row of the batch that belongs to it
 
 
-def cut_attention_rows(rows, chunk_tiles=None, heads=1, slots=1):
-    """Cuts row tiles ``(span, q0, key tiles)`` into the work items of the tensor-core attention kernel: a tile
-    whose key range is longer than ``chunk_tiles`` (+1) becomes pieces of that many key tiles, which leave partial
-    results for the merge kernel.  With ``chunk_tiles=None`` the piece is as long as the work allows: the tiles of
-    all ``heads`` spread over ``slots`` resident blocks give each block so many tiles anyway, and shorter pieces
-    would only add partial results to merge (between 4 and 16).  Returns ``(items, merges, parts)``: items
-    ``(key tiles, span, q0, first key tile, key tiles, part or -1)`` longest first, merges ``(span, q0, first part,
-    parts)``, and the number of partial results."""
-    if chunk_tiles is None:
-        total = sum(r[2] for r in rows)
-        chunk_tiles = min(16, max(4, -(-total * heads // max(1, slots))))
+# What the tensor-core attention kernel's time is made of, fitted to B200 measurements (14 heads of 64, one prompt of
+# 2,048 to 8,192 rows, pieces of 4 to 64 key tiles; the fit is within 6 us of every measurement): microseconds per key
+# tile of the busiest block, a fixed cost of the merge kernel if anything is cut, and its cost per partial result and
+# head.  Only their ratios matter here.
+_TILE_US, _MERGE_US, _PART_US = 2.56, 10.2, 0.026
+
+
+def _cut(rows, chunk_tiles):
     items, merges, parts = [], [], 0
     for i, q0, ntiles in rows:
         if ntiles <= chunk_tiles + 1:
@@ -60,6 +58,55 @@ def cut_attention_rows(rows, chunk_tiles=None, heads=1, slots=1):
         parts += nchunks
     items.sort(key=lambda t: -t[0])
     return items, merges, parts
+
+
+def _busiest_block(items, heads: int, slots: int) -> float:
+    """Key tiles of the block with the most work when the kernel deals the items (times ``heads``, heads fastest) to
+    ``slots`` blocks: one item of every round of ``slots`` items, every other round backwards."""
+    lengths = np.repeat(np.fromiter((t[0] for t in items), dtype=np.int64, count=len(items)), heads)
+    grid = min(len(lengths), max(1, slots))
+    idx = np.arange(len(lengths))
+    pos = idx % grid
+    slot = np.where((idx // grid) % 2 == 0, pos, grid - 1 - pos)
+    return float(np.bincount(slot, weights=lengths, minlength=grid).max())
+
+
+def cut_attention_rows(rows, chunk_tiles=None, heads=1, slots=1):
+    """Cuts row tiles ``(span, q0, key tiles)`` into the work items of the tensor-core attention kernel: a tile
+    whose key range is longer than ``chunk_tiles`` (+1) becomes pieces of that many key tiles, which leave partial
+    results for the merge kernel.  With ``chunk_tiles=None`` the piece length is chosen for the step: a few candidates
+    (the share of key tiles that a block gets anyway when all ``heads`` are spread over ``slots`` resident blocks, some
+    multiples of it, and no cut at all) are dealt to the blocks as the kernel deals them, and the one with the least
+    estimated time wins: the busiest block's tiles plus what the merge of the partial results costs.  (Measured, one
+    prompt, 14 heads, 296 blocks: 2,048 rows 41 us with pieces of 7 against 47 uncut; 4,096 rows 88 us uncut against
+    101 with pieces of 16; 8,192 rows 279 against 319.)  Returns ``(items, merges, parts)``: items ``(key tiles, span,
+    q0, first key tile, key tiles, part or -1)`` longest first, merges ``(span, q0, first part, parts)``, and the
+    number of partial results."""
+    if chunk_tiles is not None or not rows:
+        return _cut(rows, chunk_tiles if chunk_tiles is not None else 1)
+    key = (tuple(r[2] for r in rows), heads, slots)
+    chunk = _chosen_chunk.get(key)
+    if chunk is None:
+        longest = max(key[0])
+        share = sum(key[0]) * heads / max(1, slots)
+        candidates = sorted({min(longest, max(4, math.ceil(share * f))) for f in (0.34, 0.5, 0.75, 1.0, 1.5, 2.0, 3.0)}
+                            | {longest})
+        best = None
+        for c in candidates:
+            items, _, parts = _cut(rows, c)
+            cost = _TILE_US * _busiest_block(items, heads, slots)
+            if parts:
+                cost += _MERGE_US + _PART_US * parts * heads
+            if best is None or cost < best[0] - 1e-9:
+                best = (cost, c)
+        chunk = best[1]
+        if len(_chosen_chunk) >= 4096:          # steps of ever new shapes: start over rather than grow
+            _chosen_chunk.clear()
+        _chosen_chunk[key] = chunk
+    return _cut(rows, chunk)
+
+
+_chosen_chunk: Dict[tuple, int] = {}      # the piece length chosen for (the rows' key tiles, heads, slots)
 
 
 class StepContext:
@@ -154,8 +201,8 @@ class StepContext:
         of 128 query rows whose key range (in tiles of 128 keys) is cut into pieces of ``chunk_tiles``, longest
         first, so that a long prompt's last rows do not set the kernel's time.  With ``chunk_tiles=None`` the
         piece is as long as the work allows: the tiles of all ``heads`` spread over ``slots`` resident blocks give
-        each block so many tiles anyway, and shorter pieces would only add partial results to merge (between 4
-        and 16).  ``select`` names the spans by index instead of all of at least ``min_len`` rows.  Returns
+        each block so many tiles anyway, and shorter pieces would only add partial results to merge (see
+        :func:`cut_attention_rows`).  ``select`` names the spans by index instead of all of at least ``min_len`` rows.  Returns
         ``(tile_span, tile_q0, count, cut)`` with ``cut`` as ``ops.paged_attention_tcgen05`` takes it."""
         key = ("items", min_len, window, chunk_tiles, heads, slots, select)
         hit = self._tiles.get(key)
