@@ -137,5 +137,41 @@ def _build(bdir: str, lib: str, verbose: bool) -> None:
         print(f"[lightllm_b200] built {LIB_NAME} in {time.time() - t0:.0f} s", file=sys.stderr, flush=True)
 
 
+HOST_DIR = os.path.join(CSRC_DIR, "host")
+TOOL_NAME = "generate"
+
+
+def tool_path(build: bool = True, verbose: bool = True) -> str:
+    """Path of the C++ ``generate`` program (``csrc/host/generate.cpp``), built beside the kernel library and linked
+    to it (it finds the library in its own folder).  It is rebuilt when its sources or the library's change."""
+    lib = library_path(build, verbose)
+    bdir = os.path.dirname(lib)
+    tool = os.path.join(bdir, TOOL_NAME)
+    stamp = os.path.join(bdir, "generate.fingerprint.txt")
+    h = hashlib.sha256(_fingerprint().encode())
+    for name in sorted(os.listdir(HOST_DIR)):
+        if name.endswith((".cpp", ".h")):
+            h.update(name.encode())
+            with open(os.path.join(HOST_DIR, name), "rb") as f:
+                h.update(f.read())
+    fp = h.hexdigest()[:16]
+    if os.path.isfile(tool) and os.path.isfile(stamp):
+        with open(stamp) as f:
+            if f.read().strip() == fp:
+                return tool
+    if not build:
+        raise BuildError(f"{tool} is missing or stale and building was not allowed")
+    if verbose:
+        print(f"[lightllm_b200] building {TOOL_NAME} in {bdir}", file=sys.stderr, flush=True)
+    tmp = tool + f".tmp{os.getpid()}"
+    _run([_nvcc(), "-O2", "-std=c++17", "-I", CSRC_DIR, os.path.join(HOST_DIR, "generate.cpp"), "-o", tmp,
+          "-L", bdir, "-l:" + LIB_NAME, "-lcudart", "-Xlinker", "-rpath=$ORIGIN"])
+    os.replace(tmp, tool)
+    with open(stamp, "w") as f:
+        f.write(fp)
+    return tool
+
+
 if __name__ == "__main__":
     print(library_path())
+    print(tool_path())

@@ -29,4 +29,4 @@ LLB_EXPORT const char* llb_last_error() { return g_last_error; }
 LLB_EXPORT unsigned long long llb_launch_count() { return g_launches; }
 
 // Version tag checked by the Python binding, so that a stale library is rebuilt.
-LLB_EXPORT int llb_abi_version() { return 20; }
+LLB_EXPORT int llb_abi_version() { return 21; }

@@ -17,7 +17,7 @@ from . import build as _build
 
 F32, BF16 = 0, 1
 EPI_STORE, EPI_STORE_F32, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
-ABI_VERSION = 20
+ABI_VERSION = 21
 
 _lib: Optional[ctypes.CDLL] = None
 

@@ -325,6 +325,39 @@ LLB_EXPORT int llb_step_layers(const LlbModelDesc* model, const LlbStepArgs* ste
     return e.run();
 }
 
+namespace {
+int head(Exec& e, const LlbNormDesc* norm, const void* head_w, int vocab, const int* rows, int R, float* logits) {
+    void* x = e.take((long long)R * e.m.hidden * e.es);
+    int rc = 0;
+    if (!e.dry)
+        rc = llb_rmsnorm(e.s.residual, LLB_F32, norm->weight, norm->weight_dtype, x, e.m.act_dtype, rows, R, e.m.hidden, norm->eps,
+                         e.s.stream);
+    if (rc) return rc;
+    return e.linear(x, head_w, nullptr, LLB_EPI_STORE_F32, logits, nullptr, R, vocab, e.m.hidden);
+}
+}  // namespace
+
+LLB_EXPORT long long llb_step_head_workspace_need(const LlbModelDesc* model, const LlbStepArgs* step, int vocab, int R) {
+    if (!model || !step || R < 0 || vocab <= 0) return -1;
+    if (R == 0) return 0;
+    Exec e(*model, *step, true);
+    if (head(e, nullptr, nullptr, vocab, nullptr, R, nullptr)) return -1;
+    return e.peak;
+}
+
+LLB_EXPORT int llb_step_head(const LlbModelDesc* model, const LlbStepArgs* step, const LlbNormDesc* norm, const void* head_w,
+                             int vocab, const int* rows, int R, float* logits) {
+    if (R == 0) return 0;
+    LLB_REQUIRE(model && step && norm && head_w && rows && logits && step->residual && step->workspace, "head: null argument");
+    LLB_REQUIRE(R > 0 && vocab > 0, "head: bad sizes (R=%d, vocab=%d)", R, vocab);
+    LLB_REQUIRE(model->act_dtype == LLB_F32 || model->act_dtype == LLB_BF16, "head: unknown dtype %d", model->act_dtype);
+    const long long need = llb_step_head_workspace_need(model, step, vocab, R);
+    LLB_REQUIRE(need >= 0 && need <= step->workspace_bytes, "head: the workspace has %lld bytes, %d rows need %lld",
+                step->workspace_bytes, R, need);
+    Exec e(*model, *step, false);
+    return head(e, norm, head_w, vocab, rows, R, logits);
+}
+
 LLB_EXPORT void llb_step_struct_sizes(int* out) {
     out[0] = (int)sizeof(LlbNormDesc);
     out[1] = (int)sizeof(LlbAttentionDesc);

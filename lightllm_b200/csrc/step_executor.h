@@ -121,6 +121,12 @@ typedef struct {
 int llb_step_layers(const LlbModelDesc* model, const LlbStepArgs* step);
 // Bytes of workspace that this step needs (what llb_step_layers would carve out of step->workspace).
 long long llb_step_workspace_need(const LlbModelDesc* model, const LlbStepArgs* step);
+// The model's head over chosen rows of the stream: the norm of rows `rows` [R] of step->residual, then the contraction
+// with head_w [vocab, hidden] into logits [R, vocab] (float), with the kernels that llb_step_layers would choose for a
+// contraction of that shape.  It takes its activations from step->workspace (llb_step_head_workspace_need).
+int llb_step_head(const LlbModelDesc* model, const LlbStepArgs* step, const LlbNormDesc* norm, const void* head_w, int vocab,
+                  const int* rows, int R, float* logits);
+long long llb_step_head_workspace_need(const LlbModelDesc* model, const LlbStepArgs* step, int vocab, int R);
 // sizeof of the six structs above, in their order, for the binding to compare with its own.
 void llb_step_struct_sizes(int* out);
 

@@ -93,3 +93,60 @@ def test_bench_ops_times_every_operator():
         assert want in names, names
     assert all(r["us"] > 0 and r["MB"] > 0 for r in recs if r["op"] != "mma_issue")
     assert all(r["cycles_per_mma"] > 0 for r in recs if r["op"] == "mma_issue")
+
+
+# ---- the C++ generate program (csrc/host/generate.cpp) -------------------------------------------------------------------
+def run_cpp_generate(*args, ok=True):
+    from lightllm_b200.csrc.build import tool_path
+    proc = subprocess.run([tool_path(), *map(str, args)], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=600)
+    assert (proc.returncode == 0) == ok, proc.stderr[-3000:]
+    return proc.stdout if ok else proc.stderr
+
+
+def cpp_outputs(text):
+    return [(list(map(int, m.group(1).split())), m.group(2)) for m in re.finditer(r"generated:\s*([\d ]+)\((\w+)\)", text)]
+
+
+@pytest.mark.parametrize("name", ["E", "D"])
+def test_cpp_generate_follows_the_plain_implementation(tmp_path, name):
+    """Three prompts through the C++ program, with a token budget that cuts the longer prompts into portions which run
+    beside the decoded tokens of the requests that started earlier: every token is the plain implementation's choice
+    for the same history.  E has heads of 128 and an untied head; D (without its window) heads of 64 in groups of 3
+    and a tied head."""
+    import random
+    from tests.test_engine_gpu import assert_greedy_follows_plain
+    cfg = config(name)
+    cfg["use_sliding_window"] = False
+    d = str(tmp_path / "m")
+    write_random_model(cfg, seed=11, out_dir=d, store_dtype="bfloat16")
+    cfg, w = P.read_model_dir(d)
+    rng = random.Random(4)
+    prompts = [[rng.randrange(cfg["vocab_size"]) for _ in range(n)] for n in (5, 300, 139)]
+    args = []
+    for p in prompts:
+        args += p + ["/"]
+    out = run_cpp_generate(d, *args[:-1], "--temperature", 0, "--max-new-tokens", 20, "--eos-token-id", 100000,
+                           "--max-batch-tokens", 128, "--max-seq-len", 512)
+    got = cpp_outputs(out)
+    assert [why for _, why in got] == ["length"] * 3
+    assert all(len(o) == 20 for o, _ in got)
+    assert_greedy_follows_plain(cfg, w, prompts, [o for o, _ in got], name, "bfloat16")
+    # and the Python entry point, which runs the same kernels over the same cuts of the layers, says the same
+    from lightllm_b200 import Engine
+    eng = Engine(d, dtype="bfloat16", max_seq_len=512, max_batch_tokens=128, max_seqs=4)
+    ref = eng.generate(prompts, max_new_tokens=20, temperature=0.0, eos_token_id=-1)
+    same = sum(a == b for (o, _), r in zip(got, ref) for a, b in zip(o, r))
+    assert same >= 54, (got, ref)          # a near-tie may fall the other way where the two cut their steps differently
+
+
+def test_cpp_generate_samples_the_same_tokens_for_the_same_seed(tmp_path):
+    d = str(tmp_path / "m")
+    write_random_model(config("E"), seed=3, out_dir=d, store_dtype="bfloat16")
+    a = cpp_outputs(run_cpp_generate(d, 1, 2, 3, "--seed", 5, "--max-seq-len", 64))
+    b = cpp_outputs(run_cpp_generate(d, 1, 2, 3, "--seed", 5, "--max-seq-len", 64))
+    c = cpp_outputs(run_cpp_generate(d, 1, 2, 3, "--seed", 6, "--max-seq-len", 64))
+    assert a == b and a != c
+    assert len(a[0][0]) == 12 or a[0][1] == "eos"          # the reference's 12 new tokens (tests/test_generate.cpp:148-149)
+    # a long prompt that ends at the sequence limit
+    long = cpp_outputs(run_cpp_generate(d, *range(1, 60), "--temperature", 0, "--max-seq-len", 64, "--eos-token-id", 100000))
+    assert long[0][1] == "max_seq_len" and len(long[0][0]) == 5
