@@ -12,7 +12,7 @@
 //
 // Options (names and defaults of python -m lightllm_b200.cli.generate): --max-new-tokens 12, --temperature 0.8,
 // --top-k 40, --top-p 0.9, --min-p 0, --seed 42, --eos-token-id (default: config.json's), --max-seq-len 2048,
-// --max-batch-tokens 2048.  Temperature 0 is greedy.  Sampling draws its uniforms from a generator of its own
+// --max-batch-tokens 2048; --timing prints times, --no-graphs issues every step launch by launch.  Temperature 0 is greedy.  Sampling draws its uniforms from a generator of its own
 // (splitmix64 of seed, request and step), so sampled tokens repeat for a seed but are not the Python entry point's.
 #include <cuda_runtime.h>
 #include <fcntl.h>
@@ -481,7 +481,7 @@ struct Options {
     int max_new_tokens = 12, top_k = 40, max_seq_len = 2048, max_batch_tokens = 2048, eos = -1;
     double temperature = 0.8, top_p = 0.9, min_p = 0.0;
     long long seed = 42;
-    bool timing = false;
+    bool timing = false, graphs = true;
 };
 
 Options parse_args(int argc, char** argv) {
@@ -511,10 +511,11 @@ Options parse_args(int argc, char** argv) {
         else if (a == "--max-batch-tokens") o.max_batch_tokens = (int)number(value(i), "--max-batch-tokens");
         else if (a == "--dtype") { if (value(i) != "bfloat16") die("--dtype: this program runs bfloat16 only; python -m lightllm_b200.cli.generate runs float32"); }
         else if (a == "--timing") o.timing = true;
+        else if (a == "--no-graphs") o.graphs = false;
         else if (a == "-h" || a == "--help") {
             std::printf("usage: generate <model_dir> [token ids ... [/ token ids ...]] [--max-new-tokens N] [--temperature T] [--top-k K]\n"
                         "                [--top-p P] [--min-p P] [--seed S] [--eos-token-id ID] [--max-seq-len N] [--max-batch-tokens N]\n"
-                        "                [--timing]\n");
+                        "                [--timing] [--no-graphs]\n");
             std::exit(0);
         } else if (a == "/") {
             if (cur.empty()) die("an empty prompt before '/'");
@@ -650,7 +651,9 @@ int main(int argc, char** argv) {
     std::set<int> eos(cfg.eos.begin(), cfg.eos.end());
     if (opt.eos >= 0) eos = {opt.eos};
     const int cluster_splits = llb_paged_decode_mma_cluster_splits();
-    long long steps = 0, prompt_tokens = 0, new_tokens = 0;
+    long long steps = 0, prompt_tokens = 0, new_tokens = 0, graph_steps = 0;
+    std::map<std::pair<int, int>, cudaGraphExec_t> graphs;          // by (requests, block-table width) of a decoding step
+    std::set<std::pair<int, int>> seen_shapes;
     double first_token_s = 0;
     const auto t0 = std::chrono::steady_clock::now();
 
@@ -819,39 +822,65 @@ int main(int argc, char** argv) {
         if (need < 0) die(std::string("the step cannot be laid out: ") + llb_last_error());
         if (need > workspace_bytes) {
             if (workspace) { cuda_ok(cudaStreamSynchronize(dev.stream), "synchronize"); dev.release(workspace); }
+            for (auto& g : graphs) cudaGraphExecDestroy(g.second);          // they name the old workspace
+            graphs.clear();
             workspace_bytes = need + need / 4 + (1 << 20);
             workspace = dev.alloc((size_t)workspace_bytes);
         }
         step.workspace = workspace;
         step.workspace_bytes = workspace_bytes;
 
-        lib_ok(llb_embedding(step.token_ids, w.embed, w.embed_dtype, residual, T, D, V, flags + 1, dev.stream), "embedding");
-        lib_ok(llb_step_layers(&model, &step), "layers");
-        if (R > 0) {
+        if (R > 0 && opt.temperature != 0.0) {
+            float *temp = samp_host, *top_p = samp_host + nreq, *min_p = samp_host + 2 * nreq, *uni = samp_host + 3 * nreq;
+            int* top_k = (int*)(samp_host + 4 * nreq);
+            int k = 0;
+            for (const Span& s : spans) {
+                if (!s.want) continue;
+                const Request& q = reqs[(size_t)s.request];
+                temp[k] = (float)opt.temperature;
+                top_p[k] = (float)opt.top_p;
+                min_p[k] = (float)opt.min_p;
+                top_k[k] = opt.top_k;
+                const uint64_t bits = splitmix64(splitmix64((uint64_t)opt.seed) ^ splitmix64(((uint64_t)s.request << 32) | (uint64_t)q.generated.size()));
+                uni[k] = (float)((bits >> 40) * (1.0 / 16777216.0));        // 24 bits: in [0, 1)
+                ++k;
+            }
+            cuda_ok(cudaMemcpyAsync(samp_dev, samp_host, (size_t)nreq * 5 * 4, cudaMemcpyHostToDevice, dev.stream), "copy of the sampling parameters");
+        }
+        // every launch of the step: they read the step's integers and parameters from fixed places of the device
+        auto issue = [&]() {
+            lib_ok(llb_embedding(step.token_ids, w.embed, w.embed_dtype, residual, T, D, V, flags + 1, dev.stream), "embedding");
+            lib_ok(llb_step_layers(&model, &step), "layers");
+            if (R == 0) return;
             lib_ok(llb_step_head(&model, &step, &w.final_norm, w.head, V, meta_dev + o_want, R, logits), "head");
-            if (opt.temperature == 0.0) {
+            if (opt.temperature == 0.0)
                 lib_ok(llb_argmax(logits, R, V, V, out_dev, R <= argmax_rows ? argmax_scratch : nullptr, argmax_rows, dev.stream), "argmax");
-            } else {
-                float *temp = samp_host, *top_p = samp_host + nreq, *min_p = samp_host + 2 * nreq, *uni = samp_host + 3 * nreq;
-                int* top_k = (int*)(samp_host + 4 * nreq);
-                int k = 0;
-                for (const Span& s : spans) {
-                    if (!s.want) continue;
-                    const Request& q = reqs[(size_t)s.request];
-                    temp[k] = (float)opt.temperature;
-                    top_p[k] = (float)opt.top_p;
-                    min_p[k] = (float)opt.min_p;
-                    top_k[k] = opt.top_k;
-                    const uint64_t bits = splitmix64(splitmix64((uint64_t)opt.seed) ^ splitmix64(((uint64_t)s.request << 32) | (uint64_t)q.generated.size()));
-                    uni[k] = (float)((bits >> 40) * (1.0 / 16777216.0));        // 24 bits: in [0, 1)
-                    ++k;
-                }
-                cuda_ok(cudaMemcpyAsync(samp_dev, samp_host, (size_t)nreq * 5 * 4, cudaMemcpyHostToDevice, dev.stream), "copy of the sampling parameters");
+            else
                 lib_ok(llb_sample(logits, R, V, V, samp_dev, (const int*)(samp_dev + 4 * nreq), samp_dev + nreq, samp_dev + 2 * nreq,
                                   samp_dev + 3 * nreq, out_dev, dev.stream), "sample");
+        };
+        // A decoding step of a shape seen before (so many requests, so wide a block table) is replayed as a CUDA graph:
+        // its launches depend on nothing else, and its arrays lie where they lay the first time.
+        const std::pair<int, int> shape{S, P};
+        if (decode_only && opt.graphs && seen_shapes.count(shape)) {
+            auto it = graphs.find(shape);
+            if (it == graphs.end()) {
+                cudaGraph_t graph = nullptr;
+                cudaGraphExec_t exec = nullptr;
+                cuda_ok(cudaStreamBeginCapture(dev.stream, cudaStreamCaptureModeThreadLocal), "cudaStreamBeginCapture");
+                issue();
+                cuda_ok(cudaStreamEndCapture(dev.stream, &graph), "cudaStreamEndCapture");
+                cuda_ok(cudaGraphInstantiate(&exec, graph, 0), "cudaGraphInstantiate");
+                cudaGraphDestroy(graph);
+                it = graphs.emplace(shape, exec).first;
             }
-            cuda_ok(cudaMemcpyAsync(out_host, out_dev, (size_t)R * 4, cudaMemcpyDeviceToHost, dev.stream), "copy of the tokens");
+            cuda_ok(cudaGraphLaunch(it->second, dev.stream), "cudaGraphLaunch");
+            ++graph_steps;
+        } else {
+            issue();
+            if (decode_only) seen_shapes.insert(shape);
         }
+        if (R > 0) cuda_ok(cudaMemcpyAsync(out_host, out_dev, (size_t)R * 4, cudaMemcpyDeviceToHost, dev.stream), "copy of the tokens");
         cuda_ok(cudaMemcpyAsync(out_host + nreq, flags, 8, cudaMemcpyDeviceToHost, dev.stream), "copy of the error flags");
         cuda_ok(cudaStreamSynchronize(dev.stream), "the step");
         if (out_host[nreq] != 0) die("a kernel gave up waiting (code " + std::to_string(out_host[nreq]) + "); the step's results are not valid");
@@ -890,9 +919,10 @@ int main(int argc, char** argv) {
         std::printf(" (%s)\n", q.reason ? q.reason : "?");
     }
     if (opt.timing)
-        std::fprintf(stderr, "[generate] %lld steps: %lld prompt tokens, first token after %.1f ms; %lld new tokens in %.1f ms (%.0f tokens/s)\n",
-                     steps, prompt_tokens, first_token_s * 1e3, new_tokens, total_s * 1e3, new_tokens / std::max(total_s, 1e-9));
+        std::fprintf(stderr, "[generate] %lld steps (%lld as graphs): %lld prompt tokens, first token after %.1f ms; %lld new tokens in %.1f ms (%.0f tokens/s)\n",
+                     steps, graph_steps, prompt_tokens, first_token_s * 1e3, new_tokens, total_s * 1e3, new_tokens / std::max(total_s, 1e-9));
     if ((long long)free_pages.size() != pool_pages) die("internal: " + std::to_string(pool_pages - (long long)free_pages.size()) + " pages were not given back");
+    for (auto& g : graphs) cudaGraphExecDestroy(g.second);
     cudaFreeHost(meta_host);
     cudaFreeHost(samp_host);
     cudaFreeHost(out_host);
