@@ -154,7 +154,7 @@ def main(argv=None) -> int:
     rows, pos, zero = i32(list(range(B))), i32([C] * B), i32([0] * B)
     kv_bytes = B * (C + 1) * Hkv * hd * 2 * 2
     if ops.paged_decode_mma_supports(Hq, Hkv, hd):
-        nsplit = max(1, min(8, 3 * 148 // (B * Hkv), -(-(C + 1) // 128)))
+        nsplit = max(1, min(8, ops.decode_mma_resident(hd) * 148 // (B * Hkv), -(-(C + 1) // 128)))
         run("paged_decode_mma", lambda: ops.paged_decode_mma(qd, kcd, vcd, od, rows, zero, B, rows, pos, btd, pages_per, page, Hq,
                                                              Hkv, hd, 0, 1 / math.sqrt(hd), nsplit, None), kv_bytes)
         big = 24           # more pieces than a cluster merges: the pieces meet in scratch and a second kernel merges them

@@ -3,8 +3,8 @@
 // The G query heads that share a kv head (G <= 16) are the 16 rows of a warp-level MMA tile
 // (mma.sync m16n8k16), so a 32-key tile of K and V costs a few dozen instructions instead of the
 // thousands the CUDA-core kernel spends on it.  Each warp streams its own key tiles: cp.async copies
-// the page rows into the warp's shared-memory buffers (two buffers, so the next tile is in flight
-// while this one is computed), ldmatrix reads them as MMA fragments (K as is, V transposed), scores
+// the page rows into the warp's shared-memory buffers (two or three, so the next tiles are in flight
+// while this one is computed; tiles of 32 or 16 keys, see Shape below), ldmatrix reads them as MMA fragments (K as is, V transposed), scores
 // and the online softmax stay in registers in float (src/kv_cache/paged_attention.cu:153-163, with
 // this library's departures: -inf start, exact acc / l, the token's own key visible).  The four warps
 // of a block are merged through shared memory.  With 2 to 16 splits the blocks of one (request, kv head)
@@ -23,7 +23,6 @@ namespace {
 
 using namespace wm;
 
-constexpr int BK = 32;          // keys per tile
 constexpr int NWARPS = 4;
 constexpr int MERGE_MAX_SPLITS = 256;
 constexpr int CLUSTER_MAX_SPLITS = 16;      // beyond the portable 8 the kernel opts in to larger clusters
@@ -66,16 +65,20 @@ __device__ __forceinline__ uint32_t tile_addr(uint32_t base, int row, int chunk)
     return base + (uint32_t)row * (HD * 2) + (uint32_t)((chunk ^ (row & 7)) * 16);
 }
 
-template <int HD, bool CLUSTER>
+// BK keys a tile (16 or 32), NST tile buffers a warp: NST - 1 tiles are in flight while one is computed.
+template <int HD, bool CLUSTER, int BK, int NST>
 __global__ void __launch_bounds__(NWARPS * 32) paged_decode_mma_kernel(DecodeParams p) {
+    static_assert((BK == 16 || BK == 32) && NST >= 2 && NST <= 8, "tile shape");
     constexpr int CH = HD / 8;                 // 16-byte chunks per row
     constexpr int TILE_BYTES = BK * HD * 2;
+    constexpr int NK = BK / 8;                 // n-tiles of S (8 keys each)
+    constexpr int KJ = BK / 16;                // k-steps of P V (16 keys each)
     constexpr int KS = HD / 16;                // k-steps of Q K^T
     constexpr int NT = HD / 8;                 // n-tiles of P V
     extern __shared__ __align__(128) uint8_t smem[];
-    // per warp: K[2], V[2]; afterwards reused for the merge of the warps
+    // per warp: K[NST], V[NST]; afterwards reused for the merge of the warps
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t wbase = smem_addr(smem) + warp * 4 * TILE_BYTES;
+    const uint32_t wbase = smem_addr(smem) + warp * 2 * NST * TILE_BYTES;
     const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     const int G = p.Hq / p.Hkv;
 
@@ -96,13 +99,20 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_decode_mma_kernel(DecodePar
     }
     const size_t row_stride = (size_t)p.Hkv * HD;
     // cache row of this lane's key in a tile that starts at kb (only block tables are read: no dependency)
-    auto slot_of = [&](int kb) -> long long {
+    // (an int: a row of a head is 128 bytes or more, so a plane of 2^31 rows would not fit the device's memory)
+    auto slot_of = [&](int kb) -> int {
         const int kpos = kb + lane;
-        if (kpos >= khi) return -1;
-        return (long long)bt[kpos / p.page_size] * p.page_size + (kpos % p.page_size);
+        if (lane >= BK || kpos >= khi) return -1;
+        return bt[kpos / p.page_size] * p.page_size + (kpos % p.page_size);
     };
     const int kb_first = klo + warp * BK;
-    long long slot_next = kb_first < khi ? slot_of(kb_first) : -1;
+    // the cache rows of the tiles that go out before the first one is awaited
+    int slot_ahead[NST - 1];
+#pragma unroll
+    for (int a = 0; a < NST - 1; ++a) slot_ahead[a] = slot_of(kb_first + a * NWARPS * BK);
+    // ... and of the tile that goes out in the first iteration: every later one is looked up an iteration before it
+    // is needed, so that the block table's latency is not part of an iteration
+    int slot_q = slot_of(kb_first + (NST - 1) * NWARPS * BK);
 
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
@@ -119,16 +129,17 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_decode_mma_kernel(DecodePar
             qf[s][3] = r1 < G ? *reinterpret_cast<const uint32_t*>(qb + r1 * HD + s * 16 + 8 + c) : 0u;
         }
     }
-    // Issue the copies of one tile into buffer `buf`: 32 rows x CH chunks of K and of V.
-    auto issue = [&](int buf, long long slot) {
-        const uint32_t kbase = wbase + buf * TILE_BYTES, vbase = wbase + (2 + buf) * TILE_BYTES;
+    // Issue the copies of one tile into buffer `buf`: BK rows x CH chunks of K and of V (nothing for a tile beyond
+    // the range: `slot` is -1 in every lane), as one group.
+    auto issue = [&](int buf, int slot, bool in_range) {
+        const uint32_t kbase = wbase + buf * TILE_BYTES, vbase = wbase + (NST + buf) * TILE_BYTES;
 #pragma unroll
-        for (int it = 0; it < CH; ++it) {
+        for (int it = 0; in_range && it < BK * CH / 32; ++it) {
             const int idx = it * 32 + lane;
             const int row = idx / CH, ch = idx % CH;
-            const long long s = __shfl_sync(0xffffffffu, slot, row);
+            const int s = __shfl_sync(0xffffffffu, slot, row);
             const bool valid = s >= 0;
-            const size_t off = (valid ? (size_t)s : 0) * row_stride + (size_t)kvh * HD + ch * 8;
+            const size_t off = (size_t)(valid ? s : 0) * row_stride + (size_t)(kvh * HD + ch * 8);
             cp_async16(tile_addr<HD>(kbase, row, ch), p.k_cache + off, valid);
             cp_async16(tile_addr<HD>(vbase, row, ch), p.v_cache + off, valid);
         }
@@ -141,26 +152,26 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_decode_mma_kernel(DecodePar
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
 
     int buf = 0;
-    if (kb_first < khi) issue(0, slot_next);
-    for (int kb = kb_first; kb < khi; kb += NWARPS * BK) {
-        const int kb_next = kb + NWARPS * BK;
-        if (kb_next < khi) {
-            issue(buf ^ 1, slot_of(kb_next));
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
-        __syncwarp();
-        const uint32_t kbase = wbase + buf * TILE_BYTES, vbase = wbase + (2 + buf) * TILE_BYTES;
-
-        // S[16 x 32] = Q K^T: four n-tiles of 8 keys.
-        float s[4][4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
+    for (int a = 0; a < NST - 1; ++a) issue(a, slot_ahead[a], kb_first + a * NWARPS * BK < khi);
+    for (int kb = kb_first; kb < khi; kb += NWARPS * BK) {
+        // the tile NST - 1 ahead goes into the buffer that the last iteration read; then all but the newest NST - 1
+        // groups are complete, this tile's among them
+        const int kb_ahead = kb + (NST - 1) * NWARPS * BK;
+        issue(buf == 0 ? NST - 1 : buf - 1, slot_q, kb_ahead < khi);
+        slot_q = slot_of(kb_ahead + NWARPS * BK);
+        cp_async_wait<NST - 1>();
+        __syncwarp();
+        const uint32_t kbase = wbase + buf * TILE_BYTES, vbase = wbase + (NST + buf) * TILE_BYTES;
+
+        // S[16 x BK] = Q K^T: n-tiles of 8 keys.
+        float s[NK][4];
+#pragma unroll
+        for (int i = 0; i < NK; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
 #pragma unroll
         for (int ks = 0; ks < KS; ks += 2) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
+            for (int i = 0; i < NK; ++i) {
                 // matrices: keys 8i..8i+7 x dims [16ks, +8), [16ks+8, +8), [16ks+16, +8), [16ks+24, +8)
                 uint32_t b[4];
                 ldmatrix_x4(tile_addr<HD>(kbase, i * 8 + (lane & 7), ks * 2 + (lane >> 3)), b);
@@ -172,7 +183,7 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_decode_mma_kernel(DecodePar
         const int c0 = (lane & 3) * 2;
         float mt[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < NK; ++i) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int key = kb + i * 8 + c0 + (e & 1);
@@ -191,9 +202,9 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_decode_mma_kernel(DecodePar
             m_run[h] = m_new;
         }
         float lt[2] = {0.0f, 0.0f};
-        uint32_t pf[2][4];      // P as A fragments for the two k-steps of 16 keys
+        uint32_t pf[KJ][4];     // P as A fragments for the k-steps of 16 keys
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < NK; ++i) {
             const float p0 = fast_exp2(s[i][0] - m_run[0]), p1 = fast_exp2(s[i][1] - m_run[0]);
             const float p2 = fast_exp2(s[i][2] - m_run[1]), p3 = fast_exp2(s[i][3] - m_run[1]);
             lt[0] += p0 + p1;
@@ -215,7 +226,7 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_decode_mma_kernel(DecodePar
         }
         // O[16 x HD] += P[16 x 32] V[32 x HD]: V fragments come transposed out of shared memory.
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {              // k-step: keys 16j .. 16j+15
+        for (int j = 0; j < KJ; ++j) {             // k-step: keys 16j .. 16j+15
 #pragma unroll
             for (int i = 0; i < NT; i += 2) {      // two n-tiles (16 dims) per ldmatrix.x4
                 // matrices: (keys 16j..+7, dims 8i..), (keys 16j+8..+15, dims 8i..), (keys 16j..+7, dims 8i+8..), (keys 16j+8.., dims 8i+8..)
@@ -226,9 +237,10 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_decode_mma_kernel(DecodePar
                 mma_bf16(o[i + 1], pf[j], b[2], b[3]);
             }
         }
-        buf ^= 1;
+        buf = buf + 1 == NST ? 0 : buf + 1;
         __syncwarp();
     }
+    cp_async_wait<0>();         // the empty groups of the tiles beyond the range
 
     // Merge the four warps through shared memory (the tile buffers are free now).
     __syncthreads();
@@ -377,42 +389,71 @@ cudaError_t launch_pdl_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, 
     return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
-template <int HD>
-int launch(const DecodeParams& p, int num_tiles, cudaStream_t stream) {
-    constexpr size_t smem = (size_t)NWARPS * 4 * BK * HD * 2;      // also covers the merges: 4 x 16 x HD floats + m, l,
-                                                                   // and the block's own 16 x HD floats + m, l
+// The tile shape of each head size.  What paces a warp is the issue of its own instructions (a tile of 16 keys of 128
+// dimensions is some 300 of them, and a warp alone on its scheduler issues a dependent instruction every few cycles),
+// not the bytes it has in flight: buffers for five tiles ahead with one block an SM measured slower than two buffers,
+// and what helps is more warps an SM.  Measured over 64 requests of 8,192 keys, 4 kv heads of 128 (1.07 GB): 242 us
+// with tiles of 32 keys, two buffers and one block an SM; 190 us (5.6 TB/s) with tiles of 16 keys, three buffers and
+// two blocks an SM.  Heads of 64 hold three blocks an SM with tiles of 32 keys already; other shapes measured the same
+// within 2 us there.
+template <int HD> struct Shape;
+template <> struct Shape<64> { static constexpr int BK = 32, NST = 2; };
+template <> struct Shape<128> { static constexpr int BK = 16, NST = 3; };
+
+template <int HD, int BK, int NST>
+struct Launcher {
+    static constexpr size_t smem = (size_t)NWARPS * 2 * NST * BK * HD * 2;     // also covers the merges: 4 x 16 x HD floats
+                                                                               // + m, l, and the block's own 16 x HD + m, l
     static_assert(smem >= (size_t)(NWARPS + 1) * (16 * HD * 4 + 16 * 2 * 4), "merge area does not fit");
-    static bool configured = false;
-    if (!configured) {
+    static int configure() {
+        static bool configured = false;
+        if (configured) return 0;
         cudaError_t e = cudaSuccess;
         if (smem > 48 * 1024) {
-            e = cudaFuncSetAttribute(paged_decode_mma_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            e = cudaFuncSetAttribute(paged_decode_mma_kernel<HD, false, BK, NST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e == cudaSuccess)
-                e = cudaFuncSetAttribute(paged_decode_mma_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                e = cudaFuncSetAttribute(paged_decode_mma_kernel<HD, true, BK, NST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         }
         if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(paged_decode_mma_kernel<HD, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+            e = cudaFuncSetAttribute(paged_decode_mma_kernel<HD, true, BK, NST>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
         if (e != cudaSuccess) return llb_fail("decode attention: cannot set the kernel's attributes (%zu bytes of shared "
                                               "memory, clusters of %d): %s", smem, CLUSTER_MAX_SPLITS, cudaGetErrorString(e));
         configured = true;
+        return 0;
     }
-    const bool cluster = p.nsplit > 1 && p.nsplit <= CLUSTER_MAX_SPLITS;
-    cudaError_t e;
-    if (cluster)
-        e = launch_pdl_cluster(paged_decode_mma_kernel<HD, true>, dim3(num_tiles, p.Hkv, p.nsplit), dim3(NWARPS * 32), smem,
-                               stream, p);
-    else
-        e = launch_pdl(paged_decode_mma_kernel<HD, false>, dim3(num_tiles, p.Hkv, p.nsplit), dim3(NWARPS * 32), smem,
-                       stream, p);
-    if (e != cudaSuccess) return llb_fail("decode attention: launch failed: %s", cudaGetErrorString(e));
-    int rc = llb_check_launch("paged_decode_mma");
-    if (rc) return rc;
-    if (p.nsplit > 1 && !cluster) {
-        e = launch_pdl(decode_merge_kernel, dim3(num_tiles, p.Hq), dim3(32), 0, stream, p, HD);
-        if (e != cudaSuccess) return llb_fail("decode merge: launch failed: %s", cudaGetErrorString(e));
-        rc = llb_check_launch("decode_merge");
+    // Blocks of this kernel that one SM holds at a time: its shared memory (228 KB, 1 KB of each block the system's) is what
+    // limits them (the kernels take 128 to 168 registers a thread, which allows three blocks of 128 threads or more).
+    static int resident() { return (int)((228 * 1024) / (smem + 1024)); }
+    static int launch(const DecodeParams& p, int num_tiles, cudaStream_t stream) {
+        int rc = configure();
+        if (rc) return rc;
+        const bool cluster = p.nsplit > 1 && p.nsplit <= CLUSTER_MAX_SPLITS;
+        cudaError_t e;
+        if (cluster)
+            e = launch_pdl_cluster(paged_decode_mma_kernel<HD, true, BK, NST>, dim3(num_tiles, p.Hkv, p.nsplit), dim3(NWARPS * 32),
+                                   smem, stream, p);
+        else
+            e = launch_pdl(paged_decode_mma_kernel<HD, false, BK, NST>, dim3(num_tiles, p.Hkv, p.nsplit), dim3(NWARPS * 32), smem,
+                           stream, p);
+        if (e != cudaSuccess) return llb_fail("decode attention: launch failed: %s", cudaGetErrorString(e));
+        rc = llb_check_launch("paged_decode_mma");
+        if (rc) return rc;
+        if (p.nsplit > 1 && !cluster) {
+            e = launch_pdl(decode_merge_kernel, dim3(num_tiles, p.Hq), dim3(32), 0, stream, p, HD);
+            if (e != cudaSuccess) return llb_fail("decode merge: launch failed: %s", cudaGetErrorString(e));
+            rc = llb_check_launch("decode_merge");
+        }
+        return rc;
     }
-    return rc;
+};
+
+template <int HD>
+int launch(const DecodeParams& p, int num_tiles, cudaStream_t stream) {
+    return Launcher<HD, Shape<HD>::BK, Shape<HD>::NST>::launch(p, num_tiles, stream);
+}
+template <int HD>
+int resident() {
+    return Launcher<HD, Shape<HD>::BK, Shape<HD>::NST>::resident();
 }
 
 }  // namespace
@@ -420,6 +461,14 @@ int launch(const DecodeParams& p, int num_tiles, cudaStream_t stream) {
 // Whether this kernel takes the shape (else the CUDA-core kernel of attention_simt.cu is the one to call).
 LLB_EXPORT int llb_paged_decode_mma_supports(int Hq, int Hkv, int hd) {
     return Hkv > 0 && Hq % Hkv == 0 && Hq / Hkv <= 16 && (hd == 64 || hd == 128);
+}
+
+// Blocks of the kernel that an SM holds at a time for this head size (what a planner divides by when it chooses the
+// split count), or a negative code.
+LLB_EXPORT int llb_paged_decode_mma_resident(int hd) {
+    if (hd == 64) return resident<64>();
+    if (hd == 128) return resident<128>();
+    return llb_fail("decode attention: head size %d is not supported", hd);
 }
 
 // The largest split count that is merged inside the attention kernel, through a thread-block cluster.

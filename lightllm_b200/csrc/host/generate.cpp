@@ -47,6 +47,7 @@ int llb_sample(const float* logits, int R, int V, long long stride, const float*
                const float* min_p, const float* uniform, int* out, cudaStream_t stream);
 int llb_paged_decode_mma_supports(int Hq, int Hkv, int hd);
 int llb_paged_decode_mma_cluster_splits();
+int llb_paged_decode_mma_resident(int hd);
 int llb_attention_tcgen05_supports(int hd, int page_size);
 }
 
@@ -651,6 +652,8 @@ int main(int argc, char** argv) {
     std::set<int> eos(cfg.eos.begin(), cfg.eos.end());
     if (opt.eos >= 0) eos = {opt.eos};
     const int cluster_splits = llb_paged_decode_mma_cluster_splits();
+    const int blocks_per_sm = llb_paged_decode_mma_resident(hd);
+    if (blocks_per_sm <= 0) die(std::string("decode attention: ") + llb_last_error());
     long long steps = 0, prompt_tokens = 0, new_tokens = 0, graph_steps = 0;
     std::map<std::pair<int, int>, cudaGraphExec_t> graphs;          // by (requests, block-table width) of a decoding step
     std::set<std::pair<int, int>> seen_shapes;
@@ -730,7 +733,7 @@ int main(int argc, char** argv) {
             const int bound = P * PAGE;
             int nsplit = std::max(1, std::min(std::max(1, ceil_div(2 * sms, (long long)nspans * cfg.kv_heads)), ceil_div(bound, 128)));
             if (bound <= CLUSTER_MERGE_MAX_KEYS) {
-                const int resident = 3 * sms / (nspans * cfg.kv_heads);
+                const int resident = blocks_per_sm * sms / (nspans * cfg.kv_heads);
                 nsplit = std::max(1, std::min(std::min(8, cluster_splits), std::min(resident, ceil_div(bound, 128))));
             }
             return nsplit;

@@ -378,6 +378,20 @@ def paged_decode_mma_supports(num_heads: int, num_kv_heads: int, head_dim: int) 
 _cluster_splits: Optional[int] = None
 
 
+_decode_resident = {}
+
+
+def decode_mma_resident(head_dim: int) -> int:
+    """Blocks of the decode attention kernel that one SM holds at a time for this head size."""
+    n = _decode_resident.get(head_dim)
+    if n is None:
+        n = int(lib().llb_paged_decode_mma_resident(head_dim))
+        if n <= 0:
+            raise KernelError(lib().llb_last_error().decode("utf-8", "replace"))
+        _decode_resident[head_dim] = n
+    return n
+
+
 def decode_mma_cluster_splits() -> int:
     """Up to this many splits the decode attention merges inside the kernel (a thread-block cluster); more
     need scratch and the merge kernel."""

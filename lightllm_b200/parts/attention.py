@@ -211,8 +211,8 @@ class AttentionMixer(Mixer):
             if mma and span <= CLUSTER_MERGE_MAX_KEYS:
                 # Pieces that one thread-block cluster merges inside the kernel, which saves the merge kernel's
                 # round trip: at most 8 (larger clusters start more slowly), and no more blocks than are resident
-                # at once (three per SM).
-                resident = 3 * L.num_sms(ctx.device) // (S * self.num_kv_heads)
+                # at once.
+                resident = ops.decode_mma_resident(self.head_dim) * L.num_sms(ctx.device) // (S * self.num_kv_heads)
                 nsplit = max(1, min(8, ops.decode_mma_cluster_splits(), resident, -(-span // 128)))
             plan = ("decode_mma" if mma else "decode_simt", ctx.tiles(1), nsplit)
         else:
@@ -250,7 +250,7 @@ class AttentionMixer(Mixer):
         if single:
             bound = ctx.max_pages * ctx.page_size
             span = bound if window == 0 else min(bound, window)
-            resident = 3 * L.num_sms(ctx.device) // (len(single) * self.num_kv_heads)
+            resident = ops.decode_mma_resident(self.head_dim) * L.num_sms(ctx.device) // (len(single) * self.num_kv_heads)
             nsplit = max(1, min(8, ops.decode_mma_cluster_splits(), resident, -(-span // 128)))
             decode = (ctx.tiles(1, select=tuple(single)), nsplit)
         simt = []
