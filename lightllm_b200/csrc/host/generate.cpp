@@ -654,7 +654,7 @@ int main(int argc, char** argv) {
     const int cluster_splits = llb_paged_decode_mma_cluster_splits();
     const int blocks_per_sm = llb_paged_decode_mma_resident(hd);
     if (blocks_per_sm <= 0) die(std::string("decode attention: ") + llb_last_error());
-    long long steps = 0, prompt_tokens = 0, new_tokens = 0, graph_steps = 0;
+    long long steps = 0, prompt_tokens = 0, new_tokens = 0, graph_steps = 0, decode_tokens = 0;
     std::map<std::pair<int, int>, cudaGraphExec_t> graphs;          // by (requests, block-table width) of a decoding step
     std::set<std::pair<int, int>> seen_shapes;
     double first_token_s = 0;
@@ -895,6 +895,7 @@ int main(int argc, char** argv) {
         for (const Span& s : spans) {
             Request& q = reqs[(size_t)s.request];
             if (q.cached < (int)q.prompt.size()) prompt_tokens += s.count;
+            else ++decode_tokens;
             q.cached += s.count;
             if (!s.want) continue;
             const int tok = out_host[k++];
@@ -921,9 +922,17 @@ int main(int argc, char** argv) {
         for (int t : q.generated) std::printf(" %d", t);
         std::printf(" (%s)\n", q.reason ? q.reason : "?");
     }
-    if (opt.timing)
-        std::fprintf(stderr, "[generate] %lld steps (%lld as graphs): %lld prompt tokens, first token after %.1f ms; %lld new tokens in %.1f ms (%.0f tokens/s)\n",
-                     steps, graph_steps, prompt_tokens, first_token_s * 1e3, new_tokens, total_s * 1e3, new_tokens / std::max(total_s, 1e-9));
+    if (opt.timing) {
+        // the figures of the reference's serving benchmark, under its names (tools/bench_server.cpp:226-245)
+        std::fprintf(stderr, "  %-30s %lld (%lld replayed as graphs)\n", "Total steps:", steps, graph_steps);
+        std::fprintf(stderr, "  %-30s %lld\n", "Prefill tokens processed:", prompt_tokens);
+        std::fprintf(stderr, "  %-30s %lld\n", "Decode steps:", decode_tokens);
+        std::fprintf(stderr, "  %-30s %lld\n", "Tokens generated:", new_tokens);
+        std::fprintf(stderr, "  %-30s %.1f ms\n", "First token after:", first_token_s * 1e3);
+        std::fprintf(stderr, "  %-30s %.4f s\n", "Elapsed time:", total_s);
+        std::fprintf(stderr, "  %-30s %.1f tok/s\n", "Generation throughput:", new_tokens / std::max(total_s, 1e-9));
+        std::fprintf(stderr, "  %-30s %.1f steps/s\n", "Steps per second:", steps / std::max(total_s, 1e-9));
+    }
     if ((long long)free_pages.size() != pool_pages) die("internal: " + std::to_string(pool_pages - (long long)free_pages.size()) + " pages were not given back");
     for (auto& g : graphs) cudaGraphExecDestroy(g.second);
     cudaFreeHost(meta_host);
