@@ -135,6 +135,7 @@ class StepContext:
         self.max_pages = 0
         self.page_size = 0
         self.decode_only = False
+        self.rowwise = False                    # a mixed step described row by row: several spans may be one request's
         self.max_context = 0
         self.dtype: torch.dtype = torch.float32
         self.device: torch.device = None

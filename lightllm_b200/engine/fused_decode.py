@@ -133,7 +133,9 @@ class FusedDecode:
         return ops.decode_layers_supports(1, D, Hq, Hkv, hd, I, rotary_dim)
 
     def takes(self, ctx) -> bool:
-        return (self.enabled and ctx.decode_only and ctx.T <= self.max_rows
+        # (one row a request: the kernel's attention stage makes a row's new key and value itself, beside the rows that
+        # read the cache, so the rows of a step described row by row, which share requests, go kernel by kernel)
+        return (self.enabled and ctx.decode_only and not ctx.rowwise and ctx.T <= self.max_rows
                 and len(ctx.block_tables) <= ops.MAX_FUSED_GROUPS)
 
     def segment_at(self, run_index: int) -> Optional[Segment]:

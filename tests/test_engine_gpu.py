@@ -395,6 +395,64 @@ def test_decode_steps_through_the_persistent_kernel(tmp_path, name, rows):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["C", "D", "E"])
+def test_small_mixed_steps_described_row_by_row(tmp_path, monkeypatch, name, dtype):
+    """Steps of few rows that mix portions and decoded tokens are given to the kernels row by row (every token a span
+    of its own): the logits follow the plain implementation as they do with the portions kept whole, the step has the
+    shape of a decoding batch, and two steps of different composition but as many rows and wanted places replay one
+    CUDA graph.  C has a window on its upper layers (two cache groups), D heads of 64 with a window, E heads of 128."""
+    d = model_dir(tmp_path, name, seed=31, store="float32" if dtype == "float32" else "bfloat16", edit=sharpen(3.0))
+    cfg, w = P.read_model_dir(d)
+    rng = random.Random(32)
+    V, page = cfg["vocab_size"], PAGE_SIZE[name]
+    seqs = {i: [rng.randrange(V) for _ in range(120)] for i in range(5)}
+    ref = {i: P.plain_forward(cfg, w, s) for i, s in seqs.items()}
+    tol = atol_for({"C": "C sharp"}.get(name, name + " sharp"), dtype, ref)
+
+    def run(rowwise: bool):
+        monkeypatch.setenv("LLB_ROWWISE_STEPS", "1" if rowwise else "0")
+        core = EngineCore(d, EngineOptions(dtype=dtype, max_seq_len=256, max_batch_tokens=256, page_size=page,
+                                           num_pages=6 * (-(-128 // page) + 1), max_seqs=6))
+        for i in range(5):
+            core.open(i)
+        got, shapes = [], []
+        at = {i: 0 for i in range(5)}
+
+        def step(parts):             # parts: (request, tokens, wanted places)
+            entries = []
+            for i, n, want in parts:
+                entries.append(StepEntry(i, seqs[i][at[i]: at[i] + n], want))
+            out = core.step(entries)
+            ctx = core.runner.last_ctx
+            shapes.append((ctx.T, ctx.num_spans, ctx.decode_only))
+            k = 0
+            for i, n, want in parts:
+                for wpl in want:
+                    got.append((i, at[i] + wpl, out[k].float().cpu()))
+                    k += 1
+                at[i] += n
+        step([(0, 70, [69]), (1, 40, [39])])                 # long enough to stay portions: 110 rows
+        step([(0, 1, [0]), (1, 1, [0]), (2, 17, [16])])      # 19 rows, three wanted
+        step([(0, 1, [0]), (2, 1, [0]), (3, 17, [16])])      # other requests, the same counts: the same shape
+        step([(0, 1, [0]), (2, 1, [0]), (4, 17, [16])])      # third sight: replayed
+        step([(3, 2, [0, 1]), (4, 5, [4]), (1, 3, [2])])     # portions only, down to two tokens
+        step([(i, 1, [0]) for i in range(5)])                # a plain decoding batch
+        core.runner.check_device_errors()
+        return got, shapes, core.runner.graph_replays
+
+    row, shapes_row, replays_row = run(True)
+    whole, shapes_whole, _ = run(False)
+    assert shapes_row == [(110, 2, False), (19, 19, True), (19, 19, True), (19, 19, True), (10, 10, True), (5, 5, True)]
+    assert shapes_whole == [(110, 2, False), (19, 3, False), (19, 3, False), (19, 3, False), (10, 3, False), (5, 5, True)]
+    assert replays_row >= 2          # the shape of 19 rows is captured at its second sight and replayed at its third
+    worst = 0.0
+    for (i, pos, a), (j, pos2, b) in zip(row, whole):
+        assert (i, pos) == (j, pos2)
+        worst = max(worst, float((a - ref[i][pos]).abs().max()), float((b - ref[i][pos]).abs().max()))
+    assert worst <= tol, worst
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["B", "D", "E"])
 def test_layers_through_the_step_executor_match_the_parts(tmp_path, monkeypatch, name, dtype):
     """The same steps (a whole prompt, portions beside decoded tokens, decode steps of few and of 40 rows, a step whose
@@ -414,6 +472,7 @@ def test_layers_through_the_step_executor_match_the_parts(tmp_path, monkeypatch,
     def run(native: bool):
         monkeypatch.setenv("LLB_NATIVE_STEP", "1" if native else "0")
         monkeypatch.setenv("LLB_FUSED_DECODE", "0")          # decode steps take the layer-by-layer path as well
+        monkeypatch.setenv("LLB_ROWWISE_STEPS", "0")         # and small mixed steps keep their portions (the parts' plan)
         core = EngineCore(d, EngineOptions(dtype=dtype, max_seq_len=256, max_batch_tokens=2048, page_size=page,
                                            num_pages=(nreq + 2) * (-(-160 // page) + 1), max_seqs=nreq + 1,
                                            use_cuda_graphs=False))
