@@ -136,6 +136,8 @@ class StepContext:
         self.page_size = 0
         self.decode_only = False
         self.rowwise = False                    # a mixed step described row by row: several spans may be one request's
+        self.select_rows: Optional[torch.Tensor] = None   # row by row: the wanted rows, picked from the logits of all rows
+        self.rows_given = 0                     # the tokens that the entries brought (T counts a row-by-row step's padding)
         self.max_context = 0
         self.dtype: torch.dtype = torch.float32
         self.device: torch.device = None

@@ -42,10 +42,15 @@ class ModelRunner:
     # kernels launched one after the other (not the persistent layer kernel, whose attention stage makes a row's new key
     # and value itself and so wants one row a request), needs no work items cut for it on the host, and its shape, which
     # depends on its counts alone, comes again for a CUDA graph.  Measured at the 0.5B sizes (a 16-token portion beside 1
-    # to 16 decoded tokens, contexts of 300 to 4,000): 1.76 ms a step with the portion kept whole, 1.25 ms row by row.
+    # to 16 decoded tokens, contexts of 300 to 4,000): 1.72 ms a step with the portion kept whole, 1.18 ms row by row.
     # Each row reads its keys by itself, so the rule holds only while rows x keys stays small.
+    # Such a step is padded to a multiple of ROWWISE_BUCKET rows by repeating its last row (the same token at the same
+    # position writes the same key and value to the same place, and its output is dropped), and its logits are computed
+    # for every row and the wanted ones picked afterwards: then its shape, and its graph, depend on nothing but the
+    # bucket and the block-table width, and nearly every such step is a replay.
     ROWWISE_MAX_ROWS = 64
     ROWWISE_MAX_ROW_KEYS = 1 << 18
+    ROWWISE_BUCKET = 8
 
     def __init__(self, model: Model, cache: CacheManager, max_batch_tokens: int, max_spans: Optional[int] = None,
                  use_cuda_graphs: bool = True, max_graphs: int = 64):
@@ -60,7 +65,8 @@ class ModelRunner:
         self.max_pages = cache.max_pages_per_seq
         # Capacity of the metadata buffer (int32 words).  A step packs its arrays tightly at
         # offsets that depend only on its counts, so equal counts give equal addresses.
-        S, T, G, P = max(self.max_spans, self.ROWWISE_MAX_ROWS), self.max_batch_tokens, self.ngroups, self.max_pages
+        S, T, G, P = (max(self.max_spans, self.ROWWISE_MAX_ROWS), max(self.max_batch_tokens, self.ROWWISE_MAX_ROWS),
+                      self.ngroups, self.max_pages)
         off = 6 * S + G * S * P + T + 2 * T + G * T
         self._fixed_words = off
         off += 8 * T + 64 * S + 4096         # room for the index arrays that parts stage (tiles, work items)
@@ -147,8 +153,12 @@ class ModelRunner:
             for e in entries:
                 span_of_entry.append(spans[at])
                 at += len(e.tokens)
+            last = spans[-1]
+            padded = min(-(-T // self.ROWWISE_BUCKET) * self.ROWWISE_BUCKET, self.ROWWISE_MAX_ROWS)
+            spans += [Span(last.seq_id, last.slot, last.start, 1, T + j) for j in range(padded - T)]
         else:
             span_of_entry, rowwise = spans, False
+        real_T, T = T, len(spans) if rowwise else T
         S, G = len(spans), self.ngroups
         if len(entries) == 1:
             ids = np.asarray(entries[0].tokens, dtype=np.int64)
@@ -157,6 +167,8 @@ class ModelRunner:
         if ids.min() < 0 or ids.max() >= vocab:
             bad = int(ids[(ids < 0) | (ids >= vocab)][0])
             raise StepError(f"token id {bad} is outside the vocabulary of {vocab}")
+        if T > real_T:
+            ids = np.concatenate([ids, np.full(T - real_T, ids[-1], dtype=np.int64)])
         # Pages for the new tokens are taken before anything runs; OutOfPages leaves all as it was.
         cache.reserve_all((e.seq_id, len(e.tokens)) for e in entries)
 
@@ -166,9 +178,10 @@ class ModelRunner:
         P = min(self.max_pages, -(-(-(-max_context // ps)) // 32) * 32)
         want = [s.row + w for s, e in zip(span_of_entry, entries) for w in e.want]
         R = len(want)
+        want_words = T if rowwise else R          # row by row: a field of the bucket's size, whatever is wanted
         o, off = {}, 0
         fields = (("span_row", S), ("span_len", S), ("span_pos", S), ("span_slot", S), ("iota", S),
-                  ("zeros", S), ("block_tables", G * S * P), ("want_rows", R), ("token_ids", T),
+                  ("zeros", S), ("block_tables", G * S * P), ("want_rows", want_words), ("token_ids", T),
                   ("positions", T), ("slot_mapping", G * T))
         for name, n in fields:
             o[name] = off
@@ -223,6 +236,13 @@ class ModelRunner:
             ctx.slot_mapping = list(slots.split(T))
             ctx.block_tables = [t.view(S, P) for t in tables.split(S * P)]
         ctx.num_want = R
+        ctx.select_rows = None
+        if rowwise:
+            # the head runs over every row of the bucket; the wanted rows are picked from its result
+            ctx.select_rows = ctx.want_rows[:R]
+            ctx.want_rows = ctx.iota
+            ctx.num_want = T if R else 0
+        ctx.rows_given = real_T
         ctx.max_pages, ctx.page_size = P, ps
         ctx.decode_only = all(s.length == 1 for s in spans)
         ctx.rowwise = rowwise
@@ -242,9 +262,11 @@ class ModelRunner:
         self.last_h2d_bytes = words * 4
         if device_tokens is not None:
             # the tokens of this step are still on the device (the ids the last step sampled)
-            if device_tokens.dtype != torch.int32 or device_tokens.numel() != T or not device_tokens.is_cuda:
-                raise StepError(f"device tokens must be {T} int32 values on the device")
-            ctx.token_ids.copy_(device_tokens.reshape(-1))
+            if device_tokens.dtype != torch.int32 or device_tokens.numel() != real_T or not device_tokens.is_cuda:
+                raise StepError(f"device tokens must be {real_T} int32 values on the device")
+            ctx.token_ids[:real_T].copy_(device_tokens.reshape(-1))
+            if T > real_T:           # the padding repeats the last row, so it must bring the last row's token
+                ctx.token_ids[real_T:].copy_(device_tokens.reshape(-1)[-1:].expand(T - real_T))
         return ctx
 
     def forward(self, ctx: StepContext) -> Optional[torch.Tensor]:
@@ -295,10 +317,17 @@ class ModelRunner:
         if self.use_cuda_graphs and not ctx.late_uploads:
             logits = self._forward_graphed(ctx)
         else:
-            logits = self.forward(ctx)
+            logits = self._picked(ctx, self.forward(ctx))
         for e in entries:
             self.cache.advance(e.seq_id, len(e.tokens))
         return logits
+
+    @staticmethod
+    def _picked(ctx: StepContext, logits: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        """The wanted rows of a row-by-row step's logits (which cover every row of its bucket)."""
+        if logits is None or ctx.select_rows is None:
+            return logits
+        return logits.index_select(0, ctx.select_rows)
 
     def _forward_graphed(self, ctx: StepContext) -> Optional[torch.Tensor]:
         """A step through a CUDA graph.  The metadata buffer has equal addresses for equal counts, so a
@@ -318,9 +347,9 @@ class ModelRunner:
             # A capture costs the host about as much as four steps launched one by one.  The shapes of decoding
             # batches and of a lone portion come again hundreds of times; a step that mixes several portions and
             # tokens rarely meets its shape again, so such a shape must have come more often before it is captured.
-            settled = (ctx.decode_only and not ctx.rowwise) or ctx.num_spans == 1
+            settled = ctx.decode_only or ctx.num_spans == 1
             if seen < (2 if settled else self.MIXED_CAPTURE_AFTER):
-                return self.forward(ctx)          # the first sights of a shape (also the warm-up)
+                return self._picked(ctx, self.forward(ctx))          # the first sights of a shape (also the warm-up)
             if len(self._graphs) >= self.max_graphs:      # the least recently used graph makes room
                 del self._graphs[next(iter(self._graphs))]
             before = ops.launch_count()
@@ -334,7 +363,9 @@ class ModelRunner:
         graph.replay()
         self.graph_replays += 1
         self.graph_launches += nodes
-        return None if out is None else out.clone()
+        if out is None:
+            return None
+        return out.clone() if ctx.select_rows is None else out.index_select(0, ctx.select_rows)
 
     def check_device_errors(self) -> None:
         """Raise if a kernel flagged a fault (an id outside the vocabulary reached the device)."""
