@@ -292,6 +292,9 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (for profiling runs)")
     ap.add_argument("--sizes", choices=["1.5b", "7b"], default=None,
                     help="measure at the Qwen2.5-1.5B or 7B layer sizes instead (a line of its own, not the bench record)")
+    ap.add_argument("--prompt-len", type=int, default=None,
+                    help="tokens each request holds before decoding starts (default 2,048); with --only or --sizes, for "
+                         "measurements at other context lengths, not for the bench record")
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="run one part only and print a short line (for profiling runs, not a bench record)")
     args = ap.parse_args()
@@ -305,6 +308,12 @@ def main() -> int:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     args.warmup = max(3, args.warmup)
+    if args.prompt_len:
+        if not (args.only or args.sizes) or args.prompt_len < 16:
+            print("bench.py: --prompt-len goes with --only or --sizes and is at least 16")
+            return 2
+        global PROMPT_LEN, CONTEXT_LEN
+        PROMPT_LEN, CONTEXT_LEN = args.prompt_len, args.prompt_len + 2048
     if args.sizes:
         return run_sizes(args.sizes, min(args.steps, 64), args.warmup,
                          args.layers if args.layers != QWEN25_05B["num_hidden_layers"] else None, args.only)
@@ -334,7 +343,9 @@ def main() -> int:
                 e1.record()
                 torch.cuda.synchronize()
                 extra["replay_only_ms"] = round(e0.elapsed_time(e1) / 20, 4)
-            print(json.dumps({"only": "decode", "batch": args.batch, "ms_per_step": round(ms, 4), "launches": launches,
+            gbs = decode_bytes(core, args.batch, ctx) / (ms * 1e-3) / 1e9
+            print(json.dumps({"only": "decode", "batch": args.batch, "context": ctx, "ms_per_step": round(ms, 4),
+                              "gb_s": round(gbs, 1), "frac_of_hbm": round(gbs / pk["hbm_gbs"], 4), "launches": launches,
                               **extra}))
             return 0
         if args.only == "prefill":
