@@ -350,7 +350,9 @@ def main() -> int:
             return 0
         if args.only == "prefill":
             pre_ms = time_prefill(core, args.steps, args.warmup, rng)
-            print(json.dumps({"only": "prefill", "tokens": PROMPT_LEN, "ms": round(pre_ms, 3)}))
+            fl = flops_prefill(QWEN25_05B, args.layers, PROMPT_LEN)
+            print(json.dumps({"only": "prefill", "tokens": PROMPT_LEN, "ms": round(pre_ms, 3),
+                              "frac_of_bf16_peak": round(fl / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}))
             return 0
         args.steps = min(args.steps, 448)        # the pool holds 2,048 + 512 tokens per request
         clocks = ClockSampler()
