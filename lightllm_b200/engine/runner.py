@@ -43,13 +43,13 @@ class ModelRunner:
     # and value itself and so wants one row a request), needs no work items cut for it on the host, and its shape, which
     # depends on its counts alone, comes again for a CUDA graph.  Measured at the 0.5B sizes (a 16-token portion beside 1
     # to 16 decoded tokens, contexts of 300 to 4,000): 1.72 ms a step with the portion kept whole, 1.18 ms row by row.
-    # Each row reads its keys by itself, so the rule holds only while rows x keys stays small.
+    # Each row reads its keys by itself, so the rule holds only while the portions' rows x keys stay small.
     # Such a step is padded to a multiple of ROWWISE_BUCKET rows by repeating its last row (the same token at the same
     # position writes the same key and value to the same place, and its output is dropped), and its logits are computed
     # for every row and the wanted ones picked afterwards: then its shape, and its graph, depend on nothing but the
     # bucket and the block-table width, and nearly every such step is a replay.
     ROWWISE_MAX_ROWS = 64
-    ROWWISE_MAX_ROW_KEYS = 1 << 18
+    ROWWISE_MAX_ROW_KEYS = 1 << 17
     ROWWISE_BUCKET = 8
 
     def __init__(self, model: Model, cache: CacheManager, max_batch_tokens: int, max_spans: Optional[int] = None,
@@ -144,8 +144,9 @@ class ModelRunner:
             raise StepError(f"a request would pass the model's {self.model.spec.max_positions} positions")
 
         max_context = max(s.start + s.length for s in spans)
-        if (self.rowwise and T <= self.ROWWISE_MAX_ROWS and T * max_context <= self.ROWWISE_MAX_ROW_KEYS
-                and any(s.length > 1 for s in spans)):
+        # (what the rows of portions read beyond what the portions kept whole would: each row its keys by itself)
+        portion_keys = sum(s.length * (s.start + s.length) for s in spans if s.length > 1)
+        if self.rowwise and T <= self.ROWWISE_MAX_ROWS and 0 < portion_keys <= self.ROWWISE_MAX_ROW_KEYS:
             spans = [Span(s.seq_id, s.slot, s.start + i, 1, s.row + i) for s in spans for i in range(s.length)]
             rowwise = True
             span_of_entry = []
