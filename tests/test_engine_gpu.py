@@ -453,6 +453,44 @@ def test_small_mixed_steps_described_row_by_row(tmp_path, monkeypatch, name, dty
     assert worst <= tol, worst
 
 
+def test_token_ids_taken_from_the_device(tmp_path):
+    """``step(entries, device_tokens)`` reads the step's ids from a device tensor (the entries only give the counts):
+    a decoding batch, and a small mixed step that is described row by row and padded, where the padding has to
+    repeat the last row's id.  The logits equal those of the same steps with the ids in the entries."""
+    d = model_dir(tmp_path, "E", seed=5, store="bfloat16")
+    cfg, w = P.read_model_dir(d)
+    rng = random.Random(6)
+    V = cfg["vocab_size"]
+    seqs = {i: [rng.randrange(V) for _ in range(60)] for i in range(3)}
+
+    def run(on_device: bool):
+        core = EngineCore(d, EngineOptions(dtype="bfloat16", max_seq_len=128, max_batch_tokens=128, page_size=16,
+                                           num_pages=32, max_seqs=4, use_cuda_graphs=False))
+        for i in range(3):
+            core.open(i)
+
+        def step(parts):
+            ids = [t for i, a, b, _ in parts for t in seqs[i][a:b]]
+            if on_device:
+                dev = torch.tensor(ids, dtype=torch.int32, device="cuda")
+                entries = [StepEntry(i, [0] * (b - a), want) for i, a, b, want in parts]       # placeholders of the right count
+                return core.step(entries, dev).float().cpu()
+            return core.step([StepEntry(i, seqs[i][a:b], want) for i, a, b, want in parts]).float().cpu()
+        out = [step([(0, 0, 30, [29]), (1, 0, 20, [19])])]
+        out.append(step([(0, 30, 31, [0]), (1, 20, 21, [0]), (2, 0, 11, [10])]))          # 13 rows: row by row, padded to 16
+        assert core.runner.last_ctx.rowwise and core.runner.last_ctx.T == 16
+        out.append(step([(0, 31, 32, [0]), (1, 21, 22, [0]), (2, 11, 12, [0])]))          # a decoding batch
+        core.runner.check_device_errors()
+        return out
+
+    # the same kernels over the same numbers: what may differ is the order in which split contractions add their pieces
+    # (a quarter of the allowance against the plain implementation, as where the step executor is compared with the parts)
+    ref = {i: P.plain_forward(cfg, w, s) for i, s in seqs.items()}
+    tol = atol_for("E", "bfloat16", ref)
+    for a, b in zip(run(False), run(True)):
+        assert a.shape == b.shape and float((a - b).abs().max()) <= 0.25 * tol
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["B", "D", "E"])
 def test_layers_through_the_step_executor_match_the_parts(tmp_path, monkeypatch, name, dtype):
