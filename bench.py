@@ -233,6 +233,48 @@ def time_mixed(engine, requests, lo, hi, new_tokens, rng):
             "ttft_ms_p50": round(loop.stat("ttft", 50), 1), "tpot_ms_p50": round(loop.stat("tpot", 50), 2)}
 
 
+def time_small_mixed(core, steps, warmup, rng, portion=16, decoders=20):
+    """Steps as a loaded server runs them: one `portion`-token piece of a prompt beside the decoded tokens of 1 to 16
+    of `decoders` requests (contexts of a few hundred to a few thousand tokens), a different composition every step.
+    Milliseconds a step, host and device together (the steps are issued back to back and awaited after every hundred;
+    the median hundred is reported)."""
+    import torch
+    from lightllm_b200.engine import StepEntry
+    V = core.vocab_size
+    n = decoders + 4
+    for i in range(n):
+        core.open(i)
+        core.step([StepEntry(i, [rng.randrange(V) for _ in range(300 + 37 * i)], [0])])
+
+    held = {i: 300 + 37 * i for i in range(n)}
+    limit = core.runner.max_pages * core.cache.page_size - 64
+
+    def run(count):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for s in range(count):
+            who = rng.sample(range(decoders), rng.randrange(1, 17))
+            pre = decoders + s % 4
+            for i in who + [pre]:
+                if held[i] + portion > limit:          # a request that has grown to the limit starts over
+                    core.close(i)
+                    core.open(i)
+                    held[i] = 0
+            entries = [StepEntry(i, [rng.randrange(V)], [0]) for i in who]
+            entries.append(StepEntry(pre, [rng.randrange(V) for _ in range(portion)], []))
+            core.step(entries)
+            for i in who:
+                held[i] += 1
+            held[pre] += portion
+        torch.cuda.synchronize()
+        return (time.perf_counter() - t0) / count * 1e3
+    run(warmup)
+    blocks = sorted(run(100) for _ in range(max(1, steps // 100)))      # the median block: the host's noise stays out
+    for i in range(n):
+        core.close(i)
+    return blocks[len(blocks) // 2]
+
+
 def run_sizes(name: str, steps: int, warmup: int, layers=None, only=None) -> int:
     """Decode at batch 1 / 8 / 64 and a 2,048-token prefill at one of the larger sizes, with their roofline
     fractions, and for the 1.5B sizes the mixed workload.  Weights are drawn on the device."""
@@ -295,7 +337,7 @@ def main() -> int:
     ap.add_argument("--prompt-len", type=int, default=None,
                     help="tokens each request holds before decoding starts (default 2,048); with --only or --sizes, for "
                          "measurements at other context lengths, not for the bench record")
-    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
+    ap.add_argument("--only", choices=["decode", "prefill", "small-mixed"], default=None,
                     help="run one part only and print a short line (for profiling runs, not a bench record)")
     args = ap.parse_args()
 
@@ -347,6 +389,12 @@ def main() -> int:
             print(json.dumps({"only": "decode", "batch": args.batch, "context": ctx, "ms_per_step": round(ms, 4),
                               "gb_s": round(gbs, 1), "frac_of_hbm": round(gbs / pk["hbm_gbs"], 4), "launches": launches,
                               **extra}))
+            return 0
+        if args.only == "small-mixed":
+            ms = time_small_mixed(core, min(args.steps, 600), 150, rng)
+            r = core.runner
+            print(json.dumps({"only": "small-mixed", "ms_per_step": round(ms, 4), "row_by_row": bool(r.rowwise),
+                              "graph_replays": r.graph_replays, "graphs": len(r._graphs)}))
             return 0
         if args.only == "prefill":
             pre_ms = time_prefill(core, args.steps, args.warmup, rng)

@@ -42,7 +42,8 @@ class ModelRunner:
     # kernels launched one after the other (not the persistent layer kernel, whose attention stage makes a row's new key
     # and value itself and so wants one row a request), needs no work items cut for it on the host, and its shape, which
     # depends on its counts alone, comes again for a CUDA graph.  Measured at the 0.5B sizes (a 16-token portion beside 1
-    # to 16 decoded tokens, contexts of 300 to 4,000): 1.72 ms a step with the portion kept whole, 1.18 ms row by row.
+    # to 16 decoded tokens, contexts of 300 to 4,000; bench.py --only small-mixed): 1.73 ms a step with the portion kept
+    # whole, 1.20 ms row by row.
     # Each row reads its keys by itself, so the rule holds only while the portions' rows x keys stay small.
     # Such a step is padded to a multiple of ROWWISE_BUCKET rows by repeating its last row (the same token at the same
     # position writes the same key and value to the same place, and its output is dropped), and its logits are computed
