@@ -542,9 +542,31 @@ Options parse_args(int argc, char** argv) {
     return o;
 }
 
+// generate --cut-rows "<key tiles of row tile 0> <of row tile 1> ..." <heads> <slots>: prints how the attention kernel's
+// items would be cut (the planner alone, for the test that compares it with the Python engine's).
+int print_cut(int argc, char** argv) {
+    if (argc != 5) die("usage: generate --cut-rows \"n0 n1 ...\" <heads> <slots>");
+    std::vector<RowTile> rows;
+    const char* c = argv[2];
+    char* stop = nullptr;
+    for (;;) {
+        const long v = std::strtol(c, &stop, 10);
+        if (stop == c) break;
+        rows.push_back({0, 128 * (int)rows.size(), (int)v});
+        c = stop;
+    }
+    if (rows.empty()) die("--cut-rows: no row tiles");
+    const Cut cut = cut_attention_rows(rows, std::atoi(argv[3]), std::atoi(argv[4]));
+    for (const Item& it : cut.items) std::printf("item %d %d %d %d %d %d\n", it.len, it.span, it.q0, it.k0, it.nk, it.part);
+    for (const Merge& m : cut.merges) std::printf("merge %d %d %d %d\n", m.span, m.q0, m.first, m.count);
+    std::printf("parts %d\n", cut.parts);
+    return 0;
+}
+
 }  // namespace
 
 int main(int argc, char** argv) {
+    if (argc >= 2 && std::string(argv[1]) == "--cut-rows") return print_cut(argc, argv);
     const Options opt = parse_args(argc, argv);
     if (llb_abi_version() != EXPECTED_ABI)
         die("the kernel library has ABI " + std::to_string(llb_abi_version()) + ", this program was built for " + std::to_string(EXPECTED_ABI));

@@ -86,3 +86,24 @@ def test_command_line_errors(model_e):
     # without a device (the tests that are not marked gpu run where there is none) it says so after all checks passed
     rc, _, err = run(model_e, 1, 2, 3)
     assert rc == 0 or "no CUDA device" in err or "sm_100a" in err
+
+
+def test_its_attention_items_are_cut_as_the_engine_cuts_them():
+    """The program plans the tensor-core attention's work items itself; for the same row tiles, heads and resident
+    blocks it must choose the piece length and produce the items, merges and parts that ``engine/batch.py`` does."""
+    import random
+    from lightllm_b200.engine.batch import cut_attention_rows
+    rng = random.Random(0)
+    cases = [[16], list(range(1, 17)), list(range(1, 65)), [3, 40, 2, 9], [64] * 5]
+    cases += [[rng.randrange(1, 70) for _ in range(rng.randrange(1, 40))] for _ in range(12)]
+    for tiles in cases:
+        for heads, slots in ((14, 296), (12, 148), (28, 148), (2, 37)):
+            rows = [(0, 128 * i, n) for i, n in enumerate(tiles)]
+            items, merges, parts = cut_attention_rows(rows, None, heads, slots)
+            rc, out, err = run("--cut-rows", " ".join(map(str, tiles)), heads, slots)
+            assert rc == 0, err
+            got_items = [tuple(map(int, l.split()[1:])) for l in out.splitlines() if l.startswith("item")]
+            got_merges = [tuple(map(int, l.split()[1:])) for l in out.splitlines() if l.startswith("merge")]
+            got_parts = int(out.splitlines()[-1].split()[1])
+            assert got_items == [tuple(t) for t in items], (tiles, heads, slots)
+            assert got_merges == [tuple(m) for m in merges] and got_parts == parts
