@@ -147,6 +147,11 @@ def test_cpp_generate_samples_the_same_tokens_for_the_same_seed(tmp_path):
     c = cpp_outputs(run_cpp_generate(d, 1, 2, 3, "--seed", 6, "--max-seq-len", 64))
     assert a == b and a != c
     assert len(a[0][0]) == 12 or a[0][1] == "eos"          # the reference's 12 new tokens (tests/test_generate.cpp:148-149)
+    # top-k of one leaves the sampler no choice: the greedy tokens, whatever the temperature and the seed
+    greedy = cpp_outputs(run_cpp_generate(d, 1, 2, 3, "--temperature", 0, "--max-seq-len", 64, "--eos-token-id", 100000))
+    forced = cpp_outputs(run_cpp_generate(d, 1, 2, 3, "--temperature", 1.5, "--top-k", 1, "--seed", 9, "--max-seq-len", 64,
+                                          "--eos-token-id", 100000))
+    assert greedy == forced and len(greedy[0][0]) == 12
     # a long prompt that ends at the sequence limit
     long = cpp_outputs(run_cpp_generate(d, *range(1, 60), "--temperature", 0, "--max-seq-len", 64, "--eos-token-id", 100000))
     assert long[0][1] == "max_seq_len" and len(long[0][0]) == 5
