@@ -14,6 +14,7 @@ from typing import Dict, List, Optional, Sequence
 
 import torch
 
+from ..csrc import ops
 from ..sampling import Sampler, SamplingParams
 from .batch import StepEntry
 from .core import EngineCore
@@ -186,7 +187,7 @@ class BatchMainLoop:
         accounting (the tokens are in the cache) is done here."""
         if self.measure_device:
             begin = torch.cuda.Event(enable_timing=True)
-            begin.record()
+            begin.record(ops.torch_stream())
         logits = self.engine.step(entries, device_tokens) if device_tokens is not None else self.engine.step(entries)
         tokens_dev = tokens_host = ready = None
         if wanting:
@@ -195,10 +196,10 @@ class BatchMainLoop:
             self._pin_turn ^= 1
             tokens_host.copy_(tokens_dev, non_blocking=True)
             ready = torch.cuda.Event()
-            ready.record()
+            ready.record(ops.torch_stream())
         if self.measure_device:
             end = torch.cuda.Event(enable_timing=True)
-            end.record()
+            end.record(ops.torch_stream())
             self._device_spans.append((begin, end))
         self.scheduler.advance(sched)
         return _InFlight(sched, wanting, tokens_dev, tokens_host, ready)

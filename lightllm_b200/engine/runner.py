@@ -18,6 +18,7 @@ import numpy as np
 import torch
 
 from ..cache import CacheManager
+from ..csrc import ops
 from ..models import Model
 from ..parts import CacheView
 from ..parts.base import LazyNorm
@@ -259,7 +260,7 @@ class ModelRunner:
         ctx._staging = None
         self._dev[:words].copy_(self._host[turn][:words], non_blocking=True)
         ev = torch.cuda.Event()
-        ev.record()
+        ev.record(ops.torch_stream())
         self._host_done[turn] = ev
         self.last_h2d_bytes = words * 4
         if device_tokens is not None:
