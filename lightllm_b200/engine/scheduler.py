@@ -93,6 +93,51 @@ class ScheduleStep:
         return not self.entries
 
 
+class _Asks:
+    """What a step has promised so far: ``(request, tokens)`` pairs and the pages they need in every cache group, kept
+    as running totals so that asking whether one more request fits costs one request's arithmetic, not all of them."""
+
+    def __init__(self, cache):
+        self.cache = cache
+        self.pairs: List[tuple] = []
+        self.total = [0] * len(cache.pools)
+
+    def fits(self, seq_id, n: int, spare: int = 0) -> bool:
+        """Whether ``n`` more tokens of ``seq_id`` get their pages beside everything promised, with ``spare`` pages
+        left free in every group (what ``CacheManager.can_reserve_all`` answers for the whole list)."""
+        c = self.cache
+        if c.get(seq_id).length + n > c.max_seq_len:
+            return False
+        need = c.pages_needed(seq_id, n)
+        return all(t + x + spare <= p.free_count for t, x, p in zip(self.total, need, c.pools))
+
+    def add(self, seq_id, n: int) -> None:
+        for g, x in enumerate(self.cache.pages_needed(seq_id, n)):
+            self.total[g] += x
+        self.pairs.append((seq_id, n))
+
+    def take_all(self, pairs) -> bool:
+        """All of ``pairs`` or none (the list must be empty): the usual case of a decoding batch."""
+        c = self.cache
+        total = [0] * len(self.total)
+        for seq_id, n in pairs:
+            if c.get(seq_id).length + n > c.max_seq_len:
+                return False
+            for g, x in enumerate(c.pages_needed(seq_id, n)):
+                total[g] += x
+        if not all(t <= p.free_count for t, p in zip(total, c.pools)):
+            return False
+        self.pairs, self.total = list(pairs), total
+        return True
+
+    def drop(self, seq_id) -> None:
+        self.pairs = [a for a in self.pairs if a[0] != seq_id]
+        self.total = [0] * len(self.total)
+        for sid, n in self.pairs:
+            for g, x in enumerate(self.cache.pages_needed(sid, n)):
+                self.total[g] += x
+
+
 class Scheduler:
     def __init__(self, cache: CacheManager, chunk_size: int = 16, max_batch_tokens: int = 256,
                  max_prefill_entries: int = 999):
@@ -139,22 +184,20 @@ class Scheduler:
         out = ScheduleStep()
         cache = self.cache
         budget = self.max_batch_tokens
-        asks = []
+        asks = _Asks(cache)
 
         # Priority 1: one token for every decoding request; preempt from the back when pages run out.
         decoding = [r for r in self.running if r.state == DECODING]
         # Fast path: every decoding request gets its token (the usual case).
-        all_asks = [(r.id, 1) for r in decoding]
-        if decoding and cache.can_reserve_all(all_asks):
-            asks = all_asks
+        if decoding and asks.take_all([(r.id, 1) for r in decoding]):
             out.entries = [ScheduleEntry(r, 1, r.num_computed, False, True) for r in decoding]
             budget -= len(decoding)
             decoding = []
         i = 0
         while i < len(decoding):
             r = decoding[i]
-            if cache.can_reserve_all(asks + [(r.id, 1)]):
-                asks.append((r.id, 1))
+            if asks.fits(r.id, 1):
+                asks.add(r.id, 1)
                 out.entries.append(ScheduleEntry(r, 1, r.num_computed, False, True))
                 budget -= 1
                 i += 1
@@ -171,7 +214,7 @@ class Scheduler:
                 j = decoding.index(victim)
                 decoding.pop(j)
                 if j < i:          # it had already been given its token: take that back
-                    asks = [a for a in asks if a[0] != victim.id]
+                    asks.drop(victim.id)
                     out.entries = [e for e in out.entries if e.request is not victim]
                     budget += 1
                     i -= 1
@@ -214,7 +257,7 @@ class Scheduler:
         n = min(self.chunk_size, r.prefill_remaining(), budget)
         cache = self.cache
         while n > 0:
-            if cache.can_reserve_all(asks + [(r.id, n)]) and self._spare_ok(asks + [(r.id, n)], spare):
+            if asks.fits(r.id, n, spare):
                 return n
             # shrink to the next page edge below
             have = cache.get(r.id).length + n
@@ -222,17 +265,8 @@ class Scheduler:
             n = edge - cache.get(r.id).length
         return 0
 
-    def _spare_ok(self, asks, spare: int) -> bool:
-        if spare <= 0:
-            return True
-        total = [0] * len(self.cache.pools)
-        for seq_id, n in asks:
-            for g, need in enumerate(self.cache.pages_needed(seq_id, n)):
-                total[g] += need
-        return all(t + spare <= p.free_count for t, p in zip(total, self.cache.pools))
-
     def _add_prefill(self, out: ScheduleStep, asks, r: Request, n: int) -> None:
-        asks.append((r.id, n))
+        asks.add(r.id, n)
         last = r.num_computed + n == r.total_len()
         out.entries.append(ScheduleEntry(r, n, r.num_computed, True, last))
 
