@@ -43,8 +43,8 @@ class ModelRunner:
     # kernels launched one after the other (not the persistent layer kernel, whose attention stage makes a row's new key
     # and value itself and so wants one row a request), needs no work items cut for it on the host, and its shape, which
     # depends on its counts alone, comes again for a CUDA graph.  Measured at the 0.5B sizes (a 16-token portion beside 1
-    # to 16 decoded tokens, contexts of 300 to 4,000; bench.py --only small-mixed): 1.73 ms a step with the portion kept
-    # whole, 1.20 ms row by row.
+    # to 16 decoded tokens, contexts of 300 to 4,000; bench.py --only small-mixed): 1.65 ms a step with the portion kept
+    # whole, 1.17 ms row by row.
     # Each row reads its keys by itself, so the rule holds only while the portions' rows x keys stay small.
     # Such a step is padded to a multiple of ROWWISE_BUCKET rows by repeating its last row (the same token at the same
     # position writes the same key and value to the same place, and its output is dropped), and its logits are computed
@@ -104,6 +104,7 @@ class ModelRunner:
         self._graphs: Dict[tuple, tuple] = {}
         self._graph_seen: Dict[tuple, int] = {}
         self._graph_pool = None
+        self._capture_stream = None
         self.graph_replays = 0
         self.graph_launches = 0          # kernels launched through graph replays
         # Decode steps run the common layers as one persistent kernel per segment of the run list.
@@ -325,6 +326,34 @@ class ModelRunner:
             self.cache.advance(e.seq_id, len(e.tokens))
         return logits
 
+    def _capture(self, ctx: StepContext):
+        """The step's launches recorded into a CUDA graph, on a side stream as capture wants it.  This is what the
+        ``torch.cuda.graph`` context does without its preparations (a device synchronisation and the release of every
+        cached block of device and pinned memory, about 6 ms, after which the next allocations go to the driver again):
+        a server captures dozens of shapes while it runs, and none of them needs the memory that those give back."""
+        graph = torch.cuda.CUDAGraph()
+        current = ops.torch_stream()
+        if self._capture_stream is None:
+            self._capture_stream = torch.cuda.Stream(self.device)
+        side = self._capture_stream
+        side.wait_stream(current)
+        torch.cuda.set_stream(side)          # (not the `torch.cuda.stream` context: it asks for the current stream without
+        try:                                 # naming a device, which makes torch count the devices through the driver)
+            if self._graph_pool is None:
+                graph.capture_begin()
+            else:
+                graph.capture_begin(pool=self._graph_pool)
+            try:
+                out = self.forward(ctx)
+            finally:
+                graph.capture_end()
+        finally:
+            torch.cuda.set_stream(current)
+        current.wait_stream(side)
+        if self._graph_pool is None:
+            self._graph_pool = graph.pool()
+        return graph, out
+
     @staticmethod
     def _picked(ctx: StepContext, logits: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         """The wanted rows of a row-by-row step's logits (which cover every row of its bucket)."""
@@ -356,11 +385,7 @@ class ModelRunner:
             if len(self._graphs) >= self.max_graphs:      # the least recently used graph makes room
                 del self._graphs[next(iter(self._graphs))]
             before = ops.launch_count()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, pool=self._graph_pool):
-                out = self.forward(ctx)
-            if self._graph_pool is None:
-                self._graph_pool = graph.pool()
+            graph, out = self._capture(ctx)
             hit = self._graphs[key] = (graph, out, ops.launch_count() - before)
         graph, out, nodes = hit
         graph.replay()
