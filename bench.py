@@ -3,6 +3,8 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L]
     python bench.py --sizes 1.5b|7b          (the larger sizes of the family: a line of their own)
+    python bench.py [--sizes ..] --only decode|prefill [--prompt-len N]     (one part, at another context length)
+    python bench.py --only small-mixed       (the steps of a loaded server: a 16-token portion beside decoded tokens)
 
 Prints one JSON line.  ``value`` is decoded tokens a second over K timed decode steps of a
 batch of 8 requests that each hold a 2,048-token prompt (random weights, random token ids),
