@@ -20,13 +20,14 @@ BF16_WORST_REL = {"A": 0.014,          # replay 0.0134
                   "B": 0.017,          # replay 0.0170, long decoding 0.0136
                   "C": 0.020,          # replay 0.0196
                   "D": 0.021,          # replay 0.0200
-                  "E": 0.020,          # replay 0.0199
+                  "E": 0.022,          # replay 0.0212 (0.0199 before small mixed steps were described row by row)
                   # the same models with their q and k projections scaled up (sharp attention: a lost key shows, and
                   # rounding of the scores weighs more)
                   "A sharp": 0.016,    # 0.0157
                   "C sharp": 0.025,    # 0.0250
                   "D sharp": 0.053,    # every kind of span 0.0524; persistent decode 0.0191; merge through scratch 0.0111
-                  "E sharp": 0.036,    # persistent decode, 17 rows: 0.0352
+                  "E sharp": 0.040,    # persistent decode, 17 rows: 0.0352 in one run, 0.0400 in another (its stages add
+                                       # their pieces with atomics, in whatever order they arrive)
                   "toy": 0.035,        # the toy architectures of test_engine_gpu.py: routed 0.0343, norms 0.0186
                   "real": 0.033}       # two layers at the 0.5B sizes (test_real_sizes_gpu.py): 0.0323
 
