@@ -38,11 +38,19 @@ def main(argv=None) -> int:
     ids = [loop.submit([t % V for t in p], max_new_tokens=n, temperature=args.temperature)
            for p, n in users]
     t0 = time.perf_counter()
+    shown = 0
+
+    def show():           # a step's figures are known once its ids have been read, one step later while steps overlap
+        nonlocal shown
+        for m in loop.step_metrics[shown:]:
+            print(f"[step {m.step_number:3d}] tokens={m.tokens_processed:3d} prefill={m.prefill_tokens:3d} "
+                  f"decode={m.decode_tokens:2d} active={m.active_after}")
+        shown = len(loop.step_metrics)
     while loop.has_active():
         loop.step()
-        m = loop.step_metrics[-1]
-        print(f"[step {m.step_number:3d}] tokens={m.tokens_processed:3d} prefill={m.prefill_tokens:3d} "
-              f"decode={m.decode_tokens:2d} active={m.active_after}")
+        show()
+    loop.flush()
+    show()
     dt = time.perf_counter() - t0
     for i in ids:
         print(f"[user {i}] {loop.generated_tokens(i)} ({loop.finish_reason(i)})")

@@ -88,8 +88,9 @@ class EngineCore:
     def is_open(self, seq_id: Hashable) -> bool:
         return seq_id in self.cache.seqs
 
-    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
-        return self.runner.step(entries, device_tokens)
+    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None,
+             token_map=None) -> Optional[torch.Tensor]:
+        return self.runner.step(entries, device_tokens, token_map)
 
     def launch_count(self) -> int:
         """Kernels of the engine's own library launched so far in this process."""

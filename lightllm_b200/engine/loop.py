@@ -82,11 +82,12 @@ class _InFlight:
 
 
 class BatchMainLoop:
-    """While every running request is decoding and nothing waits, one step is kept in flight: the next step is
-    launched with the ids that the last one sampled still on the device, and the host reads those ids (ends
-    requests on an end-of-sequence id, keeps the metrics) while the GPU already runs the next step.  A request that
-    ends this way has computed one token too many, which is dropped.  ``decode_ahead=False`` launches and reads
-    back step by step, as the reference does."""
+    """One step is kept in flight whenever the next one can be decided without what it samples (no request of it can
+    end other than on an end-of-sequence id, every decoding request finds a page; ``Scheduler.can_step_ahead``), whether
+    it decodes, carries portions of prompts or both: the next step is launched with the ids that the last one sampled
+    still on the device, and the host reads those ids (ends requests on an end-of-sequence id, keeps the metrics)
+    while the GPU already runs the next step.  A request that ends this way has computed one token too many, which is
+    dropped.  ``decode_ahead=False`` launches and reads back step by step, as the reference does."""
 
     def __init__(self, engine: EngineCore, chunk_size: int = 16, max_batch_tokens: int = 256,
                  max_prefill_entries: int = 999, decode_ahead: bool = True):
@@ -146,49 +147,61 @@ class BatchMainLoop:
     def step(self) -> bool:
         """One scheduler decision run through the engine.  False when there was nothing to do."""
         prev = self._inflight
-        if prev is not None:
-            self._inflight = None
-            nxt = None
-            if self.decode_ahead and self.scheduler.can_decode_ahead(prev.sched):
-                sched = self.scheduler.step()
-                if (not sched.preempted and len(sched.entries) == len(prev.wanting)
-                        and all(e.request is r and not e.is_prefill for e, r in zip(sched.entries, prev.wanting))):
-                    entries = [StepEntry(r.id, (0,), (0,)) for r in prev.wanting]
-                    nxt = self._launch(sched, entries, prev.wanting, device_tokens=prev.tokens_dev)
-                    self.steps_ahead += 1
-                else:       # cannot happen after can_decode_ahead; the decision is taken again below
-                    raise RuntimeError("the scheduler changed its mind about a step it had declared predictable")
-            self._commit(prev)
-            if nxt is not None:
-                self._inflight = nxt
-                return True
+        self._inflight = None
+        had_prev = prev is not None
+        if prev is not None and not (self.decode_ahead and self.scheduler.can_step_ahead(prev.sched)):
+            self._commit(prev)            # the next step depends on what this one sampled: read it first
+            prev = None
         sched: ScheduleStep = self.scheduler.step()
         for r in list(self.scheduler.finished.values()):
             if not self._metrics[r.id].finished:
                 self._record_finish(r)
         if sched.empty():
-            return prev is not None
-        entries, wanting = [], []
+            if prev is not None:
+                self._commit(prev)
+            return had_prev
+        if prev is not None and sched.preempted:
+            raise RuntimeError("the scheduler preempted a request in a step it had declared predictable")
+        # Requests whose last token is still being sampled by the step in flight take it from the device.
+        pending = {r.id: i for i, r in enumerate(prev.wanting)} if prev is not None else {}
+        entries, wanting, map_rows, map_from = [], [], [], []
+        row = 0
         for e in sched.entries:
-            toks = e.request.tokens_at(e.start_pos, e.num_tokens)
-            entries.append(StepEntry(e.request.id, toks, [e.num_tokens - 1] if e.wants_logits else []))
+            r = e.request
+            if not e.is_prefill and r.id in pending and e.start_pos >= r.total_len():
+                toks = (0,) * e.num_tokens           # placeholders: the ids come from the device
+                map_rows.append(row)
+                map_from.append(pending[r.id])
+            else:
+                toks = r.tokens_at(e.start_pos, e.num_tokens)
+            entries.append(StepEntry(r.id, toks, [e.num_tokens - 1] if e.wants_logits else []))
             if e.wants_logits:
-                wanting.append(e.request)
-        flight = self._launch(sched, entries, wanting)
-        decode_only = all(not e.is_prefill and e.wants_logits for e in sched.entries)
-        if self.decode_ahead and decode_only and not sched.preempted:
+                wanting.append(r)
+            row += e.num_tokens
+        token_map = (prev.tokens_dev, map_rows, map_from) if map_rows else None
+        flight = self._launch(sched, entries, wanting, token_map=token_map)
+        if prev is not None:
+            self.steps_ahead += 1
+            self._commit(prev)
+        if self.decode_ahead and not sched.preempted:
             self._inflight = flight           # read back at the next call, after the next step has been launched
         else:
             self._commit(flight)
         return True
 
-    def _launch(self, sched: ScheduleStep, entries, wanting, device_tokens=None) -> _InFlight:
+    def _launch(self, sched: ScheduleStep, entries, wanting, token_map=None) -> _InFlight:
         """Run the step and sample; the ids start their way to the host.  The scheduler's first half of the
         accounting (the tokens are in the cache) is done here."""
         if self.measure_device:
             begin = torch.cuda.Event(enable_timing=True)
             begin.record(ops.torch_stream())
-        logits = self.engine.step(entries, device_tokens) if device_tokens is not None else self.engine.step(entries)
+        if token_map is None:
+            logits = self.engine.step(entries)
+        elif token_map[1] == token_map[2] == list(range(len(entries))) and token_map[0].numel() == len(entries) \
+                and all(len(e.tokens) == 1 for e in entries):
+            logits = self.engine.step(entries, token_map[0])          # a decoding batch: the sampled ids as they are
+        else:
+            logits = self.engine.step(entries, None, token_map)
         tokens_dev = tokens_host = ready = None
         if wanting:
             tokens_dev = self.sampler.sample_device(logits, [r.id for r in wanting], [r.sampling for r in wanting])

@@ -69,7 +69,8 @@ class ModelRunner:
         # offsets that depend only on its counts, so equal counts give equal addresses.
         S, T, G, P = (max(self.max_spans, self.ROWWISE_MAX_ROWS), max(self.max_batch_tokens, self.ROWWISE_MAX_ROWS),
                       self.ngroups, self.max_pages)
-        off = 6 * S + G * S * P + T + 2 * T + G * T
+        self._map_cap = S                    # rows of a step that may take their ids from the device (token_map)
+        off = 2 * self._map_cap + 6 * S + G * S * P + T + 2 * T + G * T
         self._fixed_words = off
         off += 8 * T + 64 * S + 4096         # room for the index arrays that parts stage (tiles, work items)
         self._words = off
@@ -117,7 +118,8 @@ class ModelRunner:
                         and len(self.native.covers) > 0 and all(self.native.covers))
 
     # ------------------------------------------------------------------------------------------
-    def _build_context(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> StepContext:
+    def _build_context(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None,
+                       token_map=None) -> StepContext:
         cache = self.cache
         vocab = self.model.spec.vocab_size
         if not entries:
@@ -184,7 +186,22 @@ class ModelRunner:
         R = len(want)
         want_words = T if rowwise else R          # row by row: a field of the bucket's size, whatever is wanted
         o, off = {}, 0
-        fields = (("span_row", S), ("span_len", S), ("span_pos", S), ("span_slot", S), ("iota", S),
+        # token_map: (ids on the device, rows of this step, places in those ids): these rows take their ids from there
+        # (the ids a step in flight is sampling).  Padding rows that repeat such a row repeat its id.
+        map_rows: List[int] = []
+        map_from: List[int] = []
+        if token_map is not None:
+            map_rows, map_from = list(token_map[1]), list(token_map[2])
+            if map_rows and T > real_T and map_rows[-1] == real_T - 1:
+                map_rows += list(range(real_T, T))
+                map_from += [map_from[-1]] * (T - real_T)
+        K = len(map_rows)
+        if K > self._map_cap:
+            raise StepError(f"{K} rows take their ids from the device; the limit is {self._map_cap}")
+        # The two lists of the map have a place of fixed size at the head of the buffer: no other array's place may depend
+        # on how many rows the map names, since a CUDA graph captured for this shape reads those arrays where they lay then.
+        fields = (("map_rows", self._map_cap), ("map_from", self._map_cap),
+                  ("span_row", S), ("span_len", S), ("span_pos", S), ("span_slot", S), ("iota", S),
                   ("zeros", S), ("block_tables", G * S * P), ("want_rows", want_words), ("token_ids", T),
                   ("positions", T), ("slot_mapping", G * T))
         for name, n in fields:
@@ -227,13 +244,18 @@ class ModelRunner:
                     raise StepError(f"request {s.seq_id!r}: a new token falls in a page that was given back")
                 sm[s.row: s.row + s.length] = rows * ps + p % ps
         host[o["want_rows"]: o["want_rows"] + R] = want
+        if K:
+            if min(map_rows) < 0 or max(map_rows) >= T or min(map_from) < 0 or max(map_from) >= token_map[0].numel():
+                raise StepError("the map of device token ids names a row or a place that does not exist")
+            host[o["map_rows"]: o["map_rows"] + K] = map_rows
+            host[o["map_from"]: o["map_from"] + K] = map_from
 
         d = self._dev
         ctx = StepContext()
         ctx.T, ctx.spans = T, spans
         # one view per field, cut in one call (a slice each costs the host a microsecond or more)
-        (ctx.span_row, ctx.span_len, ctx.span_pos, ctx.span_slot, ctx.iota, ctx.zeros, tables, ctx.want_rows,
-         ctx.token_ids, ctx.positions, slots) = d[:words].split_with_sizes([n for _, n in fields])
+        (map_rows_dev, map_from_dev, ctx.span_row, ctx.span_len, ctx.span_pos, ctx.span_slot, ctx.iota, ctx.zeros, tables,
+         ctx.want_rows, ctx.token_ids, ctx.positions, slots) = d[:words].split_with_sizes([n for _, n in fields])
         if G == 1:
             ctx.slot_mapping, ctx.block_tables = [slots], [tables.view(S, P)]
         else:
@@ -271,6 +293,11 @@ class ModelRunner:
             ctx.token_ids[:real_T].copy_(device_tokens.reshape(-1))
             if T > real_T:           # the padding repeats the last row, so it must bring the last row's token
                 ctx.token_ids[real_T:].copy_(device_tokens.reshape(-1)[-1:].expand(T - real_T))
+        if K:
+            src = token_map[0]
+            if src.dtype != torch.int32 or not src.is_cuda:
+                raise StepError("mapped device tokens must be int32 values on the device")
+            ctx.token_ids[map_rows_dev[:K]] = src.reshape(-1).index_select(0, map_from_dev[:K])
         return ctx
 
     def forward(self, ctx: StepContext) -> Optional[torch.Tensor]:
@@ -310,13 +337,16 @@ class ModelRunner:
             return m.head.forward(LazyNorm(residual, m.final_norm, ctx, rows=ctx.want_rows), ctx)
         return m.head.forward(m.final_norm.forward_rows(residual, ctx.want_rows, ctx), ctx)
 
-    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None,
+             token_map=None) -> Optional[torch.Tensor]:
         """One step.  Returns the logits at the wanted places, in the order of the entries and of
         each entry's ``want``, as a float32 ``[wanted, vocab]`` tensor on the device (``None`` if
         nothing is wanted).  Afterwards every request holds its new tokens.  With ``device_tokens`` (int32,
         one per token of the step, on the device) the entries' own token ids only give the counts: the step
-        reads its ids from that tensor, so ids that were sampled on the device need not visit the host."""
-        ctx = self._build_context(entries, device_tokens)
+        reads its ids from that tensor, so ids that were sampled on the device need not visit the host.
+        ``token_map = (ids, rows, places)`` does the same for some rows only: row ``rows[i]`` of the step takes
+        ``ids[places[i]]`` (int32 on the device), the other rows the entries' own ids."""
+        ctx = self._build_context(entries, device_tokens, token_map)
         self.last_ctx = ctx          # kept for inspection (which kernels the step's plan chose)
         if self.use_cuda_graphs and not ctx.late_uploads:
             logits = self._forward_graphed(ctx)

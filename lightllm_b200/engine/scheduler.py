@@ -324,6 +324,23 @@ class Scheduler:
                 return False
         return self.cache.can_reserve_all([(r.id, 1) for r in self.running])
 
+    def can_step_ahead(self, step: ScheduleStep) -> bool:
+        """Whether the step after ``step`` (launched, advanced, not yet committed) can be decided now, whatever
+        ``step`` held (portions of prompts, decoded tokens, both): none of the requests that are sampling a token in
+        it can end with that token other than by an end-of-sequence id, and every decoding request finds room for one
+        more token, so that deciding the next step preempts nobody.  (A request that does end on an end-of-sequence id
+        has then computed one token too many, which is dropped.)"""
+        if step.preempted:
+            return False
+        limit = self.cache.max_seq_len
+        for e in step.entries:
+            if not e.wants_logits:
+                continue
+            r = e.request
+            if r.state != DECODING or len(r.output_tokens) + 2 > r.max_new_tokens or r.total_len() + 2 > limit:
+                return False
+        return self.cache.can_reserve_all([(r.id, 1) for r in self.running if r.state == DECODING])
+
     # ---- internals ---------------------------------------------------------------------------------
     def _release(self, r: Request) -> None:
         if r in self.running:

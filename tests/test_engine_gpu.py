@@ -491,6 +491,46 @@ def test_token_ids_taken_from_the_device(tmp_path):
         assert a.shape == b.shape and float((a - b).abs().max()) <= 0.25 * tol
 
 
+@pytest.mark.parametrize("rowwise", ["1", "0"])
+def test_some_rows_take_their_ids_from_the_device(tmp_path, monkeypatch, rowwise):
+    """``step(entries, None, (ids, rows, places))``: some rows of a mixed step (the decoded tokens of requests whose
+    last id a step in flight is still sampling) take their ids from a device tensor, the rest from the entries.  The
+    same shape of step comes nine times, with none, one or both of its decoded rows mapped, so that its CUDA graph is
+    captured on the way and replayed with maps of other lengths: no array that the graph reads may move with the map.
+    With the portions kept whole the step's attention items are staged behind the fixed arrays, which is where a map
+    of varying length once pushed them aside."""
+    monkeypatch.setenv("LLB_ROWWISE_STEPS", rowwise)
+    d = model_dir(tmp_path, "E", seed=9, store="bfloat16")
+    cfg, w = P.read_model_dir(d)
+    rng = random.Random(10)
+    V = cfg["vocab_size"]
+    seqs = {i: [rng.randrange(V) for _ in range(120)] for i in range(3)}
+    ref = {i: P.plain_forward(cfg, w, s) for i, s in seqs.items()}
+    tol = atol_for("E", "bfloat16", ref)
+    core = EngineCore(d, EngineOptions(dtype="bfloat16", max_seq_len=256, max_batch_tokens=128, page_size=16,
+                                       num_pages=40, max_seqs=4))
+    at = {0: 40, 1: 35, 2: 0}
+    for i in range(3):
+        core.open(i)
+    core.step([StepEntry(0, seqs[0][:40], []), StepEntry(1, seqs[1][:35], [])])
+    worst = 0.0
+    for n in range(9):
+        mapped = [(0, 1), (0,), (), (1,)][n % 4]            # which of the two decoded rows take their id from the device
+        ids_dev = torch.tensor([seqs[1][at[1]], 7, seqs[0][at[0]]], dtype=torch.int32, device="cuda")   # places 0 and 2 are used
+        place = {0: 2, 1: 0}
+        entries = [StepEntry(i, [0] if i in mapped else [seqs[i][at[i]]], [0]) for i in (0, 1)]
+        entries.append(StepEntry(2, seqs[2][at[2]: at[2] + 8], []))
+        token_map = (ids_dev, [i for i in (0, 1) if i in mapped], [place[i] for i in (0, 1) if i in mapped]) if mapped else None
+        out = core.step(entries, None, token_map).float().cpu()
+        for k, i in enumerate((0, 1)):
+            worst = max(worst, float((out[k] - ref[i][at[i]]).abs().max()))
+            at[i] += 1
+        at[2] += 8
+    core.runner.check_device_errors()
+    assert core.runner.graph_replays >= 3
+    assert worst <= tol, worst
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["B", "D", "E"])
 def test_layers_through_the_step_executor_match_the_parts(tmp_path, monkeypatch, name, dtype):

@@ -218,3 +218,49 @@ def test_a_step_can_be_decided_before_the_last_one_is_read():
     assert s.finished[0].output_tokens == [10, 12, 13, 14, 15, 16]
     assert m.free_pages() == 50
     m.check()
+
+
+def test_steps_with_portions_can_be_decided_ahead_too():
+    """``can_step_ahead``: the step after a launched one is decided before its tokens are known whenever no request
+    that samples in it can end by length, whatever the step holds: a whole prompt, a portion beside decoded tokens.
+    The next step gives the request that has just finished its prompt a decode token at the next position (its id
+    comes from the device), goes on with the other prompt's portions, and preempts nobody."""
+    m = manager(50)
+    s = Scheduler(m, 8, 12)                               # portions of 8 tokens, 12 tokens a step
+    s.add_request(Request(0, [1] * 5, max_new_tokens=6, eos_token_id=99))
+    s.add_request(Request(1, [2] * 20, max_new_tokens=4, eos_token_id=99))
+
+    def launch():
+        st = s.step()
+        s.cache.reserve_all((e.request.id, e.num_tokens) for e in st.entries)
+        for e in st.entries:
+            s.cache.advance(e.request.id, e.num_tokens)
+        s.advance(st)
+        return st
+
+    st0 = launch()                                        # request 0 whole (5, wants logits) + 7 tokens of request 1
+    assert [(e.request.id, e.num_tokens, e.wants_logits) for e in st0.entries] == [(0, 5, True), (1, 7, False)]
+    assert s.can_step_ahead(st0)
+    st1 = launch()                                        # before st0's token is known
+    assert [(e.request.id, e.num_tokens, e.start_pos, e.is_prefill) for e in st1.entries] == [(0, 1, 5, False), (1, 8, 7, True)]
+    assert s.running[0].total_len() == 5                  # the token of st0 is not there yet: the entry's id is the device's
+    assert s.commit(st0, {0: 10}) == []
+    assert s.can_step_ahead(st1) and not st1.preempted
+    st2 = launch()
+    assert [(e.request.id, e.num_tokens, e.start_pos) for e in st2.entries] == [(0, 1, 6), (1, 5, 15)]
+    assert st2.entries[1].wants_logits                    # request 1's prompt ends in this step
+    s.commit(st1, {0: 11})
+    assert s.can_step_ahead(st2)
+    st3 = launch()                                        # both decode; request 1's first token comes from the device
+    assert [(e.request.id, e.start_pos, e.is_prefill) for e in st3.entries] == [(0, 7, False), (1, 20, False)]
+    s.commit(st2, {0: 12, 1: 30})
+    assert s.can_step_ahead(st3)                          # request 0 samples its 4th of 6, request 1 its 2nd of 4
+    st4 = launch()
+    s.commit(st3, {0: 13, 1: 31})
+    assert s.can_step_ahead(st4)                          # request 1 samples its 3rd of 4: the step after samples the last
+    st5 = launch()
+    s.commit(st4, {0: 14, 1: 32})
+    assert not s.can_step_ahead(st5)                      # both end by length with st5's tokens
+    done = s.commit(st5, {0: 15, 1: 33})
+    assert sorted(r.id for r in done) == [0, 1]
+    assert s.finished[0].output_tokens == [10, 11, 12, 13, 14, 15] and s.finished[1].output_tokens == [30, 31, 32, 33]
