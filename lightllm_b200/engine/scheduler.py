@@ -311,19 +311,6 @@ class Scheduler:
                 done.append(r)
         return done
 
-    def can_decode_ahead(self, step: ScheduleStep) -> bool:
-        """Whether the step after ``step`` (launched, advanced, not yet committed) can be decided now: ``step``
-        gave every running request one decode token, nothing waits, none of them can end with the token it is
-        sampling other than by an end-of-sequence id, and every one finds room for one more token."""
-        if self.waiting or step.preempted or len(step.entries) != len(self.running):
-            return False
-        for e, r in zip(step.entries, self.running):
-            if e.request is not r or e.is_prefill or not e.wants_logits or r.state != DECODING:
-                return False
-            if len(r.output_tokens) + 2 > r.max_new_tokens or r.total_len() + 2 > self.cache.max_seq_len:
-                return False
-        return self.cache.can_reserve_all([(r.id, 1) for r in self.running])
-
     def can_step_ahead(self, step: ScheduleStep) -> bool:
         """Whether the step after ``step`` (launched, advanced, not yet committed) can be decided now, whatever
         ``step`` held (portions of prompts, decoded tokens, both): none of the requests that are sampling a token in

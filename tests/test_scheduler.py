@@ -194,25 +194,25 @@ def test_a_step_can_be_decided_before_the_last_one_is_read():
         return st
 
     first = launch()                                     # both prompts whole, both want logits
-    assert not s.can_decode_ahead(first)                 # a prompt step is read at once
+    assert s.can_step_ahead(first)                       # a prompt step's successor can be decided too; here it is read first
     assert s.commit(first, {0: 10, 1: 11}) == []
     st1 = launch()                                       # decode step 1
-    assert s.can_decode_ahead(st1)
+    assert s.can_step_ahead(st1)
     st2 = launch()                                       # decided and launched before st1's tokens are known
     assert [e.start_pos for e in st2.entries] == [e.start_pos + 1 for e in st1.entries]
     assert s.commit(st1, {0: 12, 1: 99}) != []           # request 1 ends on its end-of-sequence id ...
     assert s.finished[1].output_tokens == [11, 99]
-    assert not s.can_decode_ahead(st2)                   # ... so the batch has changed
+    assert not s.can_step_ahead(st2)                   # ... so the batch has changed
     assert s.commit(st2, {0: 13, 1: 55}) == []           # its token of the step launched ahead is dropped
     assert s.finished[1].output_tokens == [11, 99] and s.running[0].output_tokens == [10, 12, 13]
     st3 = launch()
-    assert s.can_decode_ahead(st3)                       # it samples the 4th of 6 tokens: one more step is safe
+    assert s.can_step_ahead(st3)                       # it samples the 4th of 6 tokens: one more step is safe
     st4 = launch()
     s.commit(st3, {0: 14})
-    assert s.can_decode_ahead(st4)                       # the 5th; the step after it samples the last
+    assert s.can_step_ahead(st4)                       # the 5th; the step after it samples the last
     st5 = launch()
     s.commit(st4, {0: 15})
-    assert not s.can_decode_ahead(st5)                   # the request ends by length with st5's token
+    assert not s.can_step_ahead(st5)                   # the request ends by length with st5's token
     done = s.commit(st5, {0: 16})
     assert [r.id for r in done] == [0] and s.finished[0].finish_reason == "length"
     assert s.finished[0].output_tokens == [10, 12, 13, 14, 15, 16]
