@@ -406,7 +406,7 @@ class ModelRunner:
             self._graph_seen[key] = seen
             if len(self._graph_seen) > 4096:              # shapes seen once and never again
                 self._graph_seen.clear()
-            # A capture costs the host about as much as four steps launched one by one.  The shapes of decoding
+            # A capture costs the host a few milliseconds, as much as several steps.  The shapes of decoding
             # batches and of a lone portion come again hundreds of times; a step that mixes several portions and
             # tokens rarely meets its shape again, so such a shape must have come more often before it is captured.
             settled = ctx.decode_only or ctx.num_spans == 1
