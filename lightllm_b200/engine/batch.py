@@ -109,6 +109,23 @@ def cut_attention_rows(rows, chunk_tiles=None, heads=1, slots=1):
 _chosen_chunk: Dict[tuple, int] = {}      # the piece length chosen for (the rows' key tiles, heads, slots)
 
 
+def rows_as_spans(spans: List[Span], bucket: int, max_rows: int):
+    """A mixed step described row by row: every token a span of its own (its request's slot, its own position, its own
+    row), then the last row repeated until the rows are a multiple of ``bucket`` (at most ``max_rows``).  Returns the
+    new spans and, for every span that came in, the span of its first row (the rows keep their order, so a wanted place
+    ``w`` of an entry is still row ``first.row + w``)."""
+    rows = [Span(s.seq_id, s.slot, s.start + i, 1, s.row + i) for s in spans for i in range(s.length)]
+    firsts, at = [], 0
+    for s in spans:
+        firsts.append(rows[at])
+        at += s.length
+    T = len(rows)
+    padded = min(-(-T // bucket) * bucket, max_rows)
+    last = rows[-1]
+    rows += [Span(last.seq_id, last.slot, last.start, 1, T + j) for j in range(padded - T)]
+    return rows, firsts
+
+
 class StepContext:
     """Everything a part may read while a step runs.
 

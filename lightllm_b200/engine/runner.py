@@ -22,7 +22,7 @@ from ..csrc import ops
 from ..models import Model
 from ..parts import CacheView
 from ..parts.base import LazyNorm
-from .batch import Span, StepContext, StepEntry
+from .batch import Span, StepContext, StepEntry, rows_as_spans
 from .fused_decode import FusedDecode
 from .native_step import NativeLayers
 
@@ -152,16 +152,8 @@ class ModelRunner:
         # (what the rows of portions read beyond what the portions kept whole would: each row its keys by itself)
         portion_keys = sum(s.length * (s.start + s.length) for s in spans if s.length > 1)
         if self.rowwise and T <= self.ROWWISE_MAX_ROWS and 0 < portion_keys <= self.ROWWISE_MAX_ROW_KEYS:
-            spans = [Span(s.seq_id, s.slot, s.start + i, 1, s.row + i) for s in spans for i in range(s.length)]
+            spans, span_of_entry = rows_as_spans(spans, self.ROWWISE_BUCKET, self.ROWWISE_MAX_ROWS)
             rowwise = True
-            span_of_entry = []
-            at = 0
-            for e in entries:
-                span_of_entry.append(spans[at])
-                at += len(e.tokens)
-            last = spans[-1]
-            padded = min(-(-T // self.ROWWISE_BUCKET) * self.ROWWISE_BUCKET, self.ROWWISE_MAX_ROWS)
-            spans += [Span(last.seq_id, last.slot, last.start, 1, T + j) for j in range(padded - T)]
         else:
             span_of_entry, rowwise = spans, False
         real_T, T = T, len(spans) if rowwise else T

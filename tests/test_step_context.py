@@ -127,3 +127,21 @@ def test_every_span_of_a_mixed_step_goes_to_the_kernel_for_its_shape(tmp_path, m
     assert bq == 1 and nsplit >= 2 and rows_span.tolist() == [0, 1, 1, 1, 1, 1] and rows_q0.tolist() == [0, 0, 1, 2, 3, 4]
     (tile_span, _, _), bq, nsplit = simt[1]                              # the rest in tiles of rows
     assert bq >= 1 and nsplit == 1 and sorted(set(tile_span.tolist())) == [2, 3, 4]
+
+
+def test_a_mixed_step_described_row_by_row():
+    """``rows_as_spans``: every token of every span becomes a span of one row at its own position, the rows keep their
+    order (so an entry's wanted place is still its first row plus the place), and the last row is repeated up to a
+    multiple of the bucket, never beyond the row limit."""
+    from lightllm_b200.engine.batch import Span, rows_as_spans
+    spans = [Span("a", 3, 40, 1, 0), Span("b", 5, 100, 4, 1), Span("c", 7, 0, 2, 5)]
+    rows, firsts = rows_as_spans(spans, 8, 64)
+    assert [(s.seq_id, s.start, s.length, s.row) for s in rows[:7]] == [
+        ("a", 40, 1, 0), ("b", 100, 1, 1), ("b", 101, 1, 2), ("b", 102, 1, 3), ("b", 103, 1, 4), ("c", 0, 1, 5), ("c", 1, 1, 6)]
+    assert [s.slot for s in rows[:7]] == [3, 5, 5, 5, 5, 7, 7]
+    assert [(f.seq_id, f.row) for f in firsts] == [("a", 0), ("b", 1), ("c", 5)]
+    assert len(rows) == 8 and (rows[7].seq_id, rows[7].start, rows[7].slot, rows[7].row) == ("c", 1, 7, 7)   # the padding
+    rows, _ = rows_as_spans([Span("a", 0, 10, 16, 0)], 8, 64)
+    assert len(rows) == 16                                   # already a multiple of the bucket: no padding
+    rows, _ = rows_as_spans([Span("a", 0, 10, 61, 0)], 8, 62)
+    assert len(rows) == 62 and all(r.start == 70 for r in rows[61:])      # the bucket stops at the row limit
